@@ -1,0 +1,117 @@
+"""ctypes loader for libtnns_b200.so.  There is no fallback: if the library is missing
+or does not load, importing a symbol raises."""
+from __future__ import annotations
+
+import ctypes as C
+from pathlib import Path
+
+_PKG = Path(__file__).resolve().parent
+_LIB = None
+
+
+class Shape(C.Structure):
+    """``tnns_shape_t`` of include/tnns_b200.h."""
+    _fields_ = [(n, C.c_int) for n in ("N", "C", "H", "W", "KN", "KH", "KW", "PH", "PW", "SH", "SW")]
+
+    @property
+    def OH(self):
+        return (self.H + 2 * self.PH - self.KH) // self.SH + 1
+
+    @property
+    def OW(self):
+        return (self.W + 2 * self.PW - self.KW) // self.SW + 1
+
+
+class Testcase(C.Structure):
+    """``testcase_t``: field order of the reference's include/tnns/data.h:4-25."""
+    _fields_ = [
+        ("type", C.c_int), ("batchcount", C.c_int), ("channelcount", C.c_int),
+        ("inputW", C.c_int), ("inputH", C.c_int), ("kernelcount", C.c_int),
+        ("kernelW", C.c_int), ("kernelH", C.c_int), ("paddingW", C.c_int), ("paddingH", C.c_int),
+        ("strideW", C.c_int), ("strideH", C.c_int), ("preluAlpha", C.c_float),
+        ("input_thresholds", C.POINTER(C.c_float)), ("input", C.POINTER(C.c_float)),
+        ("kernel", C.POINTER(C.c_float)),
+        ("quantized_kernel_packing0", C.POINTER(C.c_int64)),
+        ("quantized_kernel_packing1", C.POINTER(C.c_int64)),
+        ("quantized_kernel_packing2", C.POINTER(C.c_int64)),
+        ("output", C.POINTER(C.c_float)),
+    ]
+
+
+class GemmTestcase(C.Structure):
+    """``testcase_tnns_gemm_t``: include/tnns/data.h:27-41 of the reference."""
+    _fields_ = [
+        ("m", C.c_int), ("p", C.c_int), ("p_packed", C.c_int), ("n", C.c_int),
+        ("x", C.POINTER(C.c_float)), ("w", C.POINTER(C.c_float)),
+        ("x_packing0", C.POINTER(C.c_int64)), ("x_packing1", C.POINTER(C.c_int64)),
+        ("x_packing2", C.POINTER(C.c_int64)), ("w_packing0", C.POINTER(C.c_int64)),
+        ("w_packing1", C.POINTER(C.c_int64)), ("w_packing2", C.POINTER(C.c_int64)),
+        ("output", C.POINTER(C.c_float)),
+    ]
+
+
+# name -> (restype, argtypes); every symbol include/tnns_b200.h declares
+_vp, _i, _f, _sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
+_pf, _pi64 = C.POINTER(C.c_float), C.POINTER(C.c_int64)
+_pshape = C.POINTER(Shape)
+SIGNATURES = {
+    "tnns_conv": (None, [C.POINTER(Testcase)]),
+    "tnns_gemm": (None, [C.POINTER(GemmTestcase)]),
+    "mm_tnn": (_vp, [_vp, _vp, _i, _i, _i, _i, _i, _f]),
+    "mm_tbn": (_vp, [_vp, _vp, _i, _i, _i, _i, _i, _f]),
+    "mm_btn": (_vp, [_vp, _vp, _i, _i, _i, _i, _i, _f]),
+    "mm_bnn": (_vp, [_vp, _vp, _i, _i, _i, _i, _i, _i, _f]),
+    "t2r_p2_opt": (_vp, [_vp, _vp] + [_i] * 10),
+    "b2r": (_vp, [_vp, _vp] + [_i] * 10),
+    "tnns_pack_weights_ternary": (_vp, [_vp, _vp, _i, _i, _i, _i]),
+    "tnns_pack_weights_binary": (_vp, [_vp, _vp, _i, _i, _i, _i]),
+    "tnns_cuda_create": (_i, [_i, C.POINTER(_vp)]),
+    "tnns_cuda_destroy": (None, [_vp]),
+    "tnns_out_dim": (_i, [_i, _i, _i, _i]),
+    "tnns_k_words": (_i, [_i, _i, _i]),
+    "tnns_k_padded": (_i, [_i, _i, _i]),
+    "tnns_packed_bytes": (_sz, [_i, _pshape]),
+    "tnns_cuda_upload_weights": (_i, [_vp, _i, _vp, _i, _i, _i, _i, C.POINTER(_vp)]),
+    "tnns_cuda_upload_weights_packed": (_i, [_vp, _i, _vp, _i, _i, _i, C.POINTER(_vp)]),
+    "tnns_cuda_free_weights": (None, [_vp, _vp]),
+    "tnns_cuda_pack": (_i, [_vp, _i, _vp, _vp, _vp, _pshape, _i, _i, _vp]),
+    "tnns_cuda_gemm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp]),
+    "tnns_cuda_conv": (_i, [_vp, _vp, _vp, _vp, _vp, _pshape, _f, _i, _i, _i, _vp]),
+    "tnns_cuda_conv_ws": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _pshape, _f, _i, _i, _i, _vp]),
+    "tnns_cuda_conv_host": (_i, [_vp, _vp, _vp, _vp, _vp, _pshape, _f, _i]),
+    "tnns_cuda_sync": (_i, [_vp]),
+    "tnns_cuda_malloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
+    "tnns_cuda_free": (None, [_vp, _vp]),
+    "tnns_cuda_memcpy_h2d": (_i, [_vp, _vp, _vp, _sz]),
+    "tnns_cuda_memcpy_d2h": (_i, [_vp, _vp, _vp, _sz]),
+    "tnns_cuda_launch_count": (C.c_ulonglong, []),
+    "tnns_cuda_last_error": (_i, []),
+    "tnns_cuda_strerror": (C.c_char_p, [_i]),
+    "tnns_cuda_error_detail": (C.c_char_p, []),
+}
+
+
+def library_path() -> Path:
+    return _PKG / "libtnns_b200.so"
+
+
+def load_library():
+    """Load libtnns_b200.so and bind every declared symbol.  Raises if it is absent."""
+    global _LIB
+    if _LIB is not None:
+        return _LIB
+    path = library_path()
+    if not path.exists():
+        raise ImportError(
+            f"{path} is missing: build it with `python -m fastertnn_b200._build` (needs nvcc). "
+            "There is no CPU fallback.")
+    lib = C.CDLL(str(path))
+    for name, (res, args) in SIGNATURES.items():
+        fn = getattr(lib, name)  # AttributeError if the symbol is not exported
+        fn.restype = res
+        fn.argtypes = args
+    lib.libc_free = C.CDLL(None).free
+    lib.libc_free.argtypes = [C.c_void_p]
+    lib.libc_free.restype = None
+    _LIB = lib
+    return lib

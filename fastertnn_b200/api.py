@@ -1,0 +1,311 @@
+"""Python host side of libtnns_b200: the reference's operator interface over numpy arrays
+(host pointers, same argument meaning and ownership as include/tnns/tnns_cpu.h,
+include/tnns/mm.h, include/tnns/ternarize2row.h, include/tnns/binarize2row.h of the
+reference) and the device-resident API over raw device pointers.
+
+Every function here ends in a call into the shared library; none computes anything on
+the CPU.
+"""
+from __future__ import annotations
+
+import ctypes as C
+
+import numpy as np
+
+from ._lib import GemmTestcase, Shape, Testcase, load_library
+
+TNN, TBN, BTN, BNN = 0, 1, 2, 3
+NCHW, NHWC = 0, 1
+PACK_AUTO, PACK_GATHER, PACK_STAGED = 0, 1, 2
+GEMM_AUTO, GEMM_POPC_SIMPLE, GEMM_POPC_TILED, GEMM_I8_TC = 0, 1, 2, 3
+
+
+class TnnsError(RuntimeError):
+    def __init__(self, status: int, detail: str):
+        super().__init__(f"tnns_b200 error {status}: {detail}")
+        self.status = status
+        self.detail = detail
+
+
+def _check(rc: int):
+    if rc != 0:
+        lib = load_library()
+        raise TnnsError(rc, f"{lib.tnns_cuda_strerror(rc).decode()}: {lib.tnns_cuda_error_detail().decode()}")
+
+
+def _last_error() -> TnnsError:
+    lib = load_library()
+    rc = lib.tnns_cuda_last_error()
+    return TnnsError(rc, f"{lib.tnns_cuda_strerror(rc).decode()}: {lib.tnns_cuda_error_detail().decode()}")
+
+
+def out_dim(size: int, pad: int, k: int, stride: int) -> int:
+    return load_library().tnns_out_dim(size, pad, k, stride)
+
+
+def k_words(C_: int, KH: int, KW: int) -> int:
+    return load_library().tnns_k_words(C_, KH, KW)
+
+
+def k_padded(C_: int, KH: int, KW: int) -> int:
+    return load_library().tnns_k_padded(C_, KH, KW)
+
+
+def packed_bytes(type_: int, shape: Shape) -> int:
+    return load_library().tnns_packed_bytes(type_, C.byref(shape))
+
+
+def _f32(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.float32)
+
+
+def _i64(a) -> np.ndarray:
+    return np.ascontiguousarray(a, dtype=np.int64)
+
+
+def _ptr(a: np.ndarray) -> int:
+    return a.ctypes.data
+
+
+def _take_floats(ptr: int, count: int) -> np.ndarray:
+    """Copy a malloc'd float buffer returned by the library into numpy and free it."""
+    lib = load_library()
+    out = np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_float)), shape=(count,)).copy()
+    lib.libc_free(ptr)
+    return out
+
+
+def _take_words(ptr: int, count: int) -> np.ndarray:
+    lib = load_library()
+    out = np.ctypeslib.as_array(C.cast(ptr, C.POINTER(C.c_int64)), shape=(count,)).copy()
+    lib.libc_free(ptr)
+    return out
+
+
+# --------------------------------------------------------------------------------------------
+# Drop-in interface (host arrays)
+# --------------------------------------------------------------------------------------------
+
+def pack_weights_ternary(w, thresholds) -> np.ndarray:
+    """fp32 [KN][C][KH][KW] -> packing-2 rows (reference: ternarize_opt_avx2, src/utils.c:468)."""
+    w = _f32(w)
+    KN, C_, KH, KW = w.shape
+    thr = _f32(thresholds)
+    assert thr.shape == (KN,)
+    p = load_library().tnns_pack_weights_ternary(_ptr(w), _ptr(thr), KN, C_, KH, KW)
+    if not p:
+        raise MemoryError("tnns_pack_weights_ternary")
+    return _take_words(p, KN * 2 * k_padded(C_, KH, KW)).reshape(KN, -1)
+
+
+def pack_weights_binary(w, thresholds) -> np.ndarray:
+    """fp32 [KN][C][KH][KW] -> one-plane rows (reference: binarize_opt_avx2, src/utils.c:672)."""
+    w = _f32(w)
+    KN, C_, KH, KW = w.shape
+    thr = _f32(thresholds)
+    assert thr.shape == (KN,)
+    p = load_library().tnns_pack_weights_binary(_ptr(w), _ptr(thr), KN, C_, KH, KW)
+    if not p:
+        raise MemoryError("tnns_pack_weights_binary")
+    return _take_words(p, KN * k_padded(C_, KH, KW)).reshape(KN, -1)
+
+
+def tnns_conv(type_: int, x, thresholds, packed_kernel, kernel_hw, padding=(0, 0), stride=(1, 1), alpha=0.5) -> np.ndarray:
+    """One layer through the drop-in ``tnns_conv(testcase_t*)``.
+
+    x: fp32 NCHW; thresholds: one per image; packed_kernel: KN rows in the layout the type
+    expects.  Returns fp32 NCHW [N][KN][OH][OW].
+    """
+    lib = load_library()
+    x = _f32(x)
+    N, C_, H, W = x.shape
+    thr = _f32(thresholds)
+    pk = _i64(packed_kernel)
+    KN = pk.shape[0]
+    KH, KW = kernel_hw
+    t = Testcase()
+    t.type = type_
+    t.batchcount, t.channelcount, t.inputH, t.inputW = N, C_, H, W
+    t.kernelcount, t.kernelH, t.kernelW = KN, KH, KW
+    t.paddingH, t.paddingW = padding
+    t.strideH, t.strideW = stride
+    t.preluAlpha = alpha
+    t.input_thresholds = thr.ctypes.data_as(C.POINTER(C.c_float))
+    t.input = x.ctypes.data_as(C.POINTER(C.c_float))
+    t.quantized_kernel_packing2 = pk.ctypes.data_as(C.POINTER(C.c_int64))
+    lib.tnns_conv(C.byref(t))
+    if not t.output:
+        raise _last_error()
+    OH = out_dim(H, padding[0], KH, stride[0])
+    OW = out_dim(W, padding[1], KW, stride[1])
+    return _take_floats(C.cast(t.output, C.c_void_p).value, N * KN * OH * OW).reshape(N, KN, OH, OW)
+
+
+def tnns_gemm(x_packing2, w_packing2, m: int, n: int, p_packed: int, out: np.ndarray | None = None) -> np.ndarray:
+    """Packed TNN GEMM with alpha = 1 through ``tnns_gemm(testcase_tnns_gemm_t*)``."""
+    lib = load_library()
+    xa, wa = _i64(x_packing2), _i64(w_packing2)
+    t = GemmTestcase()
+    t.m, t.n, t.p_packed, t.p = m, n, p_packed, p_packed * 64
+    t.x_packing2 = xa.ctypes.data_as(C.POINTER(C.c_int64))
+    t.w_packing2 = wa.ctypes.data_as(C.POINTER(C.c_int64))
+    if out is not None:
+        assert out.dtype == np.float32 and out.flags.c_contiguous and out.size == m * n
+        t.output = out.ctypes.data_as(C.POINTER(C.c_float))
+        lib.tnns_gemm(C.byref(t))
+        return out
+    lib.tnns_gemm(C.byref(t))
+    if not t.output:
+        raise _last_error()
+    return _take_floats(C.cast(t.output, C.c_void_p).value, m * n).reshape(m, n)
+
+
+def _mm(name, a, b, N, OH, OW, KN, K, alpha, K_unpack=None):
+    lib = load_library()
+    a, b = _i64(a), _i64(b)
+    fn = getattr(lib, name)
+    p = fn(_ptr(a), _ptr(b), N, OH, OW, KN, K, alpha) if K_unpack is None else fn(_ptr(a), _ptr(b), N, OH, OW, KN, K, K_unpack, alpha)
+    if not p:
+        raise _last_error()
+    return _take_floats(p, N * KN * OH * OW).reshape(N, KN, OH, OW)
+
+
+def mm_tnn(a, b, N, OH, OW, KN, K, alpha):
+    return _mm("mm_tnn", a, b, N, OH, OW, KN, K, alpha)
+
+
+def mm_tbn(a, b, N, OH, OW, KN, K, alpha):
+    return _mm("mm_tbn", a, b, N, OH, OW, KN, K, alpha)
+
+
+def mm_btn(a, b, N, OH, OW, KN, K, alpha):
+    return _mm("mm_btn", a, b, N, OH, OW, KN, K, alpha)
+
+
+def mm_bnn(a, b, N, OH, OW, KN, K, K_unpack, alpha):
+    return _mm("mm_bnn", a, b, N, OH, OW, KN, K, alpha, K_unpack=K_unpack)
+
+
+def _pack_host(name, planes, x, thresholds, kernel_hw, padding, stride):
+    lib = load_library()
+    x = _f32(x)
+    N, C_, H, W = x.shape
+    thr = _f32(thresholds)
+    KH, KW = kernel_hw
+    p = getattr(lib, name)(_ptr(x), _ptr(thr), N, C_, H, W, padding[0], padding[1], KH, KW, stride[0], stride[1])
+    if not p:
+        raise _last_error()
+    rows = N * out_dim(H, padding[0], KH, stride[0]) * out_dim(W, padding[1], KW, stride[1])
+    return _take_words(p, rows * planes * k_padded(C_, KH, KW)).reshape(rows, -1)
+
+
+def t2r_p2_opt(x, thresholds, kernel_hw, padding=(0, 0), stride=(1, 1)) -> np.ndarray:
+    """Ternarize + pack + im2row of a host NCHW tensor; rows of 2*Kp int64 (packing-2)."""
+    return _pack_host("t2r_p2_opt", 2, x, thresholds, kernel_hw, padding, stride)
+
+
+def b2r(x, thresholds, kernel_hw, padding=(0, 0), stride=(1, 1)) -> np.ndarray:
+    """Binarize + pack + im2row of a host NCHW tensor; rows of Kp int64 (one plane)."""
+    return _pack_host("b2r", 1, x, thresholds, kernel_hw, padding, stride)
+
+
+# --------------------------------------------------------------------------------------------
+# Device-resident interface (raw device pointers; torch supplies memory and streams)
+# --------------------------------------------------------------------------------------------
+
+class Weights:
+    """Device copy of one layer's packed kernel."""
+
+    def __init__(self, ctx: "Context", handle: int, type_: int, KN: int):
+        self.ctx, self.handle, self.type, self.KN = ctx, handle, type_, KN
+
+    def free(self):
+        if self.handle:
+            load_library().tnns_cuda_free_weights(self.ctx.handle, self.handle)
+            self.handle = None
+
+
+class Context:
+    """One ``tnns_cuda_ctx`` (per host thread and device)."""
+
+    def __init__(self, device: int = 0):
+        lib = load_library()
+        h = C.c_void_p()
+        _check(lib.tnns_cuda_create(device, C.byref(h)))
+        self.handle = h.value
+        self.device = device
+        self.lib = lib
+
+    def close(self):
+        if self.handle:
+            self.lib.tnns_cuda_destroy(self.handle)
+            self.handle = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    # -- weights
+    def upload_weights(self, type_: int, packed: np.ndarray, C_: int, KH: int, KW: int) -> Weights:
+        pk = _i64(packed)
+        KN = pk.shape[0]
+        h = C.c_void_p()
+        _check(self.lib.tnns_cuda_upload_weights(self.handle, type_, _ptr(pk), KN, C_, KH, KW, C.byref(h)))
+        return Weights(self, h.value, type_, KN)
+
+    def upload_weights_packed(self, type_: int, packed: np.ndarray, K_words: int, K_unpack: int = 0) -> Weights:
+        pk = _i64(packed)
+        KN = pk.shape[0]
+        h = C.c_void_p()
+        _check(self.lib.tnns_cuda_upload_weights_packed(self.handle, type_, _ptr(pk), KN, K_words, K_unpack, C.byref(h)))
+        return Weights(self, h.value, type_, KN)
+
+    # -- kernels on device pointers
+    def pack(self, ternary: bool, d_x: int, d_thr: int, d_packed: int, shape: Shape, layout=NCHW, algo=PACK_AUTO, stream=0):
+        _check(self.lib.tnns_cuda_pack(self.handle, int(ternary), d_x, d_thr, d_packed, C.byref(shape), layout, algo, stream))
+
+    def gemm(self, w: Weights, d_a: int, d_y: int, N: int, OH: int, OW: int, alpha: float, layout=NCHW, algo=GEMM_AUTO, stream=0):
+        _check(self.lib.tnns_cuda_gemm(self.handle, w.handle, d_a, d_y, N, OH, OW, alpha, layout, algo, stream))
+
+    def conv(self, w: Weights, d_x: int, d_thr: int, d_y: int, shape: Shape, alpha: float, layout=NCHW, pack_algo=PACK_AUTO,
+             gemm_algo=GEMM_AUTO, stream=0):
+        _check(self.lib.tnns_cuda_conv(self.handle, w.handle, d_x, d_thr, d_y, C.byref(shape), alpha, layout, pack_algo,
+                                       gemm_algo, stream))
+
+    def conv_ws(self, w: Weights, d_x: int, d_thr: int, d_y: int, d_ws: int, ws_bytes: int, shape: Shape, alpha: float,
+                layout=NCHW, pack_algo=PACK_AUTO, gemm_algo=GEMM_AUTO, stream=0):
+        _check(self.lib.tnns_cuda_conv_ws(self.handle, w.handle, d_x, d_thr, d_y, d_ws, ws_bytes, C.byref(shape), alpha, layout,
+                                          pack_algo, gemm_algo, stream))
+
+    def conv_host(self, w: Weights, h_x: int, h_thr: int, h_y: int, shape: Shape, alpha: float, layout=NCHW):
+        """Host-pointer layer (addresses of pinned or pageable buffers)."""
+        _check(self.lib.tnns_cuda_conv_host(self.handle, w.handle, h_x, h_thr, h_y, C.byref(shape), alpha, layout))
+
+    def sync(self):
+        _check(self.lib.tnns_cuda_sync(self.handle))
+
+    # -- memory helpers (so tests need nothing but numpy)
+    def malloc(self, nbytes: int) -> int:
+        p = C.c_void_p()
+        _check(self.lib.tnns_cuda_malloc(self.handle, nbytes, C.byref(p)))
+        return p.value
+
+    def free(self, p: int):
+        self.lib.tnns_cuda_free(self.handle, p)
+
+    def to_device(self, a: np.ndarray) -> int:
+        a = np.ascontiguousarray(a)
+        p = self.malloc(max(a.nbytes, 16))
+        _check(self.lib.tnns_cuda_memcpy_h2d(self.handle, p, _ptr(a), a.nbytes))
+        return p
+
+    def to_host(self, p: int, shape, dtype) -> np.ndarray:
+        out = np.empty(shape, dtype=dtype)
+        _check(self.lib.tnns_cuda_memcpy_d2h(self.handle, _ptr(out), p, out.nbytes))
+        return out
+
+
+def launch_count() -> int:
+    return load_library().tnns_cuda_launch_count()

@@ -1,0 +1,392 @@
+// Device-resident C ABI: contexts, weights, error reporting, layer entry points.
+#include <algorithm>
+#include <cstdarg>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <new>
+
+#include "internal.h"
+
+// ---------------------------------------------------------------------------------------
+// thread-local error state
+// ---------------------------------------------------------------------------------------
+static thread_local int tl_status = TNNS_OK;
+static thread_local char tl_detail[512] = "";
+static thread_local unsigned long long tl_launches = 0;
+
+int tnns_fail(int status, const char* fmt, ...) {
+    tl_status = status;
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(tl_detail, sizeof(tl_detail), fmt, ap);
+    va_end(ap);
+    return status;
+}
+void tnns_count_launch(void) { tl_launches++; }
+
+extern "C" {
+
+int tnns_cuda_last_error(void) { return tl_status; }
+const char* tnns_cuda_error_detail(void) { return tl_detail; }
+unsigned long long tnns_cuda_launch_count(void) { return tl_launches; }
+
+const char* tnns_cuda_strerror(int status) {
+    switch (status) {
+        case TNNS_OK: return "success";
+        case TNNS_ERR_INVALID: return "invalid argument";
+        case TNNS_ERR_CUDA: return "CUDA runtime error";
+        case TNNS_ERR_NOMEM: return "out of memory";
+        case TNNS_ERR_UNSUPPORTED: return "shape not supported by the requested algorithm";
+        case TNNS_ERR_DEVICE_WAIT: return "bounded on-device wait expired";
+        default: return "unknown status";
+    }
+}
+
+int tnns_out_dim(int in, int pad, int k, int stride) { return (in + 2 * pad - k) / stride + 1; }
+int tnns_k_words(int C, int KH, int KW) { return KH * KW * ((C + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS); }
+int tnns_k_padded(int C, int KH, int KW) { return 4 * ((tnns_k_words(C, KH, KW) + 3) / 4); }
+
+}  // extern "C"
+
+int tnns_make_geom(const tnns_shape_t* s, TnnsGeom* g) {
+    if (!s) return tnns_fail(TNNS_ERR_INVALID, "shape is NULL");
+    if (s->N < 0 || s->C <= 0 || s->H <= 0 || s->W <= 0 || s->KN < 0 || s->KH <= 0 || s->KW <= 0 || s->PH < 0 || s->PW < 0 ||
+        s->SH <= 0 || s->SW <= 0)
+        return tnns_fail(TNNS_ERR_INVALID, "non-positive dimension in shape (N=%d C=%d H=%d W=%d KN=%d KH=%d KW=%d P=%d,%d S=%d,%d)",
+                         s->N, s->C, s->H, s->W, s->KN, s->KH, s->KW, s->PH, s->PW, s->SH, s->SW);
+    if (s->H + 2 * s->PH < s->KH || s->W + 2 * s->PW < s->KW)
+        return tnns_fail(TNNS_ERR_INVALID, "kernel %dx%d larger than padded image %dx%d", s->KH, s->KW, s->H + 2 * s->PH,
+                         s->W + 2 * s->PW);
+    g->N = s->N; g->C = s->C; g->H = s->H; g->W = s->W;
+    g->KN = s->KN; g->KH = s->KH; g->KW = s->KW;
+    g->PH = s->PH; g->PW = s->PW; g->SH = s->SH; g->SW = s->SW;
+    g->OH = tnns_out_dim(s->H, s->PH, s->KH, s->SH);
+    g->OW = tnns_out_dim(s->W, s->PW, s->KW, s->SW);
+    g->Cp = (s->C + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS;
+    g->Kw = s->KH * s->KW * g->Cp;
+    g->Kp = 4 * ((g->Kw + 3) / 4);
+    return TNNS_OK;
+}
+
+static inline bool type_act_ternary(int type) { return type == TNN || type == TBN; }
+static inline bool type_wgt_ternary(int type) { return type == TNN || type == BTN; }
+
+extern "C" {
+
+size_t tnns_packed_bytes(int type, const tnns_shape_t* s) {
+    TnnsGeom g;
+    if (tnns_make_geom(s, &g) != TNNS_OK) return 0;
+    return (size_t)g.N * g.OH * g.OW * g.Kp * 8 * (type_act_ternary(type) ? 2 : 1);
+}
+
+int tnns_cuda_create(int device, tnns_cuda_ctx** out) {
+    if (!out) return tnns_fail(TNNS_ERR_INVALID, "ctx out-pointer is NULL");
+    *out = nullptr;
+    int count = 0;
+    TNNS_CUDA_TRY(cudaGetDeviceCount(&count));
+    if (device < 0 || device >= count) return tnns_fail(TNNS_ERR_INVALID, "device %d out of range (have %d)", device, count);
+    TNNS_CUDA_TRY(cudaSetDevice(device));
+    tnns_cuda_ctx* ctx = new (std::nothrow) tnns_cuda_ctx();
+    if (!ctx) return tnns_fail(TNNS_ERR_NOMEM, "host allocation of context failed");
+    memset(ctx, 0, sizeof(*ctx));
+    ctx->device = device;
+    cudaDeviceProp prop;
+    cudaError_t e = cudaGetDeviceProperties(&prop, device);
+    if (e == cudaSuccess && prop.major != 10) {
+        delete ctx;
+        return tnns_fail(TNNS_ERR_UNSUPPORTED, "device %d is sm_%d%d; this library contains sm_100a code only", device,
+                         prop.major, prop.minor);
+    }
+    if (e == cudaSuccess) e = cudaMalloc(&ctx->d_status, sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMemset(ctx->d_status, 0, sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaMallocHost(&ctx->h_status, sizeof(unsigned int));
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->s_copy_in, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->s_compute, cudaStreamNonBlocking);
+    if (e == cudaSuccess) e = cudaStreamCreateWithFlags(&ctx->s_copy_out, cudaStreamNonBlocking);
+    for (int i = 0; i < 2 && e == cudaSuccess; i++) {
+        e = cudaEventCreateWithFlags(&ctx->ev_in[i], cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_done[i], cudaEventDisableTiming);
+        if (e == cudaSuccess) e = cudaEventCreateWithFlags(&ctx->ev_out[i], cudaEventDisableTiming);
+    }
+    if (e != cudaSuccess) {
+        tnns_cuda_destroy(ctx);
+        return tnns_fail(TNNS_ERR_CUDA, "context set-up failed: %s", cudaGetErrorString(e));
+    }
+    ctx->sm_count = prop.multiProcessorCount;
+    ctx->smem_optin = prop.sharedMemPerBlockOptin;
+    *out = ctx;
+    return TNNS_OK;
+}
+
+void tnns_cuda_destroy(tnns_cuda_ctx* ctx) {
+    if (!ctx) return;
+    cudaSetDevice(ctx->device);
+    cudaDeviceSynchronize();
+    if (ctx->workspace) cudaFree(ctx->workspace);
+    if (ctx->d_status) cudaFree(ctx->d_status);
+    if (ctx->h_status) cudaFreeHost(ctx->h_status);
+    for (int i = 0; i < 2; i++) {
+        if (ctx->stage_in[i]) cudaFree(ctx->stage_in[i]);
+        if (ctx->stage_out[i]) cudaFree(ctx->stage_out[i]);
+        if (ctx->stage_pack[i]) cudaFree(ctx->stage_pack[i]);
+        if (ctx->ev_in[i]) cudaEventDestroy(ctx->ev_in[i]);
+        if (ctx->ev_done[i]) cudaEventDestroy(ctx->ev_done[i]);
+        if (ctx->ev_out[i]) cudaEventDestroy(ctx->ev_out[i]);
+    }
+    if (ctx->stage_thr) cudaFree(ctx->stage_thr);
+    if (ctx->s_copy_in) cudaStreamDestroy(ctx->s_copy_in);
+    if (ctx->s_compute) cudaStreamDestroy(ctx->s_compute);
+    if (ctx->s_copy_out) cudaStreamDestroy(ctx->s_copy_out);
+    delete ctx;
+}
+
+int tnns_cuda_sync(tnns_cuda_ctx* ctx) {
+    if (!ctx) return tnns_fail(TNNS_ERR_INVALID, "ctx is NULL");
+    TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
+    TNNS_CUDA_TRY(cudaDeviceSynchronize());
+    TNNS_CUDA_TRY(cudaMemcpy(ctx->h_status, ctx->d_status, sizeof(unsigned int), cudaMemcpyDeviceToHost));
+    if (*ctx->h_status != 0) {
+        const unsigned int code = *ctx->h_status;
+        cudaMemset(ctx->d_status, 0, sizeof(unsigned int));
+        return tnns_fail(TNNS_ERR_DEVICE_WAIT, "device status word = 0x%x (a bounded wait gave up)", code);
+    }
+    return TNNS_OK;
+}
+
+// --- plain memory helpers so C callers need no CUDA headers -------------------------------
+int tnns_cuda_malloc(tnns_cuda_ctx* ctx, size_t bytes, void** out) {
+    if (!ctx || !out) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
+    *out = nullptr;
+    TNNS_CUDA_TRY(cudaMalloc(out, bytes ? bytes : 16));
+    return TNNS_OK;
+}
+void tnns_cuda_free(tnns_cuda_ctx* ctx, void* p) {
+    if (!ctx || !p) return;
+    cudaSetDevice(ctx->device);
+    cudaFree(p);
+}
+int tnns_cuda_memcpy_h2d(tnns_cuda_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (!ctx || (bytes && (!dst || !src))) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
+    TNNS_CUDA_TRY(cudaMemcpy(dst, src, bytes, cudaMemcpyHostToDevice));
+    return TNNS_OK;
+}
+int tnns_cuda_memcpy_d2h(tnns_cuda_ctx* ctx, void* dst, const void* src, size_t bytes) {
+    if (!ctx || (bytes && (!dst || !src))) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
+    TNNS_CUDA_TRY(cudaMemcpy(dst, src, bytes, cudaMemcpyDeviceToHost));
+    return TNNS_OK;
+}
+
+// --- weights ---------------------------------------------------------------------------------
+static int upload_weights_impl(tnns_cuda_ctx* ctx, int type, const int64_t* packed_host, int KN, int C, int KH, int KW,
+                               int K_words, int K_unpack, tnns_cuda_weights** out) {
+    if (!ctx || !packed_host || !out) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    *out = nullptr;
+    if (type < TNN || type > BNN) return tnns_fail(TNNS_ERR_INVALID, "unknown network type %d", type);
+    if (KN <= 0 || K_words <= 0 || K_unpack < 0) return tnns_fail(TNNS_ERR_INVALID, "non-positive weight dimension");
+    TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
+    tnns_cuda_weights* w = new (std::nothrow) tnns_cuda_weights();
+    if (!w) return tnns_fail(TNNS_ERR_NOMEM, "host allocation failed");
+    memset(w, 0, sizeof(*w));
+    w->type = type; w->KN = KN; w->C = C; w->KH = KH; w->KW = KW; w->device = ctx->device;
+    w->Cp = C > 0 ? (C + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS : 0;
+    w->Kw = K_words;
+    w->Kp = 4 * ((K_words + 3) / 4);
+    w->K_unpack = K_unpack;
+    w->packed_bytes = (size_t)KN * w->Kp * 8 * (type_wgt_ternary(type) ? 2 : 1);
+    cudaError_t e = cudaMalloc(&w->d_packed, w->packed_bytes);
+    if (e == cudaSuccess) e = cudaMemcpy(w->d_packed, packed_host, w->packed_bytes, cudaMemcpyHostToDevice);
+    if (e != cudaSuccess) {
+        tnns_cuda_free_weights(ctx, w);
+        return tnns_fail(e == cudaErrorMemoryAllocation ? TNNS_ERR_NOMEM : TNNS_ERR_CUDA, "weight upload failed: %s",
+                         cudaGetErrorString(e));
+    }
+    *out = w;
+    return TNNS_OK;
+}
+
+int tnns_cuda_upload_weights(tnns_cuda_ctx* ctx, int type, const int64_t* packed_host, int KN, int C, int KH, int KW,
+                             tnns_cuda_weights** out) {
+    if (C <= 0 || KH <= 0 || KW <= 0) return tnns_fail(TNNS_ERR_INVALID, "non-positive weight dimension");
+    return upload_weights_impl(ctx, type, packed_host, KN, C, KH, KW, tnns_k_words(C, KH, KW), C * KH * KW, out);
+}
+
+int tnns_cuda_upload_weights_packed(tnns_cuda_ctx* ctx, int type, const int64_t* packed_host, int KN, int K_words,
+                                    int K_unpack, tnns_cuda_weights** out) {
+    return upload_weights_impl(ctx, type, packed_host, KN, 0, 0, 0, K_words, K_unpack, out);
+}
+
+void tnns_cuda_free_weights(tnns_cuda_ctx* ctx, tnns_cuda_weights* w) {
+    if (!w) return;
+    if (ctx) cudaSetDevice(ctx->device);
+    if (w->d_packed) cudaFree(w->d_packed);
+    if (w->d_i8) cudaFree(w->d_i8);
+    delete w;
+}
+
+// --- kernels -----------------------------------------------------------------------------------
+int tnns_cuda_pack(tnns_cuda_ctx* ctx, int ternary, const float* d_x, const float* d_thr, int64_t* d_packed,
+                   const tnns_shape_t* s, int layout, int algo, void* stream) {
+    if (!ctx || !d_x || !d_thr || !d_packed) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    TnnsGeom g;
+    int rc = tnns_make_geom(s, &g);
+    if (rc) return rc;
+    if (reinterpret_cast<uintptr_t>(d_packed) & 15) return tnns_fail(TNNS_ERR_INVALID, "packed buffer must be 16-byte aligned");
+    if (algo < TNNS_PACK_AUTO || algo > TNNS_PACK_STAGED) return tnns_fail(TNNS_ERR_INVALID, "unknown pack algorithm %d", algo);
+    return tnns_launch_pack(ctx, ternary != 0, d_x, d_thr, d_packed, g, layout, algo, (cudaStream_t)stream);
+}
+
+int tnns_cuda_gemm(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const int64_t* d_a, float* d_y, int N, int OH, int OW,
+                   float alpha, int layout, int algo, void* stream) {
+    if (!ctx || !w || !d_a || !d_y) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    if (N < 0 || OH <= 0 || OW <= 0) return tnns_fail(TNNS_ERR_INVALID, "non-positive output dimension");
+    if (layout != TNNS_NCHW && layout != TNNS_NHWC) return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
+    if (w->device != ctx->device) return tnns_fail(TNNS_ERR_INVALID, "weights live on device %d, context on %d", w->device, ctx->device);
+    if (reinterpret_cast<uintptr_t>(d_a) & 15) return tnns_fail(TNNS_ERR_INVALID, "packed operand must be 16-byte aligned");
+    const long long M = (long long)N * OH * OW;
+    const int K_unpack = w->K_unpack;
+    switch (algo) {
+        case TNNS_GEMM_POPC_SIMPLE:
+            return tnns_launch_gemm_popc(ctx, w->type, d_a, w->d_packed, d_y, M, w->KN, w->Kp, OH * OW, K_unpack, alpha, layout,
+                                         false, (cudaStream_t)stream);
+        case TNNS_GEMM_AUTO:
+        case TNNS_GEMM_POPC_TILED:
+            return tnns_launch_gemm_popc(ctx, w->type, d_a, w->d_packed, d_y, M, w->KN, w->Kp, OH * OW, K_unpack, alpha, layout,
+                                         true, (cudaStream_t)stream);
+        case TNNS_GEMM_I8_TC:
+            return tnns_fail(TNNS_ERR_UNSUPPORTED, "tensor-core GEMM is not built into this library version");
+        default:
+            return tnns_fail(TNNS_ERR_INVALID, "unknown GEMM algorithm %d", algo);
+    }
+}
+
+int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y,
+                      void* d_workspace, size_t workspace_bytes, const tnns_shape_t* s, float alpha, int layout, int pack_algo,
+                      int gemm_algo, void* stream) {
+    if (!ctx || !w || !d_x || !d_thr || !d_y || !d_workspace) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    TnnsGeom g;
+    int rc = tnns_make_geom(s, &g);
+    if (rc) return rc;
+    if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW)
+        return tnns_fail(TNNS_ERR_INVALID, "shape (KN=%d C=%d %dx%d) does not match the uploaded weights (KN=%d C=%d %dx%d)", s->KN,
+                         s->C, s->KH, s->KW, w->KN, w->C, w->KH, w->KW);
+    const size_t need = tnns_packed_bytes(w->type, s);
+    if (workspace_bytes < need) return tnns_fail(TNNS_ERR_INVALID, "workspace of %zu bytes, need %zu", workspace_bytes, need);
+    if (g.N == 0) return TNNS_OK;
+    rc = tnns_cuda_pack(ctx, type_act_ternary(w->type), d_x, d_thr, (int64_t*)d_workspace, s, layout, pack_algo, stream);
+    if (rc) return rc;
+    return tnns_cuda_gemm(ctx, w, (const int64_t*)d_workspace, d_y, g.N, g.OH, g.OW, alpha, layout, gemm_algo, stream);
+}
+
+int tnns_cuda_conv(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y,
+                   const tnns_shape_t* s, float alpha, int layout, int pack_algo, int gemm_algo, void* stream) {
+    if (!ctx || !w) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    TnnsGeom g;
+    int rc = tnns_make_geom(s, &g);
+    if (rc) return rc;
+    const size_t need = std::max<size_t>(tnns_packed_bytes(w->type, s), 16);
+    if (ctx->workspace_bytes < need) {
+        TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
+        // earlier launches may still read the old workspace
+        TNNS_CUDA_TRY(cudaDeviceSynchronize());
+        if (ctx->workspace) cudaFree(ctx->workspace);
+        ctx->workspace = nullptr;
+        ctx->workspace_bytes = 0;
+        TNNS_CUDA_TRY(cudaMalloc(&ctx->workspace, need));
+        ctx->workspace_bytes = need;
+    }
+    return tnns_cuda_conv_ws(ctx, w, d_x, d_thr, d_y, ctx->workspace, ctx->workspace_bytes, s, alpha, layout, pack_algo, gemm_algo,
+                             stream);
+}
+
+// --- host-buffer layer: sliced, copy/compute overlapped -------------------------------------------
+// Grows a pair of equally sized device buffers; on failure both are released and the
+// recorded size drops to zero, so a later call starts from a clean state.
+static int grow_pair(void* p[2], size_t* have, size_t need) {
+    if (*have >= need && p[0] && p[1]) return TNNS_OK;
+    for (int i = 0; i < 2; i++) {
+        if (p[i]) cudaFree(p[i]);
+        p[i] = nullptr;
+    }
+    *have = 0;
+    for (int i = 0; i < 2; i++) {
+        cudaError_t e = cudaMalloc(&p[i], need);
+        if (e != cudaSuccess) {
+            if (p[0]) cudaFree(p[0]);
+            p[0] = p[1] = nullptr;
+            return tnns_fail(e == cudaErrorMemoryAllocation ? TNNS_ERR_NOMEM : TNNS_ERR_CUDA, "staging allocation of %zu bytes failed: %s",
+                             need, cudaGetErrorString(e));
+        }
+    }
+    *have = need;
+    return TNNS_OK;
+}
+
+int tnns_cuda_conv_host(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* h_x, const float* h_thr, float* h_y,
+                        const tnns_shape_t* s, float alpha, int layout) {
+    if (!ctx || !w || !h_x || !h_thr || !h_y) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    TnnsGeom g;
+    int rc = tnns_make_geom(s, &g);
+    if (rc) return rc;
+    if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW)
+        return tnns_fail(TNNS_ERR_INVALID, "shape does not match the uploaded weights");
+    if (g.N == 0) return TNNS_OK;
+    TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
+
+    // slice the batch: about eight slices so copies and kernels overlap, at least one image each
+    const int nb = std::max(1, (g.N + 7) / 8);
+    const size_t in_img = (size_t)g.C * g.H * g.W * sizeof(float);
+    const size_t out_img = (size_t)g.KN * g.OH * g.OW * sizeof(float);
+    tnns_shape_t ss = *s;
+    ss.N = nb;
+    const size_t pack_slice = std::max<size_t>(tnns_packed_bytes(w->type, &ss), 16);
+
+    // staging buffers are shared by both slots' sizes; growing needs the device idle
+    bool must_grow = ctx->stage_in_bytes < in_img * nb || ctx->stage_out_bytes < out_img * nb ||
+                     ctx->stage_pack_bytes < pack_slice || ctx->stage_thr_count < (size_t)g.N;
+    if (must_grow) {
+        TNNS_CUDA_TRY(cudaDeviceSynchronize());
+        if ((rc = grow_pair(ctx->stage_in, &ctx->stage_in_bytes, in_img * nb))) return rc;
+        if ((rc = grow_pair(ctx->stage_out, &ctx->stage_out_bytes, out_img * nb))) return rc;
+        if ((rc = grow_pair(ctx->stage_pack, &ctx->stage_pack_bytes, pack_slice))) return rc;
+        if (ctx->stage_thr_count < (size_t)g.N) {
+            if (ctx->stage_thr) cudaFree(ctx->stage_thr);
+            ctx->stage_thr = nullptr;
+            ctx->stage_thr_count = 0;
+            TNNS_CUDA_TRY(cudaMalloc(&ctx->stage_thr, (size_t)g.N * sizeof(float)));
+            ctx->stage_thr_count = (size_t)g.N;
+        }
+    }
+
+    TNNS_CUDA_TRY(cudaMemcpyAsync(ctx->stage_thr, h_thr, (size_t)g.N * sizeof(float), cudaMemcpyHostToDevice, ctx->s_copy_in));
+    int k = 0;
+    for (int n0 = 0; n0 < g.N; n0 += nb, k++) {
+        const int slot = k & 1;
+        const int cnt = std::min(nb, g.N - n0);
+        ss.N = cnt;
+        if (k >= 2) TNNS_CUDA_TRY(cudaStreamWaitEvent(ctx->s_copy_in, ctx->ev_done[slot], 0));  // kernels of slice k-2 done with stage_in
+        TNNS_CUDA_TRY(cudaMemcpyAsync(ctx->stage_in[slot], (const char*)h_x + (size_t)n0 * in_img, in_img * cnt, cudaMemcpyHostToDevice,
+                                      ctx->s_copy_in));
+        TNNS_CUDA_TRY(cudaEventRecord(ctx->ev_in[slot], ctx->s_copy_in));
+        TNNS_CUDA_TRY(cudaStreamWaitEvent(ctx->s_compute, ctx->ev_in[slot], 0));
+        if (k >= 2) TNNS_CUDA_TRY(cudaStreamWaitEvent(ctx->s_compute, ctx->ev_out[slot], 0));  // download of slice k-2 done with stage_out
+        rc = tnns_cuda_conv_ws(ctx, w, (const float*)ctx->stage_in[slot], ctx->stage_thr + n0, (float*)ctx->stage_out[slot],
+                               ctx->stage_pack[slot], ctx->stage_pack_bytes, &ss, alpha, layout, TNNS_PACK_AUTO, TNNS_GEMM_AUTO,
+                               ctx->s_compute);
+        if (rc) { cudaDeviceSynchronize(); return rc; }
+        TNNS_CUDA_TRY(cudaEventRecord(ctx->ev_done[slot], ctx->s_compute));
+        TNNS_CUDA_TRY(cudaStreamWaitEvent(ctx->s_copy_out, ctx->ev_done[slot], 0));
+        TNNS_CUDA_TRY(cudaMemcpyAsync((char*)h_y + (size_t)n0 * out_img, ctx->stage_out[slot], out_img * cnt, cudaMemcpyDeviceToHost,
+                                      ctx->s_copy_out));
+        TNNS_CUDA_TRY(cudaEventRecord(ctx->ev_out[slot], ctx->s_copy_out));
+    }
+    TNNS_CUDA_TRY(cudaStreamSynchronize(ctx->s_copy_out));
+    TNNS_CUDA_TRY(cudaStreamSynchronize(ctx->s_compute));
+    TNNS_CUDA_TRY(cudaStreamSynchronize(ctx->s_copy_in));
+    return TNNS_OK;
+}
+
+}  // extern "C"

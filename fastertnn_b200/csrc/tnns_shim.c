@@ -1,0 +1,250 @@
+/*
+ * Host side of the drop-in: the reference's seven entry points, written in C over the
+ * device-resident tnns_cuda_* ABI.  Each function mirrors the argument meaning, buffer
+ * ownership and result layout of the reference function it replaces; failures never
+ * abort: they return NULL (or leave data->output NULL) and record an error that
+ * tnns_cuda_last_error() reports.
+ *
+ * One context per host thread is created on first use (device from the environment
+ * variable TNNS_B200_DEVICE, default 0) together with a small cache of uploaded packed
+ * weights, keyed by host address, geometry and a 64-bit content hash, so that a layer
+ * called repeatedly (the reference's timing loops do that) uploads its weights once.
+ */
+#define _ISOC11_SOURCE
+#include <stdint.h>
+#include <stdio.h>
+#include <stdlib.h>
+#include <string.h>
+
+#include "tnns_b200.h"
+
+#define WORD_BITS 64
+#define WCACHE_SLOTS 16
+
+typedef struct {
+    const void* host;
+    uint64_t hash;
+    int type, KN, C, KH, KW, K_words, K_unpack;
+    tnns_cuda_weights* w;
+    unsigned long long stamp;
+} wcache_entry;
+
+static _Thread_local tnns_cuda_ctx* tl_ctx = NULL;
+static _Thread_local wcache_entry tl_wcache[WCACHE_SLOTS];
+static _Thread_local unsigned long long tl_stamp = 0;
+
+static tnns_cuda_ctx* default_ctx(void) {
+    if (!tl_ctx) {
+        const char* env = getenv("TNNS_B200_DEVICE");
+        int dev = env ? atoi(env) : 0;
+        if (tnns_cuda_create(dev, &tl_ctx) != TNNS_OK) tl_ctx = NULL;
+    }
+    return tl_ctx;
+}
+
+/* Four independent multiply-xor lanes over 64-bit words; only has to tell apart
+ * different weight tensors that happen to reuse one heap address. */
+static uint64_t hash_words(const int64_t* p, size_t words) {
+    uint64_t h[4] = {0x9E3779B97F4A7C15ull, 0xC2B2AE3D27D4EB4Full, 0x165667B19E3779F9ull, 0x27D4EB2F165667C5ull};
+    size_t i = 0;
+    for (; i + 4 <= words; i += 4)
+        for (int l = 0; l < 4; l++) h[l] = (h[l] ^ (uint64_t)p[i + l]) * 0x100000001B3ull + 0x632BE59BD9B4E019ull;
+    for (; i < words; i++) h[0] = (h[0] ^ (uint64_t)p[i]) * 0x100000001B3ull + 0x632BE59BD9B4E019ull;
+    uint64_t r = h[0];
+    for (int l = 1; l < 4; l++) r = (r ^ (h[l] >> 29) ^ h[l]) * 0xBF58476D1CE4E5B9ull;
+    return r ^ (r >> 31);
+}
+
+/* Weights of a layer (C, KH, KW > 0) or of a bare packed GEMM (C = KH = KW = 0). */
+static tnns_cuda_weights* cached_weights(tnns_cuda_ctx* ctx, int type, const int64_t* host, int KN, int C, int KH, int KW,
+                                         int K_words, int K_unpack) {
+    const int planes = (type == TNN || type == BTN) ? 2 : 1;
+    const size_t words = (size_t)KN * (4 * ((K_words + 3) / 4)) * planes;
+    const uint64_t h = hash_words(host, words);
+    int victim = 0;
+    for (int i = 0; i < WCACHE_SLOTS; i++) {
+        wcache_entry* e = &tl_wcache[i];
+        if (e->w && e->host == host && e->hash == h && e->type == type && e->KN == KN && e->C == C && e->KH == KH && e->KW == KW &&
+            e->K_words == K_words && e->K_unpack == K_unpack) {
+            e->stamp = ++tl_stamp;
+            return e->w;
+        }
+        if (!e->w) victim = i;
+        else if (tl_wcache[victim].w && e->stamp < tl_wcache[victim].stamp) victim = i;
+    }
+    wcache_entry* e = &tl_wcache[victim];
+    if (e->w) {
+        tnns_cuda_sync(ctx);
+        tnns_cuda_free_weights(ctx, e->w);
+        e->w = NULL;
+    }
+    tnns_cuda_weights* w = NULL;
+    int rc = C > 0 ? tnns_cuda_upload_weights(ctx, type, host, KN, C, KH, KW, &w)
+                   : tnns_cuda_upload_weights_packed(ctx, type, host, KN, K_words, K_unpack, &w);
+    if (rc != TNNS_OK) return NULL;
+    e->host = host; e->hash = h; e->type = type; e->KN = KN; e->C = C; e->KH = KH; e->KW = KW;
+    e->K_words = K_words; e->K_unpack = K_unpack; e->w = w;
+    e->stamp = ++tl_stamp;
+    return w;
+}
+
+/* ---- tnns_conv : src/tnns/tnns_cpu_mm_p2.c:83-120 ------------------------------------ */
+void tnns_conv(testcase_t* data) {
+    if (!data) return;
+    data->output = NULL;
+    tnns_cuda_ctx* ctx = default_ctx();
+    if (!ctx) return;
+    if (!data->input || !data->input_thresholds || !data->quantized_kernel_packing2) return;
+    tnns_shape_t s;
+    s.N = data->batchcount; s.C = data->channelcount; s.H = data->inputH; s.W = data->inputW;
+    s.KN = data->kernelcount; s.KH = data->kernelH; s.KW = data->kernelW;
+    s.PH = data->paddingH; s.PW = data->paddingW; s.SH = data->strideH; s.SW = data->strideW;
+    if (s.N <= 0 || s.C <= 0 || s.KN <= 0 || s.KH <= 0 || s.KW <= 0 || s.SH <= 0 || s.SW <= 0) return;
+    tnns_cuda_weights* w = cached_weights(ctx, (int)data->type, data->quantized_kernel_packing2, s.KN, s.C, s.KH, s.KW,
+                                          tnns_k_words(s.C, s.KH, s.KW), s.C * s.KH * s.KW);
+    if (!w) return;
+    const int OH = tnns_out_dim(s.H, s.PH, s.KH, s.SH), OW = tnns_out_dim(s.W, s.PW, s.KW, s.SW);
+    if (OH <= 0 || OW <= 0) return;
+    const size_t out_len = (size_t)s.N * s.KN * OH * OW;
+    float* y = (float*)calloc(out_len, sizeof(float)); /* the reference hands out calloc memory (include/tnns/mm.h:15) */
+    if (!y) return;
+    if (tnns_cuda_conv_host(ctx, w, data->input, data->input_thresholds, y, &s, data->preluAlpha, TNNS_NCHW) != TNNS_OK) {
+        free(y);
+        return;
+    }
+    data->output = y;
+}
+
+/* ---- packed GEMMs on host operands : include/tnns/mm.h:5-8 ------------------------------- */
+static float* mm_host(int type, int64_t* a, int64_t* b, int N, int OH, int OW, int KN, int K, int K_unpack, float alpha) {
+    tnns_cuda_ctx* ctx = default_ctx();
+    if (!ctx || !a || !b || N <= 0 || OH <= 0 || OW <= 0 || KN <= 0 || K <= 0) return NULL;
+    const int Kp = 4 * ((K + 3) / 4);
+    const int a_planes = (type == TNN || type == TBN) ? 2 : 1;
+    const size_t M = (size_t)N * OH * OW;
+    const size_t a_bytes = M * Kp * 8 * a_planes, y_bytes = M * KN * sizeof(float);
+    tnns_cuda_weights* w = cached_weights(ctx, type, b, KN, 0, 0, 0, K, K_unpack);
+    if (!w) return NULL;
+    void *d_a = NULL, *d_y = NULL;
+    float* y = NULL;
+    if (tnns_cuda_malloc(ctx, a_bytes, &d_a) == TNNS_OK && tnns_cuda_malloc(ctx, y_bytes, &d_y) == TNNS_OK &&
+        tnns_cuda_memcpy_h2d(ctx, d_a, a, a_bytes) == TNNS_OK &&
+        tnns_cuda_gemm(ctx, w, (const int64_t*)d_a, (float*)d_y, N, OH, OW, alpha, TNNS_NCHW, TNNS_GEMM_AUTO, NULL) == TNNS_OK) {
+        y = (float*)calloc(M * KN, sizeof(float));
+        if (y && tnns_cuda_memcpy_d2h(ctx, y, d_y, y_bytes) != TNNS_OK) { free(y); y = NULL; }
+    }
+    tnns_cuda_free(ctx, d_a);
+    tnns_cuda_free(ctx, d_y);
+    return y;
+}
+
+float* mm_tnn(int64_t* a, int64_t* b, int N, int OH, int OW, int KN, int K, float prelu_alpha) {
+    return mm_host(TNN, a, b, N, OH, OW, KN, K, 0, prelu_alpha);
+}
+float* mm_tbn(int64_t* a, int64_t* b, int N, int OH, int OW, int KN, int K, float prelu_alpha) {
+    return mm_host(TBN, a, b, N, OH, OW, KN, K, 0, prelu_alpha);
+}
+float* mm_btn(int64_t* a, int64_t* b, int N, int OH, int OW, int KN, int K, float prelu_alpha) {
+    return mm_host(BTN, a, b, N, OH, OW, KN, K, 0, prelu_alpha);
+}
+float* mm_bnn(int64_t* a, int64_t* b, int N, int OH, int OW, int KN, int K, int K_unpack, float prelu_alpha) {
+    return mm_host(BNN, a, b, N, OH, OW, KN, K, K_unpack, prelu_alpha);
+}
+
+/* ---- tnns_gemm : src/tnns/tnns_cpu_mm_p2.c:122-133 ---------------------------------------- */
+void tnns_gemm(testcase_tnns_gemm_t* data) {
+    if (!data) return;
+    float* result = mm_tnn(data->x_packing2, data->w_packing2, data->m, 1, 1, data->n, data->p_packed, 1.0f);
+    if (!result) return;
+    if (data->output) {
+        memcpy(data->output, result, (size_t)data->m * data->n * sizeof(float));
+        free(result);
+    } else {
+        data->output = result;
+    }
+}
+
+/* ---- quantise + pack + im2row on host tensors ------------------------------------------------ */
+static int64_t* pack_host(int ternary, float* x, float* thr, int N, int C, int H, int W, int PH, int PW, int KH, int KW, int SH,
+                          int SW) {
+    tnns_cuda_ctx* ctx = default_ctx();
+    if (!ctx || !x || !thr || N <= 0) return NULL;
+    tnns_shape_t s;
+    s.N = N; s.C = C; s.H = H; s.W = W; s.KN = 1; s.KH = KH; s.KW = KW; s.PH = PH; s.PW = PW; s.SH = SH; s.SW = SW;
+    const size_t out_bytes = tnns_packed_bytes(ternary ? TNN : BTN, &s);
+    if (!out_bytes) return NULL;
+    const size_t in_bytes = (size_t)N * C * H * W * sizeof(float);
+    void *d_x = NULL, *d_t = NULL, *d_p = NULL;
+    int64_t* out = NULL;
+    if (tnns_cuda_malloc(ctx, in_bytes, &d_x) == TNNS_OK && tnns_cuda_malloc(ctx, (size_t)N * sizeof(float), &d_t) == TNNS_OK &&
+        tnns_cuda_malloc(ctx, out_bytes, &d_p) == TNNS_OK && tnns_cuda_memcpy_h2d(ctx, d_x, x, in_bytes) == TNNS_OK &&
+        tnns_cuda_memcpy_h2d(ctx, d_t, thr, (size_t)N * sizeof(float)) == TNNS_OK &&
+        tnns_cuda_pack(ctx, ternary, (const float*)d_x, (const float*)d_t, (int64_t*)d_p, &s, TNNS_NCHW, TNNS_PACK_AUTO, NULL) == TNNS_OK) {
+        out = (int64_t*)aligned_alloc(32, (out_bytes + 31) / 32 * 32); /* src/tnns/ternarize2row_avx2.c:735 */
+        if (out && tnns_cuda_memcpy_d2h(ctx, out, d_p, out_bytes) != TNNS_OK) { free(out); out = NULL; }
+    }
+    tnns_cuda_free(ctx, d_x);
+    tnns_cuda_free(ctx, d_t);
+    tnns_cuda_free(ctx, d_p);
+    return out;
+}
+
+int64_t* t2r_p2_opt(float* x, float* q_thresholds, int N, int C, int H, int W, int H_pad, int W_pad, int kH, int kW, int H_stride,
+                    int W_stride) {
+    return pack_host(1, x, q_thresholds, N, C, H, W, H_pad, W_pad, kH, kW, H_stride, W_stride);
+}
+int64_t* b2r(float* x, float* q_thresholds, int N, int C, int H, int W, int H_pad, int W_pad, int kH, int kW, int H_stride,
+             int W_stride) {
+    return pack_host(0, x, q_thresholds, N, C, H, W, H_pad, W_pad, kH, kW, H_stride, W_stride);
+}
+
+/* ---- host weight packers : src/utils.c:468-521, 634-675 --------------------------------------- */
+int64_t* tnns_pack_weights_ternary(const float* w, const float* thr, int KN, int C, int KH, int KW) {
+    if (!w || !thr || KN <= 0 || C <= 0 || KH <= 0 || KW <= 0) return NULL;
+    const int Cp = (C + WORD_BITS - 1) / WORD_BITS, Kw = KH * KW * Cp, Kp = tnns_k_padded(C, KH, KW);
+    const size_t pitch = 2 * (size_t)Kp;
+    uint64_t* out = (uint64_t*)aligned_alloc(32, ((size_t)KN * pitch * 8 + 31) / 32 * 32);
+    if (!out) return NULL;
+    for (int kn = 0; kn < KN; kn++) {
+        uint64_t* row = out + (size_t)kn * pitch;
+        const float t = thr[kn];
+        for (int j = 0; j < Kp; j++) {
+            uint64_t sign = 0, zero = ~(uint64_t)0; /* pad-to-four words are zeros of the alphabet */
+            if (j < Kw) {
+                const int ic = j % Cp, tap = j / Cp; /* tap = kh*KW + kw */
+                zero = 0;
+                for (int bit = 0; bit < WORD_BITS; bit++) {
+                    const int c = ic * WORD_BITS + bit;
+                    /* channels past C are quantised as the value 0.0 */
+                    const float v = c < C ? w[((size_t)kn * C + c) * KH * KW + tap] : 0.0f;
+                    if (v > t) continue;                       /* +1 */
+                    if (v < -t) sign |= (uint64_t)1 << bit;    /* -1 */
+                    else zero |= (uint64_t)1 << bit;           /*  0 */
+                }
+            }
+            row[(size_t)(j / 4) * 8 + j % 4] = sign;
+            row[(size_t)(j / 4) * 8 + j % 4 + 4] = zero;
+        }
+    }
+    return (int64_t*)out;
+}
+
+int64_t* tnns_pack_weights_binary(const float* w, const float* thr, int KN, int C, int KH, int KW) {
+    if (!w || !thr || KN <= 0 || C <= 0 || KH <= 0 || KW <= 0) return NULL;
+    const int Cp = (C + WORD_BITS - 1) / WORD_BITS, Kw = KH * KW * Cp, Kp = tnns_k_padded(C, KH, KW);
+    uint64_t* out = (uint64_t*)aligned_alloc(32, ((size_t)KN * Kp * 8 + 31) / 32 * 32);
+    if (!out) return NULL;
+    for (int kn = 0; kn < KN; kn++)
+        for (int j = 0; j < Kp; j++) {
+            uint64_t sign = 0;
+            if (j < Kw) {
+                const int ic = j % Cp, tap = j / Cp;
+                for (int bit = 0; bit < WORD_BITS; bit++) {
+                    const int c = ic * WORD_BITS + bit;
+                    if (c < C && w[((size_t)kn * C + c) * KH * KW + tap] < thr[kn]) sign |= (uint64_t)1 << bit;
+                }
+            }
+            out[(size_t)kn * Kp + j] = sign;
+        }
+    return (int64_t*)out;
+}

@@ -1,0 +1,247 @@
+/*
+ * tnns_b200 -- C ABI of the B200 (sm_100a) implementation of FasterTNN's ternary /
+ * binary convolution + GEMM inference path.
+ *
+ * Two groups of entry points:
+ *
+ *  1. DROP-IN: the seven functions and two structs of the reference's CPU library,
+ *     with identical names, signatures, layouts and ownership rules, so the
+ *     reference's drivers (src/timing_layers.c, src/timing_gemm.c) link against
+ *     libtnns_b200.so instead of tnns_cpu_mm_p2.o + mm_p2_final_*.o +
+ *     {ternarize,binarize}2row_*.o.  They take HOST pointers and return malloc-family
+ *     host buffers.
+ *
+ *  2. DEVICE-RESIDENT: tnns_cuda_* functions over device pointers and an explicit
+ *     stream, for chained layers, per-kernel timing and multi-GPU sharding.  The
+ *     drop-in functions are thin wrappers over these.
+ *
+ * All functions have C linkage and use only plain pointers, integers and floats.
+ * File:line citations name the interface of the reference project
+ * (fpgasystems/FasterTNN) that each declaration replaces.
+ */
+#ifndef TNNS_B200_H
+#define TNNS_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------------------------------
+ * Types shared with the reference
+ * ---------------------------------------------------------------------------------------- */
+
+/* Network type: which operand is ternary (T) or binary (B); activations first.
+ * Replaces include/tnns/common.h:16. */
+enum tnns_type { TNN = 0, TBN = 1, BTN = 2, BNN = 3 };
+
+/* One convolution layer invocation.  Field order and types replace
+ * include/tnns/data.h:4-25 exactly (the struct crosses the boundary by pointer). */
+typedef struct testcase {
+    enum tnns_type type;
+    int batchcount;
+    int channelcount;
+    int inputW;
+    int inputH;
+    int kernelcount;
+    int kernelW;
+    int kernelH;
+    int paddingW;
+    int paddingH;
+    int strideW;
+    int strideH;
+    float preluAlpha;
+    float* input_thresholds;            /* one symmetric threshold per image            */
+    float* input;                       /* fp32 NCHW                                    */
+    float* kernel;                      /* fp32 weights; not read by tnns_conv          */
+    int64_t* quantized_kernel_packing0; /* not read                                     */
+    int64_t* quantized_kernel_packing1; /* not read                                     */
+    int64_t* quantized_kernel_packing2; /* packed weights, layout by type (see below)   */
+    float* output;                      /* set by tnns_conv; caller frees with free()   */
+} testcase_t;
+
+/* One packed GEMM invocation.  Replaces include/tnns/data.h:27-41. */
+typedef struct testcase_tnns_gemm {
+    int m;
+    int p;
+    int p_packed; /* 64-bit words per plane and row */
+    int n;
+    float* x;
+    float* w;
+    int64_t* x_packing0;
+    int64_t* x_packing1;
+    int64_t* x_packing2;
+    int64_t* w_packing0;
+    int64_t* w_packing1;
+    int64_t* w_packing2;
+    float* output;
+} testcase_tnns_gemm_t;
+
+/*
+ * Packed layouts (identical to the reference, so its host-packed weights upload
+ * unchanged and packed activations can be compared with memcmp):
+ *
+ *   C_pack = ceil(C/64); Kw = KH*KW*C_pack; Kp = 4*ceil(Kw/4).
+ *   Plane word j = (kh*KW + kw)*C_pack + ic holds channels 64*ic .. 64*ic+63 of the
+ *   tap (kh,kw), channel c at bit c%64, LSB first.
+ *   "packing-2" row (ternary operand): 2*Kp int64; sign word j at (j/4)*8 + j%4, zero
+ *   word j four words later (alternating 256-bit sign / 256-bit zero groups).
+ *   value -1: sign=1,zero=0; 0: sign=0,zero=1; +1: both 0.  Padding pixels, channels
+ *   past C and the words j in [Kw,Kp) are zeros (sign=0, zero=all ones).
+ *   "one-plane" row (binary operand): Kp int64, word j at j; bit=1 is -1, bit=0 is +1;
+ *   padding and tails are 0 (= +1).
+ */
+
+/* ------------------------------------------------------------------------------------------
+ * 1. Drop-in entry points (host pointers)
+ * ---------------------------------------------------------------------------------------- */
+
+/* Runs one layer on GPU 0 (or the device named by the environment variable
+ * TNNS_B200_DEVICE): quantise + pack + im2row, bitwise GEMM, PReLU.  Always sets
+ * data->output to a fresh calloc'd NCHW buffer of batch*kernelcount*OH*OW floats that
+ * the caller frees; on failure sets it to NULL and records an error (see
+ * tnns_cuda_last_error).  Replaces include/tnns/tnns_cpu.h:4 /
+ * src/tnns/tnns_cpu_mm_p2.c:83-120. */
+void tnns_conv(testcase_t* data);
+
+/* TNN GEMM on pre-packed operands with PReLU alpha fixed to 1, as the reference's
+ * final build does.  If data->output is non-NULL the m*n result is copied into it,
+ * otherwise a fresh buffer is handed over.  Replaces include/tnns/tnns_cpu.h:6 /
+ * src/tnns/tnns_cpu_mm_p2.c:122-133. */
+void tnns_gemm(testcase_tnns_gemm_t* data);
+
+/* Bitwise GEMM + PReLU on packed host operands; K = 64-bit words per plane BEFORE the
+ * pad-to-four (buffers must already be Kp wide).  a has N*OH*OW rows, b has KN rows.
+ * Returns a calloc'd NCHW float buffer or NULL.  Replace include/tnns/mm.h:5-8. */
+float* mm_tnn(int64_t* a, int64_t* b, int N, int OH, int OW, int KN, int K, float prelu_alpha);
+float* mm_tbn(int64_t* a, int64_t* b, int N, int OH, int OW, int KN, int K, float prelu_alpha);
+float* mm_btn(int64_t* a, int64_t* b, int N, int OH, int OW, int KN, int K, float prelu_alpha);
+float* mm_bnn(int64_t* a, int64_t* b, int N, int OH, int OW, int KN, int K, int K_unpack, float prelu_alpha);
+
+/* Quantise + bit-pack + im2row of an fp32 NCHW host tensor.  Return a 32-byte aligned
+ * host buffer (aligned_alloc; caller frees) of N*OH*OW rows, packing-2 (t2r_p2_opt) or
+ * one-plane (b2r).  Replace include/tnns/ternarize2row.h:7 and
+ * include/tnns/binarize2row.h:4. */
+int64_t* t2r_p2_opt(float* x, float* q_thresholds, int N, int C, int H, int W, int H_pad, int W_pad,
+                    int kH, int kW, int H_stride, int W_stride);
+int64_t* b2r(float* x, float* q_thresholds, int N, int C, int H, int W, int H_pad, int W_pad, int kH,
+             int kW, int H_stride, int W_stride);
+
+/* Host-side weight packers, run once per model: fp32 [KN][C][KH][KW] plus one
+ * threshold per kernel -> packing-2 rows (ternary) or one-plane rows (binary).
+ * Buffers come from aligned_alloc(32, ..); caller frees.  Replace
+ * ternarize_opt_avx2 / binarize_opt_avx2 (include/utils.h:22,27; src/utils.c:468-521,
+ * 634-675). */
+int64_t* tnns_pack_weights_ternary(const float* w, const float* thresholds, int KN, int C, int KH, int KW);
+int64_t* tnns_pack_weights_binary(const float* w, const float* thresholds, int KN, int C, int KH, int KW);
+
+/* ------------------------------------------------------------------------------------------
+ * 2. Device-resident API
+ * ---------------------------------------------------------------------------------------- */
+
+typedef struct tnns_cuda_ctx tnns_cuda_ctx;         /* per (host thread, device) state   */
+typedef struct tnns_cuda_weights tnns_cuda_weights; /* device copy of one packed kernel  */
+
+/* Geometry of one layer; the same quantities as the testcase_t fields. */
+typedef struct tnns_shape {
+    int N, C, H, W;  /* input batch, channels, height, width   */
+    int KN, KH, KW;  /* kernels, kernel height, kernel width   */
+    int PH, PW;      /* zero padding                           */
+    int SH, SW;      /* strides                                */
+} tnns_shape_t;
+
+/* Memory layout of the fp32 activation tensors at the device boundary. */
+enum tnns_layout { TNNS_NCHW = 0, TNNS_NHWC = 1 };
+
+/* Kernel selection.  AUTO picks per shape; the others force one implementation (used
+ * by tests to cross-check them and by the benchmark to compare them). */
+enum tnns_pack_algo { TNNS_PACK_AUTO = 0, TNNS_PACK_GATHER = 1, TNNS_PACK_STAGED = 2 };
+enum tnns_gemm_algo { TNNS_GEMM_AUTO = 0, TNNS_GEMM_POPC_SIMPLE = 1, TNNS_GEMM_POPC_TILED = 2, TNNS_GEMM_I8_TC = 3 };
+
+/* Error codes returned by every tnns_cuda_* function (0 = success). */
+enum tnns_status {
+    TNNS_OK = 0,
+    TNNS_ERR_INVALID = 1,     /* NULL pointer, non-positive dimension, kernel larger than image .. */
+    TNNS_ERR_CUDA = 2,        /* a CUDA runtime call failed; see tnns_cuda_error_detail           */
+    TNNS_ERR_NOMEM = 3,       /* host or device allocation failed                                 */
+    TNNS_ERR_UNSUPPORTED = 4, /* the forced algorithm cannot run this shape                       */
+    TNNS_ERR_DEVICE_WAIT = 5  /* a bounded on-device wait expired (kernel returned early)         */
+};
+
+int tnns_cuda_create(int device, tnns_cuda_ctx** ctx);
+void tnns_cuda_destroy(tnns_cuda_ctx* ctx);
+
+/* Derived sizes.  K words are 64-bit words per plane and row. */
+int tnns_out_dim(int in, int pad, int k, int stride); /* src/tnns/tnns_cpu_mm_p2.c:7-10 */
+int tnns_k_words(int C, int KH, int KW);              /* Kw                              */
+int tnns_k_padded(int C, int KH, int KW);             /* Kp                              */
+/* Bytes of the packed im2row matrix for this type and shape. */
+size_t tnns_packed_bytes(int type, const tnns_shape_t* s);
+
+/* Copies host-packed weights (reference layout for `type`: packing-2 for TNN/BTN,
+ * one-plane for TBN/BNN) to the device and prepares the per-kernel constants and the
+ * operand images the GEMM kernels need.  Done once per layer. */
+int tnns_cuda_upload_weights(tnns_cuda_ctx* ctx, int type, const int64_t* packed_host, int KN, int C, int KH,
+                             int KW, tnns_cuda_weights** out);
+/* Same for callers that hold only a packed operand (the mm_* functions): KN rows of
+ * K_words plane words (before the pad-to-four; the buffer is Kp wide), K_unpack =
+ * number of elements per row before any padding (used by BNN only).  Weights uploaded
+ * this way serve tnns_cuda_gemm; tnns_cuda_conv rejects them. */
+int tnns_cuda_upload_weights_packed(tnns_cuda_ctx* ctx, int type, const int64_t* packed_host, int KN, int K_words,
+                                    int K_unpack, tnns_cuda_weights** out);
+void tnns_cuda_free_weights(tnns_cuda_ctx* ctx, tnns_cuda_weights* w);
+
+/* Quantise + pack + im2row on the device.  ternary != 0: packing-2 rows (t2r_p2_opt
+ * semantics), else one-plane rows (b2r semantics).  d_x: fp32 in `layout`; d_thr: N
+ * floats; d_packed: tnns_packed_bytes() bytes, 16-byte aligned.  `stream` is a
+ * cudaStream_t passed as void* (NULL = default stream).  Asynchronous. */
+int tnns_cuda_pack(tnns_cuda_ctx* ctx, int ternary, const float* d_x, const float* d_thr, int64_t* d_packed,
+                   const tnns_shape_t* s, int layout, int algo, void* stream);
+
+/* Bitwise GEMM + PReLU on the device: d_a is the packed im2row matrix of N*OH*OW rows
+ * in the layout the weights' type expects; d_y receives N*KN*OH*OW floats in `layout`
+ * (NCHW: ((n*KN+kn)*OH+oh)*OW+ow as include/tnns/mm.h:30; NHWC: row-major rows x KN).
+ * Asynchronous. */
+int tnns_cuda_gemm(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const int64_t* d_a, float* d_y, int N, int OH,
+                   int OW, float alpha, int layout, int algo, void* stream);
+
+/* Whole layer on the device: pack into the context's workspace (grown with cudaMalloc
+ * when too small), then GEMM + PReLU.  Asynchronous unless the workspace grows. */
+int tnns_cuda_conv(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y,
+                   const tnns_shape_t* s, float alpha, int layout, int pack_algo, int gemm_algo, void* stream);
+
+/* Same with caller-owned workspace of at least tnns_packed_bytes() bytes. */
+int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr,
+                      float* d_y, void* d_workspace, size_t workspace_bytes, const tnns_shape_t* s, float alpha,
+                      int layout, int pack_algo, int gemm_algo, void* stream);
+
+/* Whole layer with HOST input / output buffers (pinned memory gives full PCIe speed):
+ * the batch is cut into slices whose upload, kernels and download overlap on three
+ * streams.  Synchronous: returns when h_y is complete. */
+int tnns_cuda_conv_host(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* h_x, const float* h_thr,
+                        float* h_y, const tnns_shape_t* s, float alpha, int layout);
+
+/* Blocks until all work submitted through ctx's own streams has finished and reports
+ * any asynchronous error, including the on-device status word. */
+int tnns_cuda_sync(tnns_cuda_ctx* ctx);
+
+/* Plain device-memory helpers so that C callers need no CUDA headers.  Synchronous. */
+int tnns_cuda_malloc(tnns_cuda_ctx* ctx, size_t bytes, void** out);
+void tnns_cuda_free(tnns_cuda_ctx* ctx, void* p);
+int tnns_cuda_memcpy_h2d(tnns_cuda_ctx* ctx, void* dst, const void* src, size_t bytes);
+int tnns_cuda_memcpy_d2h(tnns_cuda_ctx* ctx, void* dst, const void* src, size_t bytes);
+
+/* Number of kernels this library has launched in the calling thread since load. */
+unsigned long long tnns_cuda_launch_count(void);
+
+/* Last error of the calling thread (sticky until the next failing call). */
+int tnns_cuda_last_error(void);
+const char* tnns_cuda_strerror(int status);
+const char* tnns_cuda_error_detail(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* TNNS_B200_H */
