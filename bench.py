@@ -1,0 +1,374 @@
+#!/usr/bin/env python
+"""Benchmark of the ternary conv hot path (quantise+pack+im2row -> bitwise GEMM + PReLU).
+
+    python bench.py --gpus N --steps K --warmup W            # this library, one rank per GPU
+    python bench.py --impl reference --gpus N --steps K ...   # the reference's CPU code path
+
+Workload: the large single TNN conv layer -- batch 64, 512 channels, 32x32, 512 kernels
+3x3, stride 1, pad 1 (M=65536, K=4608, N=512), activations uniform in [-1,1), thresholds
++-0.25, ternary weights, PReLU alpha 0.5 -- partitioned by batch index over the ranks
+(weights replicated, no collective on the data path), so the total work is fixed as N grows.
+One "step" is one pass of the whole layer.  Metric: GOPS = 2*M*N*K / time (unpadded K).
+
+Prints ONE JSON line on rank 0.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import numpy as np  # noqa: E402
+
+from fastertnn_b200 import synth  # noqa: E402
+from fastertnn_b200.shard import batch_slice  # noqa: E402
+from fastertnn_b200.workloads import CONV_LARGE, CONV_56, FC_GEMM, Layer  # noqa: E402
+
+METRIC = "ternary conv GOPS (2*M*N*K/s)"
+L2_BYTES = 126 * 1024 * 1024
+SEED_X, SEED_W = 0xC0FFEE40, 0xC0FFEE41
+WORKLOADS = {
+    "tnn_conv_large": CONV_LARGE,   # batch 64, 512x32x32 -> 512, 3x3 s1 p1
+    "tnn_conv_56": CONV_56,         # batch 1, 256x56x56 -> 256
+    "tnn_fc": FC_GEMM,              # 1024 x 4096 -> 1024
+}
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "bf16_tflops_sustained": d["bf16_tflops_sustained"],
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
+
+
+def make_inputs(N_total: int, layer: Layer, n0: int, n1: int):
+    """Images n0..n1 of the seeded batch, the thresholds and the packed ternary weights."""
+    per = layer.C * layer.H * layer.W
+    x = synth.uniform_pm1(SEED_X, (n1 - n0, layer.C, layer.H, layer.W), offset=n0 * per)
+    thr = np.full(n1 - n0, 0.25, np.float32)
+    w = synth.ternary_values(SEED_W, (layer.KN, layer.C, layer.KH, layer.KW))
+    return x, thr, w
+
+
+# ------------------------------------------------------------------------------------------------
+# clocks sampled during the timed regions
+# ------------------------------------------------------------------------------------------------
+class ClockSampler:
+    REASONS = {0x8: "hw_slowdown", 0x40: "hw_thermal_slowdown", 0x20: "sw_thermal_slowdown", 0x4: "sw_power_cap",
+               0x80: "hw_power_brake_slowdown"}
+
+    def __init__(self, uuid: str | None):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        self._h = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            h = None
+            if uuid:
+                for cand in (uuid, "GPU-" + uuid):
+                    try:
+                        h = pynvml.nvmlDeviceGetHandleByUUID(cand.encode() if isinstance(cand, str) else cand)
+                        break
+                    except Exception:
+                        continue
+            self._h = h or pynvml.nvmlDeviceGetHandleByIndex(0)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self._h = None
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                r = nv.nvmlDeviceGetCurrentClocksEventReasons(self._h)
+                for bit, name in self.REASONS.items():
+                    if r & bit:
+                        self.reasons.add(name)
+            except Exception:
+                pass
+            self._stop.wait(0.02)
+
+    def start(self):
+        if self._h is not None and self._thread is None:
+            self._stop.clear()
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        if self._thread is not None:
+            self._stop.set()
+            self._thread.join()
+            self._thread = None
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": statistics.median(self.samples), "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons),
+                "samples": len(self.samples)}
+
+
+# ------------------------------------------------------------------------------------------------
+# CPU reference (the reference's own AVX2 objects when built, else the restatement)
+# ------------------------------------------------------------------------------------------------
+def cpu_layer_pass(chk, x, thr, wp, layer: Layer, threads: int):
+    """One pass over the batch, images spread over `threads` host threads (the reference code
+    is single-threaded and re-entrant; ctypes releases the GIL during the call)."""
+    from concurrent.futures import ThreadPoolExecutor
+    N = x.shape[0]
+    bounds = [batch_slice(N, r, min(threads, N)) for r in range(min(threads, N))]
+
+    def run(b):
+        a, e = b
+        return chk.conv(0, x[a:e], thr[a:e], wp, (layer.KH, layer.KW), (layer.P, layer.P), (layer.S, layer.S), 0.5)
+
+    t0 = time.perf_counter()
+    with ThreadPoolExecutor(len(bounds)) as ex:
+        outs = list(ex.map(run, bounds))
+    return time.perf_counter() - t0, outs
+
+
+def cpu_baseline(layer: Layer, N_total: int, passes: int):
+    from oracle import binding
+    chk = binding.best()
+    threads = os.cpu_count() or 1
+    x, thr, w = make_inputs(N_total, layer, 0, N_total)
+    wp = chk.pack_weights(True, w, np.full(layer.KN, 0.5, np.float32))
+    cpu_layer_pass(chk, x[:threads], thr[:threads], wp, layer, threads)  # warm-up
+    times = [cpu_layer_pass(chk, x, thr, wp, layer, threads)[0] for _ in range(passes)]
+    t = statistics.mean(times)
+    return {"value": layer.ops(N_total) / t / 1e9, "unit": "GOPS", "cores": min(threads, N_total), "kind": chk.kind,
+            "sample": f"{passes} passes over the full {N_total}-image batch, images split over {min(threads, N_total)} host threads, "
+                      f"mean {t * 1e3:.1f} ms per pass"}
+
+
+def run_reference(args, layer: Layer, N_total: int, name: str):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return  # the reference is a CPU code path: rank 0 alone runs it
+    from oracle import binding
+    chk = binding.best()
+    threads = os.cpu_count() or 1
+    x, thr, w = make_inputs(N_total, layer, 0, N_total)
+    wp = chk.pack_weights(True, w, np.full(layer.KN, 0.5, np.float32))
+    for _ in range(args.warmup):
+        cpu_layer_pass(chk, x, thr, wp, layer, threads)
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        cpu_layer_pass(chk, x, thr, wp, layer, threads)
+    t = (time.perf_counter() - t0) / args.steps
+    val = layer.ops(N_total) / t / 1e9
+    used = min(threads, N_total)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": val, "unit": "GOPS", "n_gpus": args.gpus, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "int (64-bit popcount lanes)", "data": "synthetic",
+        "config": {"workload": name, "batch": N_total, "layer": str(layer), "layout": "NCHW"},
+        "cpu_baseline": {"value": val, "unit": "GOPS", "cores": used, "kind": chk.kind,
+                         "sample": f"each step = one pass over the full {N_total}-image batch split over {used} host threads"},
+        "e2e": {"value": val, "unit": "GOPS", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+# ------------------------------------------------------------------------------------------------
+# this library
+# ------------------------------------------------------------------------------------------------
+def run_ours(args, layer: Layer, N_total: int, name: str):
+    import torch
+    import torch.distributed as dist
+    import fastertnn_b200 as ft
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run --nproc-per-node {args.gpus}")
+    if not torch.cuda.is_available():
+        raise SystemExit("no CUDA device: this benchmark has no CPU fallback")
+    torch.cuda.set_device(local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    def max_over_ranks(v: float) -> float:
+        if world == 1:
+            return v
+        t = torch.tensor([v], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    n0, n1 = batch_slice(N_total, rank, world)
+    nloc = n1 - n0
+    x_h, thr_h, w_f = make_inputs(N_total, layer, n0, n1)
+    wp = ft.pack_weights_ternary(w_f, np.full(layer.KN, 0.5, np.float32))
+    ctx = ft.Context(local)
+    w = ctx.upload_weights(ft.TNN, wp, layer.C, layer.KH, layer.KW)
+    shape = layer.shape(nloc)
+    OH, OW = layer.OH, layer.OW
+    in_bytes, out_bytes = x_h.nbytes, nloc * layer.KN * OH * OW * 4
+    pack_bytes = ft.packed_bytes(ft.TNN, shape)
+
+    # ring of distinct buffer sets so that consecutive steps never find their data in L2
+    step_bytes = in_bytes + out_bytes + pack_bytes
+    ring = max(2, -(-3 * L2_BYTES // max(step_bytes, 1)))
+    x_pin = torch.from_numpy(x_h).pin_memory()
+    thr_pin = torch.from_numpy(thr_h).pin_memory()
+    xs, ys, ps = [], [], []
+    for r in range(ring):
+        xd = torch.empty(x_h.shape, dtype=torch.float32, device="cuda")
+        xd.copy_(x_pin)
+        if r:  # distinct data per ring slot: rotate the images
+            xd.copy_(torch.roll(xd, shifts=r, dims=0))
+        xs.append(xd)
+        ys.append(torch.empty((nloc, layer.KN, OH, OW), dtype=torch.float32, device="cuda"))
+        ps.append(torch.empty(pack_bytes // 8 + 2, dtype=torch.int64, device="cuda"))
+    thr_d = torch.from_numpy(thr_h).cuda()
+    stream = torch.cuda.Stream()
+    sp = stream.cuda_stream
+    layout = ft.NCHW
+    gemm_algo = {"auto": ft.GEMM_AUTO, "popc": ft.GEMM_POPC_TILED, "i8tc": ft.GEMM_I8_TC}[args.gemm]
+
+    def step(i, ev=None):
+        r = i % ring
+        if ev:
+            ev[0].record(stream)
+        ctx.pack(True, xs[r].data_ptr(), thr_d.data_ptr(), ps[r].data_ptr(), shape, layout, ft.PACK_AUTO, sp)
+        if ev:
+            ev[1].record(stream)
+        ctx.gemm(w, ps[r].data_ptr(), ys[r].data_ptr(), nloc, OH, OW, 0.5, layout, gemm_algo, sp)
+        if ev:
+            ev[2].record(stream)
+
+    # correctness gate on a slice small enough for the CPU checker (not timed)
+    if rank == 0 and not args.no_check:
+        from oracle import binding
+        chk = binding.best()
+        step(0)
+        torch.cuda.synchronize()
+        want = chk.conv(0, x_h[:1], thr_h[:1], wp, (layer.KH, layer.KW), (layer.P, layer.P), (layer.S, layer.S), 0.5)
+        if ys[0][:1].cpu().numpy().tobytes() != want.tobytes():
+            raise SystemExit("bench: GPU output differs from the CPU checker; refusing to time a wrong kernel")
+
+    sampler = ClockSampler(str(torch.cuda.get_device_properties(local).uuid)) if rank == 0 else None
+
+    # ---- device-resident timing -----------------------------------------------------------
+    for i in range(args.warmup):
+        step(i)
+    barrier()
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(args.steps)]
+    e_start, e_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches0 = ft.api.launch_count()
+    if sampler:
+        sampler.start()
+    e_start.record(stream)
+    for i in range(args.steps):
+        step(args.warmup + i, evs[i])
+    e_end.record(stream)
+    stream.synchronize()
+    barrier()
+    if sampler:
+        sampler.stop()
+    launches = ft.api.launch_count() - launches0
+    ms_total = max_over_ranks(e_start.elapsed_time(e_end))
+    ms_step = ms_total / args.steps
+    t_pack = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
+    t_gemm = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
+    ctx.sync()
+
+    # ---- end to end: pinned host buffers in, host buffers out, copies inside the timed region ----
+    y_pin = torch.empty((nloc, layer.KN, OH, OW), dtype=torch.float32).pin_memory()
+    for _ in range(max(1, min(args.warmup, 3))):
+        ctx.conv_host(w, x_pin.data_ptr(), thr_pin.data_ptr(), y_pin.data_ptr(), shape, 0.5, layout)
+    e2e_steps = max(3, min(args.steps, 10))
+    barrier()
+    if sampler:
+        sampler.start()
+    t0 = time.perf_counter()
+    for _ in range(e2e_steps):
+        ctx.conv_host(w, x_pin.data_ptr(), thr_pin.data_ptr(), y_pin.data_ptr(), shape, 0.5, layout)
+    torch.cuda.synchronize()
+    e2e_ms = max_over_ranks((time.perf_counter() - t0) * 1e3) / e2e_steps
+    barrier()
+    if sampler:
+        sampler.stop()
+    e2e_ok = bool(torch.equal(y_pin[:1], ys[0][:1].cpu())) if ring and args.warmup + args.steps > 0 else True
+
+    if rank == 0:
+        pk = peaks()
+        ops = layer.ops(N_total)
+        ops_loc = layer.ops(nloc)
+        pack_alg_bytes = in_bytes + pack_bytes
+        gemm_tops = ops_loc / (t_gemm * 1e-3) / 1e12
+        line = {
+            "metric": METRIC, "value": ops / (ms_step * 1e-3) / 1e9, "unit": "GOPS", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "dtype": "int32 popcount accumulate (u32 bit-plane lanes), fp32 PReLU",
+            "data": "synthetic",
+            "config": {"workload": name, "batch": N_total, "batch_per_gpu": nloc, "layer": str(layer), "layout": "NCHW",
+                       "M": N_total * OH * OW, "K": layer.C * layer.KH * layer.KW, "N": layer.KN, "gemm": args.gemm,
+                       "l2": f"ring of {ring} distinct input/workspace/output buffer sets ({ring * step_bytes >> 20} MiB) cycled "
+                             f"between steps; one set alone is {step_bytes >> 20} MiB"},
+            "gpu_launches": int(launches * world),
+            "kernels_ms": {"pack": t_pack, "gemm": t_gemm},
+            "roofline": {
+                "kernel": "pack (quantise+bit-pack+im2row)", "bound": "hbm", "achieved": pack_alg_bytes / (t_pack * 1e-3) / 1e9,
+                "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": pack_alg_bytes / (t_pack * 1e-3) / 1e9 / pk["hbm_gbs"],
+                "traffic": None, "peak_source": pk["source"]},
+            "roofline_gemm": {"kernel": "bitwise GEMM + PReLU", "achieved": gemm_tops, "unit": "TOP/s",
+                              "gemm_hbm_gbs": (pack_bytes + out_bytes) / (t_gemm * 1e-3) / 1e9},
+            "e2e": {"value": ops / (e2e_ms * 1e-3) / 1e9, "unit": "GOPS", "ms_per_step": e2e_ms, "steps": e2e_steps,
+                    "h2d_bytes_per_step": int((in_bytes + thr_h.nbytes) * world), "d2h_bytes_per_step": int(out_bytes * world),
+                    "matches_device_path": e2e_ok},
+            "clocks": sampler.summary() if sampler else None,
+        }
+        if world == 1 and not args.no_cpu:
+            line["cpu_baseline"] = cpu_baseline(layer, N_total, passes=args.cpu_passes)
+        print(json.dumps(line), flush=True)
+    w.free()
+    ctx.close()
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    ap.add_argument("--workload", choices=sorted(WORKLOADS), default="tnn_conv_large")
+    ap.add_argument("--gemm", choices=["auto", "popc", "i8tc"], default="auto")
+    ap.add_argument("--no-check", action="store_true", help="skip the pre-timing comparison with the CPU checker")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--cpu-passes", type=int, default=5)
+    args = ap.parse_args()
+    if args.warmup < 3 and args.impl == "ours":
+        args.warmup = 3
+    N_total, layer = WORKLOADS[args.workload]
+    if args.impl == "reference":
+        run_reference(args, layer, N_total, args.workload)
+    else:
+        run_ours(args, layer, N_total, args.workload)
+
+
+if __name__ == "__main__":
+    main()

@@ -40,6 +40,7 @@ def main():
         raise SystemExit("oracle/_ref/libtnns_ref.so is missing: run `make -C oracle` where the reference sources are")
     out = {}
     for c in golden_cases():
+        c = c.build()
         wp = R.pack_weights(wgt_ternary(c.type), c.w, c.w_thr)
         ap = R.pack(act_ternary(c.type), c.x, c.thr, c.kernel_hw, c.padding, c.stride)
         y = R.conv(c.type, c.x, c.thr, wp, c.kernel_hw, c.padding, c.stride, c.alpha)

@@ -59,6 +59,7 @@ def test_size_helpers():
 
 @pytest.mark.parametrize("case", extra_cases()[::2], ids=lambda c: c.name)
 def test_host_weight_packers_match_oracle(case, port_oracle):
+    case = case.build()
     t = wgt_ternary(case.type)
     mine = (ft.pack_weights_ternary if t else ft.pack_weights_binary)(case.w, case.w_thr)
     assert np.array_equal(mine, port_oracle.pack_weights(t, case.w, case.w_thr))

@@ -1,0 +1,214 @@
+"""GPU suite: every result of the CUDA path, obtained through the C ABI, is compared
+bit-for-bit with the CPU checker (the reference's own objects when oracle/_ref was built,
+else the restatement) and with the committed digests."""
+import hashlib
+import json
+from pathlib import Path
+
+import numpy as np
+import pytest
+
+import fastertnn_b200 as ft
+from cases import (BNN, BTN, TBN, TNN, act_ternary, extra_cases, make_case, reference_test_cases, to_nchw, to_nhwc,
+                   wgt_ternary)
+from fastertnn_b200.workloads import CONV_56, FC_GEMM, Layer
+
+pytestmark = pytest.mark.gpu
+
+DIGESTS = json.loads((Path(__file__).resolve().parent / "golden" / "digests.json").read_text())
+CASES = (reference_test_cases(N=2, dist="uniform", max_ops=3e9) + reference_test_cases(N=2, dist="alphabet", max_ops=3e9)
+         + extra_cases())
+
+
+def sha(a):
+    return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+
+
+def device_pack(ctx, case, layout, algo):
+    tern = act_ternary(case.type)
+    L = case.layer
+    shape = L.shape(case.N)
+    x = case.x if layout == ft.NCHW else to_nhwc(case.x)
+    d_x, d_t = ctx.to_device(x), ctx.to_device(case.thr)
+    nbytes = ft.packed_bytes(case.type, shape)
+    d_p = ctx.malloc(nbytes + 64)
+    try:
+        ctx.pack(tern, d_x, d_t, d_p, shape, layout, algo)
+        ctx.sync()
+        rows = case.N * L.OH * L.OW
+        return ctx.to_host(d_p, (rows, nbytes // 8 // rows), np.int64)
+    finally:
+        for p in (d_x, d_t, d_p):
+            ctx.free(p)
+
+
+def device_conv(ctx, case, wp, layout, pack_algo, gemm_algo):
+    L = case.layer
+    shape = L.shape(case.N)
+    w = ctx.upload_weights(case.type, wp, L.C, L.KH, L.KW)
+    x = case.x if layout == ft.NCHW else to_nhwc(case.x)
+    d_x, d_t = ctx.to_device(x), ctx.to_device(case.thr)
+    d_y = ctx.malloc(case.N * L.KN * L.OH * L.OW * 4)
+    try:
+        ctx.conv(w, d_x, d_t, d_y, shape, case.alpha, layout, pack_algo, gemm_algo)
+        ctx.sync()
+        if layout == ft.NCHW:
+            return ctx.to_host(d_y, (case.N, L.KN, L.OH, L.OW), np.float32)
+        return to_nchw(ctx.to_host(d_y, (case.N, L.OH, L.OW, L.KN), np.float32))
+    finally:
+        for p in (d_x, d_t, d_y):
+            ctx.free(p)
+        w.free()
+
+
+@pytest.mark.parametrize("case", CASES, ids=lambda c: c.name)
+def test_layer_matches_checker_and_golden(case, gpu_ctx, checker):
+    """pack (both kernels, both layouts) and GEMM (both kernels) against the checker."""
+    case = case.build()
+    tern = act_ternary(case.type)
+    wp = checker.pack_weights(wgt_ternary(case.type), case.w, case.w_thr)
+    a_ref = checker.pack(tern, case.x, case.thr, case.kernel_hw, case.padding, case.stride)
+    y_ref = checker.conv(case.type, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
+    d = DIGESTS[case.name]
+    assert sha(a_ref) == d["packed"] and sha(y_ref) == d["output"]
+    for layout in (ft.NCHW, ft.NHWC):
+        for algo in (ft.PACK_GATHER, ft.PACK_STAGED, ft.PACK_AUTO):
+            a = device_pack(gpu_ctx, case, layout, algo)
+            assert np.array_equal(a, a_ref), f"packed matrix differs (layout {layout}, algo {algo})"
+    for layout in (ft.NCHW, ft.NHWC):
+        for galgo in (ft.GEMM_POPC_SIMPLE, ft.GEMM_POPC_TILED, ft.GEMM_AUTO):
+            y = device_conv(gpu_ctx, case, wp, layout, ft.PACK_AUTO, galgo)
+            assert y.tobytes() == y_ref.tobytes(), f"output differs (layout {layout}, gemm {galgo})"
+    assert sha(device_conv(gpu_ctx, case, wp, ft.NCHW, ft.PACK_AUTO, ft.GEMM_AUTO)) == d["output"]
+
+
+@pytest.mark.parametrize("case", (reference_test_cases(N=2, dist="uniform", max_ops=3e9)[::5] + extra_cases()[::7]),
+                         ids=lambda c: c.name)
+def test_drop_in_entry_points(case, checker):
+    """The seven reference symbols, host pointers in and malloc'd host buffers out."""
+    case = case.build()
+    tern = act_ternary(case.type)
+    L = case.layer
+    wp = ft.pack_weights_ternary(case.w, case.w_thr) if wgt_ternary(case.type) else ft.pack_weights_binary(case.w, case.w_thr)
+    assert np.array_equal(wp, checker.pack_weights(wgt_ternary(case.type), case.w, case.w_thr))
+    y_ref = checker.conv(case.type, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
+    y = ft.tnns_conv(case.type, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
+    assert y.tobytes() == y_ref.tobytes()
+    a = (ft.t2r_p2_opt if tern else ft.b2r)(case.x, case.thr, case.kernel_hw, case.padding, case.stride)
+    assert np.array_equal(a, checker.pack(tern, case.x, case.thr, case.kernel_hw, case.padding, case.stride))
+    K = L.KH * L.KW * ((L.C + 63) // 64)
+    if case.type == BNN:
+        y2 = ft.mm_bnn(a, wp, case.N, L.OH, L.OW, L.KN, K, L.C * L.KH * L.KW, case.alpha)
+    else:
+        y2 = {TNN: ft.mm_tnn, TBN: ft.mm_tbn, BTN: ft.mm_btn}[case.type](a, wp, case.N, L.OH, L.OW, L.KN, K, case.alpha)
+    assert y2.tobytes() == y_ref.tobytes()
+
+
+def test_tnns_gemm_entry_point(checker):
+    """tnns_gemm: packed TNN operands, alpha fixed to 1, optional caller-owned output."""
+    m, n, words = 70, 45, 8
+    rng = np.random.default_rng(5)
+    x = rng.integers(-1, 2, size=(m, words * 64)).astype(np.float32).reshape(m, words * 64, 1, 1)
+    w = rng.integers(-1, 2, size=(n, words * 64)).astype(np.float32).reshape(n, words * 64, 1, 1)
+    xa = checker.pack(True, x, np.full(m, 0.5, np.float32), (1, 1))
+    wa = checker.pack_weights(True, w, np.full(n, 0.5, np.float32))
+    ref = checker.mm(TNN, xa, wa, m, 1, 1, n, words, 1.0).reshape(m, n)
+    got = ft.tnns_gemm(xa, wa, m, n, words)
+    assert got.tobytes() == ref.tobytes()
+    assert np.array_equal(got, x.reshape(m, -1) @ w.reshape(n, -1).T)  # alpha = 1: plain integer product
+    out = np.full((m, n), -7.0, np.float32)
+    ft.tnns_gemm(xa, wa, m, n, words, out=out)
+    assert out.tobytes() == ref.tobytes()
+
+
+@pytest.mark.parametrize("type_", [TNN, TBN, BTN])
+def test_benchmark_configs_small_enough_for_the_checker(type_, gpu_ctx, checker):
+    """The FC (GEMM) configuration and the batch-1 56x56x256 conv, at full size."""
+    for N, layer in (FC_GEMM, CONV_56):
+        if type_ != TNN and layer is FC_GEMM[1]:
+            continue
+        case = make_case(type_, layer, N, 31337 + type_, "uniform")
+        case.thr[:] = 0.25 if act_ternary(type_) else 0.0
+        wp = checker.pack_weights(wgt_ternary(type_), case.w, case.w_thr)
+        y_ref = checker.conv(type_, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
+        for layout in (ft.NCHW, ft.NHWC):
+            y = device_conv(gpu_ctx, case, wp, layout, ft.PACK_AUTO, ft.GEMM_AUTO)
+            assert y.tobytes() == y_ref.tobytes()
+
+
+def test_host_buffer_layer_matches_device_layer(gpu_ctx, checker):
+    """tnns_cuda_conv_host slices the batch and overlaps copies; results must not change."""
+    layer = Layer(128, 12, 12, 96, 3, 3, 1, 1)
+    case = make_case(TNN, layer, 19, 99, "uniform")  # 19 images -> slices of 3 with a ragged tail
+    wp = checker.pack_weights(True, case.w, case.w_thr)
+    y_ref = checker.conv(TNN, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
+    w = gpu_ctx.upload_weights(TNN, wp, layer.C, layer.KH, layer.KW)
+    y = np.empty_like(y_ref)
+    for _ in range(2):  # second call reuses the staging buffers
+        y.fill(np.nan)
+        gpu_ctx.conv_host(w, case.x.ctypes.data, case.thr.ctypes.data, y.ctypes.data, layer.shape(case.N), case.alpha)
+        assert y.tobytes() == y_ref.tobytes()
+    w.free()
+
+
+def test_empty_batch_is_a_no_op(gpu_ctx):
+    layer = Layer(64, 4, 4, 8, 3, 3, 1, 1)
+    shape = layer.shape(0)
+    wp = ft.pack_weights_ternary(np.zeros((8, 64, 3, 3), np.float32), np.full(8, 0.5, np.float32))
+    w = gpu_ctx.upload_weights(TNN, wp, 64, 3, 3)
+    d = gpu_ctx.malloc(64)
+    gpu_ctx.conv(w, d, d, d, shape, 0.5)
+    gpu_ctx.sync()
+    gpu_ctx.free(d)
+    w.free()
+
+
+def test_argument_errors_are_reported_not_fatal(gpu_ctx):
+    layer = Layer(64, 4, 4, 8, 3, 3, 1, 1)
+    wp = ft.pack_weights_ternary(np.zeros((8, 64, 3, 3), np.float32), np.full(8, 0.5, np.float32))
+    w = gpu_ctx.upload_weights(TNN, wp, 64, 3, 3)
+    d = gpu_ctx.malloc(1 << 16)
+    with pytest.raises(ft.TnnsError) as e:
+        gpu_ctx.conv(w, 0, d, d, layer.shape(1), 0.5)          # NULL input
+    assert e.value.status == 1
+    with pytest.raises(ft.TnnsError):
+        gpu_ctx.conv(w, d, d, d, Layer(32, 4, 4, 8, 3, 3, 1, 1).shape(1), 0.5)   # weights are for C=64
+    with pytest.raises(ft.TnnsError):
+        gpu_ctx.conv(w, d, d, d, Layer(64, 2, 2, 8, 3, 3, 0, 1).shape(1), 0.5)   # kernel larger than image
+    with pytest.raises(ft.TnnsError):
+        gpu_ctx.pack(True, d, d, d + 8, layer.shape(1))          # misaligned output
+    with pytest.raises(ft.TnnsError) as e:
+        gpu_ctx.conv(w, d, d, d, layer.shape(1), 0.5, gemm_algo=99)
+    assert e.value.status == 1
+    # the context is still usable afterwards
+    gpu_ctx.conv(w, d, d, d + 4096, layer.shape(1), 0.5)
+    gpu_ctx.sync()
+    gpu_ctx.free(d)
+    w.free()
+
+
+def test_large_layer_properties(gpu_ctx, checker):
+    """The large-layer configuration (512 channels, 32x32, 512 kernels) at a batch the GPU
+    runs in milliseconds, checked through properties that need no full-size CPU run:
+    (1) images 0..1 of the batch equal the checker's result for those images alone;
+    (2) the tiled and the one-thread-per-output GEMM agree on every element;
+    (3) negating the activations negates the integer accumulator (ternary quantisation with
+        symmetric thresholds is odd, the GEMM is linear)."""
+    layer = Layer(512, 32, 32, 512, 3, 3, 1, 1)
+    N = 16
+    case = make_case(TNN, layer, N, 2024, "uniform")
+    case.thr[:] = 0.25
+    wp = checker.pack_weights(True, case.w, case.w_thr)
+    y = device_conv(gpu_ctx, case, wp, ft.NCHW, ft.PACK_AUTO, ft.GEMM_AUTO)
+    y2 = checker.conv(TNN, case.x[:2], case.thr[:2], wp, case.kernel_hw, case.padding, case.stride, case.alpha)
+    assert y[:2].tobytes() == y2.tobytes()
+    y_simple = device_conv(gpu_ctx, case, wp, ft.NCHW, ft.PACK_GATHER, ft.GEMM_POPC_SIMPLE)
+    assert y.tobytes() == y_simple.tobytes()
+    neg = make_case(TNN, layer, N, 2024, "uniform")
+    neg.thr[:] = 0.25
+    neg.x = -neg.x
+    yn = device_conv(gpu_ctx, neg, wp, ft.NCHW, ft.PACK_AUTO, ft.GEMM_AUTO)
+    acc = np.where(y > 0, y, y / 0.5)
+    accn = np.where(yn > 0, yn, yn / 0.5)
+    assert np.array_equal(acc, -accn)
+    assert np.abs(acc).max() <= 4608

@@ -33,6 +33,7 @@ def test_every_digest_has_a_case():
 
 @pytest.mark.parametrize("case", CASES, ids=lambda c: c.name)
 def test_port_matches_golden(case, port_oracle):
+    case = case.build()
     d = DIGESTS[case.name]
     wp = port_oracle.pack_weights(wgt_ternary(case.type), case.w, case.w_thr)
     assert sha(wp) == d["weights"]
@@ -49,6 +50,7 @@ def test_port_matches_golden(case, port_oracle):
 
 @pytest.mark.parametrize("case", CASES[::3], ids=lambda c: c.name)
 def test_reference_objects_match_golden(case, ref_oracle):
+    case = case.build()
     d = DIGESTS[case.name]
     wp = ref_oracle.pack_weights(wgt_ternary(case.type), case.w, case.w_thr)
     assert sha(wp) == d["weights"]
@@ -62,6 +64,7 @@ def test_reference_objects_match_golden(case, ref_oracle):
 def test_reference_statements_agree(case, ref_oracle):
     """The reference's own protocol (src/timing_layers.c:142-165): tnns_conv against
     direct_pad + direct_conv2d, plus its naive packing-0 implementation."""
+    case = case.build()
     from oracle import binding
     nv = binding.naive()
     wt = wgt_ternary(case.type)
