@@ -18,6 +18,7 @@ ROOT = Path(__file__).resolve().parents[1]
 def declared_functions():
     text = (ROOT / "include" / "tnns_b200.h").read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    text = re.sub(r"^\s*#.*$", "", text, flags=re.M)  # preprocessor lines declare no functions
     names = re.findall(r"\b([A-Za-z_][A-Za-z0-9_]*)\s*\([^;{}]*\)\s*;", text)
     return sorted(set(n for n in names if n not in ("defined",)))
 
