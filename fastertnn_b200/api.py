@@ -307,5 +307,16 @@ class Context:
         return out
 
 
+def noalloc_scratch_bytes() -> int:
+    return load_library().tnns_cuda_noalloc_scratch_bytes()
+
+
+def conv_noalloc(type_: int, d_packed_weights: int, d_x: int, d_thr: int, d_y: int, shape: Shape, alpha: float, layout=NCHW,
+                 stream=0):
+    """Whole layer on the current device without any allocation: the packed matrix goes to
+    the library's built-in scratch array (see tnns_cuda_conv_noalloc in the header)."""
+    _check(load_library().tnns_cuda_conv_noalloc(type_, d_packed_weights, d_x, d_thr, d_y, C.byref(shape), alpha, layout, stream))
+
+
 def launch_count() -> int:
     return load_library().tnns_cuda_launch_count()

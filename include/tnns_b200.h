@@ -223,6 +223,35 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
 int tnns_cuda_conv_host(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* h_x, const float* h_thr,
                         float* h_y, const tnns_shape_t* s, float alpha, int layout);
 
+/* Whole layer for callers that must not allocate (no counterpart in the reference, which
+ * has no device and no allocator constraints).  Meant for hosts that cannot call
+ * cudaMalloc: servers that give all device memory to their own arena at start-up,
+ * plug-ins living inside another framework's caching allocator, or latency-critical
+ * loops where an allocation, which may synchronise the device, is forbidden.
+ *
+ * The packed im2row matrix is kept in a fixed array of TNNS_NOALLOC_SCRATCH_BYTES bytes
+ * that is part of the library image: every GPU whose context loads the library holds
+ * that much memory until the process exits.  A layer whose packed matrix
+ * (tnns_packed_bytes) is larger is refused with TNNS_ERR_UNSUPPORTED and a message that
+ * names both sizes; split the batch or use tnns_cuda_conv_ws.
+ *
+ * No context and no weights handle are needed: d_packed_weights is a device pointer to
+ * the kernel rows in the reference layout for `type` (16-byte aligned), d_x / d_thr /
+ * d_y are the caller's device buffers as for tnns_cuda_conv.  The work runs on the
+ * CURRENT device, which must own all four pointers.  The call itself uses no cudaMalloc,
+ * cudaFree or other allocating routine.  The first call on each device also looks up the
+ * device address of the scratch array and two device attributes; make that first call
+ * outside of any stream capture.
+ *
+ * All calls on a device share the one scratch array.  Nothing in it needs to start at
+ * zero (every call rewrites all of the rows it then reads), but two calls that can run
+ * at the same time on the GPU -- different streams, or different host threads -- race on
+ * it: order them on one stream or with events.  Asynchronous. */
+#define TNNS_NOALLOC_SCRATCH_BYTES (32u << 20)
+size_t tnns_cuda_noalloc_scratch_bytes(void);
+int tnns_cuda_conv_noalloc(int type, const int64_t* d_packed_weights, const float* d_x, const float* d_thr, float* d_y,
+                           const tnns_shape_t* s, float alpha, int layout, void* stream);
+
 /* Blocks until all work submitted through ctx's own streams has finished and reports
  * any asynchronous error, including the on-device status word. */
 int tnns_cuda_sync(tnns_cuda_ctx* ctx);
