@@ -81,6 +81,7 @@ SIGNATURES = {
     "tnns_cuda_conv_host": (_i, [_vp, _vp, _vp, _vp, _vp, _pshape, _f, _i]),
     "tnns_cuda_noalloc_scratch_bytes": (_sz, []),
     "tnns_cuda_conv_noalloc": (_i, [_i, _vp, _vp, _vp, _vp, _pshape, _f, _i, _vp]),
+    "tnns_cuda_pipe_rate": (_i, [_vp, _i, C.POINTER(C.c_double)]),
     "tnns_cuda_sync": (_i, [_vp]),
     "tnns_cuda_malloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "tnns_cuda_free": (None, [_vp, _vp]),

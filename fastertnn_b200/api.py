@@ -283,6 +283,12 @@ class Context:
         """Host-pointer layer (addresses of pinned or pageable buffers)."""
         _check(self.lib.tnns_cuda_conv_host(self.handle, w.handle, h_x, h_thr, h_y, C.byref(shape), alpha, layout))
 
+    def pipe_rate(self, op: int) -> float:
+        """Issue rate of LOP3 (0), POPC (1) or IADD (2) in 1e9 thread-instructions per second."""
+        v = C.c_double()
+        _check(self.lib.tnns_cuda_pipe_rate(self.handle, op, C.byref(v)))
+        return v.value
+
     def sync(self):
         _check(self.lib.tnns_cuda_sync(self.handle))
 

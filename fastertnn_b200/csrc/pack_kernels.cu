@@ -9,12 +9,17 @@
 // HBM traffic: 4 bytes read per input value plus 16*Kp (ternary) or 8*Kp (binary) bytes
 // written per output row.
 #include <algorithm>
+#include <climits>
+#include <cstdlib>
 
 #include "internal.h"
 
 namespace {
 
 constexpr int kPackThreads = 256;
+#ifndef TNNS_PACK_MINCTA
+#define TNNS_PACK_MINCTA 4
+#endif
 
 __device__ __forceinline__ void tern_accum(float v, float t, float nt, uint32_t bit, uint32_t& sign, uint32_t& nz) {
     // sign iff v < -t ; non-zero iff v < -t or v > t  (src/tnns/ternarize2row_avx2.c:444-449)
@@ -79,21 +84,69 @@ __global__ void __launch_bounds__(256) pack_gather_kernel(const float* __restric
 // ---------------------------------------------------------------------------------------
 // Staged kernel.
 //   grid.x = N * nbands ; block = 256 threads ; dynamic smem:
-//     planes * Lmax * Cp   uint64   packed pixels of the band (plane 0 sign, plane 1 zero)
-//     Kp                   uint32   tap table: j -> (kh<<24 | kw<<16 | ic)
+//     planes * Lmax * Cp   uint64   packed pixels of the band, [pixel][ic] (plane 0 sign, 1 zero)
+//     Kp                   int32    tap table: word offset of plane word j relative to the
+//                                   window's first pixel, (kh*W + kw)*Cp + ic ; INT_MIN for the
+//                                   words added by the pad-to-four
+//     Kp                   uint32   tap table: kh<<16 | kw  (border windows only)
 // LAYOUT 0: NCHW, one thread packs VEC neighbouring pixels over 64 channels (loads are
 //           coalesced along W, channel stride H*W).
 // LAYOUT 1: NHWC, one warp packs 32 neighbouring channels of a pixel with __ballot_sync.
+// PAIR:     C_pack is even, so plane words 2k and 2k+1 of a row are neighbours in shared
+//           memory and move as one 128-bit load.
 // ---------------------------------------------------------------------------------------
-template <bool TERNARY, int LAYOUT, int VEC>
-__global__ void __launch_bounds__(kPackThreads)
+constexpr int kPadWord = INT_MIN;
+
+// Branch-free quantisation.  For finite fp32 a, b the rounded difference a-b is negative
+// exactly when a < b (gradual underflow keeps non-zero differences non-zero, and x-x is +0),
+// so the predicates are read off sign bits:
+//   ternary sign     v < -t   <=>  signbit(v + t)
+//   ternary non-zero |v| > t  <=>  signbit(t - |v|)   (equals "v < -t or v > t" for every t)
+//   binary  sign     v <  t   <=>  signbit(v - t)
+// and pushed into the plane word with one funnel shift each: acc = (acc << 1) | signbit.
+// Channels are therefore visited from 31 down to 0 so that channel b ends at bit b.
+__device__ __forceinline__ uint32_t push_sign(uint32_t acc, float d) {
+    return __funnelshift_l(__float_as_uint(d), acc, 1);
+}
+
+template <bool TERNARY, int VEC>
+__device__ __forceinline__ void quantise_batch(const float* __restrict__ q, size_t HW, float t, uint32_t (&sg)[VEC],
+                                               uint32_t (&nzb)[VEC]) {
+    // channels q[7*HW] .. q[0] (descending), eight at a time: all loads first, then the pushes
+    float vals[8][VEC];
+#pragma unroll
+    for (int k = 0; k < 8; k++) {
+        const float* pk = q + (size_t)(7 - k) * HW;
+        if (VEC == 4) {
+            const float4 f = __ldg(reinterpret_cast<const float4*>(pk));
+            vals[k][0] = f.x; vals[k][1 % VEC] = f.y; vals[k][2 % VEC] = f.z; vals[k][3 % VEC] = f.w;
+        } else {
+            vals[k][0] = __ldg(pk);
+        }
+    }
+#pragma unroll
+    for (int k = 0; k < 8; k++)
+#pragma unroll
+        for (int v = 0; v < VEC; v++) {
+            if (TERNARY) {
+                sg[v] = push_sign(sg[v], vals[k][v] + t);
+                nzb[v] = push_sign(nzb[v], t - fabsf(vals[k][v]));
+            } else {
+                sg[v] = push_sign(sg[v], (vals[k][v] + 0.0f) - t);  // + 0.0f turns -0 into +0: (-0) - (+0) would be -0
+            }
+        }
+}
+
+template <bool TERNARY, int LAYOUT, int VEC, bool PAIR>
+__global__ void __launch_bounds__(kPackThreads, TNNS_PACK_MINCTA)
 pack_staged_kernel(const float* __restrict__ x, const float* __restrict__ thr, uint4* __restrict__ out, TnnsGeom g,
                    int BOH, int nbands, int Lmax, FastDiv divU, FastDiv divOW, FastDiv divL) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     constexpr int PLANES = TERNARY ? 2 : 1;
     uint64_t* sm_sign = reinterpret_cast<uint64_t*>(smem_raw);
     uint64_t* sm_zero = sm_sign + (size_t)Lmax * g.Cp;  // only valid when TERNARY
-    uint32_t* jtab = reinterpret_cast<uint32_t*>(sm_sign + (size_t)PLANES * Lmax * g.Cp);
+    int* joff = reinterpret_cast<int*>(sm_sign + (size_t)PLANES * Lmax * g.Cp);
+    uint32_t* jtap = reinterpret_cast<uint32_t*>(joff + g.Kp);
 
     const int tid = threadIdx.x;
     const int n = blockIdx.x / nbands;
@@ -102,16 +155,20 @@ pack_staged_kernel(const float* __restrict__ x, const float* __restrict__ thr, u
     const int boh = min(BOH, g.OH - oh0);
     const int ih_lo = max(oh0 * g.SH - g.PH, 0);
     const int ih_hi = min((oh0 + boh - 1) * g.SH - g.PH + g.KH, g.H);  // exclusive
-    const int L = max(ih_hi - ih_lo, 0) * g.W;                          // pixels held in smem
-    const float t = thr[n], nt = -t;
+    const int nrow = max(ih_hi - ih_lo, 0);                              // input rows held in smem
+    const int L = nrow * g.W;                                            // pixels held in smem
+    const float t = thr[n] + 0.0f, nt = -t;  // + 0.0f: a threshold of -0 behaves as +0 in every compare
 
     for (int j = tid; j < g.Kp; j += kPackThreads) {
-        uint32_t e = 0xFFFFFFFFu;  // words added by the pad-to-four
+        int off = kPadWord;
+        uint32_t tap = 0;
         if (j < g.Kw) {
             const int ic = j % g.Cp, kw = (j / g.Cp) % g.KW, kh = j / (g.Cp * g.KW);
-            e = ((uint32_t)kh << 24) | ((uint32_t)kw << 16) | (uint32_t)ic;
+            off = (kh * g.W + kw) * g.Cp + ic;
+            tap = ((uint32_t)kh << 16) | (uint32_t)kw;
         }
-        jtab[j] = e;
+        joff[j] = off;
+        jtap[j] = tap;
     }
 
     // ---------------- phase 1: quantise + pack the band's input pixels ----------------
@@ -120,50 +177,46 @@ pack_staged_kernel(const float* __restrict__ x, const float* __restrict__ thr, u
         const int LV = L / VEC;  // VEC divides L by construction (host checks W % VEC == 0)
         const int items = g.Cp * LV;
         for (int id = tid; id < items; id += kPackThreads) {
-            const int ic = (LV == divL.d) ? (int)divL.div((uint32_t)id) : id / LV;
+            const int ic = (LV == (int)divL.d) ? (int)divL.div((uint32_t)id) : id / LV;
             const int p = (id - ic * LV) * VEC;
             const int nch = min(TNNS_WORD_BITS, g.C - ic * TNNS_WORD_BITS);
             const float* src = x + ((size_t)n * g.C + (size_t)ic * TNNS_WORD_BITS) * HW + (size_t)ih_lo * g.W + p;
-            uint32_t sg[VEC][2], nzb[VEC][2];
+            uint32_t sg[2][VEC], nzb[2][VEC];
 #pragma unroll
-            for (int v = 0; v < VEC; v++) { sg[v][0] = sg[v][1] = 0; nzb[v][0] = nzb[v][1] = 0; }
+            for (int v = 0; v < VEC; v++) { sg[0][v] = sg[1][v] = 0; nzb[0][v] = nzb[1][v] = 0; }
 #pragma unroll
             for (int half = 0; half < 2; half++) {
                 if (nch >= 32 * half + 32) {
-#pragma unroll 16
-                    for (int b = 0; b < 32; b++) {
-                        const float* q = src + (size_t)(32 * half + b) * HW;
-                        float vals[VEC];
-                        if (VEC == 4) {
-                            const float4 f = __ldg(reinterpret_cast<const float4*>(q));
-                            vals[0] = f.x; vals[1 % VEC] = f.y; vals[2 % VEC] = f.z; vals[3 % VEC] = f.w;
-                        } else {
-                            vals[0] = __ldg(q);
-                        }
-#pragma unroll
-                        for (int v = 0; v < VEC; v++) {
-                            if (TERNARY) tern_accum(vals[v], t, nt, 1u << b, sg[v][half], nzb[v][half]);
-                            else if (vals[v] < t) sg[v][half] |= 1u << b;
-                        }
-                    }
+#pragma unroll 1
+                    for (int b0 = 24; b0 >= 0; b0 -= 8)  // one batch of eight loads in flight per thread
+                        quantise_batch<TERNARY, VEC>(src + (size_t)(32 * half + b0) * HW, HW, t, sg[half], nzb[half]);
                 } else {
-                    const int lim = nch - 32 * half;  // may be <= 0
-                    for (int b = 0; b < lim; b++) {
+                    const int lim = nch - 32 * half;  // channels present in this half-word; may be <= 0
+                    for (int b = 31; b >= 0; b--) {
                         const float* q = src + (size_t)(32 * half + b) * HW;
 #pragma unroll
                         for (int v = 0; v < VEC; v++) {
-                            const float val = __ldg(q + v);
-                            if (TERNARY) tern_accum(val, t, nt, 1u << b, sg[v][half], nzb[v][half]);
-                            else if (val < t) sg[v][half] |= 1u << b;
+                            if (b < lim) {
+                                const float val = __ldg(q + v);
+                                if (TERNARY) {
+                                    sg[half][v] = push_sign(sg[half][v], val + t);
+                                    nzb[half][v] = push_sign(nzb[half][v], t - fabsf(val));
+                                } else {
+                                    sg[half][v] = push_sign(sg[half][v], (val + 0.0f) - t);
+                                }
+                            } else {  // absent channel: sign 0, non-zero 0
+                                sg[half][v] <<= 1;
+                                if (TERNARY) nzb[half][v] <<= 1;
+                            }
                         }
                     }
                 }
             }
 #pragma unroll
             for (int v = 0; v < VEC; v++) {
-                const size_t at = (size_t)(p + v) * g.Cp + ic;
-                sm_sign[at] = ((uint64_t)sg[v][1] << 32) | sg[v][0];
-                if (TERNARY) sm_zero[at] = ~(((uint64_t)nzb[v][1] << 32) | nzb[v][0]);
+                const int at = (p + v) * g.Cp + ic;
+                sm_sign[at] = ((uint64_t)sg[1][v] << 32) | sg[0][v];
+                if (TERNARY) sm_zero[at] = ~(((uint64_t)nzb[1][v] << 32) | nzb[0][v]);
             }
         }
     } else {
@@ -217,52 +270,68 @@ pack_staged_kernel(const float* __restrict__ x, const float* __restrict__ thr, u
     __syncthreads();
 
     // ---------------- phase 2: emit the band's im2row rows ----------------
-    const uint32_t U = TERNARY ? (uint32_t)g.Kp : (uint32_t)g.Kp / 2;  // 16-byte chunks per row
-    const uint32_t chunks = (uint32_t)(boh * g.OW) * U;
+    // One unit = plane words (2k, 2k+1) of one output row: for a ternary row the sign pair and
+    // the zero pair (two 16-byte stores 32 bytes apart), for a binary row one 16-byte store.
+    const uint32_t UP = (uint32_t)g.Kp / 2;                              // units per row
+    const uint32_t U = TERNARY ? (uint32_t)g.Kp : (uint32_t)g.Kp / 2;   // 16-byte chunks per row
+    const uint32_t units = (uint32_t)(boh * g.OW) * UP;
     uint4* dst = out + ((size_t)n * g.OH + oh0) * g.OW * U;
-    for (uint32_t q = tid; q < chunks; q += kPackThreads) {
+    for (uint32_t q = tid; q < units; q += kPackThreads) {
         const uint32_t row = divU.div(q);
-        const uint32_t u = q - row * U;
+        const uint32_t k = q - row * UP;
         const uint32_t ohl = divOW.div(row);
         const int ow = (int)(row - ohl * g.OW);
-        const int ihb = (oh0 + (int)ohl) * g.SH - g.PH - ih_lo;  // relative to the smem band
-        const int iwb = ow * g.SW - g.PW;
-        int plane, j0;
-        if (TERNARY) { plane = (u >> 1) & 1; j0 = (int)((u >> 2) * 4 + (u & 1) * 2); }
-        else { plane = 0; j0 = (int)(2 * u); }
-        const uint64_t* sm = plane ? sm_zero : sm_sign;
-        const uint64_t padv = plane ? ~0ull : 0ull;
-        uint64_t w[2];
-#pragma unroll
-        for (int k = 0; k < 2; k++) {
-            const uint32_t e = jtab[j0 + k];
-            uint64_t val = padv;
-            if (e != 0xFFFFFFFFu) {
-                const int ihr = ihb + (int)(e >> 24);
-                const int iw = iwb + (int)((e >> 16) & 0xFF);
-                const int ic = (int)(e & 0xFFFF);
-                // ihr is relative to ih_lo; rows above/below the image fall outside [0, ih_hi-ih_lo)
-                if (ihr >= 0 && ihr < ih_hi - ih_lo && iw >= 0 && iw < g.W) val = sm[(size_t)(ihr * g.W + iw) * g.Cp + ic];
+        const int ih0 = (oh0 + (int)ohl) * g.SH - g.PH - ih_lo;  // window origin relative to the smem band
+        const int iw0 = ow * g.SW - g.PW;
+        const int base = (ih0 * g.W + iw0) * g.Cp;
+        const bool interior = ih0 >= 0 && ih0 + g.KH <= nrow && iw0 >= 0 && iw0 + g.KW <= g.W;
+        const int2 o = *reinterpret_cast<const int2*>(joff + 2 * k);
+        uint64_t s0 = 0, s1 = 0, z0 = ~0ull, z1 = ~0ull;
+        if (PAIR && interior && o.x != kPadWord) {
+            // C_pack even: word 2k+1 follows word 2k in shared memory and both are real taps
+            const uint4 sv = *reinterpret_cast<const uint4*>(sm_sign + base + o.x);
+            s0 = ((uint64_t)sv.y << 32) | sv.x; s1 = ((uint64_t)sv.w << 32) | sv.z;
+            if (TERNARY) {
+                const uint4 zv = *reinterpret_cast<const uint4*>(sm_zero + base + o.x);
+                z0 = ((uint64_t)zv.y << 32) | zv.x; z1 = ((uint64_t)zv.w << 32) | zv.z;
             }
-            w[k] = val;
+        } else {
+            const uint2 tp = *reinterpret_cast<const uint2*>(jtap + 2 * k);
+            if (o.x != kPadWord) {
+                const int ih = ih0 + (int)(tp.x >> 16), iw = iw0 + (int)(tp.x & 0xFFFF);
+                if (ih >= 0 && ih < nrow && iw >= 0 && iw < g.W) { s0 = sm_sign[base + o.x]; if (TERNARY) z0 = sm_zero[base + o.x]; }
+            }
+            if (o.y != kPadWord) {
+                const int ih = ih0 + (int)(tp.y >> 16), iw = iw0 + (int)(tp.y & 0xFFFF);
+                if (ih >= 0 && ih < nrow && iw >= 0 && iw < g.W) { s1 = sm_sign[base + o.y]; if (TERNARY) z1 = sm_zero[base + o.y]; }
+            }
         }
-        dst[q] = make_uint4((uint32_t)w[0], (uint32_t)(w[0] >> 32), (uint32_t)w[1], (uint32_t)(w[1] >> 32));
+        if (TERNARY) {
+            uint4* d = dst + (size_t)row * U + (k >> 1) * 4 + (k & 1);
+            d[0] = make_uint4((uint32_t)s0, (uint32_t)(s0 >> 32), (uint32_t)s1, (uint32_t)(s1 >> 32));
+            d[2] = make_uint4((uint32_t)z0, (uint32_t)(z0 >> 32), (uint32_t)z1, (uint32_t)(z1 >> 32));
+        } else {
+            dst[(size_t)row * U + k] = make_uint4((uint32_t)s0, (uint32_t)(s0 >> 32), (uint32_t)s1, (uint32_t)(s1 >> 32));
+        }
     }
 }
 
 template <bool TERNARY, int LAYOUT, int VEC>
 int launch_staged(tnns_cuda_ctx* ctx, const float* d_x, const float* d_thr, void* d_packed, const TnnsGeom& g, int BOH,
                   int Lmax, size_t smem, cudaStream_t stream) {
-    auto kern = pack_staged_kernel<TERNARY, LAYOUT, VEC>;
-    if (smem > 48 * 1024) TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     const int nbands = (g.OH + BOH - 1) / BOH;
-    const uint32_t U = TERNARY ? g.Kp : g.Kp / 2;
+    const uint32_t UP = g.Kp / 2;
     const int LV = std::max(Lmax / VEC, 1);
-    kern<<<g.N * nbands, kPackThreads, smem, stream>>>(d_x, d_thr, reinterpret_cast<uint4*>(d_packed), g, BOH, nbands, Lmax,
-                                                       tnns_fastdiv(U), tnns_fastdiv(g.OW), tnns_fastdiv(LV));
-    tnns_count_launch();
-    TNNS_CUDA_TRY(cudaGetLastError());
-    return TNNS_OK;
+    const bool pair = (g.Cp % 2) == 0;
+    auto launch = [&](auto kern) -> int {
+        if (smem > 48 * 1024) TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        kern<<<g.N * nbands, kPackThreads, smem, stream>>>(d_x, d_thr, reinterpret_cast<uint4*>(d_packed), g, BOH, nbands, Lmax,
+                                                           tnns_fastdiv(UP), tnns_fastdiv(g.OW), tnns_fastdiv(LV));
+        tnns_count_launch();
+        TNNS_CUDA_TRY(cudaGetLastError());
+        return TNNS_OK;
+    };
+    return pair ? launch(pack_staged_kernel<TERNARY, LAYOUT, VEC, true>) : launch(pack_staged_kernel<TERNARY, LAYOUT, VEC, false>);
 }
 
 }  // namespace
@@ -295,20 +364,23 @@ int tnns_launch_pack(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const f
 
     const int planes = ternary ? 2 : 1;
     // staged kernel limits: tap table fields and 32-bit chunk counters
-    bool staged_ok = g.KH < 256 && g.KW < 256 && g.Cp < 65536;
+    bool staged_ok = g.KH < 65536 && g.KW < 65536 &&
+                     (long long)(g.KH * (long long)g.W + g.KW) * g.Cp < (1LL << 30);
     int BOH = 0, Lmax = 0;
     size_t smem = 0;
     if (staged_ok) {
-        const size_t budget_pref = 64 * 1024, budget_max = ctx->smem_optin;
+        // bands small enough for four resident blocks per SM, and at least two blocks per SM
+        const size_t budget_pref = 48 * 1024, budget_max = ctx->smem_optin;
+        const int min_blk = 2;
         auto smem_for = [&](int boh) {
-            return (size_t)planes * band_input_rows(g, boh) * g.W * g.Cp * 8 + (size_t)g.Kp * 4;
+            return (size_t)planes * band_input_rows(g, boh) * g.W * g.Cp * 8 + (size_t)g.Kp * 8;
         };
         if (smem_for(1) > budget_max) staged_ok = false;
         else {
             BOH = g.OH;
             while (BOH > 1 && smem_for(BOH) > budget_pref) BOH = (BOH + 1) / 2;
             // enough thread blocks to fill the machine twice over, if the layer allows it
-            while (BOH > 1 && (long long)g.N * ((g.OH + BOH - 1) / BOH) < 2LL * ctx->sm_count) BOH = (BOH + 1) / 2;
+            while (BOH > 1 && (long long)g.N * ((g.OH + BOH - 1) / BOH) < (long long)min_blk * ctx->sm_count) BOH = (BOH + 1) / 2;
             Lmax = band_input_rows(g, BOH) * g.W;
             smem = smem_for(BOH);
             if ((unsigned long long)BOH * g.OW * g.Kp >= (1ull << 31)) staged_ok = false;

@@ -262,6 +262,11 @@ void tnns_cuda_free(tnns_cuda_ctx* ctx, void* p);
 int tnns_cuda_memcpy_h2d(tnns_cuda_ctx* ctx, void* dst, const void* src, size_t bytes);
 int tnns_cuda_memcpy_d2h(tnns_cuda_ctx* ctx, void* dst, const void* src, size_t bytes);
 
+/* Measurement utility: issue rate of one integer instruction kind over the whole GPU
+ * (op 0 = LOP3, 1 = POPC, 2 = IADD), in 1e9 thread-instructions per second.  Gives the
+ * denominator for "fraction of the integer pipe" figures of the popcount GEMM. */
+int tnns_cuda_pipe_rate(tnns_cuda_ctx* ctx, int op, double* giga_per_s);
+
 /* Number of kernels this library has launched in the calling thread since load. */
 unsigned long long tnns_cuda_launch_count(void);
 

@@ -9,8 +9,8 @@ import numpy as np
 import pytest
 
 import fastertnn_b200 as ft
-from cases import (BNN, BTN, TBN, TNN, act_ternary, extra_cases, make_case, reference_test_cases, to_nchw, to_nhwc,
-                   wgt_ternary)
+from cases import (BNN, BTN, TBN, TNN, act_ternary, extra_cases, make_case, reference_test_cases, special_value_case, to_nchw,
+                   to_nhwc, wgt_ternary)
 from fastertnn_b200.workloads import CONV_56, FC_GEMM, Layer
 
 pytestmark = pytest.mark.gpu
@@ -102,6 +102,23 @@ def test_drop_in_entry_points(case, checker):
     else:
         y2 = {TNN: ft.mm_tnn, TBN: ft.mm_tbn, BTN: ft.mm_btn}[case.type](a, wp, case.N, L.OH, L.OW, L.KN, K, case.alpha)
     assert y2.tobytes() == y_ref.tobytes()
+
+
+@pytest.mark.parametrize("type_", [TNN, TBN, BTN, BNN])
+def test_special_values(type_, gpu_ctx, checker):
+    """+-0, values equal to and next to the thresholds, denormals and infinities quantise as
+    in the reference, in every pack kernel and layout."""
+    case = special_value_case(type_)
+    a_ref = checker.pack(act_ternary(type_), case.x, case.thr, case.kernel_hw, case.padding, case.stride)
+    for layout in (ft.NCHW, ft.NHWC):
+        for algo in (ft.PACK_GATHER, ft.PACK_STAGED):
+            assert np.array_equal(device_pack(gpu_ctx, case, layout, algo), a_ref), (layout, algo)
+    # W not a multiple of four takes the scalar-load variant of the staged kernel
+    odd = special_value_case(type_)
+    odd.layer = Layer(96, 6, 7, 16, 3, 3, 1, 1)
+    odd.x = np.ascontiguousarray(odd.x[:, :, :, :7])
+    a_ref = checker.pack(act_ternary(type_), odd.x, odd.thr, odd.kernel_hw, odd.padding, odd.stride)
+    assert np.array_equal(device_pack(gpu_ctx, odd, ft.NCHW, ft.PACK_STAGED), a_ref)
 
 
 def test_tnns_gemm_entry_point(checker):

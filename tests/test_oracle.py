@@ -9,7 +9,7 @@ from pathlib import Path
 import numpy as np
 import pytest
 
-from cases import act_ternary, extra_cases, reference_test_cases, wgt_ternary
+from cases import act_ternary, extra_cases, reference_test_cases, special_value_case, wgt_ternary
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 DIGESTS = json.loads((GOLDEN / "digests.json").read_text())
@@ -97,3 +97,13 @@ def test_prelu_zero_is_positive_zero(port_oracle):
     wp = port_oracle.pack_weights(True, w, np.full(4, 0.5, np.float32))
     y = port_oracle.conv(0, x, np.array([0.25], np.float32), wp, (3, 3), (1, 1), (1, 1), 0.5)
     assert np.all(y.view(np.uint32) == 0)
+
+
+@pytest.mark.parametrize("type_", [0, 1, 2, 3])
+def test_special_values_port_equals_reference_objects(type_, port_oracle, ref_oracle):
+    """+-0, values equal to and next to the thresholds, denormals, infinities."""
+    c = special_value_case(type_)
+    t = act_ternary(type_)
+    a_p = port_oracle.pack(t, c.x, c.thr, c.kernel_hw, c.padding, c.stride)
+    a_r = ref_oracle.pack(t, c.x, c.thr, c.kernel_hw, c.padding, c.stride)
+    assert np.array_equal(a_p, a_r)
