@@ -204,6 +204,11 @@ static int upload_weights_impl(tnns_cuda_ctx* ctx, int type, const int64_t* pack
         return tnns_fail(e == cudaErrorMemoryAllocation ? TNNS_ERR_NOMEM : TNNS_ERR_CUDA, "weight upload failed: %s",
                          cudaGetErrorString(e));
     }
+    int rc = tnns_build_i8_weights(ctx, w);
+    if (rc != TNNS_OK) {
+        tnns_cuda_free_weights(ctx, w);
+        return rc;
+    }
     *out = w;
     return TNNS_OK;
 }
@@ -257,7 +262,7 @@ int tnns_cuda_gemm(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const int64_t
             return tnns_launch_gemm_popc(ctx, w->type, d_a, w->d_packed, d_y, M, w->KN, w->Kp, OH * OW, K_unpack, alpha, layout,
                                          true, (cudaStream_t)stream);
         case TNNS_GEMM_I8_TC:
-            return tnns_fail(TNNS_ERR_UNSUPPORTED, "tensor-core GEMM is not built into this library version");
+            return tnns_launch_gemm_i8_tc(ctx, w, d_a, d_y, M, OH * OW, alpha, layout, (cudaStream_t)stream);
         default:
             return tnns_fail(TNNS_ERR_INVALID, "unknown GEMM algorithm %d", algo);
     }

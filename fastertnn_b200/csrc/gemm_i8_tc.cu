@@ -1,0 +1,417 @@
+// Bitwise GEMM + PReLU on the 5th-generation tensor cores: the packed {-1,0,+1} / {-1,+1}
+// operands are expanded to int8 on the fly and multiplied with tcgen05.mma.kind::i8, int32
+// accumulators in tensor memory.  Because |acc| <= 64*Kp the integer result is exact, so the
+// output is bit-identical to the popcount kernels (reference: mm_tnn / mm_tbn / mm_btn /
+// mm_bnn, src/tnns/mm_p2_final_*_avx2.c).
+//
+// One persistent block per SM, 320 threads in four roles:
+//   warp 0      weight producer: one bulk async copy (TMA engine, no multicast) per stage of a
+//               pre-expanded, pre-swizzled int8 weight tile (built once per layer at upload)
+//   warp 1      MMA issuer: one thread issues four tcgen05.mma (K = 32 each) per stage and
+//               commits to the stage's "empty" barrier; owns the tensor-memory allocation
+//   warps 2-5   activation expanders: thread = row; load the packed planes from global memory,
+//               expand 128 elements (4 lanes per plane) to int8 with LOP3/PRMT and store them in
+//               the 128-byte-swizzled K-major layout the MMA descriptor expects
+//   warps 6-9   epilogue: tcgen05.ld the finished accumulator (double buffered in tensor
+//               memory), apply the BNN constant and PReLU, store fp32 (NCHW: 32 consecutive
+//               pixels per warp and kernel -> 128-byte stores)
+// Every mbarrier wait is bounded; on expiry the kernel raises a status word, all roles leave
+// their loops, tensor memory is freed and the kernel returns.
+//
+// The order of the K elements inside a 128-element chunk is whatever the expansion routine
+// produces; activations and weights go through the same routine, so the permutation cancels
+// in the dot product.
+#include <algorithm>
+
+#include "internal.h"
+
+namespace {
+
+constexpr int BM = 128;        // rows per tile (tensor-memory lanes)
+constexpr int KCH = 128;       // K elements = bytes per row and stage (one swizzle atom)
+constexpr int NSTG = 4;        // smem ring depth
+constexpr int A_STAGE = BM * KCH;
+constexpr int NTHREADS = 320;
+constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_EXP0 = 2, WARP_EPI0 = 6;
+constexpr unsigned STATUS_WAIT_EXPIRED = 0x100;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+
+// Bounded wait: gives up after about a second, raises the status word and the block-wide
+// abort flag.  Returns false when the caller must leave its loop.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int* status, unsigned code) {
+    if (mbar_try_wait(bar, parity)) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 256; i++)
+            if (mbar_try_wait(bar, parity)) return true;
+        if (*abort_flag) return false;
+        if (clock64() - t0 > 2000000000LL) {
+            *abort_flag = 1;
+            atomicOr(status, STATUS_WAIT_EXPIRED | code);
+            return false;
+        }
+    }
+}
+
+__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem), "l"(src),
+                 "r"(bytes), "r"(bar)
+                 : "memory");
+}
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 B apart, 8-row
+// groups 1024 B apart (stride byte offset), descriptor version 1 (sm_100).
+__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;              // leading byte offset (unused with swizzle)
+    d |= (uint64_t)(1024 >> 4) << 32;    // stride byte offset
+    d |= (uint64_t)1 << 46;              // version
+    d |= (uint64_t)2 << 61;              // SWIZZLE_128B
+    return d;
+}
+
+// 32 elements (one 32-bit lane per plane) -> 32 int8 in a fixed permuted order, as eight words.
+// code = zero<<1 | sign : 0 -> +1, 1 -> -1, 2 or 3 -> 0 (a set zero bit wins, as az|bz does).
+__device__ __forceinline__ void expand32(uint32_t s, uint32_t z, uint32_t (&w)[8]) {
+    constexpr uint32_t TAB = 0x0000FF01u;
+    const uint32_t x = (s & 0x55555555u) | ((z << 1) & 0xAAAAAAAAu);   // codes of even elements
+    const uint32_t y = ((s >> 1) & 0x55555555u) | (z & 0xAAAAAAAAu);   // codes of odd elements
+    const uint32_t e0 = x & 0x33333333u, e1 = (x >> 2) & 0x33333333u;
+    const uint32_t e2 = y & 0x33333333u, e3 = (y >> 2) & 0x33333333u;
+    w[0] = __byte_perm(TAB, 0, e0); w[1] = __byte_perm(TAB, 0, e0 >> 16);
+    w[2] = __byte_perm(TAB, 0, e1); w[3] = __byte_perm(TAB, 0, e1 >> 16);
+    w[4] = __byte_perm(TAB, 0, e2); w[5] = __byte_perm(TAB, 0, e2 >> 16);
+    w[6] = __byte_perm(TAB, 0, e3); w[7] = __byte_perm(TAB, 0, e3 >> 16);
+}
+
+// Writes the 128 int8 of one row and chunk (four lanes) into a swizzled tile image.
+// `tile` points at row 0 of a 1024-byte aligned tile; generic pointer (smem or global).
+__device__ __forceinline__ void store_row_chunk(unsigned char* tile, int r, const uint4& s, const uint4& z) {
+    const uint32_t sl[4] = {s.x, s.y, s.z, s.w}, zl[4] = {z.x, z.y, z.z, z.w};
+    unsigned char* row = tile + (size_t)r * KCH;
+#pragma unroll
+    for (int l = 0; l < 4; l++) {
+        uint32_t w[8];
+        expand32(sl[l], zl[l], w);
+        *reinterpret_cast<uint4*>(row + (((2 * l) ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        *reinterpret_cast<uint4*>(row + (((2 * l + 1) ^ (r & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// One-time weight expansion: packed rows -> int8 tile images, [n_tile][chunk][BN rows][128 B],
+// swizzled exactly as the MMA reads them, rows past KN left zero.
+// ---------------------------------------------------------------------------------------
+__global__ void expand_weights_kernel(const uint4* __restrict__ packed, unsigned char* __restrict__ img, int KN, int Kp, int BN,
+                                      int two_planes) {
+    const int nch = Kp / 2;
+    const long long total = (long long)KN * nch;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int kn = (int)(i / nch), c = (int)(i - (long long)kn * nch);
+        const int g = c >> 1, h = c & 1;
+        uint4 s, z = make_uint4(0, 0, 0, 0);
+        if (two_planes) {
+            const uint4* grp = packed + ((size_t)kn * Kp) + (size_t)g * 4;  // row pitch Kp uint4, group 4 uint4
+            s = grp[h];
+            z = grp[2 + h];
+        } else {
+            const uint4* grp = packed + ((size_t)kn * (Kp / 2)) + (size_t)g * 2;
+            s = grp[h];
+        }
+        unsigned char* tile = img + ((size_t)(kn / BN) * nch + c) * (size_t)BN * KCH;
+        store_row_chunk(tile, kn % BN, s, z);
+    }
+}
+
+struct GemmArgs {
+    const uint4* A;             // packed activations
+    const unsigned char* Bimg;  // expanded weights
+    float* y;
+    long long M;
+    int KN, Kp, OHW, layout;
+    int a_two_planes;
+    int acc_bias;               // added to the integer dot product (BNN: K_unpack - 64*Kp)
+    float alpha;
+    unsigned int* status;
+};
+
+template <int BN>
+__global__ void __launch_bounds__(NTHREADS, 1) gemm_i8_tc_kernel(GemmArgs p) {
+    constexpr int B_STAGE = BN * KCH;
+    constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sA = smem;
+    unsigned char* sB = smem + NSTG * A_STAGE;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + NSTG * B_STAGE);
+    // barriers: full[NSTG], empty[NSTG], tmem_full[2], tmem_empty[2]
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + NSTG), bar_tfull = smem_u32(bars + 2 * NSTG),
+                   bar_tempty = smem_u32(bars + 2 * NSTG + 2);
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTG + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int nchunks = p.Kp / 2;
+    const int ntn = (p.KN + BN - 1) / BN;
+    const long long ntm = (p.M + BM - 1) / BM;
+    const long long ntiles = ntm * ntn;
+
+    if (tid == 0) {
+        for (int s = 0; s < NSTG; s++) {
+            mbar_init(bar_full + 8 * s, 5);   // weight producer + four expander warps
+            mbar_init(bar_empty + 8 * s, 1);  // tcgen05.commit
+        }
+        for (int b = 0; b < 2; b++) {
+            mbar_init(bar_tfull + 8 * b, 1);
+            mbar_init(bar_tempty + 8 * b, 4);  // four epilogue warps
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == WARP_MMA) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == WARP_TMA) {
+        if (lane == 0) {
+            uint32_t it = 0;
+            for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+                const int n_tile = (int)(t % ntn);
+                const unsigned char* src = p.Bimg + (size_t)n_tile * nchunks * B_STAGE;
+                for (int c = 0; c < nchunks; c++, it++) {
+                    const int s = it % NSTG;
+                    if (!mbar_wait(bar_empty + 8 * s, ((it / NSTG) & 1) ^ 1, abort_flag, p.status, 1)) goto done;
+                    mbar_arrive_expect_tx(bar_full + 8 * s, B_STAGE);
+                    bulk_g2s(smem_u32(sB + s * B_STAGE), src + (size_t)c * B_STAGE, B_STAGE, bar_full + 8 * s);
+                }
+            }
+        }
+    } else if (warp == WARP_MMA) {
+        if (lane == 0) {
+            uint32_t it = 0, lt = 0;
+            for (long long t = blockIdx.x; t < ntiles; t += gridDim.x, lt++) {
+                const int buf = lt & 1;
+                if (!mbar_wait(bar_tempty + 8 * buf, ((lt >> 1) & 1) ^ 1, abort_flag, p.status, 2)) goto done;
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + buf * BN;
+                for (int c = 0; c < nchunks; c++, it++) {
+                    const int s = it % NSTG;
+                    if (!mbar_wait(bar_full + 8 * s, (it / NSTG) & 1, abort_flag, p.status, 3)) goto done;
+                    tc_fence_after();
+                    const uint64_t da = make_desc(smem_u32(sA + s * A_STAGE)), db = make_desc(smem_u32(sB + s * B_STAGE));
+#pragma unroll
+                    for (int k = 0; k < KCH / 32; k++) tc_mma_i8(d_tmem, da + 2 * k, db + 2 * k, IDESC, (c | k) ? 1u : 0u);
+                    tc_commit(bar_empty + 8 * s);  // stage reusable once these MMAs have read it
+                }
+                tc_commit(bar_tfull + 8 * buf);    // accumulator complete
+            }
+        }
+    } else if (warp < WARP_EPI0) {
+        // ---------------- activation expanders ----------------
+        const int r = tid - WARP_EXP0 * 32;  // row of the tile
+        uint32_t it = 0;
+        const int groups = p.Kp / 4;
+        const size_t pitch = p.a_two_planes ? (size_t)p.Kp : (size_t)p.Kp / 2;  // uint4 per row
+        const int gsz = p.a_two_planes ? 4 : 2;                                    // uint4 per group
+        for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+            const long long m0 = (t / ntn) * BM;
+            const uint4* arow = p.A + (size_t)min(m0 + r, p.M - 1) * pitch;
+            uint4 cur[4], nxt[4];
+#pragma unroll
+            for (int q = 0; q < 4; q++) cur[q] = (q < gsz) ? __ldg(arow + q) : make_uint4(0, 0, 0, 0);
+            for (int g = 0; g < groups; g++) {
+                if (g + 1 < groups) {
+#pragma unroll
+                    for (int q = 0; q < 4; q++) nxt[q] = (q < gsz) ? __ldg(arow + (size_t)(g + 1) * gsz + q) : make_uint4(0, 0, 0, 0);
+                }
+#pragma unroll
+                for (int h = 0; h < 2; h++, it++) {
+                    const int s = it % NSTG;
+                    if (!mbar_wait(bar_empty + 8 * s, ((it / NSTG) & 1) ^ 1, abort_flag, p.status, 4)) goto done;
+                    const uint4 sg = cur[h];
+                    const uint4 zr = p.a_two_planes ? cur[2 + h] : make_uint4(0, 0, 0, 0);
+                    store_row_chunk(sA + s * A_STAGE, r, sg, zr);
+                    fence_proxy_async();  // generic-proxy smem writes -> visible to the tensor core's async proxy
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                }
+#pragma unroll
+                for (int q = 0; q < 4; q++) cur[q] = nxt[q];
+            }
+        }
+    } else {
+        // ---------------- epilogue ----------------
+        const int q = warp & 3;  // tensor-memory lane quadrant this warp may access
+        uint32_t lt = 0;
+        for (long long t = blockIdx.x; t < ntiles; t += gridDim.x, lt++) {
+            const int buf = lt & 1;
+            const long long m0 = (t / ntn) * BM;
+            const int n0 = (int)(t % ntn) * BN;
+            if (!mbar_wait(bar_tfull + 8 * buf, (lt >> 1) & 1, abort_flag, p.status, 5)) goto done;
+            tc_fence_after();
+            const long long row = m0 + q * 32 + lane;
+            const bool row_ok = row < p.M;
+            const long long n_img = row_ok ? row / p.OHW : 0;
+            const int rem = (int)(row - n_img * p.OHW);
+            float* ybase = (p.layout == TNNS_NHWC) ? p.y + (size_t)row * p.KN : p.y + (size_t)n_img * p.KN * p.OHW + rem;
+#pragma unroll 1
+            for (int cb = 0; cb < BN; cb += 32) {
+                uint32_t v[32];
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + cb);
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                    : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]),
+                      "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]),
+                      "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]),
+                      "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+                    : "r"(taddr)
+                    : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (row_ok) {
+                    float f[32];
+#pragma unroll
+                    for (int j = 0; j < 32; j++) {
+                        const int acc = (int)v[j] + p.acc_bias;
+                        f[j] = acc > 0 ? (float)acc : (float)acc * p.alpha;
+                    }
+                    const int c0 = n0 + cb;
+                    if (p.layout == TNNS_NHWC) {
+                        if (c0 + 32 <= p.KN && (p.KN & 3) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4)
+                                *reinterpret_cast<float4*>(ybase + c0 + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++)
+                                if (c0 + j < p.KN) ybase[c0 + j] = f[j];
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (c0 + j < p.KN) ybase[(size_t)(c0 + j) * p.OHW] = f[j];
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+        }
+    }
+
+done:
+    __syncwarp();
+    if (*abort_flag && warp == WARP_TMA && lane == 0) {
+        // a wait gave up: give the bulk copies already issued time to land before smem is released
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == WARP_MMA) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+template <int BN>
+int launch_bn(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream) {
+    const size_t smem = 1024 + (size_t)NSTG * (A_STAGE + BN * KCH) + 256;
+    auto kern = gemm_i8_tc_kernel<BN>;
+    TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    const long long tiles = ((a.M + BM - 1) / BM) * ((a.KN + BN - 1) / BN);
+    const int grid = (int)std::min<long long>(tiles, ctx->sm_count);
+    kern<<<grid, NTHREADS, smem, stream>>>(a);
+    tnns_count_launch();
+    TNNS_CUDA_TRY(cudaGetLastError());
+    return TNNS_OK;
+}
+
+}  // namespace
+
+int tnns_i8_tile_n(int KN) { return KN <= 64 ? 64 : (KN <= 128 ? 128 : 256); }
+
+int tnns_build_i8_weights(tnns_cuda_ctx* ctx, tnns_cuda_weights* w) {
+    const int BN = tnns_i8_tile_n(w->KN);
+    const int ntn = (w->KN + BN - 1) / BN, nch = w->Kp / 2;
+    w->i8_bytes = (size_t)ntn * nch * BN * KCH;
+    w->i8_kchunks = nch;
+    TNNS_CUDA_TRY(cudaMalloc(&w->d_i8, w->i8_bytes));
+    TNNS_CUDA_TRY(cudaMemset(w->d_i8, 0, w->i8_bytes));
+    const bool two = (w->type == TNN || w->type == BTN);
+    const long long total = (long long)w->KN * nch;
+    const int blocks = (int)std::min<long long>((total + 127) / 128, 4096);
+    expand_weights_kernel<<<blocks, 128>>>(reinterpret_cast<const uint4*>(w->d_packed), reinterpret_cast<unsigned char*>(w->d_i8), w->KN,
+                                            w->Kp, BN, two ? 1 : 0);
+    tnns_count_launch();
+    TNNS_CUDA_TRY(cudaGetLastError());
+    TNNS_CUDA_TRY(cudaDeviceSynchronize());
+    return TNNS_OK;
+}
+
+int tnns_launch_gemm_i8_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_a, float* d_y, long long M, int OHW,
+                           float alpha, int layout, cudaStream_t stream) {
+    if (M == 0) return TNNS_OK;
+    if (!w->d_i8) return tnns_fail(TNNS_ERR_UNSUPPORTED, "weights carry no int8 operand image");
+    GemmArgs a;
+    a.A = reinterpret_cast<const uint4*>(d_a);
+    a.Bimg = reinterpret_cast<const unsigned char*>(w->d_i8);
+    a.y = d_y;
+    a.M = M;
+    a.KN = w->KN;
+    a.Kp = w->Kp;
+    a.OHW = OHW;
+    a.layout = layout;
+    a.a_two_planes = (w->type == TNN || w->type == TBN) ? 1 : 0;
+    a.acc_bias = (w->type == BNN) ? w->K_unpack - 64 * w->Kp : 0;
+    a.alpha = alpha;
+    a.status = ctx->d_status;
+    switch (tnns_i8_tile_n(w->KN)) {
+        case 64: return launch_bn<64>(ctx, a, stream);
+        case 128: return launch_bn<128>(ctx, a, stream);
+        default: return launch_bn<256>(ctx, a, stream);
+    }
+}

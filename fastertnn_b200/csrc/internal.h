@@ -69,6 +69,12 @@ int tnns_launch_gemm_popc(tnns_cuda_ctx* ctx, int type, const void* d_a, const v
                           int KN, int Kp, int OHW, int K_unpack, float alpha, int layout, bool tiled,
                           cudaStream_t stream);
 
+// tensor-core path (gemm_i8_tc.cu)
+int tnns_i8_tile_n(int KN);
+int tnns_build_i8_weights(tnns_cuda_ctx* ctx, tnns_cuda_weights* w);
+int tnns_launch_gemm_i8_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_a, float* d_y, long long M, int OHW,
+                           float alpha, int layout, cudaStream_t stream);
+
 // Division by a runtime-constant divisor without the hardware divide sequence.
 // Exact for every 32-bit unsigned numerator (Granlund-Montgomery round-up method).
 struct FastDiv {

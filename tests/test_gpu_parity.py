@@ -76,7 +76,7 @@ def test_layer_matches_checker_and_golden(case, gpu_ctx, checker):
             a = device_pack(gpu_ctx, case, layout, algo)
             assert np.array_equal(a, a_ref), f"packed matrix differs (layout {layout}, algo {algo})"
     for layout in (ft.NCHW, ft.NHWC):
-        for galgo in (ft.GEMM_POPC_SIMPLE, ft.GEMM_POPC_TILED, ft.GEMM_AUTO):
+        for galgo in (ft.GEMM_POPC_SIMPLE, ft.GEMM_POPC_TILED, ft.GEMM_I8_TC, ft.GEMM_AUTO):
             y = device_conv(gpu_ctx, case, wp, layout, ft.PACK_AUTO, galgo)
             assert y.tobytes() == y_ref.tobytes(), f"output differs (layout {layout}, gemm {galgo})"
     assert sha(device_conv(gpu_ctx, case, wp, ft.NCHW, ft.PACK_AUTO, ft.GEMM_AUTO)) == d["output"]
