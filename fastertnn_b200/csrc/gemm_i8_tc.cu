@@ -22,17 +22,30 @@
 // produces; activations and weights go through the same routine, so the permutation cancels
 // in the dot product.
 #include <algorithm>
+#include <cstdlib>
 
 #include "internal.h"
 
 namespace {
 
-constexpr int BM = 128;        // rows per tile (tensor-memory lanes)
+constexpr int BM = 128;        // rows per accumulator (tensor-memory lanes)
 constexpr int KCH = 128;       // K elements = bytes per row and stage (one swizzle atom)
-constexpr int NSTG = 4;        // smem ring depth
-constexpr int A_STAGE = BM * KCH;
-constexpr int NTHREADS = 320;
-constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_EXP0 = 2, WARP_EPI0 = 6;
+constexpr int A_SUB = BM * KCH;  // bytes of one 128-row activation sub-tile per stage
+constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_EXP0 = 2;
+// A block owns MT stacked 128-row sub-tiles (MT*128 rows) and BN kernels: every weight stage
+// that arrives from L2 feeds MT MMAs, which is what keeps the L2 -> SM weight traffic below
+// the tensor pipe's appetite.  Roles: warp 0 weight producer, warp 1 MMA issuer, NG groups of
+// 4*MT expander warps, 4*MT epilogue warps.
+template <int BN, int MT>
+struct TcCfg {
+    static constexpr int NSTG = (MT == 1) ? 4 : 3;                 // smem ring depth
+    static constexpr int A_STAGE = MT * A_SUB, B_STAGE = BN * KCH;
+    static constexpr int NBUF = (MT * BN <= 256) ? 2 : 1;           // accumulator sets in tensor memory
+    static constexpr int NG = (MT == 1) ? 4 : 2;                    // expander groups (stages expanded concurrently)
+    static constexpr int WARP_EPI0 = WARP_EXP0 + 4 * MT * NG;
+    static constexpr int NTHREADS = 32 * (2 + 4 * MT * NG + 4 * MT);
+    static constexpr size_t SMEM = 1024 + (size_t)NSTG * (A_STAGE + B_STAGE) + 256;
+};
 constexpr unsigned STATUS_WAIT_EXPIRED = 0x100;
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -171,11 +184,14 @@ struct GemmArgs {
     int acc_bias;               // added to the integer dot product (BNN: K_unpack - 64*Kp)
     float alpha;
     unsigned int* status;
+    int dbg;  // experiment knob: 1 skip expansion, 2 skip weight copies, 4 skip epilogue stores
 };
 
-template <int BN>
-__global__ void __launch_bounds__(NTHREADS, 1) gemm_i8_tc_kernel(GemmArgs p) {
-    constexpr int B_STAGE = BN * KCH;
+template <int BN, int MT>
+__global__ void __launch_bounds__(TcCfg<BN, MT>::NTHREADS, 1) gemm_i8_tc_kernel(GemmArgs p) {
+    using Cfg = TcCfg<BN, MT>;
+    constexpr int NSTG = Cfg::NSTG, A_STAGE = Cfg::A_STAGE, B_STAGE = Cfg::B_STAGE, NBUF = Cfg::NBUF, WARP_EPI0 = Cfg::WARP_EPI0, NG = Cfg::NG;
+    constexpr int BMT = MT * BM;  // rows per block tile
     constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -191,17 +207,17 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_i8_tc_kernel(GemmArgs p) {
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nchunks = p.Kp / 2;
     const int ntn = (p.KN + BN - 1) / BN;
-    const long long ntm = (p.M + BM - 1) / BM;
+    const long long ntm = (p.M + BMT - 1) / BMT;
     const long long ntiles = ntm * ntn;
 
     if (tid == 0) {
         for (int s = 0; s < NSTG; s++) {
-            mbar_init(bar_full + 8 * s, 5);   // weight producer + four expander warps
+            mbar_init(bar_full + 8 * s, 1 + 4 * MT);  // weight producer + the expander warps
             mbar_init(bar_empty + 8 * s, 1);  // tcgen05.commit
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(bar_tfull + 8 * b, 1);
-            mbar_init(bar_tempty + 8 * b, 4);  // four epilogue warps
+            mbar_init(bar_tempty + 8 * b, 4 * MT);  // the epilogue warps
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -224,6 +240,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_i8_tc_kernel(GemmArgs p) {
                 for (int c = 0; c < nchunks; c++, it++) {
                     const int s = it % NSTG;
                     if (!mbar_wait(bar_empty + 8 * s, ((it / NSTG) & 1) ^ 1, abort_flag, p.status, 1)) goto done;
+                    if (p.dbg & 2) { mbar_arrive(bar_full + 8 * s); continue; }
                     mbar_arrive_expect_tx(bar_full + 8 * s, B_STAGE);
                     bulk_g2s(smem_u32(sB + s * B_STAGE), src + (size_t)c * B_STAGE, B_STAGE, bar_full + 8 * s);
                 }
@@ -233,17 +250,21 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_i8_tc_kernel(GemmArgs p) {
         if (lane == 0) {
             uint32_t it = 0, lt = 0;
             for (long long t = blockIdx.x; t < ntiles; t += gridDim.x, lt++) {
-                const int buf = lt & 1;
-                if (!mbar_wait(bar_tempty + 8 * buf, ((lt >> 1) & 1) ^ 1, abort_flag, p.status, 2)) goto done;
+                const int buf = lt % NBUF;
+                if (!mbar_wait(bar_tempty + 8 * buf, ((lt / NBUF) & 1) ^ 1, abort_flag, p.status, 2)) goto done;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * BN;
+                const uint32_t d_tmem = tmem_base + buf * MT * BN;
                 for (int c = 0; c < nchunks; c++, it++) {
                     const int s = it % NSTG;
                     if (!mbar_wait(bar_full + 8 * s, (it / NSTG) & 1, abort_flag, p.status, 3)) goto done;
                     tc_fence_after();
-                    const uint64_t da = make_desc(smem_u32(sA + s * A_STAGE)), db = make_desc(smem_u32(sB + s * B_STAGE));
+                    const uint64_t db = make_desc(smem_u32(sB + s * B_STAGE));
 #pragma unroll
-                    for (int k = 0; k < KCH / 32; k++) tc_mma_i8(d_tmem, da + 2 * k, db + 2 * k, IDESC, (c | k) ? 1u : 0u);
+                    for (int mt = 0; mt < MT; mt++) {
+                        const uint64_t da = make_desc(smem_u32(sA + s * A_STAGE + mt * A_SUB));
+#pragma unroll
+                        for (int k = 0; k < KCH / 32; k++) tc_mma_i8(d_tmem + mt * BN, da + 2 * k, db + 2 * k, IDESC, (c | k) ? 1u : 0u);
+                    }
                     tc_commit(bar_empty + 8 * s);  // stage reusable once these MMAs have read it
                 }
                 tc_commit(bar_tfull + 8 * buf);    // accumulator complete
@@ -251,46 +272,62 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_i8_tc_kernel(GemmArgs p) {
         }
     } else if (warp < WARP_EPI0) {
         // ---------------- activation expanders ----------------
-        const int r = tid - WARP_EXP0 * 32;  // row of the tile
-        uint32_t it = 0;
-        const int groups = p.Kp / 4;
+        // NG groups of MT*128 threads; thread = row.  Group k expands the stages it = k, k+NG,
+        // k+2*NG, ... of the block's flat (tile, chunk) sequence, so NG stages are being
+        // expanded at the same time and one slow dependency chain never starves the MMA.
+        // The packed planes of a row come straight from global memory (L2); a register ring keeps
+        // PF of this group's stages of loads in flight, running ahead across tile boundaries.
+        const int e = tid - WARP_EXP0 * 32;
+        const int grp = e / BMT;
+        const int r = e - grp * BMT;  // row of the block tile, 0 .. MT*128-1
+        constexpr int PF = 4;
         const size_t pitch = p.a_two_planes ? (size_t)p.Kp : (size_t)p.Kp / 2;  // uint4 per row
-        const int gsz = p.a_two_planes ? 4 : 2;                                    // uint4 per group
-        for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
-            const long long m0 = (t / ntn) * BM;
-            const uint4* arow = p.A + (size_t)min(m0 + r, p.M - 1) * pitch;
-            uint4 cur[4], nxt[4];
+        const int gsz = p.a_two_planes ? 4 : 2;                                    // uint4 per 256-element group
+        uint4 ring_s[PF], ring_z[PF];
+        // prefetch cursor: (tile, chunk) of the next load of this group
+        long long pf_t = blockIdx.x;
+        int pf_c = grp;
+        while (pf_c >= nchunks) { pf_c -= nchunks; pf_t += gridDim.x; }
+        auto fetch = [&](uint4& ds, uint4& dz) {
+            if (pf_t < ntiles) {
+                const uint4* row = p.A + (size_t)min((pf_t / ntn) * BMT + r, p.M - 1) * pitch + (size_t)(pf_c >> 1) * gsz + (pf_c & 1);
+                ds = __ldg(row);
+                dz = p.a_two_planes ? __ldg(row + 2) : make_uint4(0, 0, 0, 0);
+                pf_c += NG;
+                while (pf_c >= nchunks) { pf_c -= nchunks; pf_t += gridDim.x; }
+            }
+        };
 #pragma unroll
-            for (int q = 0; q < 4; q++) cur[q] = (q < gsz) ? __ldg(arow + q) : make_uint4(0, 0, 0, 0);
-            for (int g = 0; g < groups; g++) {
-                if (g + 1 < groups) {
+        for (int i = 0; i < PF; i++) fetch(ring_s[i], ring_z[i]);
+        long long my_tiles = (ntiles - blockIdx.x + gridDim.x - 1) / gridDim.x;
+        if (blockIdx.x >= ntiles) my_tiles = 0;
+        const long long total_it = my_tiles * nchunks;
+        for (long long it0 = grp; it0 < total_it; it0 += (long long)NG * PF) {
 #pragma unroll
-                    for (int q = 0; q < 4; q++) nxt[q] = (q < gsz) ? __ldg(arow + (size_t)(g + 1) * gsz + q) : make_uint4(0, 0, 0, 0);
-                }
-#pragma unroll
-                for (int h = 0; h < 2; h++, it++) {
-                    const int s = it % NSTG;
-                    if (!mbar_wait(bar_empty + 8 * s, ((it / NSTG) & 1) ^ 1, abort_flag, p.status, 4)) goto done;
-                    const uint4 sg = cur[h];
-                    const uint4 zr = p.a_two_planes ? cur[2 + h] : make_uint4(0, 0, 0, 0);
-                    store_row_chunk(sA + s * A_STAGE, r, sg, zr);
+            for (int i = 0; i < PF; i++) {
+                const long long it = it0 + (long long)i * NG;
+                if (it < total_it) {
+                    const int s = (int)(it % NSTG);
+                    if (!mbar_wait(bar_empty + 8 * s, (uint32_t)((it / NSTG) & 1) ^ 1, abort_flag, p.status, 4)) goto done;
+                    if (!(p.dbg & 1)) store_row_chunk(sA + s * A_STAGE + (r >> 7) * A_SUB, r & 127, ring_s[i], ring_z[i]);
                     fence_proxy_async();  // generic-proxy smem writes -> visible to the tensor core's async proxy
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_full + 8 * s);
+                    fetch(ring_s[i], ring_z[i]);
                 }
-#pragma unroll
-                for (int q = 0; q < 4; q++) cur[q] = nxt[q];
             }
         }
     } else {
         // ---------------- epilogue ----------------
-        const int q = warp & 3;  // tensor-memory lane quadrant this warp may access
+        const int q = warp & 3;                 // tensor-memory lane quadrant this warp may access
+        const int sub = (warp - WARP_EPI0) >> 2;  // which 128-row sub-tile (accumulator) it drains
+        const int bias_magic = 0x4B400000 + p.acc_bias;
         uint32_t lt = 0;
         for (long long t = blockIdx.x; t < ntiles; t += gridDim.x, lt++) {
-            const int buf = lt & 1;
-            const long long m0 = (t / ntn) * BM;
+            const int buf = lt % NBUF;
+            const long long m0 = (t / ntn) * BMT + sub * BM;
             const int n0 = (int)(t % ntn) * BN;
-            if (!mbar_wait(bar_tfull + 8 * buf, (lt >> 1) & 1, abort_flag, p.status, 5)) goto done;
+            if (!mbar_wait(bar_tfull + 8 * buf, (lt / NBUF) & 1, abort_flag, p.status, 5)) goto done;
             tc_fence_after();
             const long long row = m0 + q * 32 + lane;
             const bool row_ok = row < p.M;
@@ -300,7 +337,7 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_i8_tc_kernel(GemmArgs p) {
 #pragma unroll 1
             for (int cb = 0; cb < BN; cb += 32) {
                 uint32_t v[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + cb);
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((buf * MT + sub) * BN + cb);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -312,16 +349,25 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_i8_tc_kernel(GemmArgs p) {
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (row_ok) {
+                if (cb + 32 >= BN) {
+                    // the last slice is in registers: hand the accumulator back before storing it
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+                }
+                if (row_ok && !(p.dbg & 4)) {
+                    // int -> float without the conversion unit: for |a| < 2^22 the float with bit
+                    // pattern 0x4B400000 + a is 1.5*2^23 + a exactly, so subtracting 1.5*2^23 gives a.
                     float f[32];
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
-                        const int acc = (int)v[j] + p.acc_bias;
-                        f[j] = acc > 0 ? (float)acc : (float)acc * p.alpha;
+                        const float a = __int_as_float((int)v[j] + bias_magic) - 12582912.0f;
+                        f[j] = a * (a > 0.f ? 1.0f : p.alpha);  // PReLU; a == 0 stays +0
                     }
                     const int c0 = n0 + cb;
+                    const bool full = c0 + 32 <= p.KN;
                     if (p.layout == TNNS_NHWC) {
-                        if (c0 + 32 <= p.KN && (p.KN & 3) == 0) {
+                        if (full && (p.KN & 3) == 0) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 4)
                                 *reinterpret_cast<float4*>(ybase + c0 + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
@@ -331,15 +377,18 @@ __global__ void __launch_bounds__(NTHREADS, 1) gemm_i8_tc_kernel(GemmArgs p) {
                                 if (c0 + j < p.KN) ybase[c0 + j] = f[j];
                         }
                     } else {
+                        float* yc = ybase + (size_t)c0 * p.OHW;
+                        if (full) {
 #pragma unroll
-                        for (int j = 0; j < 32; j++)
-                            if (c0 + j < p.KN) ybase[(size_t)(c0 + j) * p.OHW] = f[j];
+                            for (int j = 0; j < 32; j++, yc += p.OHW) *yc = f[j];
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 32; j++, yc += p.OHW)
+                                if (c0 + j < p.KN) *yc = f[j];
+                        }
                     }
                 }
             }
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
         }
     }
 
@@ -357,17 +406,26 @@ done:
     }
 }
 
-template <int BN>
-int launch_bn(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream) {
-    const size_t smem = 1024 + (size_t)NSTG * (A_STAGE + BN * KCH) + 256;
-    auto kern = gemm_i8_tc_kernel<BN>;
-    TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
-    const long long tiles = ((a.M + BM - 1) / BM) * ((a.KN + BN - 1) / BN);
+template <int BN, int MT>
+int launch_cfg(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream) {
+    using Cfg = TcCfg<BN, MT>;
+    auto kern = gemm_i8_tc_kernel<BN, MT>;
+    TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
+    const long long tiles = ((a.M + MT * BM - 1) / (MT * BM)) * ((a.KN + BN - 1) / BN);
     const int grid = (int)std::min<long long>(tiles, ctx->sm_count);
-    kern<<<grid, NTHREADS, smem, stream>>>(a);
+    kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, stream>>>(a);
     tnns_count_launch();
     TNNS_CUDA_TRY(cudaGetLastError());
     return TNNS_OK;
+}
+
+// One 128-row accumulator per block measured fastest on every layer shape tried (more blocks in
+// flight, deeper ring); the MT = 2 form halves the weight traffic per MMA and is kept for
+// experiments with other shapes.
+template <int BN>
+int launch_bn(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream) {
+    const char* force = getenv("TNNS_TC_MT");  // experiment knob
+    return (force && atoi(force) == 2) ? launch_cfg<BN, 2>(ctx, a, stream) : launch_cfg<BN, 1>(ctx, a, stream);
 }
 
 }  // namespace
@@ -396,6 +454,7 @@ int tnns_launch_gemm_i8_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const
                            float alpha, int layout, cudaStream_t stream) {
     if (M == 0) return TNNS_OK;
     if (!w->d_i8) return tnns_fail(TNNS_ERR_UNSUPPORTED, "weights carry no int8 operand image");
+    if (w->Kp >= 65536) return tnns_fail(TNNS_ERR_UNSUPPORTED, "rows of %d plane words exceed the tensor-core path's exact range", w->Kp);
     GemmArgs a;
     a.A = reinterpret_cast<const uint4*>(d_a);
     a.Bimg = reinterpret_cast<const unsigned char*>(w->d_i8);
@@ -409,6 +468,7 @@ int tnns_launch_gemm_i8_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const
     a.acc_bias = (w->type == BNN) ? w->K_unpack - 64 * w->Kp : 0;
     a.alpha = alpha;
     a.status = ctx->d_status;
+    a.dbg = getenv("TNNS_TC_DBG") ? atoi(getenv("TNNS_TC_DBG")) : 0;
     switch (tnns_i8_tile_n(w->KN)) {
         case 64: return launch_bn<64>(ctx, a, stream);
         case 128: return launch_bn<128>(ctx, a, stream);
