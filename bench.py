@@ -292,6 +292,7 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
     ms_step = ms_total / args.steps
     t_pack = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
     t_gemm = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
+    ctx_lop3_rate = ctx.pipe_rate(0) if args.gemm == "popc" else 0.0
     ctx.sync()
 
     # ---- end to end: pinned host buffers in, host buffers out, copies inside the timed region ----
@@ -318,10 +319,21 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
         ops_loc = layer.ops(nloc)
         pack_alg_bytes = in_bytes + pack_bytes
         gemm_tops = ops_loc / (t_gemm * 1e-3) / 1e12
+        if args.gemm == "popc":
+            # integer-pipe kernel: 5.5 LOP3 per 32-bit lane and output, LOP3 issues 64 lanes/clk/SM
+            # (measured with tnns_cuda_pipe_rate: 18.5e12 thread-instructions/s on this part)
+            lop3 = ctx_lop3_rate
+            gemm_kernel_name, gemm_bound = "gemm_popc_tiled_kernel (LOP3 carry-save popcount GEMM + PReLU)", "int"
+            gemm_peak = lop3 * 1e9 * 64.0 / 5.5 / 1e12
+            gemm_peak_source = "measured LOP3 issue rate x 64 ops per lane / 5.5 LOP3 per lane"
+        else:
+            gemm_kernel_name, gemm_bound = "gemm_i8_tc_kernel (tcgen05.mma kind::i8 GEMM + PReLU)", "tensor"
+            gemm_peak = 2.0 * pk["bf16_tflops"]
+            gemm_peak_source = f"2 x {pk['source']} bf16 burst figure (int8 dense rate = 2 x bf16)"
         line = {
             "metric": METRIC, "value": ops / (ms_step * 1e-3) / 1e9, "unit": "GOPS", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
-            "dtype": "int32 popcount accumulate (u32 bit-plane lanes), fp32 PReLU",
+            "dtype": "int8 operands expanded from 2-bit planes, int32 accumulate, fp32 PReLU" if args.gemm != "popc" else "u32 bit-plane lanes, int32 popcount accumulate, fp32 PReLU",
             "data": "synthetic",
             "config": {"workload": name, "batch": N_total, "batch_per_gpu": nloc, "layer": str(layer), "layout": "NCHW",
                        "M": N_total * OH * OW, "K": layer.C * layer.KH * layer.KW, "N": layer.KN, "gemm": args.gemm,
@@ -329,12 +341,18 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
                              f"between steps; one set alone is {step_bytes >> 20} MiB"},
             "gpu_launches": int(launches * world),
             "kernels_ms": {"pack": t_pack, "gemm": t_gemm},
+            # dominant kernel: the GEMM.  Its roof is the tensor pipe; the int8 rate of this part is
+            # twice its bf16 rate, and bf16 is what MEASURED_PEAKS.json holds (cuBLAS, burst figure
+            # for a kernel timed alone), so peak = 2 x measured bf16.
             "roofline": {
-                "kernel": "pack (quantise+bit-pack+im2row)", "bound": "hbm", "achieved": pack_alg_bytes / (t_pack * 1e-3) / 1e9,
-                "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": pack_alg_bytes / (t_pack * 1e-3) / 1e9 / pk["hbm_gbs"],
-                "traffic": None, "peak_source": pk["source"]},
-            "roofline_gemm": {"kernel": "bitwise GEMM + PReLU", "achieved": gemm_tops, "unit": "TOP/s",
-                              "gemm_hbm_gbs": (pack_bytes + out_bytes) / (t_gemm * 1e-3) / 1e9},
+                "kernel": gemm_kernel_name, "bound": gemm_bound, "achieved": gemm_tops, "peak": gemm_peak, "unit": "TFLOP/s",
+                "frac": gemm_tops / gemm_peak, "traffic": None, "peak_source": gemm_peak_source,
+                "algorithmic_ops_per_launch": ops_loc, "ms_per_launch": t_gemm},
+            "roofline_pack": {
+                "kernel": "pack_staged_kernel (quantise + bit-pack + im2row)", "bound": "hbm",
+                "achieved": pack_alg_bytes / (t_pack * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": pack_alg_bytes / (t_pack * 1e-3) / 1e9 / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                "algorithmic_bytes_per_launch": pack_alg_bytes, "ms_per_launch": t_pack},
             "e2e": {"value": ops / (e2e_ms * 1e-3) / 1e9, "unit": "GOPS", "ms_per_step": e2e_ms, "steps": e2e_steps,
                     "h2d_bytes_per_step": int((in_bytes + thr_h.nbytes) * world), "d2h_bytes_per_step": int(out_bytes * world),
                     "matches_device_path": e2e_ok},

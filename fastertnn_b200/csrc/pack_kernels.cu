@@ -21,14 +21,6 @@ constexpr int kPackThreads = 256;
 #define TNNS_PACK_MINCTA 4
 #endif
 
-__device__ __forceinline__ void tern_accum(float v, float t, float nt, uint32_t bit, uint32_t& sign, uint32_t& nz) {
-    // sign iff v < -t ; non-zero iff v < -t or v > t  (src/tnns/ternarize2row_avx2.c:444-449)
-    const bool neg = v < nt;
-    const bool pos = v > t;
-    if (neg) sign |= bit;
-    if (neg || pos) nz |= bit;
-}
-
 // ---------------------------------------------------------------------------------------
 // Reference-shaped kernel: one thread per plane word, channels fetched straight from
 // global memory.  Slow (strided reads, every pixel re-quantised KH*KW times) but handles
