@@ -6,9 +6,13 @@
 
 Workload: the large single TNN conv layer -- batch 64, 512 channels, 32x32, 512 kernels
 3x3, stride 1, pad 1 (M=65536, K=4608, N=512), activations uniform in [-1,1), thresholds
-+-0.25, ternary weights, PReLU alpha 0.5 -- partitioned by batch index over the ranks
-(weights replicated, no collective on the data path), so the total work is fixed as N grows.
-One "step" is one pass of the whole layer.  Metric: GOPS = 2*M*N*K / time (unpadded K).
++-0.25, ternary weights, PReLU alpha 0.5.  Rows of the im2row matrix are independent, so the
+layer is partitioned by batch index with the weights replicated and no collective on the data
+path.  By default every rank processes one full 64-image batch of the seeded stream (rank r
+owns images 64r .. 64r+63; the job's batch is 64*N, "scaling": "weak"); --scaling strong keeps
+the job at 64 images and gives each rank 64/N of them.  The default run also reports the
+fixed-64-image figure as "fixed_total_batch".  One "step" is one pass of the job's batch.
+Metric: GOPS = 2*M*N*K / time (unpadded K).
 
 Prints ONE JSON line on rank 0.
 """
@@ -34,6 +38,13 @@ from fastertnn_b200.shard import batch_slice  # noqa: E402
 from fastertnn_b200.workloads import CONV_LARGE, CONV_56, FC_GEMM, Layer  # noqa: E402
 
 METRIC = "ternary conv GOPS (2*M*N*K/s)"
+# dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
+# profiles/ (large layer, 64 images per launch), kept per image so that a rank's share scales.
+NCU_TRAFFIC_PER_IMAGE = {
+    ("tnn_conv_large", "tc"): 155.5e6 / 64,
+    ("tnn_conv_large", "popc"): 419.3e6 / 64,
+    ("tnn_conv_large", "pack"): 155.8e6 / 64,
+}
 L2_BYTES = 126 * 1024 * 1024
 SEED_X, SEED_W = 0xC0FFEE40, 0xC0FFEE41
 WORKLOADS = {
@@ -175,7 +186,7 @@ def run_reference(args, layer: Layer, N_total: int, name: str):
     used = min(threads, N_total)
     line = {
         "impl": "reference", "metric": METRIC, "value": val, "unit": "GOPS", "n_gpus": args.gpus, "steps": args.steps,
-        "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": "int (64-bit popcount lanes)", "data": "synthetic",
         "config": {"workload": name, "batch": N_total, "layer": str(layer), "layout": "NCHW"},
         "cpu_baseline": {"value": val, "unit": "GOPS", "cores": used, "kind": chk.kind,
@@ -216,6 +227,9 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return float(t.item())
 
+    N_cfg = N_total
+    if args.scaling == "weak":
+        N_total = N_cfg * world
     n0, n1 = batch_slice(N_total, rank, world)
     nloc = n1 - n0
     x_h, thr_h, w_f = make_inputs(N_total, layer, n0, n1)
@@ -289,6 +303,33 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
         sampler.stop()
     launches = ft.api.launch_count() - launches0
     ms_total = max_over_ranks(e_start.elapsed_time(e_end))
+
+    # the same layer with the job fixed at the configured batch, partitioned over the ranks
+    fixed = None
+    if args.scaling == "weak" and world > 1:
+        f0, f1 = batch_slice(N_cfg, rank, world)
+        nfix = f1 - f0
+        fshape = layer.shape(nfix)
+
+        def fstep(i):
+            r = i % ring
+            ctx.pack(True, xs[r].data_ptr(), thr_d.data_ptr(), ps[r].data_ptr(), fshape, layout, ft.PACK_AUTO, sp)
+            ctx.gemm(w, ps[r].data_ptr(), ys[r].data_ptr(), nfix, OH, OW, 0.5, layout, gemm_algo, sp)
+
+        for i in range(args.warmup):
+            fstep(i)
+        barrier()
+        f_start, f_end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f_start.record(stream)
+        for i in range(args.steps):
+            fstep(i)
+        f_end.record(stream)
+        stream.synchronize()
+        barrier()
+        f_ms = max_over_ranks(f_start.elapsed_time(f_end)) / args.steps
+        fixed = {"batch": N_cfg, "batch_per_gpu": nfix, "ms_per_step": f_ms, "value": layer.ops(N_cfg) / (f_ms * 1e-3) / 1e9,
+                 "unit": "GOPS", "scaling": "strong",
+                 "note": "per-GPU working set is below L2 size at this split; buffers still rotate through the ring"}
     ms_step = ms_total / args.steps
     t_pack = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
     t_gemm = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
@@ -319,6 +360,10 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
         ops_loc = layer.ops(nloc)
         pack_alg_bytes = in_bytes + pack_bytes
         gemm_tops = ops_loc / (t_gemm * 1e-3) / 1e12
+        per_img = NCU_TRAFFIC_PER_IMAGE.get((name, "popc" if args.gemm == "popc" else "tc"))
+        gemm_traffic = per_img * nloc if per_img else None
+        per_img = NCU_TRAFFIC_PER_IMAGE.get((name, "pack"))
+        pack_traffic = per_img * nloc if per_img else None
         if args.gemm == "popc":
             # integer-pipe kernel: 5.5 LOP3 per 32-bit lane and output, LOP3 issues 64 lanes/clk/SM
             # (measured with tnns_cuda_pipe_rate: 18.5e12 thread-instructions/s on this part)
@@ -332,7 +377,7 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
             gemm_peak_source = f"2 x {pk['source']} bf16 burst figure (int8 dense rate = 2 x bf16)"
         line = {
             "metric": METRIC, "value": ops / (ms_step * 1e-3) / 1e9, "unit": "GOPS", "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+            "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
             "dtype": "int8 operands expanded from 2-bit planes, int32 accumulate, fp32 PReLU" if args.gemm != "popc" else "u32 bit-plane lanes, int32 popcount accumulate, fp32 PReLU",
             "data": "synthetic",
             "config": {"workload": name, "batch": N_total, "batch_per_gpu": nloc, "layer": str(layer), "layout": "NCHW",
@@ -346,18 +391,20 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
             # for a kernel timed alone), so peak = 2 x measured bf16.
             "roofline": {
                 "kernel": gemm_kernel_name, "bound": gemm_bound, "achieved": gemm_tops, "peak": gemm_peak, "unit": "TFLOP/s",
-                "frac": gemm_tops / gemm_peak, "traffic": None, "peak_source": gemm_peak_source,
+                "frac": gemm_tops / gemm_peak, "traffic": gemm_traffic, "peak_source": gemm_peak_source,
                 "algorithmic_ops_per_launch": ops_loc, "ms_per_launch": t_gemm},
             "roofline_pack": {
                 "kernel": "pack_staged_kernel (quantise + bit-pack + im2row)", "bound": "hbm",
                 "achieved": pack_alg_bytes / (t_pack * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": pack_alg_bytes / (t_pack * 1e-3) / 1e9 / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"],
+                "frac": pack_alg_bytes / (t_pack * 1e-3) / 1e9 / pk["hbm_gbs"], "traffic": pack_traffic, "peak_source": pk["source"],
                 "algorithmic_bytes_per_launch": pack_alg_bytes, "ms_per_launch": t_pack},
             "e2e": {"value": ops / (e2e_ms * 1e-3) / 1e9, "unit": "GOPS", "ms_per_step": e2e_ms, "steps": e2e_steps,
                     "h2d_bytes_per_step": int((in_bytes + thr_h.nbytes) * world), "d2h_bytes_per_step": int(out_bytes * world),
                     "matches_device_path": e2e_ok},
             "clocks": sampler.summary() if sampler else None,
         }
+        if fixed:
+            line["fixed_total_batch"] = fixed
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline(layer, N_total, passes=args.cpu_passes)
         print(json.dumps(line), flush=True)
@@ -375,6 +422,8 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="tnn_conv_large")
     ap.add_argument("--gemm", choices=["auto", "popc", "i8tc"], default="auto")
+    ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
+                    help="weak: every rank processes the configured batch; strong: the configured batch is split over the ranks")
     ap.add_argument("--no-check", action="store_true", help="skip the pre-timing comparison with the CPU checker")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--cpu-passes", type=int, default=5)

@@ -1,0 +1,47 @@
+"""Chained layers on the device: the output of one layer is the next layer's input, as the
+reference's end-to-end timing mode does on the host (src/timing_layers.c:188-201 of the
+reference: ``test->input = test->output`` between layers).  Activations stay in HBM as fp32
+in the chosen layout; every layer re-quantises its input with its own thresholds."""
+from __future__ import annotations
+
+import numpy as np
+
+from . import api
+from .workloads import Layer
+
+
+class ConvStack:
+    def __init__(self, ctx: api.Context, type_: int, layers: list[Layer], packed_weights: list[np.ndarray], batch: int,
+                 threshold: float, alpha: float = 0.5, layout: int = api.NCHW):
+        assert len(layers) == len(packed_weights)
+        for a, b in zip(layers, layers[1:]):
+            if (a.KN, a.OH, a.OW) != (b.C, b.H, b.W):
+                raise ValueError(f"layer output {a.KN}x{a.OH}x{a.OW} does not feed {b.C}x{b.H}x{b.W}")
+        self.ctx, self.type, self.layers, self.batch, self.alpha, self.layout = ctx, type_, layers, batch, alpha, layout
+        self.weights = [ctx.upload_weights(type_, pw, L.C, L.KH, L.KW) for L, pw in zip(layers, packed_weights)]
+        sizes = [batch * layers[0].C * layers[0].H * layers[0].W] + [batch * L.KN * L.OH * L.OW for L in layers]
+        self.sizes = sizes
+        big = max(sizes) * 4
+        self.buf = [ctx.malloc(big), ctx.malloc(big)]  # ping-pong activation buffers
+        self.d_thr = ctx.to_device(np.full(batch, threshold, np.float32))
+
+    def input_ptr(self) -> int:
+        return self.buf[0]
+
+    def output_ptr(self) -> int:
+        return self.buf[len(self.layers) % 2]
+
+    def run(self, stream: int = 0):
+        """Enqueue all layers; input must already be in input_ptr()."""
+        for i, (L, w) in enumerate(zip(self.layers, self.weights)):
+            self.ctx.conv(w, self.buf[i % 2], self.d_thr, self.buf[(i + 1) % 2], L.shape(self.batch), self.alpha, self.layout,
+                          stream=stream)
+
+    def ops(self) -> int:
+        return sum(L.ops(self.batch) for L in self.layers)
+
+    def close(self):
+        for w in self.weights:
+            w.free()
+        for p in self.buf + [self.d_thr]:
+            self.ctx.free(p)

@@ -229,3 +229,30 @@ def test_large_layer_properties(gpu_ctx, checker):
     accn = np.where(yn > 0, yn, yn / 0.5)
     assert np.array_equal(acc, -accn)
     assert np.abs(acc).max() <= 4608
+
+
+def test_resnet18_style_stack_chained_on_device(gpu_ctx, checker):
+    """The 11-layer ternary stack (two convs per stage, stride-2 transitions), batch 2: layers
+    chained on the device, each output re-ternarised with +-0.25 as the next input, against the
+    checker chained the same way on the host."""
+    from fastertnn_b200 import synth
+    from fastertnn_b200.stack import ConvStack
+    from fastertnn_b200.workloads import RESNET18_STACK
+    N = 2
+    x = synth.uniform_pm1(77, (N, 64, 56, 56))
+    thr = np.full(N, 0.25, np.float32)
+    pws = []
+    for i, L in enumerate(RESNET18_STACK):
+        w = synth.ternary_values(500 + i, (L.KN, L.C, L.KH, L.KW))
+        pws.append(checker.pack_weights(True, w, np.full(L.KN, 0.5, np.float32)))
+    want = x
+    for L, pw in zip(RESNET18_STACK, pws):
+        want = checker.conv(TNN, want, thr, pw, (L.KH, L.KW), (L.P, L.P), (L.S, L.S), 0.5)
+    st = ConvStack(gpu_ctx, TNN, RESNET18_STACK, pws, N, 0.25)
+    gpu_ctx.lib.tnns_cuda_memcpy_h2d(gpu_ctx.handle, st.input_ptr(), x.ctypes.data, x.nbytes)
+    st.run()
+    gpu_ctx.sync()
+    got = gpu_ctx.to_host(st.output_ptr(), want.shape, np.float32)
+    st.close()
+    assert got.tobytes() == want.tobytes()
+    assert np.count_nonzero(got) > 0
