@@ -259,7 +259,7 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
     stream = torch.cuda.Stream()
     sp = stream.cuda_stream
     layout = ft.NCHW
-    gemm_algo = {"auto": ft.GEMM_AUTO, "popc": ft.GEMM_POPC_TILED, "i8tc": ft.GEMM_I8_TC}[args.gemm]
+    gemm_algo = {"auto": ft.GEMM_AUTO, "popc": ft.GEMM_POPC_TILED, "i8tc": ft.GEMM_I8_TC, "f4tc": ft.GEMM_F4_TC}[args.gemm]
 
     def step(i, ev=None):
         r = i % ring
@@ -360,7 +360,7 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
         ops_loc = layer.ops(nloc)
         pack_alg_bytes = in_bytes + pack_bytes
         gemm_tops = ops_loc / (t_gemm * 1e-3) / 1e12
-        per_img = NCU_TRAFFIC_PER_IMAGE.get((name, "popc" if args.gemm == "popc" else "tc"))
+        per_img = NCU_TRAFFIC_PER_IMAGE.get((name, {"popc": "popc", "i8tc": "tc"}.get(args.gemm, "f4")))
         gemm_traffic = per_img * nloc if per_img else None
         per_img = NCU_TRAFFIC_PER_IMAGE.get((name, "pack"))
         pack_traffic = per_img * nloc if per_img else None
@@ -371,14 +371,18 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
             gemm_kernel_name, gemm_bound = "gemm_popc_tiled_kernel (LOP3 carry-save popcount GEMM + PReLU)", "int"
             gemm_peak = lop3 * 1e9 * 64.0 / 5.5 / 1e12
             gemm_peak_source = "measured LOP3 issue rate x 64 ops per lane / 5.5 LOP3 per lane"
-        else:
-            gemm_kernel_name, gemm_bound = "gemm_i8_tc_kernel (tcgen05.mma kind::i8 GEMM + PReLU)", "tensor"
+        elif args.gemm == "i8tc":
+            gemm_kernel_name, gemm_bound = "gemm_tc_kernel<F4=false> (tcgen05.mma kind::i8 GEMM + PReLU)", "tensor"
             gemm_peak = 2.0 * pk["bf16_tflops"]
             gemm_peak_source = f"2 x {pk['source']} bf16 burst figure (int8 dense rate = 2 x bf16)"
+        else:
+            gemm_kernel_name, gemm_bound = "gemm_tc_kernel<F4=true> (tcgen05.mma kind::mxf4 GEMM, unit scales, + PReLU)", "tensor"
+            gemm_peak = 4.0 * pk["bf16_tflops"]
+            gemm_peak_source = f"4 x {pk['source']} bf16 burst figure (4-bit dense rate = 4 x bf16)"
         line = {
             "metric": METRIC, "value": ops / (ms_step * 1e-3) / 1e9, "unit": "GOPS", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
-            "dtype": "int8 operands expanded from 2-bit planes, int32 accumulate, fp32 PReLU" if args.gemm != "popc" else "u32 bit-plane lanes, int32 popcount accumulate, fp32 PReLU",
+            "dtype": ("e2m1 operands expanded from 2-bit planes, unit block scales, fp32 accumulate (exact), fp32 PReLU" if args.gemm in ("auto", "f4tc") else "int8 operands expanded from 2-bit planes, int32 accumulate, fp32 PReLU") if args.gemm != "popc" else "u32 bit-plane lanes, int32 popcount accumulate, fp32 PReLU",
             "data": "synthetic",
             "config": {"workload": name, "batch": N_total, "batch_per_gpu": nloc, "layer": str(layer), "layout": "NCHW",
                        "M": N_total * OH * OW, "K": layer.C * layer.KH * layer.KW, "N": layer.KN, "gemm": args.gemm,
@@ -421,7 +425,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="tnn_conv_large")
-    ap.add_argument("--gemm", choices=["auto", "popc", "i8tc"], default="auto")
+    ap.add_argument("--gemm", choices=["auto", "popc", "i8tc", "f4tc"], default="auto")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
                     help="weak: every rank processes the configured batch; strong: the configured batch is split over the ranks")
     ap.add_argument("--no-check", action="store_true", help="skip the pre-timing comparison with the CPU checker")

@@ -17,7 +17,7 @@ from ._lib import GemmTestcase, Shape, Testcase, load_library
 TNN, TBN, BTN, BNN = 0, 1, 2, 3
 NCHW, NHWC = 0, 1
 PACK_AUTO, PACK_GATHER, PACK_STAGED = 0, 1, 2
-GEMM_AUTO, GEMM_POPC_SIMPLE, GEMM_POPC_TILED, GEMM_I8_TC = 0, 1, 2, 3
+GEMM_AUTO, GEMM_POPC_SIMPLE, GEMM_POPC_TILED, GEMM_I8_TC, GEMM_F4_TC = 0, 1, 2, 3, 4
 
 
 class TnnsError(RuntimeError):

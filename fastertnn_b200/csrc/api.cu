@@ -229,6 +229,7 @@ void tnns_cuda_free_weights(tnns_cuda_ctx* ctx, tnns_cuda_weights* w) {
     if (ctx) cudaSetDevice(ctx->device);
     if (w->d_packed) cudaFree(w->d_packed);
     if (w->d_i8) cudaFree(w->d_i8);
+    if (w->d_f4) cudaFree(w->d_f4);
     delete w;
 }
 
@@ -261,15 +262,18 @@ int tnns_cuda_gemm(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const int64_t
             return tnns_launch_gemm_popc(ctx, w->type, d_a, w->d_packed, d_y, M, w->KN, w->Kp, OH * OW, K_unpack, alpha, layout,
                                          true, (cudaStream_t)stream);
         case TNNS_GEMM_AUTO:
-            // Measured on B200: the tensor-core kernel is faster than the integer-pipe kernel on
-            // every layer shape of the benchmark set (1.7x at batch-1 56x56x256, 17x at the large
-            // layer); the integer-pipe kernel remains for rows too long for its exact range.
-            if (w->d_i8 && w->Kp < 65536)
-                return tnns_launch_gemm_i8_tc(ctx, w, d_a, d_y, M, OH * OW, alpha, layout, (cudaStream_t)stream);
+            // Measured on B200 (large layer, us per launch): 4-bit tensor path 90, int8 tensor path
+            // 126, integer pipe 2140; the order is the same on every layer shape of the benchmark
+            // set down to batch-1 56x56x256 (15 / 18 / 44).  The integer-pipe kernel remains for
+            // rows too long for the tensor paths' exact range.
+            if (w->d_f4 && w->Kp < 65536)
+                return tnns_launch_gemm_tc(ctx, w, d_a, d_y, M, OH * OW, alpha, layout, true, (cudaStream_t)stream);
             return tnns_launch_gemm_popc(ctx, w->type, d_a, w->d_packed, d_y, M, w->KN, w->Kp, OH * OW, K_unpack, alpha, layout,
                                          true, (cudaStream_t)stream);
         case TNNS_GEMM_I8_TC:
-            return tnns_launch_gemm_i8_tc(ctx, w, d_a, d_y, M, OH * OW, alpha, layout, (cudaStream_t)stream);
+            return tnns_launch_gemm_tc(ctx, w, d_a, d_y, M, OH * OW, alpha, layout, false, (cudaStream_t)stream);
+        case TNNS_GEMM_F4_TC:
+            return tnns_launch_gemm_tc(ctx, w, d_a, d_y, M, OH * OW, alpha, layout, true, (cudaStream_t)stream);
         default:
             return tnns_fail(TNNS_ERR_INVALID, "unknown GEMM algorithm %d", algo);
     }

@@ -36,11 +36,17 @@ constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_EXP0 = 2;
 // that arrives from L2 feeds MT MMAs, which is what keeps the L2 -> SM weight traffic below
 // the tensor pipe's appetite.  Roles: warp 0 weight producer, warp 1 MMA issuer, NG groups of
 // 4*MT expander warps, 4*MT epilogue warps.
-template <int BN, int MT>
+// F4 selects the 4-bit form: operands as e2m1 nibbles (+1 = 0x2, -1 = 0xA, 0 = 0x0), multiplied by
+// tcgen05.mma.kind::mxf4 with every block scale equal to 1 (ue8m0 0x7F) and fp32 accumulators --
+// sums of at most 2^22 products of +-1 are exact in fp32.  A stage then covers 256 K elements in
+// the same 128 bytes per row, which halves the shared-memory traffic per multiply-accumulate and
+// doubles the tensor rate.  The block scales occupy tensor-memory columns 256.., so the
+// accumulators must fit columns 0..255.
+template <int BN, int MT, bool F4>
 struct TcCfg {
     static constexpr int NSTG = (MT == 1) ? 4 : 3;                 // smem ring depth
     static constexpr int A_STAGE = MT * A_SUB, B_STAGE = BN * KCH;
-    static constexpr int NBUF = (MT * BN <= 256) ? 2 : 1;           // accumulator sets in tensor memory
+    static constexpr int NBUF = (MT * BN <= (F4 ? 128 : 256)) ? 2 : 1;  // accumulator sets in tensor memory
     static constexpr int NG = (MT == 1) ? 4 : 2;                    // expander groups (stages expanded concurrently)
     static constexpr int WARP_EPI0 = WARP_EXP0 + 4 * MT * NG;
     static constexpr int NTHREADS = 32 * (2 + 4 * MT * NG + 4 * MT);
@@ -100,6 +106,15 @@ __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void tc_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
+__device__ __forceinline__ void tc_mma_f4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+        : "memory");
+}
 __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -149,28 +164,51 @@ __device__ __forceinline__ void store_row_chunk(unsigned char* tile, int r, cons
     }
 }
 
+// 32 elements -> 32 e2m1 nibbles (four words) in a fixed permuted order: nibble = sign<<3 | nonzero<<1.
+__device__ __forceinline__ void expand32_f4(uint32_t s, uint32_t z, uint32_t (&w)[4]) {
+    const uint32_t nz = ~z;
+    w[0] = ((s << 3) & 0x88888888u) | ((nz << 1) & 0x22222222u);
+    w[1] = ((s << 2) & 0x88888888u) | (nz & 0x22222222u);
+    w[2] = ((s << 1) & 0x88888888u) | ((nz >> 1) & 0x22222222u);
+    w[3] = (s & 0x88888888u) | ((nz >> 2) & 0x22222222u);
+}
+
+// 4-bit form: one row and stage = 256 elements = eight lanes per plane -> 128 bytes.
+__device__ __forceinline__ void store_row_stage_f4(unsigned char* tile, int r, const uint4 (&s)[2], const uint4 (&z)[2]) {
+    const uint32_t sl[8] = {s[0].x, s[0].y, s[0].z, s[0].w, s[1].x, s[1].y, s[1].z, s[1].w};
+    const uint32_t zl[8] = {z[0].x, z[0].y, z[0].z, z[0].w, z[1].x, z[1].y, z[1].z, z[1].w};
+    unsigned char* row = tile + (size_t)r * KCH;
+#pragma unroll
+    for (int l = 0; l < 8; l++) {
+        uint32_t w[4];
+        expand32_f4(sl[l], zl[l], w);
+        *reinterpret_cast<uint4*>(row + ((l ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+    }
+}
+
 // ---------------------------------------------------------------------------------------
 // One-time weight expansion: packed rows -> int8 tile images, [n_tile][chunk][BN rows][128 B],
 // swizzled exactly as the MMA reads them, rows past KN left zero.
 // ---------------------------------------------------------------------------------------
 __global__ void expand_weights_kernel(const uint4* __restrict__ packed, unsigned char* __restrict__ img, int KN, int Kp, int BN,
-                                      int two_planes) {
-    const int nch = Kp / 2;
+                                      int two_planes, int f4) {
+    const int nch = f4 ? Kp / 4 : Kp / 2;
     const long long total = (long long)KN * nch;
+    const size_t pitch = two_planes ? (size_t)Kp : (size_t)Kp / 2;  // uint4 per row
+    const int gsz = two_planes ? 4 : 2;                              // uint4 per 256-element group
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
         const int kn = (int)(i / nch), c = (int)(i - (long long)kn * nch);
-        const int g = c >> 1, h = c & 1;
-        uint4 s, z = make_uint4(0, 0, 0, 0);
-        if (two_planes) {
-            const uint4* grp = packed + ((size_t)kn * Kp) + (size_t)g * 4;  // row pitch Kp uint4, group 4 uint4
-            s = grp[h];
-            z = grp[2 + h];
-        } else {
-            const uint4* grp = packed + ((size_t)kn * (Kp / 2)) + (size_t)g * 2;
-            s = grp[h];
-        }
         unsigned char* tile = img + ((size_t)(kn / BN) * nch + c) * (size_t)BN * KCH;
-        store_row_chunk(tile, kn % BN, s, z);
+        const uint4 zero4 = make_uint4(0, 0, 0, 0);
+        if (f4) {
+            const uint4* grp = packed + (size_t)kn * pitch + (size_t)c * gsz;
+            const uint4 s[2] = {grp[0], grp[1]};
+            const uint4 z[2] = {two_planes ? grp[2] : zero4, two_planes ? grp[3] : zero4};
+            store_row_stage_f4(tile, kn % BN, s, z);
+        } else {
+            const uint4* grp = packed + (size_t)kn * pitch + (size_t)(c >> 1) * gsz;
+            store_row_chunk(tile, kn % BN, grp[c & 1], two_planes ? grp[2 + (c & 1)] : zero4);
+        }
     }
 }
 
@@ -187,12 +225,16 @@ struct GemmArgs {
     int dbg;  // experiment knob: 1 skip expansion, 2 skip weight copies, 4 skip epilogue stores
 };
 
-template <int BN, int MT>
-__global__ void __launch_bounds__(TcCfg<BN, MT>::NTHREADS, 1) gemm_i8_tc_kernel(GemmArgs p) {
-    using Cfg = TcCfg<BN, MT>;
+template <int BN, int MT, bool F4>
+__global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel(GemmArgs p) {
+    using Cfg = TcCfg<BN, MT, F4>;
     constexpr int NSTG = Cfg::NSTG, A_STAGE = Cfg::A_STAGE, B_STAGE = Cfg::B_STAGE, NBUF = Cfg::NBUF, WARP_EPI0 = Cfg::WARP_EPI0, NG = Cfg::NG;
     constexpr int BMT = MT * BM;  // rows per block tile
-    constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    // instruction descriptor: i8 -- s32 accumulate (2<<4), signed 8-bit A and B (1<<7, 1<<10);
+    // mxf4 -- e2m1 A and B (1<<7, 1<<10), ue8m0 scales (1<<23); both K-major, N>>3 at bit 17, M>>4 at bit 24
+    constexpr uint32_t IDESC = (F4 ? (1u << 23) : (2u << 4)) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
+                               ((uint32_t)(BM >> 4) << 24);
+    constexpr uint32_t SF_COL = 256;  // first tensor-memory column of the (all-ones) block scales
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* sA = smem;
@@ -205,7 +247,7 @@ __global__ void __launch_bounds__(TcCfg<BN, MT>::NTHREADS, 1) gemm_i8_tc_kernel(
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const int nchunks = p.Kp / 2;
+    const int nchunks = F4 ? p.Kp / 4 : p.Kp / 2;  // stages per tile
     const int ntn = (p.KN + BN - 1) / BN;
     const long long ntm = (p.M + BMT - 1) / BMT;
     const long long ntiles = ntm * ntn;
@@ -230,6 +272,23 @@ __global__ void __launch_bounds__(TcCfg<BN, MT>::NTHREADS, 1) gemm_i8_tc_kernel(
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    if (F4) {
+        // block scales: ue8m0 0x7F = 2^0 in every byte of columns 256..511, so whatever bytes the
+        // MMA picks as scale of a row block or column block, it reads 1.0
+        if (warp >= WARP_EPI0 && warp < WARP_EPI0 + 4) {
+            const uint32_t one = 0x7F7F7F7Fu;
+#pragma unroll 1
+            for (uint32_t c = 0; c < 256; c += 8) {
+                const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + SF_COL + c;
+                asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(one)
+                             : "memory");
+            }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        }
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+    }
 
     if (warp == WARP_TMA) {
         if (lane == 0) {
@@ -263,7 +322,10 @@ __global__ void __launch_bounds__(TcCfg<BN, MT>::NTHREADS, 1) gemm_i8_tc_kernel(
                     for (int mt = 0; mt < MT; mt++) {
                         const uint64_t da = make_desc(smem_u32(sA + s * A_STAGE + mt * A_SUB));
 #pragma unroll
-                        for (int k = 0; k < KCH / 32; k++) tc_mma_i8(d_tmem + mt * BN, da + 2 * k, db + 2 * k, IDESC, (c | k) ? 1u : 0u);
+                        for (int k = 0; k < KCH / 32; k++) {
+                            if (F4) tc_mma_f4(d_tmem + mt * BN, da + 2 * k, db + 2 * k, IDESC, tmem_base + SF_COL, tmem_base + SF_COL + 64, (c | k) ? 1u : 0u);
+                            else tc_mma_i8(d_tmem + mt * BN, da + 2 * k, db + 2 * k, IDESC, (c | k) ? 1u : 0u);
+                        }
                     }
                     tc_commit(bar_empty + 8 * s);  // stage reusable once these MMAs have read it
                 }
@@ -280,19 +342,30 @@ __global__ void __launch_bounds__(TcCfg<BN, MT>::NTHREADS, 1) gemm_i8_tc_kernel(
         const int e = tid - WARP_EXP0 * 32;
         const int grp = e / BMT;
         const int r = e - grp * BMT;  // row of the block tile, 0 .. MT*128-1
-        constexpr int PF = 4;
+        constexpr int PF = F4 ? 2 : 4;
         const size_t pitch = p.a_two_planes ? (size_t)p.Kp : (size_t)p.Kp / 2;  // uint4 per row
         const int gsz = p.a_two_planes ? 4 : 2;                                    // uint4 per 256-element group
-        uint4 ring_s[PF], ring_z[PF];
+        constexpr int RW = F4 ? 2 : 1;  // uint4 per plane and stage
+        uint4 ring_s[PF][RW], ring_z[PF][RW];
         // prefetch cursor: (tile, chunk) of the next load of this group
         long long pf_t = blockIdx.x;
         int pf_c = grp;
         while (pf_c >= nchunks) { pf_c -= nchunks; pf_t += gridDim.x; }
-        auto fetch = [&](uint4& ds, uint4& dz) {
+        auto fetch = [&](uint4 (&ds)[RW], uint4 (&dz)[RW]) {
             if (pf_t < ntiles) {
-                const uint4* row = p.A + (size_t)min((pf_t / ntn) * BMT + r, p.M - 1) * pitch + (size_t)(pf_c >> 1) * gsz + (pf_c & 1);
-                ds = __ldg(row);
-                dz = p.a_two_planes ? __ldg(row + 2) : make_uint4(0, 0, 0, 0);
+                const uint4* rowp = p.A + (size_t)min((pf_t / ntn) * BMT + r, p.M - 1) * pitch;
+                if (F4) {
+                    const uint4* row = rowp + (size_t)pf_c * gsz;
+#pragma unroll
+                    for (int q = 0; q < RW; q++) {
+                        ds[q] = __ldg(row + q);
+                        dz[q] = p.a_two_planes ? __ldg(row + 2 + q) : make_uint4(0, 0, 0, 0);
+                    }
+                } else {
+                    const uint4* row = rowp + (size_t)(pf_c >> 1) * gsz + (pf_c & 1);
+                    ds[0] = __ldg(row);
+                    dz[0] = p.a_two_planes ? __ldg(row + 2) : make_uint4(0, 0, 0, 0);
+                }
                 pf_c += NG;
                 while (pf_c >= nchunks) { pf_c -= nchunks; pf_t += gridDim.x; }
             }
@@ -309,7 +382,11 @@ __global__ void __launch_bounds__(TcCfg<BN, MT>::NTHREADS, 1) gemm_i8_tc_kernel(
                 if (it < total_it) {
                     const int s = (int)(it % NSTG);
                     if (!mbar_wait(bar_empty + 8 * s, (uint32_t)((it / NSTG) & 1) ^ 1, abort_flag, p.status, 4)) goto done;
-                    if (!(p.dbg & 1)) store_row_chunk(sA + s * A_STAGE + (r >> 7) * A_SUB, r & 127, ring_s[i], ring_z[i]);
+                    if (!(p.dbg & 1)) {
+                        unsigned char* tile = sA + s * A_STAGE + (r >> 7) * A_SUB;
+                        if constexpr (F4) store_row_stage_f4(tile, r & 127, ring_s[i], ring_z[i]);
+                        else store_row_chunk(tile, r & 127, ring_s[i][0], ring_z[i][0]);
+                    }
                     fence_proxy_async();  // generic-proxy smem writes -> visible to the tensor core's async proxy
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_full + 8 * s);
@@ -322,6 +399,7 @@ __global__ void __launch_bounds__(TcCfg<BN, MT>::NTHREADS, 1) gemm_i8_tc_kernel(
         const int q = warp & 3;                 // tensor-memory lane quadrant this warp may access
         const int sub = (warp - WARP_EPI0) >> 2;  // which 128-row sub-tile (accumulator) it drains
         const int bias_magic = 0x4B400000 + p.acc_bias;
+        const float bias_f = (float)p.acc_bias;  // +0.0f when there is none: a + 0.0f also turns a -0 sum into +0
         uint32_t lt = 0;
         for (long long t = blockIdx.x; t < ntiles; t += gridDim.x, lt++) {
             const int buf = lt % NBUF;
@@ -361,7 +439,7 @@ __global__ void __launch_bounds__(TcCfg<BN, MT>::NTHREADS, 1) gemm_i8_tc_kernel(
                     float f[32];
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
-                        const float a = __int_as_float((int)v[j] + bias_magic) - 12582912.0f;
+                        const float a = F4 ? __uint_as_float(v[j]) + bias_f : __int_as_float((int)v[j] + bias_magic) - 12582912.0f;
                         f[j] = a * (a > 0.f ? 1.0f : p.alpha);  // PReLU; a == 0 stays +0
                     }
                     const int c0 = n0 + cb;
@@ -406,10 +484,10 @@ done:
     }
 }
 
-template <int BN, int MT>
+template <int BN, int MT, bool F4>
 int launch_cfg(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream) {
-    using Cfg = TcCfg<BN, MT>;
-    auto kern = gemm_i8_tc_kernel<BN, MT>;
+    using Cfg = TcCfg<BN, MT, F4>;
+    auto kern = gemm_tc_kernel<BN, MT, F4>;
     TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
     const long long tiles = ((a.M + MT * BM - 1) / (MT * BM)) * ((a.KN + BN - 1) / BN);
     const int grid = (int)std::min<long long>(tiles, ctx->sm_count);
@@ -422,42 +500,50 @@ int launch_cfg(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream) {
 // One 128-row accumulator per block measured fastest on every layer shape tried (more blocks in
 // flight, deeper ring); the MT = 2 form halves the weight traffic per MMA and is kept for
 // experiments with other shapes.
-template <int BN>
+template <int BN, bool F4>
 int launch_bn(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream) {
     const char* force = getenv("TNNS_TC_MT");  // experiment knob
-    return (force && atoi(force) == 2) ? launch_cfg<BN, 2>(ctx, a, stream) : launch_cfg<BN, 1>(ctx, a, stream);
+    return (force && atoi(force) == 2) ? launch_cfg<BN, 2, F4>(ctx, a, stream) : launch_cfg<BN, 1, F4>(ctx, a, stream);
 }
 
 }  // namespace
 
 int tnns_i8_tile_n(int KN) { return KN <= 64 ? 64 : (KN <= 128 ? 128 : 256); }
 
+// Builds both operand images of a layer's weights: int8 (128 K elements per 128-byte row and
+// stage) and e2m1 (256 K elements per row and stage).
 int tnns_build_i8_weights(tnns_cuda_ctx* ctx, tnns_cuda_weights* w) {
     const int BN = tnns_i8_tile_n(w->KN);
-    const int ntn = (w->KN + BN - 1) / BN, nch = w->Kp / 2;
-    w->i8_bytes = (size_t)ntn * nch * BN * KCH;
-    w->i8_kchunks = nch;
-    TNNS_CUDA_TRY(cudaMalloc(&w->d_i8, w->i8_bytes));
-    TNNS_CUDA_TRY(cudaMemset(w->d_i8, 0, w->i8_bytes));
+    const int ntn = (w->KN + BN - 1) / BN;
     const bool two = (w->type == TNN || w->type == BTN);
-    const long long total = (long long)w->KN * nch;
-    const int blocks = (int)std::min<long long>((total + 127) / 128, 4096);
-    expand_weights_kernel<<<blocks, 128>>>(reinterpret_cast<const uint4*>(w->d_packed), reinterpret_cast<unsigned char*>(w->d_i8), w->KN,
-                                            w->Kp, BN, two ? 1 : 0);
-    tnns_count_launch();
-    TNNS_CUDA_TRY(cudaGetLastError());
+    for (int f4 = 0; f4 < 2; f4++) {
+        const int nch = f4 ? w->Kp / 4 : w->Kp / 2;
+        const size_t bytes = (size_t)ntn * nch * BN * KCH;
+        void* img = nullptr;
+        TNNS_CUDA_TRY(cudaMalloc(&img, bytes));
+        if (f4) { w->d_f4 = (uint8_t*)img; w->f4_bytes = bytes; }
+        else { w->d_i8 = (int8_t*)img; w->i8_bytes = bytes; w->i8_kchunks = nch; }
+        TNNS_CUDA_TRY(cudaMemset(img, 0, bytes));
+        const long long total = (long long)w->KN * nch;
+        const int blocks = (int)std::min<long long>((total + 127) / 128, 4096);
+        expand_weights_kernel<<<blocks, 128>>>(reinterpret_cast<const uint4*>(w->d_packed), reinterpret_cast<unsigned char*>(img), w->KN,
+                                                w->Kp, BN, two ? 1 : 0, f4);
+        tnns_count_launch();
+        TNNS_CUDA_TRY(cudaGetLastError());
+    }
     TNNS_CUDA_TRY(cudaDeviceSynchronize());
     return TNNS_OK;
 }
 
-int tnns_launch_gemm_i8_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_a, float* d_y, long long M, int OHW,
-                           float alpha, int layout, cudaStream_t stream) {
+int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_a, float* d_y, long long M, int OHW, float alpha,
+                        int layout, bool f4, cudaStream_t stream) {
     if (M == 0) return TNNS_OK;
-    if (!w->d_i8) return tnns_fail(TNNS_ERR_UNSUPPORTED, "weights carry no int8 operand image");
+    const void* img = f4 ? (const void*)w->d_f4 : (const void*)w->d_i8;
+    if (!img) return tnns_fail(TNNS_ERR_UNSUPPORTED, "weights carry no tensor-core operand image");
     if (w->Kp >= 65536) return tnns_fail(TNNS_ERR_UNSUPPORTED, "rows of %d plane words exceed the tensor-core path's exact range", w->Kp);
     GemmArgs a;
     a.A = reinterpret_cast<const uint4*>(d_a);
-    a.Bimg = reinterpret_cast<const unsigned char*>(w->d_i8);
+    a.Bimg = reinterpret_cast<const unsigned char*>(img);
     a.y = d_y;
     a.M = M;
     a.KN = w->KN;
@@ -469,9 +555,17 @@ int tnns_launch_gemm_i8_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const
     a.alpha = alpha;
     a.status = ctx->d_status;
     a.dbg = getenv("TNNS_TC_DBG") ? atoi(getenv("TNNS_TC_DBG")) : 0;
-    switch (tnns_i8_tile_n(w->KN)) {
-        case 64: return launch_bn<64>(ctx, a, stream);
-        case 128: return launch_bn<128>(ctx, a, stream);
-        default: return launch_bn<256>(ctx, a, stream);
+    const int bn = tnns_i8_tile_n(w->KN);
+    if (f4) {
+        switch (bn) {
+            case 64: return launch_bn<64, true>(ctx, a, stream);
+            case 128: return launch_bn<128, true>(ctx, a, stream);
+            default: return launch_bn<256, true>(ctx, a, stream);
+        }
+    }
+    switch (bn) {
+        case 64: return launch_bn<64, false>(ctx, a, stream);
+        case 128: return launch_bn<128, false>(ctx, a, stream);
+        default: return launch_bn<256, false>(ctx, a, stream);
     }
 }

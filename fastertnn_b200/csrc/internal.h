@@ -47,6 +47,8 @@ struct tnns_cuda_weights {
     int8_t* d_i8;         // {-1,0,+1} operand image for the tensor-core GEMM (may be NULL)
     size_t i8_bytes;
     int i8_kchunks;       // number of 128-element K chunks in d_i8
+    uint8_t* d_f4;        // e2m1 operand image for the 4-bit tensor-core GEMM (may be NULL)
+    size_t f4_bytes;
 };
 
 // error plumbing (thread local)
@@ -72,8 +74,8 @@ int tnns_launch_gemm_popc(tnns_cuda_ctx* ctx, int type, const void* d_a, const v
 // tensor-core path (gemm_i8_tc.cu)
 int tnns_i8_tile_n(int KN);
 int tnns_build_i8_weights(tnns_cuda_ctx* ctx, tnns_cuda_weights* w);
-int tnns_launch_gemm_i8_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_a, float* d_y, long long M, int OHW,
-                           float alpha, int layout, cudaStream_t stream);
+int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_a, float* d_y, long long M, int OHW, float alpha,
+                        int layout, bool f4, cudaStream_t stream);
 
 // Division by a runtime-constant divisor without the hardware divide sequence.
 // Exact for every 32-bit unsigned numerator (Granlund-Montgomery round-up method).

@@ -158,7 +158,13 @@ enum tnns_layout { TNNS_NCHW = 0, TNNS_NHWC = 1 };
 /* Kernel selection.  AUTO picks per shape; the others force one implementation (used
  * by tests to cross-check them and by the benchmark to compare them). */
 enum tnns_pack_algo { TNNS_PACK_AUTO = 0, TNNS_PACK_GATHER = 1, TNNS_PACK_STAGED = 2 };
-enum tnns_gemm_algo { TNNS_GEMM_AUTO = 0, TNNS_GEMM_POPC_SIMPLE = 1, TNNS_GEMM_POPC_TILED = 2, TNNS_GEMM_I8_TC = 3 };
+enum tnns_gemm_algo {
+    TNNS_GEMM_AUTO = 0,
+    TNNS_GEMM_POPC_SIMPLE = 1, /* one thread per output, integer pipe            */
+    TNNS_GEMM_POPC_TILED = 2,  /* tiled carry-save popcount GEMM, integer pipe   */
+    TNNS_GEMM_I8_TC = 3,       /* tcgen05 int8 tensor-core GEMM                  */
+    TNNS_GEMM_F4_TC = 4        /* tcgen05 4-bit (e2m1, unit scales) tensor-core GEMM */
+};
 
 /* Error codes returned by every tnns_cuda_* function (0 = success). */
 enum tnns_status {

@@ -76,7 +76,7 @@ def test_layer_matches_checker_and_golden(case, gpu_ctx, checker):
             a = device_pack(gpu_ctx, case, layout, algo)
             assert np.array_equal(a, a_ref), f"packed matrix differs (layout {layout}, algo {algo})"
     for layout in (ft.NCHW, ft.NHWC):
-        for galgo in (ft.GEMM_POPC_SIMPLE, ft.GEMM_POPC_TILED, ft.GEMM_I8_TC, ft.GEMM_AUTO):
+        for galgo in (ft.GEMM_POPC_SIMPLE, ft.GEMM_POPC_TILED, ft.GEMM_I8_TC, ft.GEMM_F4_TC, ft.GEMM_AUTO):
             y = device_conv(gpu_ctx, case, wp, layout, ft.PACK_AUTO, galgo)
             assert y.tobytes() == y_ref.tobytes(), f"output differs (layout {layout}, gemm {galgo})"
     assert sha(device_conv(gpu_ctx, case, wp, ft.NCHW, ft.PACK_AUTO, ft.GEMM_AUTO)) == d["output"]
@@ -149,8 +149,9 @@ def test_benchmark_configs_small_enough_for_the_checker(type_, gpu_ctx, checker)
         wp = checker.pack_weights(wgt_ternary(type_), case.w, case.w_thr)
         y_ref = checker.conv(type_, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
         for layout in (ft.NCHW, ft.NHWC):
-            y = device_conv(gpu_ctx, case, wp, layout, ft.PACK_AUTO, ft.GEMM_AUTO)
-            assert y.tobytes() == y_ref.tobytes()
+            for galgo in (ft.GEMM_AUTO, ft.GEMM_I8_TC, ft.GEMM_F4_TC, ft.GEMM_POPC_TILED):
+                y = device_conv(gpu_ctx, case, wp, layout, ft.PACK_AUTO, galgo)
+                assert y.tobytes() == y_ref.tobytes(), (layout, galgo)
 
 
 def test_host_buffer_layer_matches_device_layer(gpu_ctx, checker):
@@ -221,6 +222,8 @@ def test_large_layer_properties(gpu_ctx, checker):
     assert y[:2].tobytes() == y2.tobytes()
     y_simple = device_conv(gpu_ctx, case, wp, ft.NCHW, ft.PACK_GATHER, ft.GEMM_POPC_SIMPLE)
     assert y.tobytes() == y_simple.tobytes()
+    for galgo in (ft.GEMM_POPC_TILED, ft.GEMM_I8_TC, ft.GEMM_F4_TC):
+        assert device_conv(gpu_ctx, case, wp, ft.NCHW, ft.PACK_AUTO, galgo).tobytes() == y_simple.tobytes(), galgo
     neg = make_case(TNN, layer, N, 2024, "uniform")
     neg.thr[:] = 0.25
     neg.x = -neg.x
