@@ -47,9 +47,13 @@ struct TcCfg {
     static constexpr int NSTG = (MT == 1) ? 4 : 3;                 // smem ring depth
     static constexpr int A_STAGE = MT * A_SUB, B_STAGE = BN * KCH;
     static constexpr int NBUF = (MT * BN <= (F4 ? 128 : 256)) ? 2 : 1;  // accumulator sets in tensor memory
-    static constexpr int NG = (MT == 1) ? 4 : 2;                    // expander groups (stages expanded concurrently)
+    // epilogue warps per lane quadrant: with a single accumulator set the drain is not hidden
+    // behind the next tile's MMAs, so two warps share each quadrant's columns
+    static constexpr int EPW = (NBUF == 1 && MT == 1) ? 2 : 1;
+    // expander groups (stages expanded concurrently); 22 warps per block in every MT = 1 form
+    static constexpr int NG = (MT == 1) ? (EPW == 2 ? 3 : 4) : 2;
     static constexpr int WARP_EPI0 = WARP_EXP0 + 4 * MT * NG;
-    static constexpr int NTHREADS = 32 * (2 + 4 * MT * NG + 4 * MT);
+    static constexpr int NTHREADS = 32 * (2 + 4 * MT * NG + 4 * MT * EPW);
     static constexpr size_t SMEM = 1024 + (size_t)NSTG * (A_STAGE + B_STAGE) + 256;
 };
 constexpr unsigned STATUS_WAIT_EXPIRED = 0x100;
@@ -228,7 +232,7 @@ struct GemmArgs {
 template <int BN, int MT, bool F4>
 __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel(GemmArgs p) {
     using Cfg = TcCfg<BN, MT, F4>;
-    constexpr int NSTG = Cfg::NSTG, A_STAGE = Cfg::A_STAGE, B_STAGE = Cfg::B_STAGE, NBUF = Cfg::NBUF, WARP_EPI0 = Cfg::WARP_EPI0, NG = Cfg::NG;
+    constexpr int NSTG = Cfg::NSTG, A_STAGE = Cfg::A_STAGE, B_STAGE = Cfg::B_STAGE, NBUF = Cfg::NBUF, WARP_EPI0 = Cfg::WARP_EPI0, NG = Cfg::NG, EPW = Cfg::EPW;
     constexpr int BMT = MT * BM;  // rows per block tile
     // instruction descriptor: i8 -- s32 accumulate (2<<4), signed 8-bit A and B (1<<7, 1<<10);
     // mxf4 -- e2m1 A and B (1<<7, 1<<10), ue8m0 scales (1<<23); both K-major, N>>3 at bit 17, M>>4 at bit 24
@@ -259,7 +263,7 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(bar_tfull + 8 * b, 1);
-            mbar_init(bar_tempty + 8 * b, 4 * MT);  // the epilogue warps
+            mbar_init(bar_tempty + 8 * b, 4 * MT * EPW);  // the epilogue warps
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -397,7 +401,9 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
     } else {
         // ---------------- epilogue ----------------
         const int q = warp & 3;                 // tensor-memory lane quadrant this warp may access
-        const int sub = (warp - WARP_EPI0) >> 2;  // which 128-row sub-tile (accumulator) it drains
+        const int sub = ((warp - WARP_EPI0) >> 2) % MT;   // which 128-row sub-tile (accumulator) it drains
+        const int ecol = ((warp - WARP_EPI0) >> 2) / MT;  // which share of the columns
+        constexpr int ECOLS = BN / EPW;
         const int bias_magic = 0x4B400000 + p.acc_bias;
         const float bias_f = (float)p.acc_bias;  // +0.0f when there is none: a + 0.0f also turns a -0 sum into +0
         uint32_t lt = 0;
@@ -413,7 +419,7 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
             const int rem = (int)(row - n_img * p.OHW);
             float* ybase = (p.layout == TNNS_NHWC) ? p.y + (size_t)row * p.KN : p.y + (size_t)n_img * p.KN * p.OHW + rem;
 #pragma unroll 1
-            for (int cb = 0; cb < BN; cb += 32) {
+            for (int cb = ecol * ECOLS; cb < (ecol + 1) * ECOLS; cb += 32) {
                 uint32_t v[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((buf * MT + sub) * BN + cb);
                 asm volatile(
@@ -427,7 +433,7 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (cb + 32 >= BN) {
+                if (cb + 32 >= (ecol + 1) * ECOLS) {
                     // the last slice is in registers: hand the accumulator back before storing it
                     tc_fence_before();
                     __syncwarp();
@@ -448,21 +454,21 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
                         if (full && (p.KN & 3) == 0) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 4)
-                                *reinterpret_cast<float4*>(ybase + c0 + j) = make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]);
+                                __stcs(reinterpret_cast<float4*>(ybase + c0 + j), make_float4(f[j], f[j + 1], f[j + 2], f[j + 3]));
                         } else {
 #pragma unroll
                             for (int j = 0; j < 32; j++)
-                                if (c0 + j < p.KN) ybase[c0 + j] = f[j];
+                                if (c0 + j < p.KN) __stcs(ybase + c0 + j, f[j]);
                         }
                     } else {
                         float* yc = ybase + (size_t)c0 * p.OHW;
                         if (full) {
 #pragma unroll
-                            for (int j = 0; j < 32; j++, yc += p.OHW) *yc = f[j];
+                            for (int j = 0; j < 32; j++, yc += p.OHW) __stcs(yc, f[j]);
                         } else {
 #pragma unroll
                             for (int j = 0; j < 32; j++, yc += p.OHW)
-                                if (c0 + j < p.KN) *yc = f[j];
+                                if (c0 + j < p.KN) __stcs(yc, f[j]);
                         }
                     }
                 }
