@@ -1,28 +1,32 @@
-// Bitwise GEMM + PReLU on the 5th-generation tensor cores: the packed {-1,0,+1} / {-1,+1}
-// operands are expanded to int8 on the fly and multiplied with tcgen05.mma.kind::i8, int32
-// accumulators in tensor memory.  Because |acc| <= 64*Kp the integer result is exact, so the
-// output is bit-identical to the popcount kernels (reference: mm_tnn / mm_tbn / mm_btn /
-// mm_bnn, src/tnns/mm_p2_final_*_avx2.c).
+// Bitwise GEMM + PReLU on the 5th-generation tensor cores (reference: mm_tnn / mm_tbn / mm_btn /
+// mm_bnn, src/tnns/mm_p2_final_*_avx2.c).  The packed {-1,0,+1} / {-1,+1} operands are expanded
+// on the fly and multiplied by tcgen05.mma with the accumulators in tensor memory, in one of
+// two forms:
+//   int8  (F4 = false)  kind::i8, int32 accumulators, 128 K elements per 128-byte row and stage
+//   4-bit (F4 = true)   kind::mxf4 on e2m1 nibbles with every block scale = 1, fp32
+//                       accumulators, 256 K elements per row and stage (default: half the
+//                       shared-memory bytes per multiply-accumulate, twice the tensor rate)
+// Both are exact: |acc| <= 64*Kp < 2^22, so the int32 and the fp32 sums are the same integers
+// and the fp32 output is bit-identical to the popcount kernels.
 //
-// One persistent block per SM, 320 threads in four roles:
-//   warp 0      weight producer: one bulk async copy (TMA engine, no multicast) per stage of a
-//               pre-expanded, pre-swizzled int8 weight tile (built once per layer at upload)
-//   warp 1      MMA issuer: one thread issues four tcgen05.mma (K = 32 each) per stage and
-//               commits to the stage's "empty" barrier; owns the tensor-memory allocation
-//   warps 2-5   activation expanders: thread = row; load the packed planes from global memory,
-//               expand 128 elements (4 lanes per plane) to int8 with LOP3/PRMT and store them in
-//               the 128-byte-swizzled K-major layout the MMA descriptor expects
-//   warps 6-9   epilogue: tcgen05.ld the finished accumulator (double buffered in tensor
-//               memory), apply the BNN constant and PReLU, store fp32 (NCHW: 32 consecutive
-//               pixels per warp and kernel -> 128-byte stores)
+// One persistent block per SM, 22 warps in four roles:
+//   warp 0      weight producer: one bulk async copy (TMA engine, no multicast, no tensor map)
+//               per stage of a pre-expanded, pre-swizzled weight tile (built once per layer)
+//   warp 1      MMA issuer: one thread issues four tcgen05.mma per stage and commits to the
+//               stage's "empty" barrier; owns the tensor-memory allocation
+//   12-16 warps activation expanders in NG groups: thread = row; group k fills stages k, k+NG, ...
+//               so NG stages are expanded at once; packed planes come from global memory through
+//               a register prefetch ring and are stored in the 128-byte-swizzled K-major layout
+//               the MMA descriptor expects
+//   4-8 warps   epilogue: tcgen05.ld the finished accumulator, apply the BNN constant and PReLU,
+//               store fp32 (NCHW: 32 consecutive pixels per warp and kernel -> 128-byte stores)
 // Every mbarrier wait is bounded; on expiry the kernel raises a status word, all roles leave
 // their loops, tensor memory is freed and the kernel returns.
 //
-// The order of the K elements inside a 128-element chunk is whatever the expansion routine
-// produces; activations and weights go through the same routine, so the permutation cancels
-// in the dot product.
+// The order of the K elements inside a stage is whatever the expansion routine produces;
+// activations and weights go through the same routine, so the permutation cancels in the dot
+// product.
 #include <algorithm>
-#include <cstdlib>
 
 #include "internal.h"
 
@@ -226,7 +230,6 @@ struct GemmArgs {
     int acc_bias;               // added to the integer dot product (BNN: K_unpack - 64*Kp)
     float alpha;
     unsigned int* status;
-    int dbg;  // experiment knob: 1 skip expansion, 2 skip weight copies, 4 skip epilogue stores
 };
 
 template <int BN, int MT, bool F4>
@@ -303,7 +306,6 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
                 for (int c = 0; c < nchunks; c++, it++) {
                     const int s = it % NSTG;
                     if (!mbar_wait(bar_empty + 8 * s, ((it / NSTG) & 1) ^ 1, abort_flag, p.status, 1)) goto done;
-                    if (p.dbg & 2) { mbar_arrive(bar_full + 8 * s); continue; }
                     mbar_arrive_expect_tx(bar_full + 8 * s, B_STAGE);
                     bulk_g2s(smem_u32(sB + s * B_STAGE), src + (size_t)c * B_STAGE, B_STAGE, bar_full + 8 * s);
                 }
@@ -386,7 +388,7 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
                 if (it < total_it) {
                     const int s = (int)(it % NSTG);
                     if (!mbar_wait(bar_empty + 8 * s, (uint32_t)((it / NSTG) & 1) ^ 1, abort_flag, p.status, 4)) goto done;
-                    if (!(p.dbg & 1)) {
+                    {
                         unsigned char* tile = sA + s * A_STAGE + (r >> 7) * A_SUB;
                         if constexpr (F4) store_row_stage_f4(tile, r & 127, ring_s[i], ring_z[i]);
                         else store_row_chunk(tile, r & 127, ring_s[i][0], ring_z[i][0]);
@@ -439,7 +441,7 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
                     __syncwarp();
                     if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
                 }
-                if (row_ok && !(p.dbg & 4)) {
+                if (row_ok) {
                     // int -> float without the conversion unit: for |a| < 2^22 the float with bit
                     // pattern 0x4B400000 + a is 1.5*2^23 + a exactly, so subtracting 1.5*2^23 gives a.
                     float f[32];
@@ -503,13 +505,12 @@ int launch_cfg(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream) {
     return TNNS_OK;
 }
 
-// One 128-row accumulator per block measured fastest on every layer shape tried (more blocks in
-// flight, deeper ring); the MT = 2 form halves the weight traffic per MMA and is kept for
-// experiments with other shapes.
+// One 128-row accumulator per block (MT = 1) measured fastest on every layer shape tried: more
+// blocks in flight and a deeper ring; MT = 2 (two stacked accumulators, half the weight traffic
+// per MMA) was 10-70 % slower and is not instantiated.
 template <int BN, bool F4>
 int launch_bn(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream) {
-    const char* force = getenv("TNNS_TC_MT");  // experiment knob
-    return (force && atoi(force) == 2) ? launch_cfg<BN, 2, F4>(ctx, a, stream) : launch_cfg<BN, 1, F4>(ctx, a, stream);
+    return launch_cfg<BN, 1, F4>(ctx, a, stream);
 }
 
 }  // namespace
@@ -560,7 +561,6 @@ int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const vo
     a.acc_bias = (w->type == BNN) ? w->K_unpack - 64 * w->Kp : 0;
     a.alpha = alpha;
     a.status = ctx->d_status;
-    a.dbg = getenv("TNNS_TC_DBG") ? atoi(getenv("TNNS_TC_DBG")) : 0;
     const int bn = tnns_i8_tile_n(w->KN);
     if (f4) {
         switch (bn) {
