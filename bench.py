@@ -41,7 +41,8 @@ METRIC = "ternary conv GOPS (2*M*N*K/s)"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
 # profiles/ (large layer, 64 images per launch), kept per image so that a rank's share scales.
 NCU_TRAFFIC_PER_IMAGE = {
-    ("tnn_conv_large", "tc"): 155.5e6 / 64,
+    ("tnn_conv_large", "f4"): 150.9e6 / 64,
+    ("tnn_conv_large", "tc"): 153.8e6 / 64,
     ("tnn_conv_large", "popc"): 419.3e6 / 64,
     ("tnn_conv_large", "pack"): 155.8e6 / 64,
 }

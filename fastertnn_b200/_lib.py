@@ -78,6 +78,9 @@ SIGNATURES = {
     "tnns_cuda_gemm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp]),
     "tnns_cuda_conv": (_i, [_vp, _vp, _vp, _vp, _vp, _pshape, _f, _i, _i, _i, _vp]),
     "tnns_cuda_conv_ws": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _pshape, _f, _i, _i, _i, _vp]),
+    "tnns_packed_image_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "tnns_cuda_gemm_packed_out": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
+    "tnns_cuda_im2row_packed": (_i, [_vp, _i, _vp, _vp, _pshape, _vp]),
     "tnns_cuda_conv_host": (_i, [_vp, _vp, _vp, _vp, _vp, _pshape, _f, _i]),
     "tnns_cuda_noalloc_scratch_bytes": (_sz, []),
     "tnns_cuda_conv_noalloc": (_i, [_i, _vp, _vp, _vp, _vp, _pshape, _f, _i, _vp]),

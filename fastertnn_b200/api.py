@@ -279,6 +279,16 @@ class Context:
         _check(self.lib.tnns_cuda_conv_ws(self.handle, w.handle, d_x, d_thr, d_y, d_ws, ws_bytes, C.byref(shape), alpha, layout,
                                           pack_algo, gemm_algo, stream))
 
+    def gemm_packed_out(self, w: Weights, d_a: int, d_image: int, d_thr_next: int, next_ternary: bool, N: int, OH: int, OW: int,
+                        alpha: float, stream=0):
+        """GEMM + PReLU whose epilogue writes the next layer's quantised bit planes instead of fp32."""
+        _check(self.lib.tnns_cuda_gemm_packed_out(self.handle, w.handle, d_a, d_image, d_thr_next, int(next_ternary), N, OH, OW,
+                                                  alpha, stream))
+
+    def im2row_packed(self, ternary: bool, d_image: int, d_packed: int, shape: Shape, stream=0):
+        """Packed image (bit planes) -> im2row matrix of the next layer."""
+        _check(self.lib.tnns_cuda_im2row_packed(self.handle, int(ternary), d_image, d_packed, C.byref(shape), stream))
+
     def conv_host(self, w: Weights, h_x: int, h_thr: int, h_y: int, shape: Shape, alpha: float, layout=NCHW):
         """Host-pointer layer (addresses of pinned or pageable buffers)."""
         _check(self.lib.tnns_cuda_conv_host(self.handle, w.handle, h_x, h_thr, h_y, C.byref(shape), alpha, layout))
@@ -322,6 +332,10 @@ def conv_noalloc(type_: int, d_packed_weights: int, d_x: int, d_thr: int, d_y: i
     """Whole layer on the current device without any allocation: the packed matrix goes to
     the library's built-in scratch array (see tnns_cuda_conv_noalloc in the header)."""
     _check(load_library().tnns_cuda_conv_noalloc(type_, d_packed_weights, d_x, d_thr, d_y, C.byref(shape), alpha, layout, stream))
+
+
+def packed_image_bytes(ternary: bool, N: int, C_: int, H: int, W: int) -> int:
+    return load_library().tnns_packed_image_bytes(int(ternary), N, C_, H, W)
 
 
 def launch_count() -> int:

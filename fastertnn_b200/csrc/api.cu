@@ -279,6 +279,36 @@ int tnns_cuda_gemm(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const int64_t
     }
 }
 
+// --- chained layers without the fp32 round trip ------------------------------------------------
+size_t tnns_packed_image_bytes(int ternary, int N, int C, int H, int W) {
+    if (N < 0 || C <= 0 || H <= 0 || W <= 0) return 0;
+    return (size_t)N * (ternary ? 2 : 1) * H * W * ((C + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS) * 8;
+}
+
+int tnns_cuda_gemm_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const int64_t* d_a, void* d_image,
+                              const float* d_thr_next, int next_ternary, int N, int OH, int OW, float alpha, void* stream) {
+    if (!ctx || !w || !d_a || !d_image || !d_thr_next) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    if (N < 0 || OH <= 0 || OW <= 0) return tnns_fail(TNNS_ERR_INVALID, "non-positive output dimension");
+    if (w->device != ctx->device) return tnns_fail(TNNS_ERR_INVALID, "weights live on device %d, context on %d", w->device, ctx->device);
+    if ((reinterpret_cast<uintptr_t>(d_a) & 15) || (reinterpret_cast<uintptr_t>(d_image) & 15))
+        return tnns_fail(TNNS_ERR_INVALID, "packed operand and image must be 16-byte aligned");
+    if (!w->d_f4 || w->Kp >= 65536) return tnns_fail(TNNS_ERR_UNSUPPORTED, "packed output needs the tensor-core GEMM");
+    return tnns_launch_gemm_tc(ctx, w, d_a, nullptr, (long long)N * OH * OW, OH * OW, alpha, TNNS_NCHW, true, (cudaStream_t)stream,
+                               d_image, d_thr_next, next_ternary != 0);
+}
+
+int tnns_cuda_im2row_packed(tnns_cuda_ctx* ctx, int ternary, const void* d_image, int64_t* d_packed, const tnns_shape_t* s,
+                            void* stream) {
+    if (!ctx || !d_image || !d_packed) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    TnnsGeom g;
+    int rc = tnns_make_geom(s, &g);
+    if (rc) return rc;
+    if ((reinterpret_cast<uintptr_t>(d_packed) & 15) || (reinterpret_cast<uintptr_t>(d_image) & 15))
+        return tnns_fail(TNNS_ERR_INVALID, "image and packed buffer must be 16-byte aligned");
+    return tnns_launch_pack(ctx, ternary != 0, reinterpret_cast<const float*>(d_image), reinterpret_cast<const float*>(d_image), d_packed, g,
+                            TNNS_SRC_PACKED_IMAGE, TNNS_PACK_AUTO, (cudaStream_t)stream);
+}
+
 int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y,
                       void* d_workspace, size_t workspace_bytes, const tnns_shape_t* s, float alpha, int layout, int pack_algo,
                       int gemm_algo, void* stream) {

@@ -230,6 +230,10 @@ struct GemmArgs {
     int acc_bias;               // added to the integer dot product (BNN: K_unpack - 64*Kp)
     float alpha;
     unsigned int* status;
+    // optional quantised output for a following layer (instead of y): bit planes [n][plane][pixel][ic]
+    uint32_t* pimg;
+    const float* thr_next;      // one threshold per image for that quantisation
+    int next_ternary, cp_next;  // planes of the next layer's activations, its 64-channel groups
 };
 
 template <int BN, int MT, bool F4>
@@ -420,6 +424,7 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
             const long long n_img = row_ok ? row / p.OHW : 0;
             const int rem = (int)(row - n_img * p.OHW);
             float* ybase = (p.layout == TNNS_NHWC) ? p.y + (size_t)row * p.KN : p.y + (size_t)n_img * p.KN * p.OHW + rem;
+            const float tq = (p.pimg && row_ok) ? __ldg(p.thr_next + n_img) + 0.0f : 0.f;  // + 0.0f: -0 acts as +0
 #pragma unroll 1
             for (int cb = ecol * ECOLS; cb < (ecol + 1) * ECOLS; cb += 32) {
                 uint32_t v[32];
@@ -452,7 +457,30 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
                     }
                     const int c0 = n0 + cb;
                     const bool full = c0 + 32 <= p.KN;
-                    if (p.layout == TNNS_NHWC) {
+                    if (p.pimg) {
+                        // Quantise the 32 channels this thread holds for its pixel straight into one
+                        // 32-bit lane of the next layer's bit planes (same rules as the pack kernel:
+                        // sign = f < -t, non-zero = |f| > t; binary: f < t), channels past KN absent.
+                        if (c0 < p.cp_next * 64) {
+                            uint32_t sg = 0, nz = 0;
+#pragma unroll
+                            for (int j = 31; j >= 0; j--) {
+                                if (p.next_ternary) {
+                                    sg = __funnelshift_l(__float_as_uint(f[j] + tq), sg, 1);
+                                    nz = __funnelshift_l(__float_as_uint(tq - fabsf(f[j])), nz, 1);
+                                } else {
+                                    sg = __funnelshift_l(__float_as_uint((f[j] + 0.0f) - tq), sg, 1);
+                                }
+                            }
+                            const int have = p.KN - c0;
+                            const uint32_t valid = have >= 32 ? 0xFFFFFFFFu : (have > 0 ? (1u << have) - 1u : 0u);
+                            const int planes = p.next_ternary ? 2 : 1;
+                            const size_t lanes = (size_t)p.cp_next * 2;  // 32-bit lanes per pixel and plane
+                            uint32_t* px = p.pimg + ((size_t)n_img * planes * p.OHW + rem) * lanes + (c0 >> 5);
+                            px[0] = sg & valid;
+                            if (p.next_ternary) px[(size_t)p.OHW * lanes] = ~(nz & valid);
+                        }
+                    } else if (p.layout == TNNS_NHWC) {
                         if (full && (p.KN & 3) == 0) {
 #pragma unroll
                             for (int j = 0; j < 32; j += 4)
@@ -543,7 +571,7 @@ int tnns_build_i8_weights(tnns_cuda_ctx* ctx, tnns_cuda_weights* w) {
 }
 
 int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_a, float* d_y, long long M, int OHW, float alpha,
-                        int layout, bool f4, cudaStream_t stream) {
+                        int layout, bool f4, cudaStream_t stream, void* d_pimg, const float* d_thr_next, int next_ternary) {
     if (M == 0) return TNNS_OK;
     const void* img = f4 ? (const void*)w->d_f4 : (const void*)w->d_i8;
     if (!img) return tnns_fail(TNNS_ERR_UNSUPPORTED, "weights carry no tensor-core operand image");
@@ -561,6 +589,10 @@ int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const vo
     a.acc_bias = (w->type == BNN) ? w->K_unpack - 64 * w->Kp : 0;
     a.alpha = alpha;
     a.status = ctx->d_status;
+    a.pimg = reinterpret_cast<uint32_t*>(d_pimg);
+    a.thr_next = d_thr_next;
+    a.next_ternary = next_ternary;
+    a.cp_next = (w->KN + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS;
     const int bn = tnns_i8_tile_n(w->KN);
     if (f4) {
         switch (bn) {

@@ -74,8 +74,11 @@ int tnns_launch_gemm_popc(tnns_cuda_ctx* ctx, int type, const void* d_a, const v
 // tensor-core path (gemm_i8_tc.cu)
 int tnns_i8_tile_n(int KN);
 int tnns_build_i8_weights(tnns_cuda_ctx* ctx, tnns_cuda_weights* w);
+// d_pimg != NULL: write the next layer's quantised bit planes instead of fp32 (d_y unused)
 int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_a, float* d_y, long long M, int OHW, float alpha,
-                        int layout, bool f4, cudaStream_t stream);
+                        int layout, bool f4, cudaStream_t stream, void* d_pimg = nullptr, const float* d_thr_next = nullptr,
+                        int next_ternary = 1);
+#define TNNS_SRC_PACKED_IMAGE 2  // internal "layout" of tnns_launch_pack: input is already bit planes
 
 // Division by a runtime-constant divisor without the hardware divide sequence.
 // Exact for every 32-bit unsigned numerator (Granlund-Montgomery round-up method).

@@ -84,6 +84,8 @@ __global__ void __launch_bounds__(256) pack_gather_kernel(const float* __restric
 // LAYOUT 0: NCHW, one thread packs VEC neighbouring pixels over 64 channels (loads are
 //           coalesced along W, channel stride H*W).
 // LAYOUT 1: NHWC, one warp packs 32 neighbouring channels of a pixel with __ballot_sync.
+// LAYOUT 2: the input is already quantised bit planes [n][plane][pixel][ic] (written by the GEMM
+//           epilogue of the previous layer); phase 1 is a plain copy of the band's rows.
 // PAIR:     C_pack is even, so plane words 2k and 2k+1 of a row are neighbours in shared
 //           memory and move as one 128-bit load.
 // ---------------------------------------------------------------------------------------
@@ -149,7 +151,7 @@ pack_staged_kernel(const float* __restrict__ x, const float* __restrict__ thr, u
     const int ih_hi = min((oh0 + boh - 1) * g.SH - g.PH + g.KH, g.H);  // exclusive
     const int nrow = max(ih_hi - ih_lo, 0);                              // input rows held in smem
     const int L = nrow * g.W;                                            // pixels held in smem
-    const float t = thr[n] + 0.0f, nt = -t;  // + 0.0f: a threshold of -0 behaves as +0 in every compare
+    const float t = (LAYOUT == 2) ? 0.f : thr[n] + 0.0f, nt = -t;  // + 0.0f: a threshold of -0 behaves as +0 in every compare
 
     for (int j = tid; j < g.Kp; j += kPackThreads) {
         int off = kPadWord;
@@ -164,7 +166,16 @@ pack_staged_kernel(const float* __restrict__ x, const float* __restrict__ thr, u
     }
 
     // ---------------- phase 1: quantise + pack the band's input pixels ----------------
-    if (LAYOUT == 0) {
+    if (LAYOUT == 2) {
+        const uint64_t* planes = reinterpret_cast<const uint64_t*>(x);
+        const size_t HWC = (size_t)g.H * g.W * g.Cp;
+        const uint64_t* src_s = planes + (size_t)n * PLANES * HWC + (size_t)ih_lo * g.W * g.Cp;
+        const int words = L * g.Cp;
+        for (int i = tid; i < words; i += kPackThreads) {
+            sm_sign[i] = __ldg(src_s + i);
+            if (TERNARY) sm_zero[i] = __ldg(src_s + HWC + i);
+        }
+    } else if (LAYOUT == 0) {
         const size_t HW = (size_t)g.H * g.W;
         const int LV = L / VEC;  // VEC divides L by construction (host checks W % VEC == 0)
         const int items = g.Cp * LV;
@@ -348,7 +359,8 @@ int tnns_launch_pack(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const f
                      const TnnsGeom& g, int layout, int algo, cudaStream_t stream) {
     const long long rows = (long long)g.N * g.OH * g.OW;
     if (rows == 0) return TNNS_OK;
-    if (layout != TNNS_NCHW && layout != TNNS_NHWC) return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
+    if (layout != TNNS_NCHW && layout != TNNS_NHWC && layout != TNNS_SRC_PACKED_IMAGE)
+        return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
     // An NCHW tensor with one pixel per image is bit-identical to its NHWC form; the
     // channel-contiguous kernel is the coalesced one for it (fully-connected layers).
     int eff_layout = layout;
@@ -378,7 +390,7 @@ int tnns_launch_pack(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const f
             if ((unsigned long long)BOH * g.OW * g.Kp >= (1ull << 31)) staged_ok = false;
         }
     }
-    if (algo == TNNS_PACK_STAGED && !staged_ok)
+    if ((algo == TNNS_PACK_STAGED || layout == TNNS_SRC_PACKED_IMAGE) && !staged_ok)
         return tnns_fail(TNNS_ERR_UNSUPPORTED, "staged pack kernel cannot hold this geometry in shared memory");
     const bool use_staged = (algo == TNNS_PACK_STAGED) || (algo == TNNS_PACK_AUTO && staged_ok);
 
@@ -398,6 +410,9 @@ int tnns_launch_pack(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const f
         return TNNS_OK;
     }
 
+    if (layout == TNNS_SRC_PACKED_IMAGE)
+        return ternary ? launch_staged<true, 2, 1>(ctx, d_x, d_thr, d_packed, g, BOH, Lmax, smem, stream)
+                       : launch_staged<false, 2, 1>(ctx, d_x, d_thr, d_packed, g, BOH, Lmax, smem, stream);
     if (eff_layout == TNNS_NHWC) {
         return ternary ? launch_staged<true, 1, 1>(ctx, d_x, d_thr, d_packed, g, BOH, Lmax, smem, stream)
                        : launch_staged<false, 1, 1>(ctx, d_x, d_thr, d_packed, g, BOH, Lmax, smem, stream);

@@ -1,7 +1,11 @@
 """Chained layers on the device: the output of one layer is the next layer's input, as the
 reference's end-to-end timing mode does on the host (src/timing_layers.c:188-201 of the
 reference: ``test->input = test->output`` between layers).  Activations stay in HBM as fp32
-in the chosen layout; every layer re-quantises its input with its own thresholds."""
+in the chosen layout; every layer re-quantises its input with its own thresholds.
+
+``chain="packed"`` removes that fp32 round trip: every layer but the last runs its GEMM with
+the quantising epilogue (``tnns_cuda_gemm_packed_out``) and the next layer starts from the bit
+planes (``tnns_cuda_im2row_packed``); the final fp32 output is bit-identical."""
 from __future__ import annotations
 
 import numpy as np
@@ -12,7 +16,7 @@ from .workloads import Layer
 
 class ConvStack:
     def __init__(self, ctx: api.Context, type_: int, layers: list[Layer], packed_weights: list[np.ndarray], batch: int,
-                 threshold: float, alpha: float = 0.5, layout: int = api.NCHW):
+                 threshold: float, alpha: float = 0.5, layout: int = api.NCHW, chain: str = "fp32"):
         assert len(layers) == len(packed_weights)
         for a, b in zip(layers, layers[1:]):
             if (a.KN, a.OH, a.OW) != (b.C, b.H, b.W):
@@ -24,15 +28,42 @@ class ConvStack:
         big = max(sizes) * 4
         self.buf = [ctx.malloc(big), ctx.malloc(big)]  # ping-pong activation buffers
         self.d_thr = ctx.to_device(np.full(batch, threshold, np.float32))
+        self.chain = chain
+        self.act_ternary = type_ in (api.TNN, api.TBN)
+        self.extra = []
+        if chain == "packed":
+            if layout != api.NCHW:
+                raise ValueError("the packed chain is defined for NCHW input and output")
+            img = max(api.packed_image_bytes(self.act_ternary, batch, L.KN, L.OH, L.OW) for L in layers)
+            a = max(api.packed_bytes(type_, L.shape(batch)) for L in layers)
+            self.d_img = ctx.malloc(img)
+            self.d_a = ctx.malloc(a)
+            self.extra = [self.d_img, self.d_a]
+        elif chain != "fp32":
+            raise ValueError(chain)
 
     def input_ptr(self) -> int:
         return self.buf[0]
 
     def output_ptr(self) -> int:
-        return self.buf[len(self.layers) % 2]
+        return self.buf[1] if self.chain == "packed" else self.buf[len(self.layers) % 2]
 
     def run(self, stream: int = 0):
         """Enqueue all layers; input must already be in input_ptr()."""
+        if self.chain == "packed":
+            last = len(self.layers) - 1
+            for i, (L, w) in enumerate(zip(self.layers, self.weights)):
+                shape = L.shape(self.batch)
+                if i == 0:
+                    self.ctx.pack(self.act_ternary, self.buf[0], self.d_thr, self.d_a, shape, self.layout, stream=stream)
+                else:
+                    self.ctx.im2row_packed(self.act_ternary, self.d_img, self.d_a, shape, stream=stream)
+                if i < last:
+                    self.ctx.gemm_packed_out(w, self.d_a, self.d_img, self.d_thr, self.act_ternary, self.batch, L.OH, L.OW, self.alpha,
+                                             stream=stream)
+                else:
+                    self.ctx.gemm(w, self.d_a, self.buf[1], self.batch, L.OH, L.OW, self.alpha, self.layout, stream=stream)
+            return
         for i, (L, w) in enumerate(zip(self.layers, self.weights)):
             self.ctx.conv(w, self.buf[i % 2], self.d_thr, self.buf[(i + 1) % 2], L.shape(self.batch), self.alpha, self.layout,
                           stream=stream)
@@ -43,5 +74,5 @@ class ConvStack:
     def close(self):
         for w in self.weights:
             w.free()
-        for p in self.buf + [self.d_thr]:
+        for p in self.buf + [self.d_thr] + self.extra:
             self.ctx.free(p)

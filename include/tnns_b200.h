@@ -223,6 +223,25 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
                       float* d_y, void* d_workspace, size_t workspace_bytes, const tnns_shape_t* s, float alpha,
                       int layout, int pack_algo, int gemm_algo, void* stream);
 
+/* Chained layers without the fp32 round trip (the reference chains layers through fp32 host
+ * buffers, src/timing_layers.c:188-201; every layer re-quantises its input).  Between two
+ * layers only the quantised activations matter, so the GEMM can emit them directly:
+ *
+ *   "packed image" of an N x C x H x W activation tensor: bit planes [n][plane][pixel][ic] of
+ *   64-bit words, pixel = ih*W + iw, ic = 64-channel group, plane 0 sign, plane 1 zero (ternary
+ *   only), same bit meaning as the packed layouts above; tnns_packed_image_bytes() bytes.
+ *
+ * tnns_cuda_gemm_packed_out: GEMM + PReLU of the current layer whose epilogue quantises each
+ * output with d_thr_next[n] (ternary: sign = y < -t, zero = !(y < -t || y > t); binary: y < t)
+ * and writes the packed image of the N x KN x OH x OW result -- bit-identical to packing the fp32
+ * output.  tnns_cuda_im2row_packed: packed image -> im2row matrix of the next layer (the same
+ * bytes tnns_cuda_pack would produce from the fp32 tensor).  Both asynchronous. */
+size_t tnns_packed_image_bytes(int ternary, int N, int C, int H, int W);
+int tnns_cuda_gemm_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const int64_t* d_a, void* d_image,
+                              const float* d_thr_next, int next_ternary, int N, int OH, int OW, float alpha, void* stream);
+int tnns_cuda_im2row_packed(tnns_cuda_ctx* ctx, int ternary, const void* d_image, int64_t* d_packed, const tnns_shape_t* s,
+                            void* stream);
+
 /* Whole layer with HOST input / output buffers (pinned memory gives full PCIe speed):
  * the batch is cut into slices whose upload, kernels and download overlap on three
  * streams.  Synchronous: returns when h_y is complete. */

@@ -251,11 +251,53 @@ def test_resnet18_style_stack_chained_on_device(gpu_ctx, checker):
     want = x
     for L, pw in zip(RESNET18_STACK, pws):
         want = checker.conv(TNN, want, thr, pw, (L.KH, L.KW), (L.P, L.P), (L.S, L.S), 0.5)
-    st = ConvStack(gpu_ctx, TNN, RESNET18_STACK, pws, N, 0.25)
-    gpu_ctx.lib.tnns_cuda_memcpy_h2d(gpu_ctx.handle, st.input_ptr(), x.ctypes.data, x.nbytes)
-    st.run()
-    gpu_ctx.sync()
-    got = gpu_ctx.to_host(st.output_ptr(), want.shape, np.float32)
-    st.close()
-    assert got.tobytes() == want.tobytes()
-    assert np.count_nonzero(got) > 0
+    for chain in ("fp32", "packed"):
+        st = ConvStack(gpu_ctx, TNN, RESNET18_STACK, pws, N, 0.25, chain=chain)
+        gpu_ctx.lib.tnns_cuda_memcpy_h2d(gpu_ctx.handle, st.input_ptr(), x.ctypes.data, x.nbytes)
+        st.run()
+        gpu_ctx.sync()
+        got = gpu_ctx.to_host(st.output_ptr(), want.shape, np.float32)
+        st.close()
+        assert got.tobytes() == want.tobytes(), chain
+        assert np.count_nonzero(got) > 0
+
+
+@pytest.mark.parametrize("type_", [TNN, TBN, BTN, BNN])
+def test_quantising_epilogue_and_packed_im2row(type_, gpu_ctx, checker):
+    """Two chained layers with the intermediate kept as bit planes: the im2row matrix built from the
+    GEMM's quantised output equals the checker's pack of the fp32 intermediate, and the second
+    layer's fp32 output equals the checker's.  Kernel counts 100 and 40 leave ragged 32- and
+    64-channel tails in the planes; per-image thresholds differ."""
+    l1, l2 = Layer(96, 10, 9, 100, 3, 3, 1, 1), Layer(100, 10, 9, 40, 3, 3, 1, 2)
+    c1 = make_case(type_, l1, 3, 700 + type_, "uniform")
+    c2 = make_case(type_, l2, 3, 710 + type_, "uniform")
+    tern = act_ternary(type_)
+    thr2 = np.array([0.25, 3.0, 0.0], np.float32) if tern else np.array([0.0, -2.0, 1.5], np.float32)
+    w1 = checker.pack_weights(wgt_ternary(type_), c1.w, c1.w_thr)
+    w2 = checker.pack_weights(wgt_ternary(type_), c2.w, c2.w_thr)
+    y1 = checker.conv(type_, c1.x, c1.thr, w1, c1.kernel_hw, c1.padding, c1.stride, 0.5)
+    a2_ref = checker.pack(tern, y1, thr2, c2.kernel_hw, c2.padding, c2.stride)
+    y2_ref = checker.conv(type_, y1, thr2, w2, c2.kernel_hw, c2.padding, c2.stride, 0.5)
+    ctx = gpu_ctx
+    W1 = ctx.upload_weights(type_, w1, l1.C, l1.KH, l1.KW)
+    W2 = ctx.upload_weights(type_, w2, l2.C, l2.KH, l2.KW)
+    s1, s2 = l1.shape(3), l2.shape(3)
+    d_x, d_t1, d_t2 = ctx.to_device(c1.x), ctx.to_device(c1.thr), ctx.to_device(thr2)
+    d_a1 = ctx.malloc(ft.packed_bytes(type_, s1))
+    d_img = ctx.malloc(ft.api.packed_image_bytes(tern, 3, l1.KN, l1.OH, l1.OW))
+    d_a2 = ctx.malloc(ft.packed_bytes(type_, s2))
+    d_y2 = ctx.malloc(y2_ref.nbytes)
+    try:
+        ctx.pack(tern, d_x, d_t1, d_a1, s1)
+        ctx.gemm_packed_out(W1, d_a1, d_img, d_t2, tern, 3, l1.OH, l1.OW, 0.5)
+        ctx.im2row_packed(tern, d_img, d_a2, s2)
+        ctx.gemm(W2, d_a2, d_y2, 3, l2.OH, l2.OW, 0.5)
+        ctx.sync()
+        a2 = ctx.to_host(d_a2, a2_ref.shape, np.int64)
+        assert np.array_equal(a2, a2_ref)
+        assert ctx.to_host(d_y2, y2_ref.shape, np.float32).tobytes() == y2_ref.tobytes()
+    finally:
+        for p in (d_x, d_t1, d_t2, d_a1, d_img, d_a2, d_y2):
+            ctx.free(p)
+        W1.free()
+        W2.free()
