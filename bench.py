@@ -240,7 +240,10 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
     shape = layer.shape(nloc)
     OH, OW = layer.OH, layer.OW
     in_bytes, out_bytes = x_h.nbytes, nloc * layer.KN * OH * OW * 4
-    pack_bytes = ft.packed_bytes(ft.TNN, shape)
+    # default route (what tnns_cuda_conv does): quantise to a packed image, GEMM gathers its im2row
+    # rows itself; --route explicit: pack to the im2row matrix (t2r_p2_opt's job), then GEMM
+    implicit = args.route == "implicit" and args.gemm in ("auto", "f4tc")
+    pack_bytes = ft.api.packed_image_bytes(True, nloc, layer.C, layer.H, layer.W) if implicit else ft.packed_bytes(ft.TNN, shape)
 
     # ring of distinct buffer sets so that consecutive steps never find their data in L2
     step_bytes = in_bytes + out_bytes + pack_bytes
@@ -266,10 +269,16 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
         r = i % ring
         if ev:
             ev[0].record(stream)
-        ctx.pack(True, xs[r].data_ptr(), thr_d.data_ptr(), ps[r].data_ptr(), shape, layout, ft.PACK_AUTO, sp)
+        if implicit:
+            ctx.quantise(True, xs[r].data_ptr(), thr_d.data_ptr(), ps[r].data_ptr(), nloc, layer.C, layer.H, layer.W, layout, sp)
+        else:
+            ctx.pack(True, xs[r].data_ptr(), thr_d.data_ptr(), ps[r].data_ptr(), shape, layout, ft.PACK_AUTO, sp)
         if ev:
             ev[1].record(stream)
-        ctx.gemm(w, ps[r].data_ptr(), ys[r].data_ptr(), nloc, OH, OW, 0.5, layout, gemm_algo, sp)
+        if implicit:
+            ctx.gemm_implicit(w, ps[r].data_ptr(), ys[r].data_ptr(), shape, 0.5, layout, sp)
+        else:
+            ctx.gemm(w, ps[r].data_ptr(), ys[r].data_ptr(), nloc, OH, OW, 0.5, layout, gemm_algo, sp)
         if ev:
             ev[2].record(stream)
 
@@ -314,8 +323,12 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
 
         def fstep(i):
             r = i % ring
-            ctx.pack(True, xs[r].data_ptr(), thr_d.data_ptr(), ps[r].data_ptr(), fshape, layout, ft.PACK_AUTO, sp)
-            ctx.gemm(w, ps[r].data_ptr(), ys[r].data_ptr(), nfix, OH, OW, 0.5, layout, gemm_algo, sp)
+            if implicit:
+                ctx.quantise(True, xs[r].data_ptr(), thr_d.data_ptr(), ps[r].data_ptr(), nfix, layer.C, layer.H, layer.W, layout, sp)
+                ctx.gemm_implicit(w, ps[r].data_ptr(), ys[r].data_ptr(), fshape, 0.5, layout, sp)
+            else:
+                ctx.pack(True, xs[r].data_ptr(), thr_d.data_ptr(), ps[r].data_ptr(), fshape, layout, ft.PACK_AUTO, sp)
+                ctx.gemm(w, ps[r].data_ptr(), ys[r].data_ptr(), nfix, OH, OW, 0.5, layout, gemm_algo, sp)
 
         for i in range(args.warmup):
             fstep(i)
@@ -363,7 +376,7 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
         gemm_tops = ops_loc / (t_gemm * 1e-3) / 1e12
         per_img = NCU_TRAFFIC_PER_IMAGE.get((name, {"popc": "popc", "i8tc": "tc"}.get(args.gemm, "f4")))
         gemm_traffic = per_img * nloc if per_img else None
-        per_img = NCU_TRAFFIC_PER_IMAGE.get((name, "pack"))
+        per_img = NCU_TRAFFIC_PER_IMAGE.get((name, "quantise" if implicit else "pack"))
         pack_traffic = per_img * nloc if per_img else None
         if args.gemm == "popc":
             # integer-pipe kernel: 5.5 LOP3 per 32-bit lane and output, LOP3 issues 64 lanes/clk/SM
@@ -387,10 +400,11 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
             "data": "synthetic",
             "config": {"workload": name, "batch": N_total, "batch_per_gpu": nloc, "layer": str(layer), "layout": "NCHW",
                        "M": N_total * OH * OW, "K": layer.C * layer.KH * layer.KW, "N": layer.KN, "gemm": args.gemm,
+                       "route": "quantise -> GEMM with implicit im2row" if implicit else "pack (im2row matrix) -> GEMM",
                        "l2": f"ring of {ring} distinct input/workspace/output buffer sets ({ring * step_bytes >> 20} MiB) cycled "
                              f"between steps; one set alone is {step_bytes >> 20} MiB"},
             "gpu_launches": int(launches * world),
-            "kernels_ms": {"pack": t_pack, "gemm": t_gemm},
+            "kernels_ms": {("quantise" if implicit else "pack"): t_pack, "gemm": t_gemm},
             # dominant kernel: the GEMM.  Its roof is the tensor pipe; the int8 rate of this part is
             # twice its bf16 rate, and bf16 is what MEASURED_PEAKS.json holds (cuBLAS, burst figure
             # for a kernel timed alone), so peak = 2 x measured bf16.
@@ -399,7 +413,7 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
                 "frac": gemm_tops / gemm_peak, "traffic": gemm_traffic, "peak_source": gemm_peak_source,
                 "algorithmic_ops_per_launch": ops_loc, "ms_per_launch": t_gemm},
             "roofline_pack": {
-                "kernel": "pack_staged_kernel (quantise + bit-pack + im2row)", "bound": "hbm",
+                "kernel": ("pack_staged_kernel<IMG_OUT> (quantise + bit-pack to a packed image)" if implicit else "pack_staged_kernel (quantise + bit-pack + im2row)"), "bound": "hbm",
                 "achieved": pack_alg_bytes / (t_pack * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": pack_alg_bytes / (t_pack * 1e-3) / 1e9 / pk["hbm_gbs"], "traffic": pack_traffic, "peak_source": pk["source"],
                 "algorithmic_bytes_per_launch": pack_alg_bytes, "ms_per_launch": t_pack},
@@ -427,6 +441,9 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="tnn_conv_large")
     ap.add_argument("--gemm", choices=["auto", "popc", "i8tc", "f4tc"], default="auto")
+    ap.add_argument("--route", choices=["implicit", "explicit"], default="implicit",
+                    help="implicit: quantise + GEMM gathering its own im2row rows (the library's default layer route); "
+                         "explicit: pack to the im2row matrix, then GEMM")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
                     help="weak: every rank processes the configured batch; strong: the configured batch is split over the ranks")
     ap.add_argument("--no-check", action="store_true", help="skip the pre-timing comparison with the CPU checker")

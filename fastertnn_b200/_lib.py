@@ -79,6 +79,8 @@ SIGNATURES = {
     "tnns_cuda_conv": (_i, [_vp, _vp, _vp, _vp, _vp, _pshape, _f, _i, _i, _i, _vp]),
     "tnns_cuda_conv_ws": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _pshape, _f, _i, _i, _i, _vp]),
     "tnns_packed_image_bytes": (_sz, [_i, _i, _i, _i, _i]),
+    "tnns_cuda_quantise": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
+    "tnns_cuda_gemm_implicit": (_i, [_vp, _vp, _vp, _vp, _pshape, _f, _i, _vp]),
     "tnns_cuda_gemm_packed_out": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
     "tnns_cuda_im2row_packed": (_i, [_vp, _i, _vp, _vp, _pshape, _vp]),
     "tnns_cuda_conv_host": (_i, [_vp, _vp, _vp, _vp, _vp, _pshape, _f, _i]),

@@ -279,6 +279,14 @@ class Context:
         _check(self.lib.tnns_cuda_conv_ws(self.handle, w.handle, d_x, d_thr, d_y, d_ws, ws_bytes, C.byref(shape), alpha, layout,
                                           pack_algo, gemm_algo, stream))
 
+    def quantise(self, ternary: bool, d_x: int, d_thr: int, d_image: int, N: int, C_: int, H: int, W: int, layout=NCHW, stream=0):
+        """fp32 tensor -> packed image (bit planes [n][plane][pixel][ic])."""
+        _check(self.lib.tnns_cuda_quantise(self.handle, int(ternary), d_x, d_thr, d_image, N, C_, H, W, layout, stream))
+
+    def gemm_implicit(self, w: Weights, d_image: int, d_y: int, shape: Shape, alpha: float, layout=NCHW, stream=0):
+        """GEMM + PReLU gathering its im2row rows from the packed image of the layer input."""
+        _check(self.lib.tnns_cuda_gemm_implicit(self.handle, w.handle, d_image, d_y, C.byref(shape), alpha, layout, stream))
+
     def gemm_packed_out(self, w: Weights, d_a: int, d_image: int, d_thr_next: int, next_ternary: bool, N: int, OH: int, OW: int,
                         alpha: float, stream=0):
         """GEMM + PReLU whose epilogue writes the next layer's quantised bit planes instead of fp32."""

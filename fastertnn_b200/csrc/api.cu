@@ -230,6 +230,7 @@ void tnns_cuda_free_weights(tnns_cuda_ctx* ctx, tnns_cuda_weights* w) {
     if (w->d_packed) cudaFree(w->d_packed);
     if (w->d_i8) cudaFree(w->d_i8);
     if (w->d_f4) cudaFree(w->d_f4);
+    if (w->d_jtab) cudaFree(w->d_jtab);
     delete w;
 }
 
@@ -279,6 +280,30 @@ int tnns_cuda_gemm(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const int64_t
     }
 }
 
+// --- quantise only, and the GEMM that gathers its own im2row rows -----------------------------------
+int tnns_cuda_quantise(tnns_cuda_ctx* ctx, int ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
+                       int W, int layout, void* stream) {
+    if (!ctx || !d_x || !d_thr || !d_image) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    if (N < 0 || C <= 0 || H <= 0 || W <= 0) return tnns_fail(TNNS_ERR_INVALID, "non-positive dimension");
+    if (reinterpret_cast<uintptr_t>(d_image) & 31) return tnns_fail(TNNS_ERR_INVALID, "image must be 32-byte aligned");
+    return tnns_launch_quantise(ctx, ternary != 0, d_x, d_thr, d_image, N, C, H, W, layout, (cudaStream_t)stream);
+}
+
+int tnns_cuda_gemm_implicit(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const tnns_shape_t* s,
+                            float alpha, int layout, void* stream) {
+    if (!ctx || !w || !d_image || !d_y) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    TnnsGeom g;
+    int rc = tnns_make_geom(s, &g);
+    if (rc) return rc;
+    if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW)
+        return tnns_fail(TNNS_ERR_INVALID, "shape does not match the uploaded weights");
+    if (layout != TNNS_NCHW && layout != TNNS_NHWC) return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
+    if (reinterpret_cast<uintptr_t>(d_image) & 31) return tnns_fail(TNNS_ERR_INVALID, "image must be 32-byte aligned");
+    if (!w->d_f4 || !w->d_jtab || w->Kp >= 65536) return tnns_fail(TNNS_ERR_UNSUPPORTED, "implicit im2row needs the 4-bit tensor-core GEMM");
+    return tnns_launch_gemm_tc(ctx, w, d_image, d_y, (long long)g.N * g.OH * g.OW, g.OH * g.OW, alpha, layout, true, (cudaStream_t)stream,
+                               nullptr, nullptr, 1, &g);
+}
+
 // --- chained layers without the fp32 round trip ------------------------------------------------
 size_t tnns_packed_image_bytes(int ternary, int N, int C, int H, int W) {
     if (N < 0 || C <= 0 || H <= 0 || W <= 0) return 0;
@@ -322,6 +347,19 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
     const size_t need = tnns_packed_bytes(w->type, s);
     if (workspace_bytes < need) return tnns_fail(TNNS_ERR_INVALID, "workspace of %zu bytes, need %zu", workspace_bytes, need);
     if (g.N == 0) return TNNS_OK;
+    // Default route: quantise the input once into a packed image (1/16 of the fp32 bytes) and let
+    // the 4-bit tensor-core GEMM gather its im2row rows from it, so the KH*KW-times larger im2row
+    // matrix is never written.  Forcing a pack or GEMM algorithm selects the explicit two-kernel
+    // route (pack to the im2row matrix, then GEMM).
+    const size_t image_bytes = tnns_packed_image_bytes(type_act_ternary(w->type), g.N, g.C, g.H, g.W);
+    if (pack_algo == TNNS_PACK_AUTO && (gemm_algo == TNNS_GEMM_AUTO || gemm_algo == TNNS_GEMM_F4_TC) && w->d_f4 && w->d_jtab &&
+        w->Kp < 65536 && image_bytes <= workspace_bytes) {
+        if (reinterpret_cast<uintptr_t>(d_workspace) & 31) return tnns_fail(TNNS_ERR_INVALID, "workspace must be 32-byte aligned");
+        rc = tnns_launch_quantise(ctx, type_act_ternary(w->type), d_x, d_thr, d_workspace, g.N, g.C, g.H, g.W, layout, (cudaStream_t)stream);
+        if (rc) return rc;
+        return tnns_launch_gemm_tc(ctx, w, d_workspace, d_y, (long long)g.N * g.OH * g.OW, g.OH * g.OW, alpha, layout, true,
+                                   (cudaStream_t)stream, nullptr, nullptr, 1, &g);
+    }
     rc = tnns_cuda_pack(ctx, type_act_ternary(w->type), d_x, d_thr, (int64_t*)d_workspace, s, layout, pack_algo, stream);
     if (rc) return rc;
     return tnns_cuda_gemm(ctx, w, (const int64_t*)d_workspace, d_y, g.N, g.OH, g.OW, alpha, layout, gemm_algo, stream);

@@ -27,6 +27,7 @@
 // activations and weights go through the same routine, so the permutation cancels in the dot
 // product.
 #include <algorithm>
+#include <vector>
 
 #include "internal.h"
 
@@ -234,6 +235,11 @@ struct GemmArgs {
     uint32_t* pimg;
     const float* thr_next;      // one threshold per image for that quantisation
     int next_ternary, cp_next;  // planes of the next layer's activations, its 64-channel groups
+    // optional implicit im2row (4-bit form): A is not a packed im2row matrix but the quantised
+    // image [n][plane][pixel][ic] of the layer input; row r, plane word j are gathered on the fly
+    const uint64_t* img;
+    const uint32_t* jtab;       // per plane word j: kh<<24 | kw<<16 | ic, 0xFFFFFFFF for pad words
+    int H, W, OW, Cp, SH, SW, PH, PW;
 };
 
 template <int BN, int MT, bool F4>
@@ -361,8 +367,67 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
         long long pf_t = blockIdx.x;
         int pf_c = grp;
         while (pf_c >= nchunks) { pf_c -= nchunks; pf_t += gridDim.x; }
+        // implicit im2row: window origin of this thread's row in the prefetch cursor's tile
+        int im_n = 0, im_ih0 = 0, im_iw0 = 0;
+        long long im_tile = -1;
+        const size_t img_plane = (size_t)p.H * p.W * p.Cp;  // words per image and plane
+        const int img_planes = p.a_two_planes ? 2 : 1;
         auto fetch = [&](uint4 (&ds)[RW], uint4 (&dz)[RW]) {
             if (pf_t < ntiles) {
+                if (F4 && p.img) {
+                    if (im_tile != pf_t) {
+                        im_tile = pf_t;
+                        const long long row = min((pf_t / ntn) * BMT + r, p.M - 1);
+                        const long long n_img = row / p.OHW;
+                        const int rem = (int)(row - n_img * p.OHW);
+                        const int oh = rem / p.OW;
+                        im_n = (int)n_img;
+                        im_ih0 = oh * p.SH - p.PH;
+                        im_iw0 = (rem - oh * p.OW) * p.SW - p.PW;
+                    }
+                    const uint64_t* base = p.img + (size_t)im_n * img_planes * img_plane;
+                    uint64_t sw[4], zw[4];
+                    if ((p.Cp & 3) == 0) {
+                        // the four words of a stage are four neighbouring channel groups of one tap
+                        const uint32_t e = __ldg(p.jtab + 4 * pf_c);
+                        const int ih = im_ih0 + (int)(e >> 24), iw = im_iw0 + (int)((e >> 16) & 0xFF);
+                        if (ih >= 0 && ih < p.H && iw >= 0 && iw < p.W) {
+                            const uint4* src = reinterpret_cast<const uint4*>(base + ((size_t)ih * p.W + iw) * p.Cp + (e & 0xFFFF));
+                            const uint4 a0 = __ldg(src), a1 = __ldg(src + 1);
+                            ds[0] = a0; ds[1 % RW] = a1;
+                            if (p.a_two_planes) {
+                                const uint4* zsrc = reinterpret_cast<const uint4*>(reinterpret_cast<const uint64_t*>(src) + img_plane);
+                                dz[0] = __ldg(zsrc); dz[1 % RW] = __ldg(zsrc + 1);
+                            } else {
+                                dz[0] = dz[1 % RW] = make_uint4(0, 0, 0, 0);
+                            }
+                        } else {
+                            const uint32_t zf = p.a_two_planes ? 0xFFFFFFFFu : 0u;  // padding: ternary zero, binary +1
+                            ds[0] = ds[1 % RW] = make_uint4(0, 0, 0, 0);
+                            dz[0] = dz[1 % RW] = make_uint4(zf, zf, zf, zf);
+                        }
+                    } else {
+#pragma unroll
+                        for (int q = 0; q < 4; q++) {
+                            const uint32_t e = __ldg(p.jtab + 4 * pf_c + q);
+                            const int ih = im_ih0 + (int)(e >> 24), iw = im_iw0 + (int)((e >> 16) & 0xFF);
+                            sw[q] = 0;
+                            zw[q] = p.a_two_planes ? ~0ull : 0ull;
+                            if (e != 0xFFFFFFFFu && ih >= 0 && ih < p.H && iw >= 0 && iw < p.W) {
+                                const uint64_t* src = base + ((size_t)ih * p.W + iw) * p.Cp + (e & 0xFFFF);
+                                sw[q] = __ldg(src);
+                                if (p.a_two_planes) zw[q] = __ldg(src + img_plane);
+                            }
+                        }
+                        ds[0] = make_uint4((uint32_t)sw[0], (uint32_t)(sw[0] >> 32), (uint32_t)sw[1], (uint32_t)(sw[1] >> 32));
+                        ds[1 % RW] = make_uint4((uint32_t)sw[2], (uint32_t)(sw[2] >> 32), (uint32_t)sw[3], (uint32_t)(sw[3] >> 32));
+                        dz[0] = make_uint4((uint32_t)zw[0], (uint32_t)(zw[0] >> 32), (uint32_t)zw[1], (uint32_t)(zw[1] >> 32));
+                        dz[1 % RW] = make_uint4((uint32_t)zw[2], (uint32_t)(zw[2] >> 32), (uint32_t)zw[3], (uint32_t)(zw[3] >> 32));
+                    }
+                    pf_c += NG;
+                    while (pf_c >= nchunks) { pf_c -= nchunks; pf_t += gridDim.x; }
+                    return;
+                }
                 const uint4* rowp = p.A + (size_t)min((pf_t / ntn) * BMT + r, p.M - 1) * pitch;
                 if (F4) {
                     const uint4* row = rowp + (size_t)pf_c * gsz;
@@ -566,12 +631,23 @@ int tnns_build_i8_weights(tnns_cuda_ctx* ctx, tnns_cuda_weights* w) {
         tnns_count_launch();
         TNNS_CUDA_TRY(cudaGetLastError());
     }
+    // tap table for the implicit-im2row form: plane word j -> kh<<24 | kw<<16 | ic
+    if (w->C > 0 && w->KH < 256 && w->KW < 256 && w->Cp < 65536) {
+        std::vector<uint32_t> tab(w->Kp, 0xFFFFFFFFu);
+        for (int j = 0; j < w->Kw; j++) {
+            const int ic = j % w->Cp, kw = (j / w->Cp) % w->KW, kh = j / (w->Cp * w->KW);
+            tab[j] = ((uint32_t)kh << 24) | ((uint32_t)kw << 16) | (uint32_t)ic;
+        }
+        TNNS_CUDA_TRY(cudaMalloc(&w->d_jtab, tab.size() * sizeof(uint32_t)));
+        TNNS_CUDA_TRY(cudaMemcpy(w->d_jtab, tab.data(), tab.size() * sizeof(uint32_t), cudaMemcpyHostToDevice));
+    }
     TNNS_CUDA_TRY(cudaDeviceSynchronize());
     return TNNS_OK;
 }
 
 int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_a, float* d_y, long long M, int OHW, float alpha,
-                        int layout, bool f4, cudaStream_t stream, void* d_pimg, const float* d_thr_next, int next_ternary) {
+                        int layout, bool f4, cudaStream_t stream, void* d_pimg, const float* d_thr_next, int next_ternary,
+                        const TnnsGeom* implicit_geom) {
     if (M == 0) return TNNS_OK;
     const void* img = f4 ? (const void*)w->d_f4 : (const void*)w->d_i8;
     if (!img) return tnns_fail(TNNS_ERR_UNSUPPORTED, "weights carry no tensor-core operand image");
@@ -593,6 +669,17 @@ int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const vo
     a.thr_next = d_thr_next;
     a.next_ternary = next_ternary;
     a.cp_next = (w->KN + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS;
+    a.img = nullptr;
+    a.jtab = nullptr;
+    a.H = a.W = a.OW = a.Cp = a.SH = a.SW = a.PH = a.PW = 0;
+    if (implicit_geom) {
+        // d_a is the quantised image of the layer input, not an im2row matrix
+        if (!f4 || !w->d_jtab) return tnns_fail(TNNS_ERR_UNSUPPORTED, "implicit im2row needs the 4-bit tensor-core GEMM and layer geometry");
+        const TnnsGeom& g = *implicit_geom;
+        a.img = reinterpret_cast<const uint64_t*>(d_a);
+        a.jtab = w->d_jtab;
+        a.H = g.H; a.W = g.W; a.OW = g.OW; a.Cp = g.Cp; a.SH = g.SH; a.SW = g.SW; a.PH = g.PH; a.PW = g.PW;
+    }
     const int bn = tnns_i8_tile_n(w->KN);
     if (f4) {
         switch (bn) {

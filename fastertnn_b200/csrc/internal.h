@@ -49,6 +49,7 @@ struct tnns_cuda_weights {
     int i8_kchunks;       // number of 128-element K chunks in d_i8
     uint8_t* d_f4;        // e2m1 operand image for the 4-bit tensor-core GEMM (may be NULL)
     size_t f4_bytes;
+    uint32_t* d_jtab;     // plane word j -> kh<<24 | kw<<16 | ic (implicit im2row), NULL without layer geometry
 };
 
 // error plumbing (thread local)
@@ -77,8 +78,13 @@ int tnns_build_i8_weights(tnns_cuda_ctx* ctx, tnns_cuda_weights* w);
 // d_pimg != NULL: write the next layer's quantised bit planes instead of fp32 (d_y unused)
 int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_a, float* d_y, long long M, int OHW, float alpha,
                         int layout, bool f4, cudaStream_t stream, void* d_pimg = nullptr, const float* d_thr_next = nullptr,
-                        int next_ternary = 1);
+                        int next_ternary = 1, const TnnsGeom* implicit_geom = nullptr);
+// implicit_geom != NULL: d_a is the quantised image [n][plane][pixel][ic] of the layer input and
+// the kernel gathers the im2row rows itself (4-bit form only)
 #define TNNS_SRC_PACKED_IMAGE 2  // internal "layout" of tnns_launch_pack: input is already bit planes
+// quantise only: fp32 tensor -> packed image [n][plane][pixel][ic] (no im2row)
+int tnns_launch_quantise(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
+                         int W, int layout, cudaStream_t stream);
 
 // Division by a runtime-constant divisor without the hardware divide sequence.
 // Exact for every 32-bit unsigned numerator (Granlund-Montgomery round-up method).

@@ -131,7 +131,10 @@ __device__ __forceinline__ void quantise_batch(const float* __restrict__ q, size
         }
 }
 
-template <bool TERNARY, int LAYOUT, int VEC, bool PAIR>
+// IMG_OUT: stop after phase 1 and write the band's packed pixels out as they are (quantise only:
+//           the packed image [n][plane][pixel][ic] that the implicit-im2row GEMM reads); the
+//           geometry passed in is then that of a 1x1 stride-1 window, so bands have no halo.
+template <bool TERNARY, int LAYOUT, int VEC, bool PAIR, bool IMG_OUT>
 __global__ void __launch_bounds__(kPackThreads, TNNS_PACK_MINCTA)
 pack_staged_kernel(const float* __restrict__ x, const float* __restrict__ thr, uint4* __restrict__ out, TnnsGeom g,
                    int BOH, int nbands, int Lmax, FastDiv divU, FastDiv divOW, FastDiv divL) {
@@ -272,6 +275,18 @@ pack_staged_kernel(const float* __restrict__ x, const float* __restrict__ thr, u
     }
     __syncthreads();
 
+    if (IMG_OUT) {
+        uint64_t* img = reinterpret_cast<uint64_t*>(out);
+        const size_t HWC = (size_t)g.H * g.W * g.Cp;
+        uint64_t* dst_s = img + (size_t)n * PLANES * HWC + (size_t)ih_lo * g.W * g.Cp;
+        const int words = L * g.Cp;
+        for (int i = tid; i < words; i += kPackThreads) {
+            dst_s[i] = sm_sign[i];
+            if (TERNARY) dst_s[HWC + i] = sm_zero[i];
+        }
+        return;
+    }
+
     // ---------------- phase 2: emit the band's im2row rows ----------------
     // One unit = plane words (2k, 2k+1) of one output row: for a ternary row the sign pair and
     // the zero pair (two 16-byte stores 32 bytes apart), for a binary row one 16-byte store.
@@ -319,7 +334,7 @@ pack_staged_kernel(const float* __restrict__ x, const float* __restrict__ thr, u
     }
 }
 
-template <bool TERNARY, int LAYOUT, int VEC>
+template <bool TERNARY, int LAYOUT, int VEC, bool IMG_OUT = false>
 int launch_staged(tnns_cuda_ctx* ctx, const float* d_x, const float* d_thr, void* d_packed, const TnnsGeom& g, int BOH,
                   int Lmax, size_t smem, cudaStream_t stream) {
     const int nbands = (g.OH + BOH - 1) / BOH;
@@ -334,7 +349,8 @@ int launch_staged(tnns_cuda_ctx* ctx, const float* d_x, const float* d_thr, void
         TNNS_CUDA_TRY(cudaGetLastError());
         return TNNS_OK;
     };
-    return pair ? launch(pack_staged_kernel<TERNARY, LAYOUT, VEC, true>) : launch(pack_staged_kernel<TERNARY, LAYOUT, VEC, false>);
+    if (IMG_OUT) return launch(pack_staged_kernel<TERNARY, LAYOUT, VEC, false, true>);
+    return pair ? launch(pack_staged_kernel<TERNARY, LAYOUT, VEC, true, false>) : launch(pack_staged_kernel<TERNARY, LAYOUT, VEC, false, false>);
 }
 
 }  // namespace
@@ -424,4 +440,41 @@ int tnns_launch_pack(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const f
                        : launch_staged<false, 0, 4>(ctx, d_x, d_thr, d_packed, g, BOH, Lmax, smem, stream);
     return ternary ? launch_staged<true, 0, 1>(ctx, d_x, d_thr, d_packed, g, BOH, Lmax, smem, stream)
                    : launch_staged<false, 0, 1>(ctx, d_x, d_thr, d_packed, g, BOH, Lmax, smem, stream);
+}
+
+// Quantise only: fp32 tensor -> packed image.  Runs the staged kernel on the geometry of a 1x1
+// stride-1 window (one band = BOH image rows, no halo) with the IMG_OUT tail.
+int tnns_launch_quantise(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
+                         int W, int layout, cudaStream_t stream) {
+    if (N == 0) return TNNS_OK;
+    if (layout != TNNS_NCHW && layout != TNNS_NHWC) return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
+    TnnsGeom g;
+    g.N = N; g.C = C; g.H = H; g.W = W; g.KN = 1; g.KH = g.KW = 1; g.PH = g.PW = 0; g.SH = g.SW = 1;
+    g.OH = H; g.OW = W;
+    g.Cp = (C + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS;
+    g.Kw = g.Cp;
+    g.Kp = 4 * ((g.Kw + 3) / 4);
+    const int planes = ternary ? 2 : 1;
+    auto smem_for = [&](int boh) { return (size_t)planes * boh * W * g.Cp * 8 + (size_t)g.Kp * 8; };
+    if (smem_for(1) > ctx->smem_optin) return tnns_fail(TNNS_ERR_UNSUPPORTED, "one image row of %d x %d channels does not fit shared memory", W, C);
+    int BOH = H;
+    while (BOH > 1 && smem_for(BOH) > 48 * 1024) BOH = (BOH + 1) / 2;
+    // at least two blocks per SM, but never bands so small that a block's 256 threads lack an
+    // item each (an item = 4 pixels x 64 channels in the vector form)
+    while (BOH > 1 && (long long)N * ((H + BOH - 1) / BOH) < 2LL * ctx->sm_count &&
+           (long long)(BOH / 2) * W * g.Cp >= 4LL * kPackThreads)
+        BOH = (BOH + 1) / 2;
+    const int Lmax = BOH * W;
+    const size_t smem = smem_for(BOH);
+    int eff_layout = layout;
+    if (layout == TNNS_NCHW && H * W == 1) eff_layout = TNNS_NHWC;
+    if (eff_layout == TNNS_NHWC)
+        return ternary ? launch_staged<true, 1, 1, true>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream)
+                       : launch_staged<false, 1, 1, true>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream);
+    const bool vec4 = (W % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_x) & 15) == 0);
+    if (vec4)
+        return ternary ? launch_staged<true, 0, 4, true>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream)
+                       : launch_staged<false, 0, 4, true>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream);
+    return ternary ? launch_staged<true, 0, 1, true>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream)
+                   : launch_staged<false, 0, 1, true>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream);
 }

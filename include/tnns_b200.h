@@ -237,6 +237,16 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
  * output.  tnns_cuda_im2row_packed: packed image -> im2row matrix of the next layer (the same
  * bytes tnns_cuda_pack would produce from the fp32 tensor).  Both asynchronous. */
 size_t tnns_packed_image_bytes(int ternary, int N, int C, int H, int W);
+/* Quantise only: fp32 tensor in `layout` -> packed image (the first half of t2r_p2_opt / b2r,
+ * src/tnns/ternarize2row_avx2.c:438-452, src/tnns/binarize2row_avx2.c:15-22, without the
+ * im2row scatter).  d_image: tnns_packed_image_bytes() bytes, 32-byte aligned. */
+int tnns_cuda_quantise(tnns_cuda_ctx* ctx, int ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
+                       int W, int layout, void* stream);
+/* GEMM + PReLU that gathers the im2row rows of layer `s` itself from the packed image of the
+ * layer's input (implicit im2row: the KH*KW-times larger im2row matrix is never materialised).
+ * Same result as tnns_cuda_pack + tnns_cuda_gemm.  tnns_cuda_conv takes this route by default. */
+int tnns_cuda_gemm_implicit(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const tnns_shape_t* s,
+                            float alpha, int layout, void* stream);
 int tnns_cuda_gemm_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const int64_t* d_a, void* d_image,
                               const float* d_thr_next, int next_ternary, int N, int OH, int OW, float alpha, void* stream);
 int tnns_cuda_im2row_packed(tnns_cuda_ctx* ctx, int ternary, const void* d_image, int64_t* d_packed, const tnns_shape_t* s,

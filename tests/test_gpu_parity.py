@@ -301,3 +301,67 @@ def test_quantising_epilogue_and_packed_im2row(type_, gpu_ctx, checker):
             ctx.free(p)
         W1.free()
         W2.free()
+
+
+def expected_image(checker, case):
+    """Packed image [n][plane][pixel][ic] derived from the checker's 1x1 pack of the same tensor
+    (for a 1x1 window plane word j is channel group j of the pixel)."""
+    tern = act_ternary(case.type)
+    L = case.layer
+    Cp = (L.C + 63) // 64
+    rows = checker.pack(tern, case.x, case.thr, (1, 1)).view(np.uint64)          # [N*H*W][planes*Kp]
+    Kp = rows.shape[1] // (2 if tern else 1)
+    j = np.arange(Cp)
+    if tern:
+        sign = rows[:, (j // 4) * 8 + j % 4]
+        zero = rows[:, (j // 4) * 8 + j % 4 + 4]
+        img = np.stack([sign.reshape(case.N, L.H * L.W, Cp), zero.reshape(case.N, L.H * L.W, Cp)], axis=1)
+    else:
+        img = rows[:, :Cp].reshape(case.N, 1, L.H * L.W, Cp)
+    assert Kp >= Cp
+    return np.ascontiguousarray(img)
+
+
+IMPLICIT_LAYERS = [
+    Layer(256, 12, 10, 72, 3, 3, 1, 1),    # C_pack = 4: a stage is one tap, 128-bit gathers
+    Layer(512, 9, 9, 300, 3, 3, 1, 2),     # stride 2, kernel count with a tail
+    Layer(64, 11, 13, 64, 3, 3, 1, 1),     # C_pack = 1: a stage spans four taps, Kw = 9 -> pad words
+    Layer(200, 7, 7, 40, 5, 3, 2, 1),      # C_pack = 4 with a channel tail, non-square kernel, pad 2
+    Layer(130, 6, 6, 33, 2, 2, 3, 1),      # padding wider than the kernel, C_pack = 3
+    Layer(320, 1, 1, 96, 1, 1, 0, 1),      # fully connected
+]
+
+
+@pytest.mark.parametrize("type_", [TNN, TBN, BTN, BNN])
+@pytest.mark.parametrize("layer", IMPLICIT_LAYERS, ids=str)
+def test_quantise_and_implicit_im2row_gemm(type_, layer, gpu_ctx, checker):
+    """The default layer route: quantise to a packed image, then the GEMM gathers its im2row rows
+    itself.  Image against the checker's 1x1 pack, output against the checker's layer, both layouts."""
+    case = make_case(type_, layer, 3, 900 + type_, "uniform")
+    tern = act_ternary(type_)
+    wp = checker.pack_weights(wgt_ternary(type_), case.w, case.w_thr)
+    y_ref = checker.conv(type_, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
+    img_ref = expected_image(checker, case)
+    ctx = gpu_ctx
+    w = ctx.upload_weights(type_, wp, layer.C, layer.KH, layer.KW)
+    d_t = ctx.to_device(case.thr)
+    d_img = ctx.malloc(ft.api.packed_image_bytes(tern, case.N, layer.C, layer.H, layer.W))
+    d_y = ctx.malloc(y_ref.nbytes)
+    try:
+        for layout in (ft.NCHW, ft.NHWC):
+            d_x = ctx.to_device(case.x if layout == ft.NCHW else to_nhwc(case.x))
+            ctx.quantise(tern, d_x, d_t, d_img, case.N, layer.C, layer.H, layer.W, layout)
+            ctx.gemm_implicit(w, d_img, d_y, layer.shape(case.N), case.alpha, layout)
+            ctx.sync()
+            ctx.free(d_x)
+            img = ctx.to_host(d_img, img_ref.shape, np.uint64)
+            assert np.array_equal(img, img_ref), layout
+            if layout == ft.NCHW:
+                y = ctx.to_host(d_y, y_ref.shape, np.float32)
+            else:
+                y = to_nchw(ctx.to_host(d_y, (case.N, layer.OH, layer.OW, layer.KN), np.float32))
+            assert y.tobytes() == y_ref.tobytes(), layout
+    finally:
+        for p in (d_t, d_img, d_y):
+            ctx.free(p)
+        w.free()
