@@ -41,7 +41,9 @@ METRIC = "ternary conv GOPS (2*M*N*K/s)"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
 # profiles/ (large layer, 64 images per launch), kept per image so that a rank's share scales.
 NCU_TRAFFIC_PER_IMAGE = {
-    ("tnn_conv_large", "f4"): 150.9e6 / 64,
+    ("tnn_conv_large", "f4"): 86.2e6 / 64,        # implicit im2row: reads the 8.4 MB image, not the im2row matrix
+    ("tnn_conv_large", "f4_explicit"): 150.9e6 / 64,
+    ("tnn_conv_large", "quantise"): 138.7e6 / 64,
     ("tnn_conv_large", "tc"): 153.8e6 / 64,
     ("tnn_conv_large", "popc"): 419.3e6 / 64,
     ("tnn_conv_large", "pack"): 155.8e6 / 64,
@@ -374,7 +376,7 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
         ops_loc = layer.ops(nloc)
         pack_alg_bytes = in_bytes + pack_bytes
         gemm_tops = ops_loc / (t_gemm * 1e-3) / 1e12
-        per_img = NCU_TRAFFIC_PER_IMAGE.get((name, {"popc": "popc", "i8tc": "tc"}.get(args.gemm, "f4")))
+        per_img = NCU_TRAFFIC_PER_IMAGE.get((name, {"popc": "popc", "i8tc": "tc"}.get(args.gemm, "f4" if implicit else "f4_explicit")))
         gemm_traffic = per_img * nloc if per_img else None
         per_img = NCU_TRAFFIC_PER_IMAGE.get((name, "quantise" if implicit else "pack"))
         pack_traffic = per_img * nloc if per_img else None
