@@ -73,6 +73,7 @@ SIGNATURES = {
     "tnns_packed_bytes": (_sz, [_i, _pshape]),
     "tnns_cuda_upload_weights": (_i, [_vp, _i, _vp, _i, _i, _i, _i, C.POINTER(_vp)]),
     "tnns_cuda_upload_weights_packed": (_i, [_vp, _i, _vp, _i, _i, _i, C.POINTER(_vp)]),
+    "tnns_cuda_pack_weights": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _vp]),
     "tnns_cuda_free_weights": (None, [_vp, _vp]),
     "tnns_cuda_pack": (_i, [_vp, _i, _vp, _vp, _vp, _pshape, _i, _i, _vp]),
     "tnns_cuda_gemm": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _f, _i, _i, _vp]),
@@ -87,6 +88,7 @@ SIGNATURES = {
     "tnns_cuda_noalloc_scratch_bytes": (_sz, []),
     "tnns_cuda_conv_noalloc": (_i, [_i, _vp, _vp, _vp, _vp, _pshape, _f, _i, _vp]),
     "tnns_cuda_pipe_rate": (_i, [_vp, _i, C.POINTER(C.c_double)]),
+    "tnns_cuda_selftest_wait_expiry": (_i, [_vp]),
     "tnns_cuda_sync": (_i, [_vp]),
     "tnns_cuda_malloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "tnns_cuda_free": (None, [_vp, _vp]),

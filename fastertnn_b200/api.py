@@ -262,6 +262,10 @@ class Context:
         _check(self.lib.tnns_cuda_upload_weights_packed(self.handle, type_, _ptr(pk), KN, K_words, K_unpack, C.byref(h)))
         return Weights(self, h.value, type_, KN)
 
+    def pack_weights_device(self, ternary: bool, d_w: int, d_thr: int, d_packed: int, KN: int, C_: int, KH: int, KW: int, stream=0):
+        """fp32 weights on the device -> packed rows on the device (same bytes as the host packers)."""
+        _check(self.lib.tnns_cuda_pack_weights(self.handle, int(ternary), d_w, d_thr, d_packed, KN, C_, KH, KW, stream))
+
     # -- kernels on device pointers
     def pack(self, ternary: bool, d_x: int, d_thr: int, d_packed: int, shape: Shape, layout=NCHW, algo=PACK_AUTO, stream=0):
         _check(self.lib.tnns_cuda_pack(self.handle, int(ternary), d_x, d_thr, d_packed, C.byref(shape), layout, algo, stream))

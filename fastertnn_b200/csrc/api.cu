@@ -154,6 +154,15 @@ int tnns_cuda_sync(tnns_cuda_ctx* ctx) {
     return TNNS_OK;
 }
 
+// Failure-detection self-test: launches a kernel whose only mbarrier wait can never be satisfied.
+// The bounded wait gives up after about a second, the kernel returns normally, and the next
+// tnns_cuda_sync reports TNNS_ERR_DEVICE_WAIT; the context stays usable.
+int tnns_cuda_selftest_wait_expiry(tnns_cuda_ctx* ctx) {
+    if (!ctx) return tnns_fail(TNNS_ERR_INVALID, "ctx is NULL");
+    TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
+    return tnns_launch_wait_selftest(ctx, 0);
+}
+
 // --- plain memory helpers so C callers need no CUDA headers -------------------------------
 int tnns_cuda_malloc(tnns_cuda_ctx* ctx, size_t bytes, void** out) {
     if (!ctx || !out) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
@@ -198,7 +207,8 @@ static int upload_weights_impl(tnns_cuda_ctx* ctx, int type, const int64_t* pack
     w->K_unpack = K_unpack;
     w->packed_bytes = (size_t)KN * w->Kp * 8 * (type_wgt_ternary(type) ? 2 : 1);
     cudaError_t e = cudaMalloc(&w->d_packed, w->packed_bytes);
-    if (e == cudaSuccess) e = cudaMemcpy(w->d_packed, packed_host, w->packed_bytes, cudaMemcpyHostToDevice);
+    // cudaMemcpyDefault: the packed rows may live on the host or (packed by tnns_cuda_pack_weights) on a device
+    if (e == cudaSuccess) e = cudaMemcpy(w->d_packed, packed_host, w->packed_bytes, cudaMemcpyDefault);
     if (e != cudaSuccess) {
         tnns_cuda_free_weights(ctx, w);
         return tnns_fail(e == cudaErrorMemoryAllocation ? TNNS_ERR_NOMEM : TNNS_ERR_CUDA, "weight upload failed: %s",
@@ -232,6 +242,13 @@ void tnns_cuda_free_weights(tnns_cuda_ctx* ctx, tnns_cuda_weights* w) {
     if (w->d_f4) cudaFree(w->d_f4);
     if (w->d_jtab) cudaFree(w->d_jtab);
     delete w;
+}
+
+int tnns_cuda_pack_weights(tnns_cuda_ctx* ctx, int ternary, const float* d_w, const float* d_thr, int64_t* d_packed, int KN, int C,
+                           int KH, int KW, void* stream) {
+    if (!ctx || !d_w || !d_thr || !d_packed) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    if (KN <= 0 || C <= 0 || KH <= 0 || KW <= 0) return tnns_fail(TNNS_ERR_INVALID, "non-positive weight dimension");
+    return tnns_launch_pack_weights(ctx, ternary != 0, d_w, d_thr, d_packed, KN, C, KH, KW, (cudaStream_t)stream);
 }
 
 // --- kernels -----------------------------------------------------------------------------------

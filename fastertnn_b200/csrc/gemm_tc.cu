@@ -174,12 +174,16 @@ __device__ __forceinline__ void store_row_chunk(unsigned char* tile, int r, cons
 }
 
 // 32 elements -> 32 e2m1 nibbles (four words) in a fixed permuted order: nibble = sign<<3 | nonzero<<1.
+// x gathers, per nibble, the sign bits of elements 4i+3, 4i+2 (bits 3, 2) over their non-zero
+// bits (bits 1, 0); masking x with 0xA gives the nibbles of the elements 4i+3, masking x<<1 those
+// of the elements 4i+2; y does the same for 4i+1 and 4i.  Ten integer operations per 32 elements.
 __device__ __forceinline__ void expand32_f4(uint32_t s, uint32_t z, uint32_t (&w)[4]) {
-    const uint32_t nz = ~z;
-    w[0] = ((s << 3) & 0x88888888u) | ((nz << 1) & 0x22222222u);
-    w[1] = ((s << 2) & 0x88888888u) | (nz & 0x22222222u);
-    w[2] = ((s << 1) & 0x88888888u) | ((nz >> 1) & 0x22222222u);
-    w[3] = (s & 0x88888888u) | ((nz >> 2) & 0x22222222u);
+    const uint32_t x = (s & 0xCCCCCCCCu) | (~(z >> 2) & 0x33333333u);
+    const uint32_t y = ((s << 2) & 0xCCCCCCCCu) | (~z & 0x33333333u);
+    w[0] = x & 0xAAAAAAAAu;
+    w[1] = (x << 1) & 0xAAAAAAAAu;
+    w[2] = y & 0xAAAAAAAAu;
+    w[3] = (y << 1) & 0xAAAAAAAAu;
 }
 
 // 4-bit form: one row and stage = 256 elements = eight lanes per plane -> 128 bytes.
@@ -517,8 +521,15 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
                     float f[32];
 #pragma unroll
                     for (int j = 0; j < 32; j++) {
-                        const float a = F4 ? __uint_as_float(v[j]) + bias_f : __int_as_float((int)v[j] + bias_magic) - 12582912.0f;
-                        f[j] = a * (a > 0.f ? 1.0f : p.alpha);  // PReLU; a == 0 stays +0
+                        if (F4) {
+                            // max(a,0) + alpha*min(a,0): exact (one rounding, of alpha*a), and a -0 sum
+                            // comes out as +0 because max(-0,+0) is +0
+                            const float a = p.acc_bias ? __uint_as_float(v[j]) + bias_f : __uint_as_float(v[j]);
+                            f[j] = fmaf(p.alpha, fminf(a, 0.f), fmaxf(a, 0.f));
+                        } else {
+                            const float a = __int_as_float((int)v[j] + bias_magic) - 12582912.0f;
+                            f[j] = a * (a > 0.f ? 1.0f : p.alpha);  // PReLU; a == 0 stays +0
+                        }
                     }
                     const int c0 = n0 + cb;
                     const bool full = c0 + 32 <= p.KN;
@@ -583,6 +594,20 @@ done:
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
+}
+
+// Self-test of the bounded wait: one warp waits on an mbarrier that nothing ever completes.  The
+// wait gives up after its limit, raises the status word and the kernel returns normally.
+__global__ void wait_expiry_selftest_kernel(unsigned int* status) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) mbar_wait(smem_u32(&bar), 0, &abort_flag, status, 0x7F);
 }
 
 template <int BN, int MT, bool F4>
@@ -693,4 +718,11 @@ int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const vo
         case 128: return launch_bn<128, false>(ctx, a, stream);
         default: return launch_bn<256, false>(ctx, a, stream);
     }
+}
+
+int tnns_launch_wait_selftest(tnns_cuda_ctx* ctx, cudaStream_t stream) {
+    wait_expiry_selftest_kernel<<<1, 32, 0, stream>>>(ctx->d_status);
+    tnns_count_launch();
+    TNNS_CUDA_TRY(cudaGetLastError());
+    return TNNS_OK;
 }

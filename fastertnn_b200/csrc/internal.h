@@ -86,6 +86,11 @@ int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const vo
 int tnns_launch_quantise(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
                          int W, int layout, cudaStream_t stream);
 
+int tnns_launch_pack_weights(tnns_cuda_ctx* ctx, bool ternary, const float* d_w, const float* d_thr, void* d_packed, int KN, int C,
+                             int KH, int KW, cudaStream_t stream);
+
+int tnns_launch_wait_selftest(tnns_cuda_ctx* ctx, cudaStream_t stream);
+
 // Division by a runtime-constant divisor without the hardware divide sequence.
 // Exact for every 32-bit unsigned numerator (Granlund-Montgomery round-up method).
 struct FastDiv {

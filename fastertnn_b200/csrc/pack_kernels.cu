@@ -478,3 +478,58 @@ int tnns_launch_quantise(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, con
     return ternary ? launch_staged<true, 0, 1, true>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream)
                    : launch_staged<false, 0, 1, true>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream);
 }
+
+// ---------------------------------------------------------------------------------------
+// Weight packing on the device (once per model): fp32 [KN][C][KH][KW] + one threshold per
+// kernel -> packing-2 rows (ternary) or one-plane rows (binary), the layouts of
+// ternarize_opt_avx2 / binarize_opt_avx2 (reference: src/utils.c:468-521, 634-675).  One thread
+// per plane word.  Ternary decision order as in the reference: v > t is +1, else v < -t is -1,
+// else 0; channels past C are quantised as the value 0.0.
+// ---------------------------------------------------------------------------------------
+namespace {
+template <bool TERNARY>
+__global__ void pack_weights_kernel(const float* __restrict__ w, const float* __restrict__ thr, uint64_t* __restrict__ out, int KN,
+                                    int C, int KHW, int Cp, int Kw, int Kp) {
+    const long long total = (long long)KN * Kp;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (long long)gridDim.x * blockDim.x) {
+        const int kn = (int)(i / Kp), j = (int)(i - (long long)kn * Kp);
+        uint64_t sign = 0, zero = TERNARY ? ~0ull : 0ull;  // pad-to-four words are zeros of the alphabet
+        if (j < Kw) {
+            const int ic = j % Cp, tap = j / Cp;
+            const float t = thr[kn];
+            zero = 0;
+            for (int b = 0; b < TNNS_WORD_BITS; b++) {
+                const int c = ic * TNNS_WORD_BITS + b;
+                if (TERNARY) {
+                    const float v = c < C ? w[((size_t)kn * C + c) * KHW + tap] : 0.0f;
+                    if (v > t) continue;
+                    if (v < -t) sign |= 1ull << b;
+                    else zero |= 1ull << b;
+                } else if (c < C && w[((size_t)kn * C + c) * KHW + tap] < t) {
+                    sign |= 1ull << b;
+                }
+            }
+        }
+        if (TERNARY) {
+            uint64_t* row = out + (size_t)kn * 2 * Kp + (size_t)(j >> 2) * 8 + (j & 3);
+            row[0] = sign;
+            row[4] = zero;
+        } else {
+            out[(size_t)kn * Kp + j] = sign;
+        }
+    }
+}
+}  // namespace
+
+int tnns_launch_pack_weights(tnns_cuda_ctx* ctx, bool ternary, const float* d_w, const float* d_thr, void* d_packed, int KN, int C,
+                             int KH, int KW, cudaStream_t stream) {
+    const int Cp = (C + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS, Kw = KH * KW * Cp, Kp = 4 * ((Kw + 3) / 4);
+    const long long total = (long long)KN * Kp;
+    const int blocks = (int)std::min<long long>((total + 127) / 128, (long long)ctx->sm_count * 16);
+    uint64_t* o = reinterpret_cast<uint64_t*>(d_packed);
+    if (ternary) pack_weights_kernel<true><<<blocks, 128, 0, stream>>>(d_w, d_thr, o, KN, C, KH * KW, Cp, Kw, Kp);
+    else pack_weights_kernel<false><<<blocks, 128, 0, stream>>>(d_w, d_thr, o, KN, C, KH * KW, Cp, Kw, Kp);
+    tnns_count_launch();
+    TNNS_CUDA_TRY(cudaGetLastError());
+    return TNNS_OK;
+}

@@ -186,11 +186,18 @@ int tnns_k_padded(int C, int KH, int KW);             /* Kp                     
 /* Bytes of the packed im2row matrix for this type and shape. */
 size_t tnns_packed_bytes(int type, const tnns_shape_t* s);
 
-/* Copies host-packed weights (reference layout for `type`: packing-2 for TNN/BTN,
+/* Copies packed weights (host or device memory; reference layout for `type`: packing-2 for TNN/BTN,
  * one-plane for TBN/BNN) to the device and prepares the per-kernel constants and the
  * operand images the GEMM kernels need.  Done once per layer. */
 int tnns_cuda_upload_weights(tnns_cuda_ctx* ctx, int type, const int64_t* packed_host, int KN, int C, int KH,
                              int KW, tnns_cuda_weights** out);
+/* Weight packing on the device: fp32 [KN][C][KH][KW] and one threshold per kernel, both in device
+ * memory, -> packed rows in d_packed (KN * Kp * 8 bytes, doubled for ternary), the same bytes as
+ * tnns_pack_weights_ternary / _binary produce on the host (src/utils.c:468-521, 634-675).
+ * tnns_cuda_upload_weights accepts the result (its `packed` pointer may be host or device). */
+int tnns_cuda_pack_weights(tnns_cuda_ctx* ctx, int ternary, const float* d_w, const float* d_thr, int64_t* d_packed, int KN, int C,
+                           int KH, int KW, void* stream);
+
 /* Same for callers that hold only a packed operand (the mm_* functions): KN rows of
  * K_words plane words (before the pad-to-four; the buffer is Kp wide), K_unpack =
  * number of elements per row before any padding (used by BNN only).  Weights uploaded
@@ -290,6 +297,12 @@ int tnns_cuda_conv_noalloc(int type, const int64_t* d_packed_weights, const floa
 /* Blocks until all work submitted through ctx's own streams has finished and reports
  * any asynchronous error, including the on-device status word. */
 int tnns_cuda_sync(tnns_cuda_ctx* ctx);
+
+/* Self-test of the on-device failure detection: every mbarrier wait inside the kernels is bounded
+ * (about one second); this launches a one-warp kernel whose wait can never be satisfied, so that
+ * the following tnns_cuda_sync returns TNNS_ERR_DEVICE_WAIT.  The kernel returns normally and the
+ * context remains usable. */
+int tnns_cuda_selftest_wait_expiry(tnns_cuda_ctx* ctx);
 
 /* Plain device-memory helpers so that C callers need no CUDA headers.  Synchronous. */
 int tnns_cuda_malloc(tnns_cuda_ctx* ctx, size_t bytes, void** out);

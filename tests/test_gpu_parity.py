@@ -365,3 +365,55 @@ def test_quantise_and_implicit_im2row_gemm(type_, layer, gpu_ctx, checker):
         for p in (d_t, d_img, d_y):
             ctx.free(p)
         w.free()
+
+
+@pytest.mark.parametrize("case", extra_cases()[::5] + reference_test_cases(N=1, dist="uniform", max_ops=3e9)[5::7], ids=lambda c: c.name)
+def test_device_weight_packing(case, gpu_ctx, checker):
+    """fp32 weights packed on the device equal the reference's host packers byte for byte; weights
+    uploaded from that device buffer give the same layer output."""
+    case = case.build()
+    L = case.layer
+    tern = wgt_ternary(case.type)
+    w = case.w.copy()
+    w.reshape(-1)[::7] *= 0.3      # values strictly inside the thresholds, not only the alphabet
+    w.reshape(-1)[3::11] = 0.5     # and exactly on the ternary threshold
+    want = checker.pack_weights(tern, w, case.w_thr)
+    ctx = gpu_ctx
+    d_w, d_t = ctx.to_device(w), ctx.to_device(case.w_thr)
+    d_p = ctx.malloc(want.nbytes)
+    try:
+        ctx.pack_weights_device(tern, d_w, d_t, d_p, L.KN, L.C, L.KH, L.KW)
+        ctx.sync()
+        got = ctx.to_host(d_p, want.shape, np.int64)
+        assert np.array_equal(got, want)
+        h = ft.api.C.c_void_p()
+        ft.api._check(ctx.lib.tnns_cuda_upload_weights(ctx.handle, case.type, d_p, L.KN, L.C, L.KH, L.KW, ft.api.C.byref(h)))
+        wd = ft.Weights(ctx, h.value, case.type, L.KN)
+        y_ref = checker.conv(case.type, case.x, case.thr, want, case.kernel_hw, case.padding, case.stride, case.alpha)
+        d_x, d_thr = ctx.to_device(case.x), ctx.to_device(case.thr)
+        d_y = ctx.malloc(y_ref.nbytes)
+        ctx.conv(wd, d_x, d_thr, d_y, L.shape(case.N), case.alpha)
+        ctx.sync()
+        assert ctx.to_host(d_y, y_ref.shape, np.float32).tobytes() == y_ref.tobytes()
+        for p in (d_x, d_thr, d_y):
+            ctx.free(p)
+        wd.free()
+    finally:
+        for p in (d_w, d_t, d_p):
+            ctx.free(p)
+
+
+def test_bounded_wait_expiry_is_reported_and_context_survives(gpu_ctx):
+    """Every on-device wait has a limit.  A kernel whose wait nothing satisfies returns after about
+    a second with the status word set; sync reports it once, and the same context then runs a layer."""
+    ctx = gpu_ctx
+    ft.api._check(ctx.lib.tnns_cuda_selftest_wait_expiry(ctx.handle))
+    with pytest.raises(ft.TnnsError) as e:
+        ctx.sync()
+    assert e.value.status == 5 and "wait" in e.value.detail
+    ctx.sync()  # the status word was cleared: no error the second time
+    layer = Layer(64, 6, 6, 16, 3, 3, 1, 1)
+    case = make_case(TNN, layer, 2, 4321, "uniform")
+    wp = ft.pack_weights_ternary(case.w, case.w_thr)
+    y = device_conv(ctx, case, wp, ft.NCHW, ft.PACK_AUTO, ft.GEMM_AUTO)
+    assert np.isfinite(y).all() and y.shape == (2, 16, 6, 6)
