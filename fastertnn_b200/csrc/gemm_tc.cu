@@ -45,16 +45,20 @@ constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_EXP0 = 2;
 // tcgen05.mma.kind::mxf4 with every block scale equal to 1 (ue8m0 0x7F) and fp32 accumulators --
 // sums of at most 2^22 products of +-1 are exact in fp32.  A stage then covers 256 K elements in
 // the same 128 bytes per row, which halves the shared-memory traffic per multiply-accumulate and
-// doubles the tensor rate.  The block scales occupy tensor-memory columns 256.., so the
-// accumulators must fit columns 0..255.
+// doubles the tensor rate.  The block scales occupy the top 32 tensor-memory columns (480..511),
+// which leaves 480 columns for two accumulator sets.  With BN = 256 the two sets overlap in 32
+// columns (set 0 = columns 0..255, set 1 = columns 224..479): the epilogue drains the shared
+// columns first and hands them back, so the next tile's MMAs run while the rest is drained.
 template <int BN, int MT, bool F4>
 struct TcCfg {
     static constexpr int NSTG = (MT == 1) ? 4 : 3;                 // smem ring depth
     static constexpr int A_STAGE = MT * A_SUB, B_STAGE = BN * KCH;
-    static constexpr int NBUF = (MT * BN <= (F4 ? 128 : 256)) ? 2 : 1;  // accumulator sets in tensor memory
-    // epilogue warps per lane quadrant: with a single accumulator set the drain is not hidden
-    // behind the next tile's MMAs, so two warps share each quadrant's columns
-    static constexpr int EPW = (NBUF == 1 && MT == 1) ? 2 : 1;
+    static constexpr bool OVL = F4 && MT == 1 && BN == 256;        // overlapping accumulator sets
+    static constexpr int NBUF = (OVL || MT * BN <= (F4 ? 128 : 256)) ? 2 : 1;  // accumulator sets in tensor memory
+    static constexpr int ACC_OFF = OVL ? BN - 32 : MT * BN;        // column distance between the sets
+    // epilogue warps per lane quadrant: two share each quadrant's columns where the drain is
+    // not (or only partly) hidden behind the next tile's MMAs
+    static constexpr int EPW = ((NBUF == 1 || OVL) && MT == 1) ? 2 : 1;
     // expander groups (stages expanded concurrently); 22 warps per block in every MT = 1 form
     static constexpr int NG = (MT == 1) ? (EPW == 2 ? 3 : 4) : 2;
     static constexpr int WARP_EPI0 = WARP_EXP0 + 4 * MT * NG;
@@ -255,7 +259,9 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
     // mxf4 -- e2m1 A and B (1<<7, 1<<10), ue8m0 scales (1<<23); both K-major, N>>3 at bit 17, M>>4 at bit 24
     constexpr uint32_t IDESC = (F4 ? (1u << 23) : (2u << 4)) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
                                ((uint32_t)(BM >> 4) << 24);
-    constexpr uint32_t SF_COL = 256;  // first tensor-memory column of the (all-ones) block scales
+    constexpr bool OVL = Cfg::OVL;
+    constexpr int ACC_OFF = Cfg::ACC_OFF;
+    constexpr uint32_t SF_COL = 480;  // first tensor-memory column of the (all-ones) block scales
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     unsigned char* sA = smem;
@@ -294,12 +300,13 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     if (F4) {
-        // block scales: ue8m0 0x7F = 2^0 in every byte of columns 256..511, so whatever bytes the
-        // MMA picks as scale of a row block or column block, it reads 1.0
+        // block scales: ue8m0 0x7F = 2^0 in every byte of columns 480..511 (16 columns for the
+        // row scales, 16 for the column scales; one MMA reads at most four of each), so whatever
+        // bytes the MMA picks as scale of a row block or column block, it reads 1.0
         if (warp >= WARP_EPI0 && warp < WARP_EPI0 + 4) {
             const uint32_t one = 0x7F7F7F7Fu;
 #pragma unroll 1
-            for (uint32_t c = 0; c < 256; c += 8) {
+            for (uint32_t c = 0; c < 32; c += 8) {
                 const uint32_t taddr = tmem_base + ((uint32_t)((warp & 3) * 32) << 16) + SF_COL + c;
                 asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(one)
                              : "memory");
@@ -330,9 +337,11 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
             uint32_t it = 0, lt = 0;
             for (long long t = blockIdx.x; t < ntiles; t += gridDim.x, lt++) {
                 const int buf = lt % NBUF;
-                if (!mbar_wait(bar_tempty + 8 * buf, ((lt / NBUF) & 1) ^ 1, abort_flag, p.status, 2)) goto done;
+                // overlapping sets: one barrier, completed once per tile when the columns shared
+                // with the previous tile's set have been drained; otherwise one barrier per set
+                if (!mbar_wait(OVL ? bar_tempty : bar_tempty + 8 * buf, (OVL ? (lt & 1) : ((lt / NBUF) & 1)) ^ 1, abort_flag, p.status, 2)) goto done;
                 tc_fence_after();
-                const uint32_t d_tmem = tmem_base + buf * MT * BN;
+                const uint32_t d_tmem = tmem_base + buf * ACC_OFF;
                 for (int c = 0; c < nchunks; c++, it++) {
                     const int s = it % NSTG;
                     if (!mbar_wait(bar_full + 8 * s, (it / NSTG) & 1, abort_flag, p.status, 3)) goto done;
@@ -343,7 +352,7 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
                         const uint64_t da = make_desc(smem_u32(sA + s * A_STAGE + mt * A_SUB));
 #pragma unroll
                         for (int k = 0; k < KCH / 32; k++) {
-                            if (F4) tc_mma_f4(d_tmem + mt * BN, da + 2 * k, db + 2 * k, IDESC, tmem_base + SF_COL, tmem_base + SF_COL + 64, (c | k) ? 1u : 0u);
+                            if (F4) tc_mma_f4(d_tmem + mt * BN, da + 2 * k, db + 2 * k, IDESC, tmem_base + SF_COL, tmem_base + SF_COL + 16, (c | k) ? 1u : 0u);
                             else tc_mma_i8(d_tmem + mt * BN, da + 2 * k, db + 2 * k, IDESC, (c | k) ? 1u : 0u);
                         }
                     }
@@ -494,10 +503,16 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
             const int rem = (int)(row - n_img * p.OHW);
             float* ybase = (p.layout == TNNS_NHWC) ? p.y + (size_t)row * p.KN : p.y + (size_t)n_img * p.KN * p.OHW + rem;
             const float tq = (p.pimg && row_ok) ? __ldg(p.thr_next + n_img) + 0.0f : 0.f;  // + 0.0f: -0 acts as +0
+            // overlapping sets: start with the 32 columns shared with the other set (the last of
+            // set 0, the first of set 1) if this warp owns them, and release after the first slice
+            constexpr int NSL = ECOLS / 32;
+            int start = 0;
+            if (OVL && buf == 0 && ecol == EPW - 1) start = NSL - 1;
 #pragma unroll 1
-            for (int cb = ecol * ECOLS; cb < (ecol + 1) * ECOLS; cb += 32) {
+            for (int i = 0; i < NSL; i++) {
+                const int cb = ecol * ECOLS + ((i + start) % NSL) * 32;
                 uint32_t v[32];
-                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((buf * MT + sub) * BN + cb);
+                const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * ACC_OFF + sub * BN + cb);
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -509,11 +524,12 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
                     : "r"(taddr)
                     : "memory");
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                if (cb + 32 >= (ecol + 1) * ECOLS) {
-                    // the last slice is in registers: hand the accumulator back before storing it
+                if (OVL ? (i == 0) : (i == NSL - 1)) {
+                    // the last slice (overlapping sets: the shared slice) is in registers: hand
+                    // the columns back before storing it
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(bar_tempty + 8 * buf);
+                    if (lane == 0) mbar_arrive(OVL ? bar_tempty : bar_tempty + 8 * buf);
                 }
                 if (row_ok) {
                     // int -> float without the conversion unit: for |a| < 2^22 the float with bit
