@@ -244,8 +244,26 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
     in_bytes, out_bytes = x_h.nbytes, nloc * layer.KN * OH * OW * 4
     # default route (what tnns_cuda_conv does): quantise to a packed image, GEMM gathers its im2row
     # rows itself; --route explicit: pack to the im2row matrix (t2r_p2_opt's job), then GEMM
-    implicit = args.route == "implicit" and args.gemm in ("auto", "f4tc")
-    pack_bytes = ft.api.packed_image_bytes(True, nloc, layer.C, layer.H, layer.W) if implicit else ft.packed_bytes(ft.TNN, shape)
+    # "auto" is what tnns_cuda_conv picks: the copy-engine (im2col tensor copy) form where the layer qualifies
+    tc4 = args.gemm in ("auto", "f4tc")
+    im2col = tc4 and args.route in ("auto", "im2col") and ctx.im2col_supported(w, shape)
+    if args.route == "im2col" and not im2col:
+        raise SystemExit("bench: this workload does not qualify for the im2col tensor-copy route")
+    implicit = tc4 and (im2col or args.route in ("auto", "implicit"))
+    pack_bytes = (ft.api.e2m1_image_bytes(nloc, layer.C, layer.H, layer.W) if im2col else
+                  ft.api.packed_image_bytes(True, nloc, layer.C, layer.H, layer.W) if implicit else ft.packed_bytes(ft.TNN, shape))
+
+    def run_quantise(xp, pp, n, strm):
+        if im2col:
+            ctx.quantise_e2m1(xp, thr_d.data_ptr(), pp, n, layer.C, layer.H, layer.W, layout, strm)
+        else:
+            ctx.quantise(True, xp, thr_d.data_ptr(), pp, n, layer.C, layer.H, layer.W, layout, strm)
+
+    def run_gemm_image(pp, yp, shp, strm):
+        if im2col:
+            ctx.gemm_im2col(w, pp, yp, shp, 0.5, layout, strm)
+        else:
+            ctx.gemm_implicit(w, pp, yp, shp, 0.5, layout, strm)
 
     # ring of distinct buffer sets so that consecutive steps never find their data in L2
     step_bytes = in_bytes + out_bytes + pack_bytes
@@ -272,13 +290,13 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
         if ev:
             ev[0].record(stream)
         if implicit:
-            ctx.quantise(True, xs[r].data_ptr(), thr_d.data_ptr(), ps[r].data_ptr(), nloc, layer.C, layer.H, layer.W, layout, sp)
+            run_quantise(xs[r].data_ptr(), ps[r].data_ptr(), nloc, sp)
         else:
             ctx.pack(True, xs[r].data_ptr(), thr_d.data_ptr(), ps[r].data_ptr(), shape, layout, ft.PACK_AUTO, sp)
         if ev:
             ev[1].record(stream)
         if implicit:
-            ctx.gemm_implicit(w, ps[r].data_ptr(), ys[r].data_ptr(), shape, 0.5, layout, sp)
+            run_gemm_image(ps[r].data_ptr(), ys[r].data_ptr(), shape, sp)
         else:
             ctx.gemm(w, ps[r].data_ptr(), ys[r].data_ptr(), nloc, OH, OW, 0.5, layout, gemm_algo, sp)
         if ev:
@@ -326,8 +344,8 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
         def fstep(i):
             r = i % ring
             if implicit:
-                ctx.quantise(True, xs[r].data_ptr(), thr_d.data_ptr(), ps[r].data_ptr(), nfix, layer.C, layer.H, layer.W, layout, sp)
-                ctx.gemm_implicit(w, ps[r].data_ptr(), ys[r].data_ptr(), fshape, 0.5, layout, sp)
+                run_quantise(xs[r].data_ptr(), ps[r].data_ptr(), nfix, sp)
+                run_gemm_image(ps[r].data_ptr(), ys[r].data_ptr(), fshape, sp)
             else:
                 ctx.pack(True, xs[r].data_ptr(), thr_d.data_ptr(), ps[r].data_ptr(), fshape, layout, ft.PACK_AUTO, sp)
                 ctx.gemm(w, ps[r].data_ptr(), ys[r].data_ptr(), nfix, OH, OW, 0.5, layout, gemm_algo, sp)
@@ -350,6 +368,8 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
     t_pack = statistics.mean(e[0].elapsed_time(e[1]) for e in evs)
     t_gemm = statistics.mean(e[1].elapsed_time(e[2]) for e in evs)
     ctx_lop3_rate = ctx.pipe_rate(0) if args.gemm == "popc" else 0.0
+    # issue-bound tcgen05.mma loop (no loads, no epilogue) on this GPU, 1e9 operations per second
+    ctx_mma_rate = ctx.pipe_rate(3 if args.gemm == "i8tc" else 4) if args.gemm != "popc" else 0.0
     ctx.sync()
 
     # ---- end to end: pinned host buffers in, host buffers out, copies inside the timed region ----
@@ -376,9 +396,9 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
         ops_loc = layer.ops(nloc)
         pack_alg_bytes = in_bytes + pack_bytes
         gemm_tops = ops_loc / (t_gemm * 1e-3) / 1e12
-        per_img = NCU_TRAFFIC_PER_IMAGE.get((name, {"popc": "popc", "i8tc": "tc"}.get(args.gemm, "f4" if implicit else "f4_explicit")))
+        per_img = NCU_TRAFFIC_PER_IMAGE.get((name, {"popc": "popc", "i8tc": "tc"}.get(args.gemm, "f4_im2col" if im2col else "f4" if implicit else "f4_explicit")))
         gemm_traffic = per_img * nloc if per_img else None
-        per_img = NCU_TRAFFIC_PER_IMAGE.get((name, "quantise" if implicit else "pack"))
+        per_img = NCU_TRAFFIC_PER_IMAGE.get((name, "quantise_e2m1" if im2col else "quantise" if implicit else "pack"))
         pack_traffic = per_img * nloc if per_img else None
         if args.gemm == "popc":
             # integer-pipe kernel: 5.5 LOP3 per 32-bit lane and output, LOP3 issues 64 lanes/clk/SM
@@ -392,7 +412,8 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
             gemm_peak = 2.0 * pk["bf16_tflops"]
             gemm_peak_source = f"2 x {pk['source']} bf16 burst figure (int8 dense rate = 2 x bf16)"
         else:
-            gemm_kernel_name, gemm_bound = "gemm_tc_kernel<F4=true> (tcgen05.mma kind::mxf4 GEMM, unit scales, + PReLU)", "tensor"
+            gemm_kernel_name, gemm_bound = ("gemm_tc_kernel<F4=true, ATMA=true> (tcgen05.mma kind::mxf4 GEMM fed by im2col tensor copies, unit scales, + PReLU)" if im2col else
+                                            "gemm_tc_kernel<F4=true> (tcgen05.mma kind::mxf4 GEMM, unit scales, + PReLU)"), "tensor"
             gemm_peak = 4.0 * pk["bf16_tflops"]
             gemm_peak_source = f"4 x {pk['source']} bf16 burst figure (4-bit dense rate = 4 x bf16)"
         line = {
@@ -402,7 +423,8 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
             "data": "synthetic",
             "config": {"workload": name, "batch": N_total, "batch_per_gpu": nloc, "layer": str(layer), "layout": "NCHW",
                        "M": N_total * OH * OW, "K": layer.C * layer.KH * layer.KW, "N": layer.KN, "gemm": args.gemm,
-                       "route": "quantise -> GEMM with implicit im2row" if implicit else "pack (im2row matrix) -> GEMM",
+                       "route": ("quantise to a 4-bit image -> GEMM fed by im2col tensor copies" if im2col else
+                                 "quantise to bit planes -> GEMM with implicit im2row" if implicit else "pack (im2row matrix) -> GEMM"),
                        "l2": f"ring of {ring} distinct input/workspace/output buffer sets ({ring * step_bytes >> 20} MiB) cycled "
                              f"between steps; one set alone is {step_bytes >> 20} MiB"},
             "gpu_launches": int(launches * world),
@@ -413,9 +435,14 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
             "roofline": {
                 "kernel": gemm_kernel_name, "bound": gemm_bound, "achieved": gemm_tops, "peak": gemm_peak, "unit": "TFLOP/s",
                 "frac": gemm_tops / gemm_peak, "traffic": gemm_traffic, "peak_source": gemm_peak_source,
-                "algorithmic_ops_per_launch": ops_loc, "ms_per_launch": t_gemm},
+                "algorithmic_ops_per_launch": ops_loc, "ms_per_launch": t_gemm,
+                # second denominator, measured live: the rate of a bare tcgen05.mma loop of the same
+                # kind and tile shape (operands resident in shared memory, no loads, no epilogue)
+                "pipe_peak": ctx_mma_rate / 1e3 if ctx_mma_rate else None,
+                "frac_of_pipe_peak": gemm_tops / (ctx_mma_rate / 1e3) if ctx_mma_rate else None},
             "roofline_pack": {
-                "kernel": ("pack_staged_kernel<IMG_OUT> (quantise + bit-pack to a packed image)" if implicit else "pack_staged_kernel (quantise + bit-pack + im2row)"), "bound": "hbm",
+                "kernel": ("pack_staged_kernel<IMG_OUT=e2m1> (quantise to a 4-bit operand image)" if im2col else
+                           "pack_staged_kernel<IMG_OUT> (quantise + bit-pack to a packed image)" if implicit else "pack_staged_kernel (quantise + bit-pack + im2row)"), "bound": "hbm",
                 "achieved": pack_alg_bytes / (t_pack * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": pack_alg_bytes / (t_pack * 1e-3) / 1e9 / pk["hbm_gbs"], "traffic": pack_traffic, "peak_source": pk["source"],
                 "algorithmic_bytes_per_launch": pack_alg_bytes, "ms_per_launch": t_pack},
@@ -443,8 +470,10 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="tnn_conv_large")
     ap.add_argument("--gemm", choices=["auto", "popc", "i8tc", "f4tc"], default="auto")
-    ap.add_argument("--route", choices=["implicit", "explicit"], default="implicit",
-                    help="implicit: quantise + GEMM gathering its own im2row rows (the library's default layer route); "
+    ap.add_argument("--route", choices=["auto", "im2col", "implicit", "explicit"], default="auto",
+                    help="auto: the library's default layer route (im2col where the layer qualifies, else implicit); "
+                         "im2col: quantise to a 4-bit image + GEMM fed by im2col tensor copies; "
+                         "implicit: quantise to bit planes + GEMM whose warps gather and expand their im2row rows; "
                          "explicit: pack to the im2row matrix, then GEMM")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="weak",
                     help="weak: every rank processes the configured batch; strong: the configured batch is split over the ranks")

@@ -291,6 +291,17 @@ class Context:
         """GEMM + PReLU gathering its im2row rows from the packed image of the layer input."""
         _check(self.lib.tnns_cuda_gemm_implicit(self.handle, w.handle, d_image, d_y, C.byref(shape), alpha, layout, stream))
 
+    def quantise_e2m1(self, d_x: int, d_thr: int, d_image: int, N: int, C_: int, H: int, W: int, layout=NCHW, stream=0):
+        """fp32 tensor -> 4-bit operand image ([n][pixel][C/2 bytes], ternary activations)."""
+        _check(self.lib.tnns_cuda_quantise_e2m1(self.handle, d_x, d_thr, d_image, N, C_, H, W, layout, stream))
+
+    def gemm_im2col(self, w: Weights, d_image: int, d_y: int, shape: Shape, alpha: float, layout=NCHW, stream=0):
+        """GEMM + PReLU whose activation tiles the copy engine gathers from the 4-bit image."""
+        _check(self.lib.tnns_cuda_gemm_im2col(self.handle, w.handle, d_image, d_y, C.byref(shape), alpha, layout, stream))
+
+    def im2col_supported(self, w: Weights, shape: Shape) -> bool:
+        return bool(self.lib.tnns_cuda_im2col_supported(w.handle, C.byref(shape)))
+
     def gemm_packed_out(self, w: Weights, d_a: int, d_image: int, d_thr_next: int, next_ternary: bool, N: int, OH: int, OW: int,
                         alpha: float, stream=0):
         """GEMM + PReLU whose epilogue writes the next layer's quantised bit planes instead of fp32."""
@@ -306,7 +317,8 @@ class Context:
         _check(self.lib.tnns_cuda_conv_host(self.handle, w.handle, h_x, h_thr, h_y, C.byref(shape), alpha, layout))
 
     def pipe_rate(self, op: int) -> float:
-        """Issue rate of LOP3 (0), POPC (1) or IADD (2) in 1e9 thread-instructions per second."""
+        """Issue rate of LOP3 (0), POPC (1) or IADD (2) in 1e9 thread-instructions per second, or of an
+        issue-bound tcgen05.mma loop, kind::i8 (3) or kind::mxf4 (4), in 1e9 operations (2*M*N*K) per second."""
         v = C.c_double()
         _check(self.lib.tnns_cuda_pipe_rate(self.handle, op, C.byref(v)))
         return v.value
@@ -348,6 +360,10 @@ def conv_noalloc(type_: int, d_packed_weights: int, d_x: int, d_thr: int, d_y: i
 
 def packed_image_bytes(ternary: bool, N: int, C_: int, H: int, W: int) -> int:
     return load_library().tnns_packed_image_bytes(int(ternary), N, C_, H, W)
+
+
+def e2m1_image_bytes(N: int, C_: int, H: int, W: int) -> int:
+    return load_library().tnns_e2m1_image_bytes(N, C_, H, W)
 
 
 def launch_count() -> int:

@@ -321,6 +321,41 @@ int tnns_cuda_gemm_implicit(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
                                nullptr, nullptr, 1, &g);
 }
 
+// --- the same with the copy engine gathering 4-bit tiles -------------------------------------------
+size_t tnns_e2m1_image_bytes(int N, int C, int H, int W) {
+    if (N < 0 || C <= 0 || H <= 0 || W <= 0) return 0;
+    return (size_t)N * H * W * ((C + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS) * 32;
+}
+
+int tnns_cuda_im2col_supported(const tnns_cuda_weights* w, const tnns_shape_t* s) {
+    TnnsGeom g;
+    if (!w || tnns_make_geom(s, &g)) return 0;
+    if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW) return 0;
+    return tnns_im2col_supported(w, g) ? 1 : 0;
+}
+
+int tnns_cuda_quantise_e2m1(tnns_cuda_ctx* ctx, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H, int W,
+                            int layout, void* stream) {
+    if (!ctx || !d_x || !d_thr || !d_image) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    if (N < 0 || C <= 0 || H <= 0 || W <= 0) return tnns_fail(TNNS_ERR_INVALID, "non-positive dimension");
+    if (reinterpret_cast<uintptr_t>(d_image) & 31) return tnns_fail(TNNS_ERR_INVALID, "image must be 32-byte aligned");
+    return tnns_launch_quantise(ctx, true, d_x, d_thr, d_image, N, C, H, W, layout, (cudaStream_t)stream, TNNS_IMG_E2M1);
+}
+
+int tnns_cuda_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const tnns_shape_t* s,
+                          float alpha, int layout, void* stream) {
+    if (!ctx || !w || !d_image || !d_y) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    TnnsGeom g;
+    int rc = tnns_make_geom(s, &g);
+    if (rc) return rc;
+    if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW)
+        return tnns_fail(TNNS_ERR_INVALID, "shape does not match the uploaded weights");
+    if (layout != TNNS_NCHW && layout != TNNS_NHWC) return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
+    if (w->device != ctx->device) return tnns_fail(TNNS_ERR_INVALID, "weights live on device %d, context on %d", w->device, ctx->device);
+    if (reinterpret_cast<uintptr_t>(d_image) & 31) return tnns_fail(TNNS_ERR_INVALID, "image must be 32-byte aligned");
+    return tnns_launch_gemm_im2col(ctx, w, d_image, d_y, g, alpha, layout, (cudaStream_t)stream);
+}
+
 // --- chained layers without the fp32 round trip ------------------------------------------------
 size_t tnns_packed_image_bytes(int ternary, int N, int C, int H, int W) {
     if (N < 0 || C <= 0 || H <= 0 || W <= 0) return 0;
@@ -368,6 +403,15 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
     // the 4-bit tensor-core GEMM gather its im2row rows from it, so the KH*KW-times larger im2row
     // matrix is never written.  Forcing a pack or GEMM algorithm selects the explicit two-kernel
     // route (pack to the im2row matrix, then GEMM).
+    // Where the layer qualifies (ternary activations, C a multiple of 256) the image is written as
+    // 4-bit operands and the copy engine delivers the GEMM's activation tiles (im2col tensor copies).
+    const bool auto_route = pack_algo == TNNS_PACK_AUTO && (gemm_algo == TNNS_GEMM_AUTO || gemm_algo == TNNS_GEMM_F4_TC);
+    if (auto_route && tnns_im2col_supported(w, g) && tnns_e2m1_image_bytes(g.N, g.C, g.H, g.W) <= workspace_bytes) {
+        if (reinterpret_cast<uintptr_t>(d_workspace) & 31) return tnns_fail(TNNS_ERR_INVALID, "workspace must be 32-byte aligned");
+        rc = tnns_launch_quantise(ctx, true, d_x, d_thr, d_workspace, g.N, g.C, g.H, g.W, layout, (cudaStream_t)stream, TNNS_IMG_E2M1);
+        if (rc) return rc;
+        return tnns_launch_gemm_im2col(ctx, w, d_workspace, d_y, g, alpha, layout, (cudaStream_t)stream);
+    }
     const size_t image_bytes = tnns_packed_image_bytes(type_act_ternary(w->type), g.N, g.C, g.H, g.W);
     if (pack_algo == TNNS_PACK_AUTO && (gemm_algo == TNNS_GEMM_AUTO || gemm_algo == TNNS_GEMM_F4_TC) && w->d_f4 && w->d_jtab &&
         w->Kp < 65536 && image_bytes <= workspace_bytes) {

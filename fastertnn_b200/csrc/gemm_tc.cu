@@ -26,6 +26,8 @@
 // The order of the K elements inside a stage is whatever the expansion routine produces;
 // activations and weights go through the same routine, so the permutation cancels in the dot
 // product.
+#include <cuda.h>  // CUtensorMap and the encode prototypes only; the entry point is looked up at run time
+
 #include <algorithm>
 #include <vector>
 
@@ -49,8 +51,13 @@ constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_EXP0 = 2;
 // which leaves 480 columns for two accumulator sets.  With BN = 256 the two sets overlap in 32
 // columns (set 0 = columns 0..255, set 1 = columns 224..479): the epilogue drains the shared
 // columns first and hands them back, so the next tile's MMAs run while the rest is drained.
-template <int BN, int MT, bool F4>
+// ATMA: the activation stage is not expanded by warps but delivered by the copy engine as one
+// im2col tensor copy from a 4-bit (e2m1) image of the layer input -- 128 output pixels x 128 bytes
+// (256 channels of one filter tap), zero-filled outside the image, written in the swizzled layout
+// the MMA reads.  No expander warps then: producer warp, MMA warp, eight epilogue warps.
+template <int BN, int MT, bool F4, bool ATMA = false>
 struct TcCfg {
+    static_assert(!ATMA || (F4 && MT == 1), "tensor-copy activations: 4-bit form, one accumulator per block");
     static constexpr int NSTG = (MT == 1) ? 4 : 3;                 // smem ring depth
     static constexpr int A_STAGE = MT * A_SUB, B_STAGE = BN * KCH;
     static constexpr bool OVL = F4 && MT == 1 && BN == 256;        // overlapping accumulator sets
@@ -58,9 +65,9 @@ struct TcCfg {
     static constexpr int ACC_OFF = OVL ? BN - 32 : MT * BN;        // column distance between the sets
     // epilogue warps per lane quadrant: two share each quadrant's columns where the drain is
     // not (or only partly) hidden behind the next tile's MMAs
-    static constexpr int EPW = ((NBUF == 1 || OVL) && MT == 1) ? 2 : 1;
+    static constexpr int EPW = (((NBUF == 1 || OVL) && MT == 1) || ATMA) ? 2 : 1;
     // expander groups (stages expanded concurrently); 22 warps per block in every MT = 1 form
-    static constexpr int NG = (MT == 1) ? (EPW == 2 ? 3 : 4) : 2;
+    static constexpr int NG = ATMA ? 0 : ((MT == 1) ? (EPW == 2 ? 3 : 4) : 2);
     static constexpr int WARP_EPI0 = WARP_EXP0 + 4 * MT * NG;
     static constexpr int NTHREADS = 32 * (2 + 4 * MT * NG + 4 * MT * EPW);
     static constexpr size_t SMEM = 1024 + (size_t)NSTG * (A_STAGE + B_STAGE) + 256;
@@ -112,6 +119,16 @@ __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uin
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem), "l"(src),
                  "r"(bytes), "r"(bar)
                  : "memory");
+}
+// im2col tensor copy: `pixels per column` base pixels starting at (w, h, n), walking the layer's
+// output lattice (stride, padding box are in the tensor map), each read at filter offset (kw, kh),
+// channels from byte c on; outside the image the copy engine writes zeros.
+__device__ __forceinline__ void tma_im2col_g2s(uint32_t dst_smem, const void* tmap, int c, int w, int h, int n, unsigned short kw,
+                                               unsigned short kh, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(kw), "h"(kh)
+        : "memory");
 }
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
@@ -177,18 +194,6 @@ __device__ __forceinline__ void store_row_chunk(unsigned char* tile, int r, cons
     }
 }
 
-// 32 elements -> 32 e2m1 nibbles (four words) in a fixed permuted order: nibble = sign<<3 | nonzero<<1.
-// x gathers, per nibble, the sign bits of elements 4i+3, 4i+2 (bits 3, 2) over their non-zero
-// bits (bits 1, 0); masking x with 0xA gives the nibbles of the elements 4i+3, masking x<<1 those
-// of the elements 4i+2; y does the same for 4i+1 and 4i.  Ten integer operations per 32 elements.
-__device__ __forceinline__ void expand32_f4(uint32_t s, uint32_t z, uint32_t (&w)[4]) {
-    const uint32_t x = (s & 0xCCCCCCCCu) | (~(z >> 2) & 0x33333333u);
-    const uint32_t y = ((s << 2) & 0xCCCCCCCCu) | (~z & 0x33333333u);
-    w[0] = x & 0xAAAAAAAAu;
-    w[1] = (x << 1) & 0xAAAAAAAAu;
-    w[2] = y & 0xAAAAAAAAu;
-    w[3] = (y << 1) & 0xAAAAAAAAu;
-}
 
 // 4-bit form: one row and stage = 256 elements = eight lanes per plane -> 128 bytes.
 __device__ __forceinline__ void store_row_stage_f4(unsigned char* tile, int r, const uint4 (&s)[2], const uint4 (&z)[2]) {
@@ -198,7 +203,7 @@ __device__ __forceinline__ void store_row_stage_f4(unsigned char* tile, int r, c
 #pragma unroll
     for (int l = 0; l < 8; l++) {
         uint32_t w[4];
-        expand32_f4(sl[l], zl[l], w);
+        tnns_expand32_f4(sl[l], zl[l], w);
         *reinterpret_cast<uint4*>(row + ((l ^ (r & 7)) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
     }
 }
@@ -250,9 +255,9 @@ struct GemmArgs {
     int H, W, OW, Cp, SH, SW, PH, PW;
 };
 
-template <int BN, int MT, bool F4>
-__global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel(GemmArgs p) {
-    using Cfg = TcCfg<BN, MT, F4>;
+template <int BN, int MT, bool F4, bool ATMA>
+__global__ void __launch_bounds__(TcCfg<BN, MT, F4, ATMA>::NTHREADS, 1) gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a) {
+    using Cfg = TcCfg<BN, MT, F4, ATMA>;
     constexpr int NSTG = Cfg::NSTG, A_STAGE = Cfg::A_STAGE, B_STAGE = Cfg::B_STAGE, NBUF = Cfg::NBUF, WARP_EPI0 = Cfg::WARP_EPI0, NG = Cfg::NG, EPW = Cfg::EPW;
     constexpr int BMT = MT * BM;  // rows per block tile
     // instruction descriptor: i8 -- s32 accumulate (2<<4), signed 8-bit A and B (1<<7, 1<<10);
@@ -281,7 +286,7 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
 
     if (tid == 0) {
         for (int s = 0; s < NSTG; s++) {
-            mbar_init(bar_full + 8 * s, 1 + 4 * MT);  // weight producer + the expander warps
+            mbar_init(bar_full + 8 * s, ATMA ? 1 : 1 + 4 * MT);  // weight producer + the expander warps
             mbar_init(bar_empty + 8 * s, 1);  // tcgen05.commit
         }
         for (int b = 0; b < 2; b++) {
@@ -324,11 +329,27 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
             for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
                 const int n_tile = (int)(t % ntn);
                 const unsigned char* src = p.Bimg + (size_t)n_tile * nchunks * B_STAGE;
+                // tensor-copy activations: base pixel of the tile's first output pixel
+                int a_n = 0, a_h = 0, a_w = 0;
+                if (ATMA) {
+                    const long long row0 = (t / ntn) * BMT;
+                    a_n = (int)(row0 / p.OHW);
+                    const int rem = (int)(row0 - (long long)a_n * p.OHW);
+                    const int oh = rem / p.OW;
+                    a_h = oh * p.SH - p.PH;
+                    a_w = (rem - oh * p.OW) * p.SW - p.PW;
+                }
                 for (int c = 0; c < nchunks; c++, it++) {
                     const int s = it % NSTG;
                     if (!mbar_wait(bar_empty + 8 * s, ((it / NSTG) & 1) ^ 1, abort_flag, p.status, 1)) goto done;
-                    mbar_arrive_expect_tx(bar_full + 8 * s, B_STAGE);
+                    mbar_arrive_expect_tx(bar_full + 8 * s, ATMA ? B_STAGE + A_STAGE : B_STAGE);
                     bulk_g2s(smem_u32(sB + s * B_STAGE), src + (size_t)c * B_STAGE, B_STAGE, bar_full + 8 * s);
+                    if (ATMA) {
+                        // the stage's four plane words are four neighbouring channel groups of one tap
+                        const uint32_t e = __ldg(p.jtab + 4 * c);
+                        tma_im2col_g2s(smem_u32(sA + s * A_STAGE), &tmap_a, (int)(e & 0xFFFF) * 32, a_w, a_h, a_n,
+                                       (unsigned short)((e >> 16) & 0xFF), (unsigned short)(e >> 24), bar_full + 8 * s);
+                    }
                 }
             }
         }
@@ -361,7 +382,7 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4>::NTHREADS, 1) gemm_tc_kernel
                 tc_commit(bar_tfull + 8 * buf);    // accumulator complete
             }
         }
-    } else if (warp < WARP_EPI0) {
+    } else if (!ATMA && warp < WARP_EPI0) {
         // ---------------- activation expanders ----------------
         // NG groups of MT*128 threads; thread = row.  Group k expands the stages it = k, k+NG,
         // k+2*NG, ... of the block's flat (tile, chunk) sequence, so NG stages are being
@@ -626,14 +647,89 @@ __global__ void wait_expiry_selftest_kernel(unsigned int* status) {
     if (threadIdx.x == 0) mbar_wait(smem_u32(&bar), 0, &abort_flag, status, 0x7F);
 }
 
-template <int BN, int MT, bool F4>
-int launch_cfg(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream) {
-    using Cfg = TcCfg<BN, MT, F4>;
-    auto kern = gemm_tc_kernel<BN, MT, F4>;
+// Issue-bound tensor-pipe rate: one block per SM keeps one 128 x 256 operand pair (pseudo-random
+// {-1,0,+1} values) in shared memory and issues `iters` groups of four MMAs on it back to back,
+// with no loads, expansion or epilogue.  What the GEMM kernel's 2*M*N*K / t is compared with.
+template <bool F4>
+__global__ void __launch_bounds__(128, 1) mma_rate_kernel(int iters, unsigned int* status) {
+    constexpr int BN = 256;
+    constexpr uint32_t IDESC = (F4 ? (1u << 23) : (2u << 4)) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    unsigned char* sA = smem;
+    unsigned char* sB = smem + A_SUB;
+    __shared__ uint64_t bar;
+    __shared__ uint32_t tmem_slot;
+    __shared__ int abort_flag;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    for (int r = tid; r < BM + BN; r += blockDim.x) {
+        uint32_t h = (uint32_t)r * 2654435761u + blockIdx.x * 40503u + 12345u;
+        uint4 sg[2], zr[2];
+        uint32_t* ps = reinterpret_cast<uint32_t*>(sg);
+        uint32_t* pz = reinterpret_cast<uint32_t*>(zr);
+        for (int i = 0; i < 8; i++) {
+            h = h * 1664525u + 1013904223u; ps[i] = h;
+            h = h * 1664525u + 1013904223u; pz[i] = h & (h >> 7);  // about a quarter zeros
+        }
+        unsigned char* tile = r < BM ? sA : sB;
+        const int rr = r < BM ? r : r - BM;
+        if (F4) store_row_stage_f4(tile, rr, sg, zr);
+        else store_row_chunk(tile, rr, sg[0], zr[0]);
+    }
+    if (tid == 0) {
+        mbar_init(smem_u32(&bar), 1);
+        abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    fence_proxy_async();
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_slot)), "r"(512u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = tmem_slot;
+    if (F4) {
+        const uint32_t one = 0x7F7F7F7Fu;
+        for (uint32_t c = 0; c < 32; c += 8) {
+            const uint32_t taddr = tmem_base + ((uint32_t)(warp * 32) << 16) + 480 + c;
+            asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1, %1, %1, %1, %1, %1, %1, %1};" ::"r"(taddr), "r"(one) : "memory");
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        tc_fence_before();
+        __syncthreads();
+        tc_fence_after();
+    }
+    if (tid == 0) {
+        const uint64_t da = make_desc(smem_u32(sA)), db = make_desc(smem_u32(sB));
+        for (int it = 0; it < iters; it++) {
+#pragma unroll
+            for (int k = 0; k < KCH / 32; k++) {
+                if (F4) tc_mma_f4(tmem_base, da + 2 * k, db + 2 * k, IDESC, tmem_base + 480, tmem_base + 496, (it | k) ? 1u : 0u);
+                else tc_mma_i8(tmem_base, da + 2 * k, db + 2 * k, IDESC, (it | k) ? 1u : 0u);
+            }
+        }
+        tc_commit(smem_u32(&bar));
+        mbar_wait(smem_u32(&bar), 0, &abort_flag, status, 8);
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+    }
+}
+
+template <int BN, int MT, bool F4, bool ATMA = false>
+int launch_cfg(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream, const CUtensorMap* tmap_a = nullptr) {
+    using Cfg = TcCfg<BN, MT, F4, ATMA>;
+    auto kern = gemm_tc_kernel<BN, MT, F4, ATMA>;
+    static const CUtensorMap no_map = {};
     TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
     const long long tiles = ((a.M + MT * BM - 1) / (MT * BM)) * ((a.KN + BN - 1) / BN);
     const int grid = (int)std::min<long long>(tiles, ctx->sm_count);
-    kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, stream>>>(a);
+    kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, stream>>>(a, tmap_a ? *tmap_a : no_map);
     tnns_count_launch();
     TNNS_CUDA_TRY(cudaGetLastError());
     return TNNS_OK;
@@ -734,6 +830,102 @@ int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const vo
         case 128: return launch_bn<128, false>(ctx, a, stream);
         default: return launch_bn<256, false>(ctx, a, stream);
     }
+}
+
+// ---------------------------------------------------------------------------------------
+// Tensor-copy activations: the tensor map of the e2m1 image and the launch
+// ---------------------------------------------------------------------------------------
+bool tnns_im2col_supported(const tnns_cuda_weights* w, const TnnsGeom& g) {
+    if (!(w->type == TNN || w->type == TBN)) return false;   // outside the image the copy engine writes 0, a ternary zero
+    if (!w->d_f4 || !w->d_jtab || w->Kp >= 65536) return false;
+    if (tnns_i8_tile_n(w->KN) != 256 && tnns_i8_tile_n(w->KN) != 128 && tnns_i8_tile_n(w->KN) != 64) return false;
+    if (g.Cp % 4 != 0) return false;                         // a stage = 256 channels of one tap = one 128-byte box row
+    if (g.KH > 255 || g.KW > 255 || g.SH > 8 || g.SW > 8) return false;          // filter offsets are 8 bits, traversal strides <= 8
+    if (g.PH > 128 || g.PW > 128 || g.PH - (g.KH - 1) < -128 || g.PW - (g.KW - 1) < -128) return false;  // box corners are 8 bits
+    return true;
+}
+
+namespace {
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const int*,
+                                   const int*, cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+int encode_im2col_map(CUtensorMap* map, const void* d_image, const TnnsGeom& g) {
+    static EncodeIm2colFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        TNNS_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &fn, cudaEnableDefault, &q));
+        if (q != cudaDriverEntryPointSuccess || !fn) return tnns_fail(TNNS_ERR_UNSUPPORTED, "the driver offers no cuTensorMapEncodeIm2col");
+        encode = reinterpret_cast<EncodeIm2colFn>(fn);
+    }
+    // the image as a (bytes-of-channels, W, H, N) tensor of bytes; a box = 128 bytes x 128 base pixels
+    const cuuint64_t cbytes = (cuuint64_t)g.Cp * 32;
+    const cuuint64_t dims[4] = {cbytes, (cuuint64_t)g.W, (cuuint64_t)g.H, (cuuint64_t)g.N};
+    const cuuint64_t strides[3] = {cbytes, cbytes * g.W, cbytes * g.W * g.H};
+    // the base pixel (top-left of the filter window) moves over [-pad, size + pad - kernel]
+    const int lower[2] = {-g.PW, -g.PH};
+    const int upper[2] = {g.PW - (g.KW - 1), g.PH - (g.KH - 1)};
+    const cuuint32_t estr[4] = {1, (cuuint32_t)g.SW, (cuuint32_t)g.SH, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(d_image), dims, strides, lower, upper, 128, BM, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return tnns_fail(TNNS_ERR_CUDA, "cuTensorMapEncodeIm2col failed with driver error %d", (int)r);
+    // Drivers up to 13.1 set a flag in im2col maps of tensors below 128 KiB that must be clear
+    // (the correction CUTLASS applies to its im2col descriptors, cute/atom/copy_traits_sm90_im2col.hpp).
+    int driver = 0;
+    TNNS_CUDA_TRY(cudaDriverGetVersion(&driver));
+    if (driver <= 13010 && cbytes * g.W * g.H * g.N < 131072) reinterpret_cast<uint64_t*>(map)[1] &= ~(1ull << 21);
+    return TNNS_OK;
+}
+}  // namespace
+
+int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const TnnsGeom& g, float alpha,
+                            int layout, cudaStream_t stream) {
+    const long long M = (long long)g.N * g.OH * g.OW;
+    if (M == 0) return TNNS_OK;
+    if (!tnns_im2col_supported(w, g)) return tnns_fail(TNNS_ERR_UNSUPPORTED, "layer shape or type outside the tensor-copy activation path");
+    if (reinterpret_cast<uintptr_t>(d_image) & 15) return tnns_fail(TNNS_ERR_INVALID, "image must be 16-byte aligned");
+    CUtensorMap map;
+    int rc = encode_im2col_map(&map, d_image, g);
+    if (rc) return rc;
+    GemmArgs a;
+    a.A = nullptr;
+    a.Bimg = reinterpret_cast<const unsigned char*>(w->d_f4);
+    a.y = d_y;
+    a.M = M;
+    a.KN = w->KN;
+    a.Kp = w->Kp;
+    a.OHW = g.OH * g.OW;
+    a.layout = layout;
+    a.a_two_planes = 1;
+    a.acc_bias = 0;
+    a.alpha = alpha;
+    a.status = ctx->d_status;
+    a.pimg = nullptr;
+    a.thr_next = nullptr;
+    a.next_ternary = 1;
+    a.cp_next = (w->KN + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS;
+    a.img = nullptr;
+    a.jtab = w->d_jtab;
+    a.H = g.H; a.W = g.W; a.OW = g.OW; a.Cp = g.Cp; a.SH = g.SH; a.SW = g.SW; a.PH = g.PH; a.PW = g.PW;
+    switch (tnns_i8_tile_n(w->KN)) {
+        case 64: return launch_cfg<64, 1, true, true>(ctx, a, stream, &map);
+        case 128: return launch_cfg<128, 1, true, true>(ctx, a, stream, &map);
+        default: return launch_cfg<256, 1, true, true>(ctx, a, stream, &map);
+    }
+}
+
+// Launches the issue-bound MMA loop on every SM; `ops` receives the 2*M*N*K operations it performs.
+int tnns_launch_mma_rate(tnns_cuda_ctx* ctx, bool f4, int iters, double* ops, cudaStream_t stream) {
+    const size_t smem = 1024 + A_SUB + 256 * KCH;
+    auto kern = f4 ? mma_rate_kernel<true> : mma_rate_kernel<false>;
+    TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+    kern<<<ctx->sm_count, 128, smem, stream>>>(iters, ctx->d_status);
+    tnns_count_launch();
+    TNNS_CUDA_TRY(cudaGetLastError());
+    *ops = (double)ctx->sm_count * iters * (KCH / 32) * 2.0 * BM * 256 * (f4 ? 64 : 32);
+    return TNNS_OK;
 }
 
 int tnns_launch_wait_selftest(tnns_cuda_ctx* ctx, cudaStream_t stream) {

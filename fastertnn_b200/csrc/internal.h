@@ -82,13 +82,26 @@ int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const vo
 // implicit_geom != NULL: d_a is the quantised image [n][plane][pixel][ic] of the layer input and
 // the kernel gathers the im2row rows itself (4-bit form only)
 #define TNNS_SRC_PACKED_IMAGE 2  // internal "layout" of tnns_launch_pack: input is already bit planes
-// quantise only: fp32 tensor -> packed image [n][plane][pixel][ic] (no im2row)
+// quantise only (no im2row): fp32 tensor -> packed image, in one of two formats
+//   TNNS_IMG_PLANES  bit planes [n][plane][pixel][ic], one 64-bit word per 64 channels
+//   TNNS_IMG_E2M1    4-bit operand image [n][pixel][ic][32 bytes]: the 64 channels of a group as the
+//                    e2m1 nibbles tnns_expand32_f4 makes of the low and the high half of its plane
+//                    words -- exactly the bytes the 4-bit GEMM keeps in shared memory, so a tensor
+//                    copy can deliver im2row tiles without any expansion (ternary activations only)
+#define TNNS_IMG_PLANES 1
+#define TNNS_IMG_E2M1 2
 int tnns_launch_quantise(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
-                         int W, int layout, cudaStream_t stream);
+                         int W, int layout, cudaStream_t stream, int format = TNNS_IMG_PLANES);
+// 4-bit GEMM + PReLU whose activation tiles the copy engine gathers (im2col tensor copies) from
+// an e2m1 image; needs ternary activations and a channel count that fills 128-byte chunks
+bool tnns_im2col_supported(const tnns_cuda_weights* w, const TnnsGeom& g);
+int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const TnnsGeom& g,
+                            float alpha, int layout, cudaStream_t stream);
 
 int tnns_launch_pack_weights(tnns_cuda_ctx* ctx, bool ternary, const float* d_w, const float* d_thr, void* d_packed, int KN, int C,
                              int KH, int KW, cudaStream_t stream);
 
+int tnns_launch_mma_rate(tnns_cuda_ctx* ctx, bool f4, int iters, double* ops, cudaStream_t stream);
 int tnns_launch_wait_selftest(tnns_cuda_ctx* ctx, cudaStream_t stream);
 
 // Division by a runtime-constant divisor without the hardware divide sequence.
@@ -103,3 +116,20 @@ struct FastDiv {
 #endif
 };
 FastDiv tnns_fastdiv(uint32_t d);
+
+#ifdef __CUDACC__
+// 32 elements (one 32-bit lane of the sign plane, one of the zero plane) -> 32 e2m1 nibbles (four
+// words) in a fixed permuted order: nibble = sign<<3 | nonzero<<1 (+1 = 0x2, -1 = 0xA, 0 = 0x0).
+// x gathers, per nibble, the sign bits of elements 4i+3, 4i+2 (bits 3, 2) over their non-zero
+// bits (bits 1, 0); masking x with 0xA gives the nibbles of the elements 4i+3, masking x<<1 those
+// of the elements 4i+2; y does the same for 4i+1 and 4i.  Ten integer operations per 32 elements.
+// Activations and weights go through this same routine, so the permutation cancels in the dot product.
+__device__ __forceinline__ void tnns_expand32_f4(uint32_t s, uint32_t z, uint32_t (&w)[4]) {
+    const uint32_t x = (s & 0xCCCCCCCCu) | (~(z >> 2) & 0x33333333u);
+    const uint32_t y = ((s << 2) & 0xCCCCCCCCu) | (~z & 0x33333333u);
+    w[0] = x & 0xAAAAAAAAu;
+    w[1] = (x << 1) & 0xAAAAAAAAu;
+    w[2] = y & 0xAAAAAAAAu;
+    w[3] = (y << 1) & 0xAAAAAAAAu;
+}
+#endif

@@ -134,7 +134,8 @@ __device__ __forceinline__ void quantise_batch(const float* __restrict__ q, size
 // IMG_OUT: stop after phase 1 and write the band's packed pixels out as they are (quantise only:
 //           the packed image [n][plane][pixel][ic] that the implicit-im2row GEMM reads); the
 //           geometry passed in is then that of a 1x1 stride-1 window, so bands have no halo.
-template <bool TERNARY, int LAYOUT, int VEC, bool PAIR, bool IMG_OUT>
+// IMG_OUT = TNNS_IMG_E2M1 writes the same pixels as 4-bit operands instead (32 bytes per 64 channels).
+template <bool TERNARY, int LAYOUT, int VEC, bool PAIR, int IMG_OUT>
 __global__ void __launch_bounds__(kPackThreads, TNNS_PACK_MINCTA)
 pack_staged_kernel(const float* __restrict__ x, const float* __restrict__ thr, uint4* __restrict__ out, TnnsGeom g,
                    int BOH, int nbands, int Lmax, FastDiv divU, FastDiv divOW, FastDiv divL) {
@@ -275,6 +276,20 @@ pack_staged_kernel(const float* __restrict__ x, const float* __restrict__ thr, u
     }
     __syncthreads();
 
+    if (IMG_OUT == TNNS_IMG_E2M1) {
+        // word i of the band = (pixel, channel group) -> 32 bytes at the same index
+        uint4* dst = out + ((size_t)n * g.H * g.W + (size_t)ih_lo * g.W) * g.Cp * 2;
+        const int words = L * g.Cp;
+        for (int i = tid; i < words; i += kPackThreads) {
+            const uint64_t s = sm_sign[i], z = TERNARY ? sm_zero[i] : 0ull;
+            uint32_t lo[4], hi[4];
+            tnns_expand32_f4((uint32_t)s, (uint32_t)z, lo);
+            tnns_expand32_f4((uint32_t)(s >> 32), (uint32_t)(z >> 32), hi);
+            dst[2 * (size_t)i] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            dst[2 * (size_t)i + 1] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        }
+        return;
+    }
     if (IMG_OUT) {
         uint64_t* img = reinterpret_cast<uint64_t*>(out);
         const size_t HWC = (size_t)g.H * g.W * g.Cp;
@@ -334,7 +349,7 @@ pack_staged_kernel(const float* __restrict__ x, const float* __restrict__ thr, u
     }
 }
 
-template <bool TERNARY, int LAYOUT, int VEC, bool IMG_OUT = false>
+template <bool TERNARY, int LAYOUT, int VEC, int IMG_OUT = 0>
 int launch_staged(tnns_cuda_ctx* ctx, const float* d_x, const float* d_thr, void* d_packed, const TnnsGeom& g, int BOH,
                   int Lmax, size_t smem, cudaStream_t stream) {
     const int nbands = (g.OH + BOH - 1) / BOH;
@@ -349,8 +364,8 @@ int launch_staged(tnns_cuda_ctx* ctx, const float* d_x, const float* d_thr, void
         TNNS_CUDA_TRY(cudaGetLastError());
         return TNNS_OK;
     };
-    if (IMG_OUT) return launch(pack_staged_kernel<TERNARY, LAYOUT, VEC, false, true>);
-    return pair ? launch(pack_staged_kernel<TERNARY, LAYOUT, VEC, true, false>) : launch(pack_staged_kernel<TERNARY, LAYOUT, VEC, false, false>);
+    if (IMG_OUT) return launch(pack_staged_kernel<TERNARY, LAYOUT, VEC, false, IMG_OUT>);
+    return pair ? launch(pack_staged_kernel<TERNARY, LAYOUT, VEC, true, 0>) : launch(pack_staged_kernel<TERNARY, LAYOUT, VEC, false, 0>);
 }
 
 }  // namespace
@@ -445,8 +460,10 @@ int tnns_launch_pack(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const f
 // Quantise only: fp32 tensor -> packed image.  Runs the staged kernel on the geometry of a 1x1
 // stride-1 window (one band = BOH image rows, no halo) with the IMG_OUT tail.
 int tnns_launch_quantise(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
-                         int W, int layout, cudaStream_t stream) {
+                         int W, int layout, cudaStream_t stream, int format) {
     if (N == 0) return TNNS_OK;
+    if (format != TNNS_IMG_PLANES && format != TNNS_IMG_E2M1) return tnns_fail(TNNS_ERR_INVALID, "unknown image format %d", format);
+    if (format == TNNS_IMG_E2M1 && !ternary) return tnns_fail(TNNS_ERR_UNSUPPORTED, "the 4-bit image holds ternary activations only");
     if (layout != TNNS_NCHW && layout != TNNS_NHWC) return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
     TnnsGeom g;
     g.N = N; g.C = C; g.H = H; g.W = W; g.KN = 1; g.KH = g.KW = 1; g.PH = g.PW = 0; g.SH = g.SW = 1;
@@ -468,15 +485,20 @@ int tnns_launch_quantise(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, con
     const size_t smem = smem_for(BOH);
     int eff_layout = layout;
     if (layout == TNNS_NCHW && H * W == 1) eff_layout = TNNS_NHWC;
-    if (eff_layout == TNNS_NHWC)
-        return ternary ? launch_staged<true, 1, 1, true>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream)
-                       : launch_staged<false, 1, 1, true>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream);
     const bool vec4 = (W % 4 == 0) && ((reinterpret_cast<uintptr_t>(d_x) & 15) == 0);
+    if (format == TNNS_IMG_E2M1) {
+        if (eff_layout == TNNS_NHWC) return launch_staged<true, 1, 1, TNNS_IMG_E2M1>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream);
+        if (vec4) return launch_staged<true, 0, 4, TNNS_IMG_E2M1>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream);
+        return launch_staged<true, 0, 1, TNNS_IMG_E2M1>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream);
+    }
+    if (eff_layout == TNNS_NHWC)
+        return ternary ? launch_staged<true, 1, 1, TNNS_IMG_PLANES>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream)
+                       : launch_staged<false, 1, 1, TNNS_IMG_PLANES>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream);
     if (vec4)
-        return ternary ? launch_staged<true, 0, 4, true>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream)
-                       : launch_staged<false, 0, 4, true>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream);
-    return ternary ? launch_staged<true, 0, 1, true>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream)
-                   : launch_staged<false, 0, 1, true>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream);
+        return ternary ? launch_staged<true, 0, 4, TNNS_IMG_PLANES>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream)
+                       : launch_staged<false, 0, 4, TNNS_IMG_PLANES>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream);
+    return ternary ? launch_staged<true, 0, 1, TNNS_IMG_PLANES>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream)
+                   : launch_staged<false, 0, 1, TNNS_IMG_PLANES>(ctx, d_x, d_thr, d_image, g, BOH, Lmax, smem, stream);
 }
 
 // ---------------------------------------------------------------------------------------

@@ -29,11 +29,41 @@ __global__ void __launch_bounds__(1024) pipe_rate_kernel(uint32_t* out, int iter
 
 }  // namespace
 
-// op: 0 = LOP3, 1 = POPC, 2 = IADD.  Result in 1e9 thread-instructions per second.
+// Tensor pipe: an issue-bound loop of tcgen05.mma on operands resident in shared memory.
+static int tensor_rate(tnns_cuda_ctx* ctx, bool f4, double* giga_per_s) {
+    const int iters = 2000;  // x 4 MMAs per block: under a millisecond
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    float best = 1e30f;
+    double ops = 0;
+    int rc = TNNS_OK;
+    for (int rep = 0; rep < 5 && rc == TNNS_OK; rep++) {
+        cudaEventRecord(e0, (cudaStream_t)0);
+        rc = tnns_launch_mma_rate(ctx, f4, iters, &ops, (cudaStream_t)0);
+        cudaEventRecord(e1, (cudaStream_t)0);
+        cudaEventSynchronize(e1);
+        float ms = 0;
+        cudaEventElapsedTime(&ms, e0, e1);
+        if (rep > 0 && ms < best) best = ms;
+    }
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    if (rc != TNNS_OK) return rc;
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return tnns_fail(TNNS_ERR_CUDA, "tensor-rate kernel failed: %s", cudaGetErrorString(e));
+    *giga_per_s = ops / (best * 1e-3) / 1e9;
+    return TNNS_OK;
+}
+
+// op: 0 = LOP3, 1 = POPC, 2 = IADD: result in 1e9 thread-instructions per second.
+// op: 3 = tcgen05.mma kind::i8, 4 = kind::mxf4 (block scales): result in 1e9 operations
+// (2*M*N*K) per second.
 extern "C" int tnns_cuda_pipe_rate(tnns_cuda_ctx* ctx, int op, double* giga_per_s) {
     if (!ctx || !giga_per_s) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
-    if (op < 0 || op > 2) return tnns_fail(TNNS_ERR_INVALID, "unknown instruction kind %d", op);
+    if (op < 0 || op > 4) return tnns_fail(TNNS_ERR_INVALID, "unknown instruction kind %d", op);
     TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
+    if (op >= 3) return tensor_rate(ctx, op == 4, giga_per_s);
     const int blocks = ctx->sm_count * 2, threads = 1024, iters = 2000;
     uint32_t* d = nullptr;
     TNNS_CUDA_TRY(cudaMalloc(&d, (size_t)blocks * threads * 4));

@@ -254,6 +254,20 @@ int tnns_cuda_quantise(tnns_cuda_ctx* ctx, int ternary, const float* d_x, const 
  * Same result as tnns_cuda_pack + tnns_cuda_gemm.  tnns_cuda_conv takes this route by default. */
 int tnns_cuda_gemm_implicit(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const tnns_shape_t* s,
                             float alpha, int layout, void* stream);
+/* The same route with the copy engine doing the gather (ternary activations, C a multiple of 256;
+ * tnns_cuda_im2col_supported says whether a layer qualifies).  tnns_cuda_quantise_e2m1 writes the
+ * quantised input as a 4-bit operand image, [n][pixel][C/2 bytes] with {-1,0,+1} as e2m1 nibbles
+ * (tnns_e2m1_image_bytes() bytes, 32-byte aligned); tnns_cuda_gemm_im2col then receives every
+ * 128-pixel x 256-channel activation tile of a filter tap as one im2col tensor copy (zero fill
+ * outside the image = the reference's padding value, src/tnns/ternarize2row_avx2.c:438-452)
+ * straight into the layout the tensor core reads: no warp expands or gathers anything.  Same
+ * result as tnns_cuda_pack + tnns_cuda_gemm; tnns_cuda_conv prefers this route where it applies. */
+size_t tnns_e2m1_image_bytes(int N, int C, int H, int W);
+int tnns_cuda_im2col_supported(const tnns_cuda_weights* w, const tnns_shape_t* s);
+int tnns_cuda_quantise_e2m1(tnns_cuda_ctx* ctx, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H, int W,
+                            int layout, void* stream);
+int tnns_cuda_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const tnns_shape_t* s,
+                          float alpha, int layout, void* stream);
 int tnns_cuda_gemm_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const int64_t* d_a, void* d_image,
                               const float* d_thr_next, int next_ternary, int N, int OH, int OW, float alpha, void* stream);
 int tnns_cuda_im2row_packed(tnns_cuda_ctx* ctx, int ternary, const void* d_image, int64_t* d_packed, const tnns_shape_t* s,
@@ -310,9 +324,12 @@ void tnns_cuda_free(tnns_cuda_ctx* ctx, void* p);
 int tnns_cuda_memcpy_h2d(tnns_cuda_ctx* ctx, void* dst, const void* src, size_t bytes);
 int tnns_cuda_memcpy_d2h(tnns_cuda_ctx* ctx, void* dst, const void* src, size_t bytes);
 
-/* Measurement utility: issue rate of one integer instruction kind over the whole GPU
- * (op 0 = LOP3, 1 = POPC, 2 = IADD), in 1e9 thread-instructions per second.  Gives the
- * denominator for "fraction of the integer pipe" figures of the popcount GEMM. */
+/* Measurement utility: issue rate of one instruction kind over the whole GPU.
+ * op 0 = LOP3, 1 = POPC, 2 = IADD: 1e9 thread-instructions per second, the denominator for
+ * "fraction of the integer pipe" figures of the popcount GEMM.
+ * op 3 = tcgen05.mma kind::i8, 4 = tcgen05.mma kind::mxf4: 1e9 operations (2*M*N*K) per second
+ * of an issue-bound loop of 128 x 256 MMAs on operands resident in shared memory (no loads,
+ * no epilogue): the tensor-pipe denominator for the tensor-core GEMMs. */
 int tnns_cuda_pipe_rate(tnns_cuda_ctx* ctx, int op, double* giga_per_s);
 
 /* Number of kernels this library has launched in the calling thread since load. */

@@ -417,3 +417,103 @@ def test_bounded_wait_expiry_is_reported_and_context_survives(gpu_ctx):
     wp = ft.pack_weights_ternary(case.w, case.w_thr)
     y = device_conv(ctx, case, wp, ft.NCHW, ft.PACK_AUTO, ft.GEMM_AUTO)
     assert np.isfinite(y).all() and y.shape == (2, 16, 6, 6)
+
+
+def test_pipe_rate_microbenchmarks_report_plausible_rates(gpu_ctx):
+    """The denominators of the pipe-utilisation figures: integer issue rates and the rate of a bare
+    tcgen05.mma loop.  LOP3 issues faster than POPC; the 4-bit MMA kind runs faster than int8;
+    both tensor rates lie between 0.5 and 20 peta-operations per second on this part."""
+    ctx = gpu_ctx
+    lop3, popc = ctx.pipe_rate(0), ctx.pipe_rate(1)
+    assert lop3 > popc > 0
+    i8, f4 = ctx.pipe_rate(3), ctx.pipe_rate(4)
+    assert 0.5e6 < i8 < f4 < 20e6
+    ctx.sync()
+    with pytest.raises(ft.TnnsError):
+        ctx.pipe_rate(5)
+
+
+def _expand32_f4_numpy(s, z):
+    """numpy restatement of the library's 32-element e2m1 expansion (uint32 in, four uint32 out)."""
+    s = s.astype(np.uint32)
+    z = z.astype(np.uint32)
+    x = (s & np.uint32(0xCCCCCCCC)) | (~(z >> np.uint32(2)) & np.uint32(0x33333333))
+    y = ((s << np.uint32(2)) & np.uint32(0xCCCCCCCC)) | (~z & np.uint32(0x33333333))
+    a = np.uint32(0xAAAAAAAA)
+    return np.stack([x & a, (x << np.uint32(1)) & a, y & a, (y << np.uint32(1)) & a], axis=-1)
+
+
+IM2COL_LAYERS = [
+    (TNN, Layer(256, 14, 14, 256, 3, 3, 1, 1), 4),     # straddles images: 196 pixels per image, 128-row tiles
+    (TNN, Layer(256, 14, 14, 256, 5, 3, 1, 2), 8),     # 5 x 3 kernel, stride 2
+    (TBN, Layer(256, 10, 10, 100, 3, 3, 1, 2), 3),     # binary weights, kernel count below one tile
+    (TNN, Layer(1024, 14, 14, 1024, 5, 5, 1, 2), 2),   # 16 channel groups, four kernel tiles
+    (TNN, Layer(256, 7, 7, 32, 3, 3, 1, 2), 1),        # image far below 128 KiB
+    (TNN, Layer(512, 1, 1, 512, 1, 1, 0, 1), 8),       # fully connected
+    (TNN, Layer(250, 9, 11, 64, 3, 3, 2, 3), 3),       # channel tail, padding 2, stride 3
+    (TBN, Layer(512, 9, 11, 300, 3, 3, 0, 1), 3),      # no padding, ragged kernel tile
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("type_,layer,N", IM2COL_LAYERS, ids=lambda v: str(v).replace(" ", ""))
+def test_e2m1_image_and_im2col_tensor_copy_gemm(type_, layer, N, gpu_ctx, checker):
+    """The copy-engine route: the 4-bit image holds the expansion of the bit-plane image, and the GEMM
+    fed by im2col tensor copies equals the reference layer bit for bit, in both tensor layouts."""
+    ctx = gpu_ctx
+    case = make_case(type_, layer, N, 6100 + layer.C + layer.KN, "uniform")
+    wp = checker.pack_weights(wgt_ternary(type_), case.w, case.w_thr)
+    want = checker.conv(type_, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
+    w = ctx.upload_weights(type_, wp, layer.C, layer.KH, layer.KW)
+    shape = layer.shape(N)
+    assert ctx.im2col_supported(w, shape)
+    Cp = (layer.C + 63) // 64
+    nb_e = ft.api.e2m1_image_bytes(N, layer.C, layer.H, layer.W)
+    nb_p = ft.api.packed_image_bytes(True, N, layer.C, layer.H, layer.W)
+    assert nb_e == N * layer.H * layer.W * Cp * 32
+    d_t = ctx.to_device(case.thr)
+    d_y = ctx.malloc(want.nbytes)
+    d_e = ctx.malloc(nb_e)
+    d_p = ctx.malloc(nb_p)
+    try:
+        for layout in (ft.NCHW, ft.NHWC):
+            d_x = ctx.to_device(case.x if layout == ft.NCHW else to_nhwc(case.x))
+            ctx.quantise_e2m1(d_x, d_t, d_e, N, layer.C, layer.H, layer.W, layout)
+            ctx.quantise(True, d_x, d_t, d_p, N, layer.C, layer.H, layer.W, layout)
+            ctx.gemm_im2col(w, d_e, d_y, shape, case.alpha, layout)
+            ctx.sync()
+            planes = ctx.to_host(d_p, (N, 2, layer.H * layer.W, Cp, 2), np.uint32)   # [n][plane][pixel][ic][lo, hi]
+            e2m1 = ctx.to_host(d_e, (N, layer.H * layer.W, Cp, 2, 4), np.uint32)     # [n][pixel][ic][lo, hi][4 words]
+            assert np.array_equal(e2m1, _expand32_f4_numpy(planes[:, 0], planes[:, 1]))
+            got = ctx.to_host(d_y, want.shape if layout == ft.NCHW else (N, layer.OH, layer.OW, layer.KN), np.float32)
+            if layout == ft.NHWC:
+                got = to_nchw(got)
+            assert got.tobytes() == want.tobytes()
+            ctx.free(d_x)
+        # the layer entry point takes this route by itself and gives the same bytes
+        y = device_conv(ctx, case, wp, ft.NCHW, ft.PACK_AUTO, ft.GEMM_AUTO)
+        assert y.tobytes() == want.tobytes()
+    finally:
+        for p in (d_t, d_y, d_e, d_p):
+            ctx.free(p)
+        w.free()
+
+
+@pytest.mark.gpu
+def test_im2col_route_declines_what_it_cannot_do(gpu_ctx, checker):
+    """Binary activations (padding is +1, which a zero-filling copy cannot produce) and channel counts
+    that do not fill 128-byte chunks stay on the gathering GEMM; asking for the route anyway is an error."""
+    ctx = gpu_ctx
+    for type_, layer in ((BTN, Layer(256, 8, 8, 64, 3, 3, 1, 1)), (TNN, Layer(128, 8, 8, 64, 3, 3, 1, 1))):
+        case = make_case(type_, layer, 2, 77, "uniform")
+        wp = checker.pack_weights(wgt_ternary(type_), case.w, case.w_thr)
+        w = ctx.upload_weights(type_, wp, layer.C, layer.KH, layer.KW)
+        shape = layer.shape(2)
+        assert not ctx.im2col_supported(w, shape)
+        d = ctx.malloc(1 << 20)
+        with pytest.raises(ft.TnnsError):
+            ctx.gemm_im2col(w, d, d, shape, 0.5)
+        ctx.free(d)
+        want = checker.conv(type_, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
+        assert device_conv(ctx, case, wp, ft.NCHW, ft.PACK_AUTO, ft.GEMM_AUTO).tobytes() == want.tobytes()
+        w.free()
