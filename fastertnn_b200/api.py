@@ -295,9 +295,10 @@ class Context:
         """fp32 tensor -> 4-bit operand image ([n][pixel][C/2 bytes], ternary activations)."""
         _check(self.lib.tnns_cuda_quantise_e2m1(self.handle, d_x, d_thr, d_image, N, C_, H, W, layout, stream))
 
-    def gemm_im2col(self, w: Weights, d_image: int, d_y: int, shape: Shape, alpha: float, layout=NCHW, stream=0):
-        """GEMM + PReLU whose activation tiles the copy engine gathers from the 4-bit image."""
-        _check(self.lib.tnns_cuda_gemm_im2col(self.handle, w.handle, d_image, d_y, C.byref(shape), alpha, layout, stream))
+    def gemm_im2col(self, w: Weights, d_image: int, d_y: int, shape: Shape, alpha: float, layout=NCHW, stream=0, pairs=0):
+        """GEMM + PReLU whose activation tiles the copy engine gathers from the 4-bit image.
+        pairs: 0 = by size, 1 = single blocks, 2 = block pairs (tcgen05.mma.cta_group::2)."""
+        _check(self.lib.tnns_cuda_gemm_im2col(self.handle, w.handle, d_image, d_y, C.byref(shape), alpha, layout, pairs, stream))
 
     def im2col_supported(self, w: Weights, shape: Shape) -> bool:
         return bool(self.lib.tnns_cuda_im2col_supported(w.handle, C.byref(shape)))
@@ -340,6 +341,11 @@ class Context:
         p = self.malloc(max(a.nbytes, 16))
         _check(self.lib.tnns_cuda_memcpy_h2d(self.handle, p, _ptr(a), a.nbytes))
         return p
+
+    def fill(self, p: int, a: np.ndarray):
+        """Overwrite an existing device buffer with a host array."""
+        a = np.ascontiguousarray(a)
+        _check(self.lib.tnns_cuda_memcpy_h2d(self.handle, p, _ptr(a), a.nbytes))
 
     def to_host(self, p: int, shape, dtype) -> np.ndarray:
         out = np.empty(shape, dtype=dtype)

@@ -343,7 +343,8 @@ int tnns_cuda_quantise_e2m1(tnns_cuda_ctx* ctx, const float* d_x, const float* d
 }
 
 int tnns_cuda_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const tnns_shape_t* s,
-                          float alpha, int layout, void* stream) {
+                          float alpha, int layout, int pairs, void* stream) {
+    if (pairs < 0 || pairs > 2) return tnns_fail(TNNS_ERR_INVALID, "pairs must be 0, 1 or 2");
     if (!ctx || !w || !d_image || !d_y) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
     TnnsGeom g;
     int rc = tnns_make_geom(s, &g);
@@ -353,7 +354,7 @@ int tnns_cuda_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const 
     if (layout != TNNS_NCHW && layout != TNNS_NHWC) return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
     if (w->device != ctx->device) return tnns_fail(TNNS_ERR_INVALID, "weights live on device %d, context on %d", w->device, ctx->device);
     if (reinterpret_cast<uintptr_t>(d_image) & 31) return tnns_fail(TNNS_ERR_INVALID, "image must be 32-byte aligned");
-    return tnns_launch_gemm_im2col(ctx, w, d_image, d_y, g, alpha, layout, (cudaStream_t)stream);
+    return tnns_launch_gemm_im2col(ctx, w, d_image, d_y, g, alpha, layout, (cudaStream_t)stream, pairs);
 }
 
 // --- chained layers without the fp32 round trip ------------------------------------------------

@@ -55,17 +55,24 @@ constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_EXP0 = 2;
 // im2col tensor copy from a 4-bit (e2m1) image of the layer input -- 128 output pixels x 128 bytes
 // (256 channels of one filter tap), zero-filled outside the image, written in the swizzled layout
 // the MMA reads.  No expander warps then: producer warp, MMA warp, eight epilogue warps.
-template <int BN, int MT, bool F4, bool ATMA = false>
+// CG = 2 (tensor-copy form only) pairs two blocks -- a cluster of two, on the two SMs of one TPC --
+// on one 256-row tile: tcgen05.mma.cta_group::2, issued by the first block for both, multiplies
+// each block's own 128 activation rows with the whole weight tile, of which each block holds
+// half.  A block then receives 32 KB instead of 48 KB per stage from L2 and the ring is six deep.
+// Both blocks' tensor copies report to the first block's "full" barrier; its commits release the
+// stage and publish the accumulator in both blocks (multicast arrive).
+template <int BN, int MT, bool F4, bool ATMA = false, int CG = 1>
 struct TcCfg {
     static_assert(!ATMA || (F4 && MT == 1), "tensor-copy activations: 4-bit form, one accumulator per block");
-    static constexpr int NSTG = (MT == 1) ? 4 : 3;                 // smem ring depth
-    static constexpr int A_STAGE = MT * A_SUB, B_STAGE = BN * KCH;
+    static_assert(CG == 1 || (CG == 2 && ATMA), "block pairs: tensor-copy form only");
+    static constexpr int NSTG = (CG == 2) ? 6 : ((MT == 1) ? 4 : 3);  // smem ring depth
+    static constexpr int A_STAGE = MT * A_SUB, B_STAGE = (BN / CG) * KCH;
     static constexpr bool OVL = F4 && MT == 1 && BN == 256;        // overlapping accumulator sets
     static constexpr int NBUF = (OVL || MT * BN <= (F4 ? 128 : 256)) ? 2 : 1;  // accumulator sets in tensor memory
     static constexpr int ACC_OFF = OVL ? BN - 32 : MT * BN;        // column distance between the sets
     // epilogue warps per lane quadrant: two share each quadrant's columns where the drain is
     // not (or only partly) hidden behind the next tile's MMAs
-    static constexpr int EPW = (((NBUF == 1 || OVL) && MT == 1) || ATMA) ? 2 : 1;
+    static constexpr int EPW = ATMA ? 2 : (((NBUF == 1 || OVL) && MT == 1) ? 2 : 1);
     // expander groups (stages expanded concurrently); 22 warps per block in every MT = 1 form
     static constexpr int NG = ATMA ? 0 : ((MT == 1) ? (EPW == 2 ? 3 : 4) : 2);
     static constexpr int WARP_EPI0 = WARP_EXP0 + 4 * MT * NG;
@@ -95,6 +102,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
         : "r"(bar), "r"(parity)
         : "memory");
     return ok != 0;
+}
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+// Address (shared::cluster window) of the same shared-memory offset in block `cta` of the cluster.
+__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta));
+    return r;
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    __syncwarp();
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
 
 // Bounded wait: gives up after about a second, raises the status word and the block-wide
@@ -130,6 +157,21 @@ __device__ __forceinline__ void tma_im2col_g2s(uint32_t dst_smem, const void* tm
         ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(kw), "h"(kh)
         : "memory");
 }
+// Block-pair forms of the tensor copies: the data lands in the executing block's shared memory,
+// the bytes are reported to `bar`, which may live in the other block of the pair (an address in
+// the shared::cluster window).  No multicast: every block fetches its own tile.
+__device__ __forceinline__ void tma_im2col_g2s_pair(uint32_t dst_smem, const void* tmap, int c, int w, int h, int n, unsigned short kw,
+                                                    unsigned short kh, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.4d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(kw), "h"(kh)
+        : "memory");
+}
+__device__ __forceinline__ void tma_tile2d_g2s_pair(uint32_t dst_smem, const void* tmap, int x, int y, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y)
+                 : "memory");
+}
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
 __device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
@@ -142,6 +184,22 @@ __device__ __forceinline__ void tc_mma_f4(uint32_t d_tmem, uint64_t a_desc, uint
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %6, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+        : "memory");
+}
+// Block-pair forms, issued by the first block of the pair for both: the commit arrives on the
+// barrier at the same shared-memory offset in both blocks.
+__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"((unsigned short)3)
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma_f4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
+                                               uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %6, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
         ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
         : "memory");
 }
@@ -255,15 +313,17 @@ struct GemmArgs {
     int H, W, OW, Cp, SH, SW, PH, PW;
 };
 
-template <int BN, int MT, bool F4, bool ATMA>
-__global__ void __launch_bounds__(TcCfg<BN, MT, F4, ATMA>::NTHREADS, 1) gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a) {
-    using Cfg = TcCfg<BN, MT, F4, ATMA>;
+template <int BN, int MT, bool F4, bool ATMA, int CG>
+__global__ void __launch_bounds__(TcCfg<BN, MT, F4, ATMA, CG>::NTHREADS, 1)
+gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b) {
+    using Cfg = TcCfg<BN, MT, F4, ATMA, CG>;
     constexpr int NSTG = Cfg::NSTG, A_STAGE = Cfg::A_STAGE, B_STAGE = Cfg::B_STAGE, NBUF = Cfg::NBUF, WARP_EPI0 = Cfg::WARP_EPI0, NG = Cfg::NG, EPW = Cfg::EPW;
-    constexpr int BMT = MT * BM;  // rows per block tile
+    constexpr int BMT = MT * BM;      // rows per block
+    constexpr int TILE_M = CG * BMT;  // rows per tile (a block pair shares one 256-row tile)
     // instruction descriptor: i8 -- s32 accumulate (2<<4), signed 8-bit A and B (1<<7, 1<<10);
     // mxf4 -- e2m1 A and B (1<<7, 1<<10), ue8m0 scales (1<<23); both K-major, N>>3 at bit 17, M>>4 at bit 24
     constexpr uint32_t IDESC = (F4 ? (1u << 23) : (2u << 4)) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) |
-                               ((uint32_t)(BM >> 4) << 24);
+                               ((uint32_t)((CG * BM) >> 4) << 24);
     constexpr bool OVL = Cfg::OVL;
     constexpr int ACC_OFF = Cfg::ACC_OFF;
     constexpr uint32_t SF_COL = 480;  // first tensor-memory column of the (all-ones) block scales
@@ -281,8 +341,11 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4, ATMA>::NTHREADS, 1) gemm_tc_
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nchunks = F4 ? p.Kp / 4 : p.Kp / 2;  // stages per tile
     const int ntn = (p.KN + BN - 1) / BN;
-    const long long ntm = (p.M + BMT - 1) / BMT;
+    const long long ntm = (p.M + TILE_M - 1) / TILE_M;
     const long long ntiles = ntm * ntn;
+    // a unit = the block (CG = 1) or the block pair (CG = 2) that walks one tile sequence
+    const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;
+    const long long unit = blockIdx.x / CG, nunits = gridDim.x / CG;
 
     if (tid == 0) {
         for (int s = 0; s < NSTG; s++) {
@@ -291,17 +354,25 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4, ATMA>::NTHREADS, 1) gemm_tc_
         }
         for (int b = 0; b < 2; b++) {
             mbar_init(bar_tfull + 8 * b, 1);
-            mbar_init(bar_tempty + 8 * b, 4 * MT * EPW);  // the epilogue warps
+            mbar_init(bar_tempty + 8 * b, CG * 4 * MT * EPW);  // the epilogue warps (of both blocks of a pair)
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    __syncwarp();
     if (warp == WARP_MMA) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        if (CG == 2) {
+            // both blocks of the pair allocate, from the same warp index, the same columns
+            asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+        } else {
+            asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512u) : "memory");
+            asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+        }
     }
     tc_fence_before();
-    __syncthreads();
+    // pair: no remote arrive, copy completion or multicast commit may reach a barrier before its block initialised it
+    if (CG == 2) cluster_sync_all(); else __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     if (F4) {
@@ -319,20 +390,23 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4, ATMA>::NTHREADS, 1) gemm_tc_
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
         }
         tc_fence_before();
-        __syncthreads();
+        if (CG == 2) cluster_sync_all(); else __syncthreads();  // pair: the first block's MMAs read both blocks' scales
         tc_fence_after();
     }
 
     if (warp == WARP_TMA) {
         if (lane == 0) {
             uint32_t it = 0;
-            for (long long t = blockIdx.x; t < ntiles; t += gridDim.x) {
+            // pair: both blocks' copies report to the first block's barrier
+            const uint32_t bar_full_lead = (CG == 2) ? mapa_shared(bar_full, 0) : bar_full;
+            for (long long t = unit; t < ntiles; t += nunits) {
                 const int n_tile = (int)(t % ntn);
                 const unsigned char* src = p.Bimg + (size_t)n_tile * nchunks * B_STAGE;
-                // tensor-copy activations: base pixel of the tile's first output pixel
+                // tensor-copy activations: base pixel of the block's first output pixel
                 int a_n = 0, a_h = 0, a_w = 0;
                 if (ATMA) {
-                    const long long row0 = (t / ntn) * BMT;
+                    long long row0 = (t / ntn) * TILE_M + (long long)rank * BMT;
+                    if (row0 >= p.M) row0 = 0;  // second block of a pair past the last row: any valid pixels, never stored
                     a_n = (int)(row0 / p.OHW);
                     const int rem = (int)(row0 - (long long)a_n * p.OHW);
                     const int oh = rem / p.OW;
@@ -342,10 +416,19 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4, ATMA>::NTHREADS, 1) gemm_tc_
                 for (int c = 0; c < nchunks; c++, it++) {
                     const int s = it % NSTG;
                     if (!mbar_wait(bar_empty + 8 * s, ((it / NSTG) & 1) ^ 1, abort_flag, p.status, 1)) goto done;
+                    if (CG == 2) {
+                        // the stage's four plane words are four neighbouring channel groups of one tap
+                        const uint32_t e = __ldg(p.jtab + 4 * c);
+                        if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, CG * (B_STAGE + A_STAGE));
+                        tma_tile2d_g2s_pair(smem_u32(sB + s * B_STAGE), &tmap_b, 0, (n_tile * nchunks + c) * BN + (int)rank * (BN / CG),
+                                            bar_full_lead + 8 * s);
+                        tma_im2col_g2s_pair(smem_u32(sA + s * A_STAGE), &tmap_a, (int)(e & 0xFFFF) * 32, a_w, a_h, a_n,
+                                            (unsigned short)((e >> 16) & 0xFF), (unsigned short)(e >> 24), bar_full_lead + 8 * s);
+                        continue;
+                    }
                     mbar_arrive_expect_tx(bar_full + 8 * s, ATMA ? B_STAGE + A_STAGE : B_STAGE);
                     bulk_g2s(smem_u32(sB + s * B_STAGE), src + (size_t)c * B_STAGE, B_STAGE, bar_full + 8 * s);
                     if (ATMA) {
-                        // the stage's four plane words are four neighbouring channel groups of one tap
                         const uint32_t e = __ldg(p.jtab + 4 * c);
                         tma_im2col_g2s(smem_u32(sA + s * A_STAGE), &tmap_a, (int)(e & 0xFFFF) * 32, a_w, a_h, a_n,
                                        (unsigned short)((e >> 16) & 0xFF), (unsigned short)(e >> 24), bar_full + 8 * s);
@@ -354,9 +437,9 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4, ATMA>::NTHREADS, 1) gemm_tc_
             }
         }
     } else if (warp == WARP_MMA) {
-        if (lane == 0) {
+        if (lane == 0 && rank == 0) {  // pair: the first block issues for both
             uint32_t it = 0, lt = 0;
-            for (long long t = blockIdx.x; t < ntiles; t += gridDim.x, lt++) {
+            for (long long t = unit; t < ntiles; t += nunits, lt++) {
                 const int buf = lt % NBUF;
                 // overlapping sets: one barrier, completed once per tile when the columns shared
                 // with the previous tile's set have been drained; otherwise one barrier per set
@@ -373,13 +456,16 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4, ATMA>::NTHREADS, 1) gemm_tc_
                         const uint64_t da = make_desc(smem_u32(sA + s * A_STAGE + mt * A_SUB));
 #pragma unroll
                         for (int k = 0; k < KCH / 32; k++) {
-                            if (F4) tc_mma_f4(d_tmem + mt * BN, da + 2 * k, db + 2 * k, IDESC, tmem_base + SF_COL, tmem_base + SF_COL + 16, (c | k) ? 1u : 0u);
+                            if (CG == 2) tc_mma_f4_pair(d_tmem, da + 2 * k, db + 2 * k, IDESC, tmem_base + SF_COL, tmem_base + SF_COL + 16, (c | k) ? 1u : 0u);
+                            else if (F4) tc_mma_f4(d_tmem + mt * BN, da + 2 * k, db + 2 * k, IDESC, tmem_base + SF_COL, tmem_base + SF_COL + 16, (c | k) ? 1u : 0u);
                             else tc_mma_i8(d_tmem + mt * BN, da + 2 * k, db + 2 * k, IDESC, (c | k) ? 1u : 0u);
                         }
                     }
-                    tc_commit(bar_empty + 8 * s);  // stage reusable once these MMAs have read it
+                    // stage reusable once these MMAs have read it (pair: in both blocks)
+                    if (CG == 2) tc_commit_pair(bar_empty + 8 * s); else tc_commit(bar_empty + 8 * s);
                 }
-                tc_commit(bar_tfull + 8 * buf);    // accumulator complete
+                // accumulator complete (pair: each block's epilogue drains its own 128 rows)
+                if (CG == 2) tc_commit_pair(bar_tfull + 8 * buf); else tc_commit(bar_tfull + 8 * buf);
             }
         }
     } else if (!ATMA && warp < WARP_EPI0) {
@@ -512,9 +598,10 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4, ATMA>::NTHREADS, 1) gemm_tc_
         const int bias_magic = 0x4B400000 + p.acc_bias;
         const float bias_f = (float)p.acc_bias;  // +0.0f when there is none: a + 0.0f also turns a -0 sum into +0
         uint32_t lt = 0;
-        for (long long t = blockIdx.x; t < ntiles; t += gridDim.x, lt++) {
+        const uint32_t bar_release = (CG == 2 && rank != 0) ? mapa_shared(bar_tempty, 0) : 0u;  // pair: the first block's barrier
+        for (long long t = unit; t < ntiles; t += nunits, lt++) {
             const int buf = lt % NBUF;
-            const long long m0 = (t / ntn) * BMT + sub * BM;
+            const long long m0 = (t / ntn) * TILE_M + (long long)rank * BMT + sub * BM;
             const int n0 = (int)(t % ntn) * BN;
             if (!mbar_wait(bar_tfull + 8 * buf, (lt / NBUF) & 1, abort_flag, p.status, 5)) goto done;
             tc_fence_after();
@@ -550,7 +637,10 @@ __global__ void __launch_bounds__(TcCfg<BN, MT, F4, ATMA>::NTHREADS, 1) gemm_tc_
                     // the columns back before storing it
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) mbar_arrive(OVL ? bar_tempty : bar_tempty + 8 * buf);
+                    if (lane == 0) {
+                        if (CG == 2 && rank != 0) mbar_arrive_cluster(bar_release + (OVL ? 0 : 8 * buf));
+                        else mbar_arrive(OVL ? bar_tempty : bar_tempty + 8 * buf);
+                    }
                 }
                 if (row_ok) {
                     // int -> float without the conversion unit: for |a| < 2^22 the float with bit
@@ -626,10 +716,13 @@ done:
         for (int i = 0; i < 1000; i++) __nanosleep(1000);
     }
     tc_fence_before();
-    __syncthreads();
+    // pair: neither block may leave (and release its shared and tensor memory) while the other can
+    // still arrive on its barriers or the first block's MMAs still use them
+    if (CG == 2) cluster_sync_all(); else __syncthreads();
     if (warp == WARP_MMA) {
         tc_fence_after();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        if (CG == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
+        else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
 }
 
@@ -721,15 +814,44 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(int iters, unsigned in
     }
 }
 
-template <int BN, int MT, bool F4, bool ATMA = false>
-int launch_cfg(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream, const CUtensorMap* tmap_a = nullptr) {
-    using Cfg = TcCfg<BN, MT, F4, ATMA>;
-    auto kern = gemm_tc_kernel<BN, MT, F4, ATMA>;
+template <int BN, int MT, bool F4, bool ATMA = false, int CG = 1>
+int launch_cfg(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream, const CUtensorMap* tmap_a = nullptr,
+               const CUtensorMap* tmap_b = nullptr) {
+    using Cfg = TcCfg<BN, MT, F4, ATMA, CG>;
+    auto kern = gemm_tc_kernel<BN, MT, F4, ATMA, CG>;
     static const CUtensorMap no_map = {};
     TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
-    const long long tiles = ((a.M + MT * BM - 1) / (MT * BM)) * ((a.KN + BN - 1) / BN);
-    const int grid = (int)std::min<long long>(tiles, ctx->sm_count);
-    kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, stream>>>(a, tmap_a ? *tmap_a : no_map);
+    const long long tiles = ((a.M + CG * MT * BM - 1) / (CG * MT * BM)) * ((a.KN + BN - 1) / BN);
+    if (CG == 1) {
+        const int grid = (int)std::min<long long>(tiles, ctx->sm_count);
+        kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, stream>>>(a, tmap_a ? *tmap_a : no_map, no_map);
+    } else {
+        // block pairs: clusters of two consecutive blocks, as many as can be resident at once (the
+        // kernel is persistent; a pair that had to wait for a free TPC would start its whole tile
+        // sequence after the others finished)
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(CG * (ctx->sm_count / CG));
+        cfg.blockDim = dim3(Cfg::NTHREADS);
+        cfg.dynamicSmemBytes = Cfg::SMEM;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = CG;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        static int max_pairs[64] = {0};  // per device
+        int& mp = max_pairs[ctx->device & 63];
+        if (mp == 0) {
+            int n = 0;
+            TNNS_CUDA_TRY(cudaOccupancyMaxActiveClusters(&n, kern, &cfg));
+            if (n <= 0) return tnns_fail(TNNS_ERR_CUDA, "no block pair of the tensor-core GEMM fits this device");
+            mp = std::min(n, ctx->sm_count / CG);
+        }
+        cfg.gridDim = dim3(CG * (int)std::min<long long>(tiles, mp));
+        TNNS_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a, tmap_a ? *tmap_a : no_map, tmap_b ? *tmap_b : no_map));
+    }
     tnns_count_launch();
     TNNS_CUDA_TRY(cudaGetLastError());
     return TNNS_OK;
@@ -880,8 +1002,35 @@ int encode_im2col_map(CUtensorMap* map, const void* d_image, const TnnsGeom& g) 
 }
 }  // namespace
 
+namespace {
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// The expanded weight image as rows of 128 bytes; a box = the 128 rows one block of a pair holds
+// of one stage.  The image is stored swizzled already, so the copy itself does not swizzle.
+int encode_weight_map(CUtensorMap* map, const tnns_cuda_weights* w, int BN) {
+    static EncodeTiledFn encode = nullptr;
+    if (!encode) {
+        void* fn = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        TNNS_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
+        if (q != cudaDriverEntryPointSuccess || !fn) return tnns_fail(TNNS_ERR_UNSUPPORTED, "the driver offers no cuTensorMapEncodeTiled");
+        encode = reinterpret_cast<EncodeTiledFn>(fn);
+    }
+    const cuuint64_t dims[2] = {KCH, (cuuint64_t)(w->f4_bytes / KCH)};
+    const cuuint64_t strides[1] = {KCH};
+    const cuuint32_t box[2] = {KCH, (cuuint32_t)(BN / 2)};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w->d_f4, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return tnns_fail(TNNS_ERR_CUDA, "cuTensorMapEncodeTiled failed with driver error %d", (int)r);
+    return TNNS_OK;
+}
+}  // namespace
+
+// pairs: 0 = decide by size, 1 = single blocks, 2 = block pairs (kernel tile of 256 only)
 int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const TnnsGeom& g, float alpha,
-                            int layout, cudaStream_t stream) {
+                            int layout, cudaStream_t stream, int pairs) {
     const long long M = (long long)g.N * g.OH * g.OW;
     if (M == 0) return TNNS_OK;
     if (!tnns_im2col_supported(w, g)) return tnns_fail(TNNS_ERR_UNSUPPORTED, "layer shape or type outside the tensor-copy activation path");
@@ -909,7 +1058,17 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     a.img = nullptr;
     a.jtab = w->d_jtab;
     a.H = g.H; a.W = g.W; a.OW = g.OW; a.Cp = g.Cp; a.SH = g.SH; a.SW = g.SW; a.PH = g.PH; a.PW = g.PW;
-    switch (tnns_i8_tile_n(w->KN)) {
+    const int bn = tnns_i8_tile_n(w->KN);
+    if (pairs == 2 && bn != 256) return tnns_fail(TNNS_ERR_UNSUPPORTED, "block pairs need more than 128 kernels");
+    // Block pairs once there are enough 256-row tiles to occupy every SM pair.
+    const long long pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((w->KN + bn - 1) / bn);
+    if (bn == 256 && (pairs == 2 || (pairs == 0 && pair_tiles >= ctx->sm_count / 2))) {
+        CUtensorMap map_b;
+        rc = encode_weight_map(&map_b, w, bn);
+        if (rc) return rc;
+        return launch_cfg<256, 1, true, true, 2>(ctx, a, stream, &map, &map_b);
+    }
+    switch (bn) {
         case 64: return launch_cfg<64, 1, true, true>(ctx, a, stream, &map);
         case 128: return launch_cfg<128, 1, true, true>(ctx, a, stream, &map);
         default: return launch_cfg<256, 1, true, true>(ctx, a, stream, &map);

@@ -96,7 +96,7 @@ int tnns_launch_quantise(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, con
 // an e2m1 image; needs ternary activations and a channel count that fills 128-byte chunks
 bool tnns_im2col_supported(const tnns_cuda_weights* w, const TnnsGeom& g);
 int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const TnnsGeom& g,
-                            float alpha, int layout, cudaStream_t stream);
+                            float alpha, int layout, cudaStream_t stream, int pairs = 0);
 
 int tnns_launch_pack_weights(tnns_cuda_ctx* ctx, bool ternary, const float* d_w, const float* d_thr, void* d_packed, int KN, int C,
                              int KH, int KW, cudaStream_t stream);

@@ -261,13 +261,16 @@ int tnns_cuda_gemm_implicit(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
  * 128-pixel x 256-channel activation tile of a filter tap as one im2col tensor copy (zero fill
  * outside the image = the reference's padding value, src/tnns/ternarize2row_avx2.c:438-452)
  * straight into the layout the tensor core reads: no warp expands or gathers anything.  Same
- * result as tnns_cuda_pack + tnns_cuda_gemm; tnns_cuda_conv prefers this route where it applies. */
+ * result as tnns_cuda_pack + tnns_cuda_gemm; tnns_cuda_conv prefers this route where it applies.
+ * pairs: 1 = one block per 128-row tile; 2 = block pairs (two SMs share a 256-row tile through
+ * tcgen05.mma.cta_group::2, each holding half of the weight tile; layers with more than 128
+ * kernels); 0 = pairs once there are enough 256-row tiles for every SM pair. */
 size_t tnns_e2m1_image_bytes(int N, int C, int H, int W);
 int tnns_cuda_im2col_supported(const tnns_cuda_weights* w, const tnns_shape_t* s);
 int tnns_cuda_quantise_e2m1(tnns_cuda_ctx* ctx, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H, int W,
                             int layout, void* stream);
 int tnns_cuda_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const tnns_shape_t* s,
-                          float alpha, int layout, void* stream);
+                          float alpha, int layout, int pairs, void* stream);
 int tnns_cuda_gemm_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const int64_t* d_a, void* d_image,
                               const float* d_thr_next, int next_ternary, int N, int OH, int OW, float alpha, void* stream);
 int tnns_cuda_im2row_packed(tnns_cuda_ctx* ctx, int ternary, const void* d_image, int64_t* d_packed, const tnns_shape_t* s,

@@ -480,7 +480,7 @@ def test_e2m1_image_and_im2col_tensor_copy_gemm(type_, layer, N, gpu_ctx, checke
             d_x = ctx.to_device(case.x if layout == ft.NCHW else to_nhwc(case.x))
             ctx.quantise_e2m1(d_x, d_t, d_e, N, layer.C, layer.H, layer.W, layout)
             ctx.quantise(True, d_x, d_t, d_p, N, layer.C, layer.H, layer.W, layout)
-            ctx.gemm_im2col(w, d_e, d_y, shape, case.alpha, layout)
+            ctx.gemm_im2col(w, d_e, d_y, shape, case.alpha, layout, 0, 1)   # single blocks
             ctx.sync()
             planes = ctx.to_host(d_p, (N, 2, layer.H * layer.W, Cp, 2), np.uint32)   # [n][plane][pixel][ic][lo, hi]
             e2m1 = ctx.to_host(d_e, (N, layer.H * layer.W, Cp, 2, 4), np.uint32)     # [n][pixel][ic][lo, hi][4 words]
@@ -489,6 +489,18 @@ def test_e2m1_image_and_im2col_tensor_copy_gemm(type_, layer, N, gpu_ctx, checke
             if layout == ft.NHWC:
                 got = to_nchw(got)
             assert got.tobytes() == want.tobytes()
+            if layer.KN > 128:
+                # block pairs (two SMs on one 256-row tile) forced at a size the heuristic would not pick
+                ctx.fill(d_y, np.full(want.size, np.nan, np.float32))
+                ctx.gemm_im2col(w, d_e, d_y, shape, case.alpha, layout, 0, 2)
+                ctx.sync()
+                got2 = ctx.to_host(d_y, got.shape if layout == ft.NCHW else (N, layer.OH, layer.OW, layer.KN), np.float32)
+                if layout == ft.NHWC:
+                    got2 = to_nchw(got2)
+                assert got2.tobytes() == want.tobytes()
+            else:
+                with pytest.raises(ft.TnnsError):
+                    ctx.gemm_im2col(w, d_e, d_y, shape, case.alpha, layout, 0, 2)
             ctx.free(d_x)
         # the layer entry point takes this route by itself and gives the same bytes
         y = device_conv(ctx, case, wp, ft.NCHW, ft.PACK_AUTO, ft.GEMM_AUTO)
