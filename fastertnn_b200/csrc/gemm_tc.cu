@@ -32,6 +32,7 @@
 #include <vector>
 
 #include "internal.h"
+#include "mbar.cuh"
 
 namespace {
 
@@ -79,68 +80,6 @@ struct TcCfg {
     static constexpr int NTHREADS = 32 * (2 + 4 * MT * NG + 4 * MT * EPW);
     static constexpr size_t SMEM = 1024 + (size_t)NSTG * (A_STAGE + B_STAGE) + 256;
 };
-constexpr unsigned STATUS_WAIT_EXPIRED = 0x100;
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(ok)
-        : "r"(bar), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-
-__device__ __forceinline__ uint32_t cluster_ctarank() {
-    uint32_t r;
-    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
-    return r;
-}
-// Address (shared::cluster window) of the same shared-memory offset in block `cta` of the cluster.
-__device__ __forceinline__ uint32_t mapa_shared(uint32_t addr, uint32_t cta) {
-    uint32_t r;
-    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(addr), "r"(cta));
-    return r;
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    __syncwarp();
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-
-// Bounded wait: gives up after about a second, raises the status word and the block-wide
-// abort flag.  Returns false when the caller must leave its loop.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, unsigned int* status, unsigned code) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 256; i++)
-            if (mbar_try_wait(bar, parity)) return true;
-        if (*abort_flag) return false;
-        if (clock64() - t0 > 2000000000LL) {
-            *abort_flag = 1;
-            atomicOr(status, STATUS_WAIT_EXPIRED | code);
-            return false;
-        }
-    }
-}
 
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem), "l"(src),
@@ -1003,28 +942,10 @@ int encode_im2col_map(CUtensorMap* map, const void* d_image, const TnnsGeom& g) 
 }  // namespace
 
 namespace {
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
-                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
 // The expanded weight image as rows of 128 bytes; a box = the 128 rows one block of a pair holds
 // of one stage.  The image is stored swizzled already, so the copy itself does not swizzle.
 int encode_weight_map(CUtensorMap* map, const tnns_cuda_weights* w, int BN) {
-    static EncodeTiledFn encode = nullptr;
-    if (!encode) {
-        void* fn = nullptr;
-        cudaDriverEntryPointQueryResult q;
-        TNNS_CUDA_TRY(cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &q));
-        if (q != cudaDriverEntryPointSuccess || !fn) return tnns_fail(TNNS_ERR_UNSUPPORTED, "the driver offers no cuTensorMapEncodeTiled");
-        encode = reinterpret_cast<EncodeTiledFn>(fn);
-    }
-    const cuuint64_t dims[2] = {KCH, (cuuint64_t)(w->f4_bytes / KCH)};
-    const cuuint64_t strides[1] = {KCH};
-    const cuuint32_t box[2] = {KCH, (cuuint32_t)(BN / 2)};
-    const cuuint32_t estr[2] = {1, 1};
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, w->d_f4, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                              CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return tnns_fail(TNNS_ERR_CUDA, "cuTensorMapEncodeTiled failed with driver error %d", (int)r);
-    return TNNS_OK;
+    return tnns_tensor_map_2d(map, 1, w->d_f4, KCH, w->f4_bytes / KCH, KCH, KCH, BN / 2);
 }
 }  // namespace
 

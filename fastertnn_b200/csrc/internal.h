@@ -92,6 +92,14 @@ int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const vo
 #define TNNS_IMG_E2M1 2
 int tnns_launch_quantise(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
                          int W, int layout, cudaStream_t stream, int format = TNNS_IMG_PLANES);
+// the same for NCHW input whose rows the copy engine can fetch (H*W a multiple of four floats,
+// 16-byte aligned base): tensor copies into a shared-memory ring instead of register loads
+bool tnns_quantise_tma_supported(const float* d_x, int H, int W, int layout);
+int tnns_launch_quantise_tma(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
+                             int W, cudaStream_t stream, int format);
+// driver-encoded descriptor of a two-dimensional tensor for the copy engine (128 bytes at `map`)
+int tnns_tensor_map_2d(void* map, int elem_bytes, const void* base, unsigned long long dim0, unsigned long long dim1,
+                       unsigned long long stride1_bytes, unsigned box0, unsigned box1);
 // 4-bit GEMM + PReLU whose activation tiles the copy engine gathers (im2col tensor copies) from
 // an e2m1 image; needs ternary activations and a channel count that fills 128-byte chunks
 bool tnns_im2col_supported(const tnns_cuda_weights* w, const TnnsGeom& g);

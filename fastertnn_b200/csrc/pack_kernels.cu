@@ -464,6 +464,8 @@ int tnns_launch_quantise(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, con
     if (N == 0) return TNNS_OK;
     if (format != TNNS_IMG_PLANES && format != TNNS_IMG_E2M1) return tnns_fail(TNNS_ERR_INVALID, "unknown image format %d", format);
     if (format == TNNS_IMG_E2M1 && !ternary) return tnns_fail(TNNS_ERR_UNSUPPORTED, "the 4-bit image holds ternary activations only");
+    if (tnns_quantise_tma_supported(d_x, H, W, layout))
+        return tnns_launch_quantise_tma(ctx, ternary, d_x, d_thr, d_image, N, C, H, W, stream, format);
     if (layout != TNNS_NCHW && layout != TNNS_NHWC) return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
     TnnsGeom g;
     g.N = N; g.C = C; g.H = H; g.W = W; g.KN = 1; g.KH = g.KW = 1; g.PH = g.PW = 0; g.SH = g.SW = 1;

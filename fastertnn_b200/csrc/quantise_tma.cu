@@ -1,0 +1,178 @@
+// Quantise-only kernel fed by the copy engine (the thresholding half of t2r_p2_opt / b2r,
+// reference: src/tnns/ternarize2row_avx2.c:438-452, src/tnns/binarize2row_avx2.c:15-22, without
+// the im2row scatter) for NCHW input.
+//
+// The input is read as a two-dimensional tensor: one row per (image, channel) with H*W floats.
+// A persistent block walks work items (image, band of 128 pixels, group of 64 channels); the
+// producer thread requests each item as ONE tensor copy -- a box of 128 pixels x 64 channels,
+// 32 KB -- into a four-deep shared-memory ring, so about 128 KB per SM are in flight towards HBM
+// at any time without holding a single register.  Two groups of four consumer warps take the
+// stages alternately: thread = pixel, 64 conflict-free shared-memory reads (lanes read
+// consecutive floats), the sign and non-zero bits pushed into the plane words branch-free, the
+// stage handed back, then the pixel's 64 channels stored as one 64-bit word per plane or as
+// 32 bytes of e2m1 operands.  The kernel is bound by HBM traffic: 4 bytes read per input value.
+#include <cuda.h>
+
+#include <algorithm>
+
+#include "internal.h"
+#include "mbar.cuh"
+
+namespace {
+
+constexpr int QL = 128;                      // pixels per band = threads per consumer group
+constexpr int QC = 64;                       // channels per stage = one plane word
+constexpr int QSTG = 4;                      // ring depth
+constexpr int QGROUPS = 2;                   // consumer groups
+// A stage must always go to the same group: a group works through its items in order, so its
+// successive waits on one stage's barrier are successive phases.  With a ring depth that is not a
+// multiple of the group count a group would meet a stage again two phases later, and a parity
+// wait cannot tell phase p from phase p + 2.
+static_assert(QSTG % QGROUPS == 0, "every stage of the ring belongs to one consumer group");
+constexpr int QTHREADS = 32 + QGROUPS * QL;  // producer warp + consumers
+constexpr int QSTAGE_BYTES = QL * QC * 4;
+constexpr size_t QSMEM = 1024 + (size_t)QSTG * QSTAGE_BYTES + 128;
+
+__device__ __forceinline__ uint32_t push_sign_bit(uint32_t acc, float d) { return __funnelshift_l(__float_as_uint(d), acc, 1); }
+
+template <bool TERNARY, int IMG>
+__global__ void __launch_bounds__(QTHREADS, 1)
+quantise_tma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __restrict__ thr, void* __restrict__ out, int N, int C, int HW,
+                    int Cp, int nbands, unsigned int* status) {
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + QSTG * QSTAGE_BYTES);
+    const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + QSTG);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * QSTG);
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const long long items = (long long)N * nbands * Cp;
+
+    if (tid == 0) {
+        for (int s = 0; s < QSTG; s++) {
+            mbar_init(bar_full + 8 * s, 1);   // the producer's arrive with the expected bytes
+            mbar_init(bar_empty + 8 * s, 4);  // the four warps of the group that read the stage
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            long long k = 0;
+            for (long long i = blockIdx.x; i < items; i += gridDim.x, k++) {
+                const int s = (int)(k % QSTG);
+                const int ic = (int)(i % Cp);
+                const long long nb = i / Cp;
+                const int band = (int)(nb % nbands), n = (int)(nb / nbands);
+                if (!mbar_wait(bar_empty + 8 * s, (uint32_t)((k / QSTG) & 1) ^ 1, abort_flag, status, 0x21)) goto done;
+                mbar_arrive_expect_tx(bar_full + 8 * s, QSTAGE_BYTES);  // the whole box, edges zero-filled
+                tma_tile2d_g2s(smem_u32(smem + s * QSTAGE_BYTES), &tmap, band * QL, n * C + ic * QC, bar_full + 8 * s);
+            }
+        }
+    } else {
+        const int grp = (warp - 1) >> 2;
+        const int p = tid - 32 - grp * QL;  // pixel of the band
+        long long k = grp;
+        for (long long i = blockIdx.x + (long long)grp * gridDim.x; i < items; i += (long long)QGROUPS * gridDim.x, k += QGROUPS) {
+            const int s = (int)(k % QSTG);
+            const int ic = (int)(i % Cp);
+            const long long nb = i / Cp;
+            const int band = (int)(nb % nbands), n = (int)(nb / nbands);
+            const int nch = min(QC, C - ic * QC);  // channels present in this group
+            const float t = __ldg(thr + n) + 0.0f;  // + 0.0f: a threshold of -0 behaves as +0 in every compare
+            if (!mbar_wait(bar_full + 8 * s, (uint32_t)((k / QSTG) & 1), abort_flag, status, 0x22)) goto done;
+            const float* sp = reinterpret_cast<const float*>(smem + s * QSTAGE_BYTES) + p;
+            uint32_t sg[2] = {0, 0}, nz[2] = {0, 0};
+            // channel b of a half ends at bit b: visit 31 .. 0 and shift left; predicates read
+            // off sign bits (v < -t <=> signbit(v + t); |v| > t <=> signbit(t - |v|); v < t <=> signbit(v - t))
+            if (nch == QC) {
+#pragma unroll
+                for (int half = 0; half < 2; half++) {
+#pragma unroll
+                    for (int b = 31; b >= 0; b--) {
+                        const float v = sp[(32 * half + b) * QL];
+                        if (TERNARY) {
+                            sg[half] = push_sign_bit(sg[half], v + t);
+                            nz[half] = push_sign_bit(nz[half], t - fabsf(v));
+                        } else {
+                            sg[half] = push_sign_bit(sg[half], (v + 0.0f) - t);
+                        }
+                    }
+                }
+            } else {
+#pragma unroll 1
+                for (int c = QC - 1; c >= 0; c--) {
+                    const int half = c >> 5;
+                    if (c < nch) {
+                        const float v = sp[c * QL];
+                        if (TERNARY) {
+                            sg[half] = push_sign_bit(sg[half], v + t);
+                            nz[half] = push_sign_bit(nz[half], t - fabsf(v));
+                        } else {
+                            sg[half] = push_sign_bit(sg[half], (v + 0.0f) - t);
+                        }
+                    } else {  // absent channel: sign 0, non-zero 0
+                        sg[half] <<= 1;
+                        nz[half] <<= 1;
+                    }
+                }
+            }
+            // every value is in registers: hand the stage back before storing
+            __syncwarp();
+            if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+            const int pix = band * QL + p;
+            if (pix < HW) {
+                if (IMG == TNNS_IMG_E2M1) {
+                    uint32_t lo[4], hi[4];
+                    tnns_expand32_f4(sg[0], ~nz[0], lo);
+                    tnns_expand32_f4(sg[1], ~nz[1], hi);
+                    uint4* dst = reinterpret_cast<uint4*>(out) + (((size_t)n * HW + pix) * Cp + ic) * 2;
+                    dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+                    dst[1] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+                } else {
+                    uint64_t* img = reinterpret_cast<uint64_t*>(out);
+                    const size_t planes = TERNARY ? 2 : 1;
+                    const size_t at = ((size_t)n * planes * HW + pix) * Cp + ic;
+                    img[at] = ((uint64_t)sg[1] << 32) | sg[0];
+                    if (TERNARY) img[at + (size_t)HW * Cp] = ~(((uint64_t)nz[1] << 32) | nz[0]);
+                }
+            }
+        }
+    }
+done:
+    __syncwarp();
+    if (*abort_flag && warp == 0 && lane == 0) {
+        // a wait gave up: give the copies already issued time to land before shared memory is released
+        for (int i = 0; i < 1000; i++) __nanosleep(1000);
+    }
+    __syncthreads();
+}
+
+}  // namespace
+
+bool tnns_quantise_tma_supported(const float* d_x, int H, int W, int layout) {
+    const long long HW = (long long)H * W;
+    return layout == TNNS_NCHW && HW % 4 == 0 && HW >= 32 && (reinterpret_cast<uintptr_t>(d_x) & 15) == 0;
+}
+
+int tnns_launch_quantise_tma(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
+                             int W, cudaStream_t stream, int format) {
+    const int HW = H * W;
+    const int Cp = (C + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS;
+    const int nbands = (HW + QL - 1) / QL;
+    alignas(64) CUtensorMap map;
+    int rc = tnns_tensor_map_2d(&map, 4, d_x, (unsigned long long)HW, (unsigned long long)N * C, (unsigned long long)HW * 4, QL, QC);
+    if (rc) return rc;
+    const long long items = (long long)N * nbands * Cp;
+    const int grid = (int)std::min<long long>(items, ctx->sm_count);
+    auto launch = [&](auto kern) -> int {
+        TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)QSMEM));
+        kern<<<grid, QTHREADS, QSMEM, stream>>>(map, d_thr, d_image, N, C, HW, Cp, nbands, ctx->d_status);
+        tnns_count_launch();
+        TNNS_CUDA_TRY(cudaGetLastError());
+        return TNNS_OK;
+    };
+    if (format == TNNS_IMG_E2M1) return launch(quantise_tma_kernel<true, TNNS_IMG_E2M1>);
+    return ternary ? launch(quantise_tma_kernel<true, TNNS_IMG_PLANES>) : launch(quantise_tma_kernel<false, TNNS_IMG_PLANES>);
+}
