@@ -433,7 +433,10 @@ int tnns_cuda_conv(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* 
     TnnsGeom g;
     int rc = tnns_make_geom(s, &g);
     if (rc) return rc;
-    const size_t need = std::max<size_t>(tnns_packed_bytes(w->type, s), 16);
+    // room for the im2row matrix (explicit route) and, where the layer qualifies, for the 4-bit
+    // image of the copy-engine route, which is larger than the matrix for 1x1 kernels
+    size_t need = std::max<size_t>(tnns_packed_bytes(w->type, s), 16);
+    if (tnns_im2col_supported(w, g)) need = std::max(need, tnns_e2m1_image_bytes(g.N, g.C, g.H, g.W));
     if (ctx->workspace_bytes < need) {
         TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
         // earlier launches may still read the old workspace
@@ -489,7 +492,8 @@ int tnns_cuda_conv_host(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const fl
     const size_t out_img = (size_t)g.KN * g.OH * g.OW * sizeof(float);
     tnns_shape_t ss = *s;
     ss.N = nb;
-    const size_t pack_slice = std::max<size_t>(tnns_packed_bytes(w->type, &ss), 16);
+    size_t pack_slice = std::max<size_t>(tnns_packed_bytes(w->type, &ss), 16);
+    if (tnns_im2col_supported(w, g)) pack_slice = std::max(pack_slice, tnns_e2m1_image_bytes(nb, g.C, g.H, g.W));
 
     // staging buffers are shared by both slots' sizes; growing needs the device idle
     bool must_grow = ctx->stage_in_bytes < in_img * nb || ctx->stage_out_bytes < out_img * nb ||
