@@ -29,6 +29,7 @@
 #include <cuda.h>  // CUtensorMap and the encode prototypes only; the entry point is looked up at run time
 
 #include <algorithm>
+#include <type_traits>
 #include <vector>
 
 #include "internal.h"
@@ -62,8 +63,9 @@ constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_EXP0 = 2;
 // half.  A block then receives 32 KB instead of 48 KB per stage from L2 and the ring is six deep.
 // Both blocks' tensor copies report to the first block's "full" barrier; its commits release the
 // stage and publish the accumulator in both blocks (multicast arrive).
-template <int BN, int MT, bool F4, bool ATMA = false, int CG = 1>
+template <int BN, int MT, bool F4, bool ATMA = false, int CG = 1, int TAPS = 1>
 struct TcCfg {
+    static_assert(TAPS == 1 || (ATMA && (TAPS == 2 || TAPS == 4)), "taps per stage row: tensor-copy form only");
     static_assert(!ATMA || (F4 && MT == 1), "tensor-copy activations: 4-bit form, one accumulator per block");
     static_assert(CG == 1 || (CG == 2 && ATMA), "block pairs: tensor-copy form only");
     static constexpr int NSTG = (CG == 2) ? 6 : ((MT == 1) ? 4 : 3);  // smem ring depth
@@ -153,6 +155,18 @@ __device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint
 
 // Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 B apart, 8-row
 // groups 1024 B apart (stride byte offset), descriptor version 1 (sm_100).
+// The same for a sub-tile whose rows are 64 or 32 bytes long (64- / 32-byte swizzle; eight-row
+// groups 512 / 256 bytes apart): taps = 2 or 4 filter taps share a 128-byte stage row, each tap in
+// a sub-tile of its own.  taps = 1 is the 128-byte form of make_desc.
+__device__ __forceinline__ uint64_t make_desc_taps(uint32_t smem_addr, int taps) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)((1024 / taps) >> 4) << 32;                       // stride byte offset
+    d |= (uint64_t)1 << 46;                                          // version
+    d |= (uint64_t)(taps == 1 ? 2 : (taps == 2 ? 4 : 6)) << 61;      // SWIZZLE_128B / _64B / _32B
+    return d;
+}
 __device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
     uint64_t d = 0;
     d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
@@ -209,8 +223,11 @@ __device__ __forceinline__ void store_row_stage_f4(unsigned char* tile, int r, c
 // One-time weight expansion: packed rows -> int8 tile images, [n_tile][chunk][BN rows][128 B],
 // swizzled exactly as the MMA reads them, rows past KN left zero.
 // ---------------------------------------------------------------------------------------
+// zero_from >= 0 (4-bit form): plane words from that index on -- the words added by the pad-to-four --
+// are written as zeros whatever the row holds there (binary rows read +1), so that an activation
+// operand may leave those K positions undefined.
 __global__ void expand_weights_kernel(const uint4* __restrict__ packed, unsigned char* __restrict__ img, int KN, int Kp, int BN,
-                                      int two_planes, int f4) {
+                                      int two_planes, int f4, int zero_from) {
     const int nch = f4 ? Kp / 4 : Kp / 2;
     const long long total = (long long)KN * nch;
     const size_t pitch = two_planes ? (size_t)Kp : (size_t)Kp / 2;  // uint4 per row
@@ -221,8 +238,17 @@ __global__ void expand_weights_kernel(const uint4* __restrict__ packed, unsigned
         const uint4 zero4 = make_uint4(0, 0, 0, 0);
         if (f4) {
             const uint4* grp = packed + (size_t)kn * pitch + (size_t)c * gsz;
-            const uint4 s[2] = {grp[0], grp[1]};
-            const uint4 z[2] = {two_planes ? grp[2] : zero4, two_planes ? grp[3] : zero4};
+            uint4 s[2] = {grp[0], grp[1]};
+            uint4 z[2] = {two_planes ? grp[2] : zero4, two_planes ? grp[3] : zero4};
+            if (zero_from >= 0 && 4 * c + 4 > zero_from) {
+                uint32_t* sw = reinterpret_cast<uint32_t*>(s);
+                uint32_t* zw = reinterpret_cast<uint32_t*>(z);
+                for (int q = 0; q < 4; q++)
+                    if (4 * c + q >= zero_from) {
+                        sw[2 * q] = sw[2 * q + 1] = 0u;
+                        zw[2 * q] = zw[2 * q + 1] = 0xFFFFFFFFu;
+                    }
+            }
             store_row_stage_f4(tile, kn % BN, s, z);
         } else {
             const uint4* grp = packed + (size_t)kn * pitch + (size_t)(c >> 1) * gsz;
@@ -252,10 +278,13 @@ struct GemmArgs {
     int H, W, OW, Cp, SH, SW, PH, PW;
 };
 
-template <int BN, int MT, bool F4, bool ATMA, int CG>
-__global__ void __launch_bounds__(TcCfg<BN, MT, F4, ATMA, CG>::NTHREADS, 1)
+// TAPS (tensor-copy form): filter taps per 128-byte stage row -- 1: a tap's 256 channels fill the
+// row (C_pack % 4 == 0); 2: C_pack = 2, two taps of 128 channels in two 64-byte-swizzled sub-tiles;
+// 4: C_pack = 1, four taps of 64 channels in four 32-byte-swizzled sub-tiles.
+template <int BN, int MT, bool F4, bool ATMA, int CG, int TAPS>
+__global__ void __launch_bounds__(TcCfg<BN, MT, F4, ATMA, CG, TAPS>::NTHREADS, 1)
 gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b) {
-    using Cfg = TcCfg<BN, MT, F4, ATMA, CG>;
+    using Cfg = TcCfg<BN, MT, F4, ATMA, CG, TAPS>;
     constexpr int NSTG = Cfg::NSTG, A_STAGE = Cfg::A_STAGE, B_STAGE = Cfg::B_STAGE, NBUF = Cfg::NBUF, WARP_EPI0 = Cfg::WARP_EPI0, NG = Cfg::NG, EPW = Cfg::EPW;
     constexpr int BMT = MT * BM;      // rows per block
     constexpr int TILE_M = CG * BMT;  // rows per tile (a block pair shares one 256-row tile)
@@ -355,29 +384,52 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                 for (int c = 0; c < nchunks; c++, it++) {
                     const int s = it % NSTG;
                     if (!mbar_wait(bar_empty + 8 * s, ((it / NSTG) & 1) ^ 1, abort_flag, p.status, 1)) goto done;
+                    // tensor-copy activations: the stage's four plane words are TAPS filter taps
+                    // (TAPS: one tap of 256 channels, two of 128 or four of 64), one copy and one sub-tile
+                    // each; words added by the pad-to-four have no tap: their sub-tile keeps what
+                    // it held (any nibble is a finite e2m1 value) and meets zero weights
+                    uint32_t tap[4];
+                    int a_bytes = 0;
+                    constexpr int wpt = 4 / TAPS, sub = A_STAGE / TAPS;  // plane words and bytes per tap
+                    if (ATMA) {
+#pragma unroll
+                        for (int q = 0; q < TAPS; q++) {
+                            tap[q] = __ldg(p.jtab + 4 * c + q * wpt);
+                            if (tap[q] != 0xFFFFFFFFu) a_bytes += sub;
+                        }
+                    }
                     if (CG == 2) {
-                        // the stage's four plane words are four neighbouring channel groups of one tap
-                        const uint32_t e = __ldg(p.jtab + 4 * c);
-                        if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, CG * (B_STAGE + A_STAGE));
+                        if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * s, CG * (B_STAGE + a_bytes));
                         tma_tile2d_g2s_pair(smem_u32(sB + s * B_STAGE), &tmap_b, 0, (n_tile * nchunks + c) * BN + (int)rank * (BN / CG),
                                             bar_full_lead + 8 * s);
-                        tma_im2col_g2s_pair(smem_u32(sA + s * A_STAGE), &tmap_a, (int)(e & 0xFFFF) * 32, a_w, a_h, a_n,
-                                            (unsigned short)((e >> 16) & 0xFF), (unsigned short)(e >> 24), bar_full_lead + 8 * s);
+#pragma unroll
+                        for (int q = 0; q < TAPS; q++)
+                            if (tap[q] != 0xFFFFFFFFu)
+                                tma_im2col_g2s_pair(smem_u32(sA + s * A_STAGE + q * sub), &tmap_a, (int)(tap[q] & 0xFFFF) * 32, a_w, a_h, a_n,
+                                                    (unsigned short)((tap[q] >> 16) & 0xFF), (unsigned short)(tap[q] >> 24), bar_full_lead + 8 * s);
                         continue;
                     }
-                    mbar_arrive_expect_tx(bar_full + 8 * s, ATMA ? B_STAGE + A_STAGE : B_STAGE);
+                    mbar_arrive_expect_tx(bar_full + 8 * s, B_STAGE + a_bytes);
                     bulk_g2s(smem_u32(sB + s * B_STAGE), src + (size_t)c * B_STAGE, B_STAGE, bar_full + 8 * s);
                     if (ATMA) {
-                        const uint32_t e = __ldg(p.jtab + 4 * c);
-                        tma_im2col_g2s(smem_u32(sA + s * A_STAGE), &tmap_a, (int)(e & 0xFFFF) * 32, a_w, a_h, a_n,
-                                       (unsigned short)((e >> 16) & 0xFF), (unsigned short)(e >> 24), bar_full + 8 * s);
+#pragma unroll
+                        for (int q = 0; q < TAPS; q++)
+                            if (tap[q] != 0xFFFFFFFFu)
+                                tma_im2col_g2s(smem_u32(sA + s * A_STAGE + q * sub), &tmap_a, (int)(tap[q] & 0xFFFF) * 32, a_w, a_h, a_n,
+                                               (unsigned short)((tap[q] >> 16) & 0xFF), (unsigned short)(tap[q] >> 24), bar_full + 8 * s);
                     }
                 }
             }
         }
     } else if (warp == WARP_MMA) {
         if (lane == 0 && rank == 0) {  // pair: the first block issues for both
-            uint32_t it = 0, lt = 0;
+            // This one thread's instruction stream paces the tensor pipe, so it is kept short: the
+            // ring slot and its phase are running counters, the descriptors of slot s are those of
+            // slot 0 plus s stage sizes (the address field counts 16-byte units and cannot carry
+            // out of its 14 bits for shared-memory addresses), K steps add constants.
+            uint32_t lt = 0, s = 0, ph = 0;
+            constexpr int KPS = 4 / TAPS;                       // 32-byte K steps per sub-tile
+            const uint64_t da0 = make_desc_taps(smem_u32(sA), TAPS), db0 = make_desc(smem_u32(sB));
             for (long long t = unit; t < ntiles; t += nunits, lt++) {
                 const int buf = lt % NBUF;
                 // overlapping sets: one barrier, completed once per tile when the columns shared
@@ -385,23 +437,25 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                 if (!mbar_wait(OVL ? bar_tempty : bar_tempty + 8 * buf, (OVL ? (lt & 1) : ((lt / NBUF) & 1)) ^ 1, abort_flag, p.status, 2)) goto done;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * ACC_OFF;
-                for (int c = 0; c < nchunks; c++, it++) {
-                    const int s = it % NSTG;
-                    if (!mbar_wait(bar_full + 8 * s, (it / NSTG) & 1, abort_flag, p.status, 3)) goto done;
+                for (int c = 0; c < nchunks; c++) {
+                    if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3)) goto done;
                     tc_fence_after();
-                    const uint64_t db = make_desc(smem_u32(sB + s * B_STAGE));
+                    const uint64_t db = db0 + (uint64_t)(s * (B_STAGE >> 4));
 #pragma unroll
                     for (int mt = 0; mt < MT; mt++) {
-                        const uint64_t da = make_desc(smem_u32(sA + s * A_STAGE + mt * A_SUB));
+                        const uint64_t da = da0 + (uint64_t)(s * (A_STAGE >> 4) + mt * (A_SUB >> 4));
 #pragma unroll
                         for (int k = 0; k < KCH / 32; k++) {
-                            if (CG == 2) tc_mma_f4_pair(d_tmem, da + 2 * k, db + 2 * k, IDESC, tmem_base + SF_COL, tmem_base + SF_COL + 16, (c | k) ? 1u : 0u);
-                            else if (F4) tc_mma_f4(d_tmem + mt * BN, da + 2 * k, db + 2 * k, IDESC, tmem_base + SF_COL, tmem_base + SF_COL + 16, (c | k) ? 1u : 0u);
-                            else tc_mma_i8(d_tmem + mt * BN, da + 2 * k, db + 2 * k, IDESC, (c | k) ? 1u : 0u);
+                            // K step k: sub-tile k / KPS, 32 bytes x (k % KPS) into its rows
+                            const uint64_t dak = da + (uint64_t)((k / KPS) * ((A_STAGE / TAPS) >> 4) + 2 * (k % KPS));
+                            if (CG == 2) tc_mma_f4_pair(d_tmem, dak, db + 2 * k, IDESC, tmem_base + SF_COL, tmem_base + SF_COL + 16, (c | k) ? 1u : 0u);
+                            else if (F4) tc_mma_f4(d_tmem + mt * BN, dak, db + 2 * k, IDESC, tmem_base + SF_COL, tmem_base + SF_COL + 16, (c | k) ? 1u : 0u);
+                            else tc_mma_i8(d_tmem + mt * BN, dak, db + 2 * k, IDESC, (c | k) ? 1u : 0u);
                         }
                     }
                     // stage reusable once these MMAs have read it (pair: in both blocks)
                     if (CG == 2) tc_commit_pair(bar_empty + 8 * s); else tc_commit(bar_empty + 8 * s);
+                    if (++s == NSTG) { s = 0; ph ^= 1; }
                 }
                 // accumulator complete (pair: each block's epilogue drains its own 128 rows)
                 if (CG == 2) tc_commit_pair(bar_tfull + 8 * buf); else tc_commit(bar_tfull + 8 * buf);
@@ -753,11 +807,11 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(int iters, unsigned in
     }
 }
 
-template <int BN, int MT, bool F4, bool ATMA = false, int CG = 1>
+template <int BN, int MT, bool F4, bool ATMA = false, int CG = 1, int TAPS = 1>
 int launch_cfg(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream, const CUtensorMap* tmap_a = nullptr,
                const CUtensorMap* tmap_b = nullptr) {
-    using Cfg = TcCfg<BN, MT, F4, ATMA, CG>;
-    auto kern = gemm_tc_kernel<BN, MT, F4, ATMA, CG>;
+    using Cfg = TcCfg<BN, MT, F4, ATMA, CG, TAPS>;
+    auto kern = gemm_tc_kernel<BN, MT, F4, ATMA, CG, TAPS>;
     static const CUtensorMap no_map = {};
     TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
     const long long tiles = ((a.M + CG * MT * BM - 1) / (CG * MT * BM)) * ((a.KN + BN - 1) / BN);
@@ -824,8 +878,13 @@ int tnns_build_i8_weights(tnns_cuda_ctx* ctx, tnns_cuda_weights* w) {
         TNNS_CUDA_TRY(cudaMemset(img, 0, bytes));
         const long long total = (long long)w->KN * nch;
         const int blocks = (int)std::min<long long>((total + 127) / 128, 4096);
+        // TBN: ternary activations meet binary weights, whose pad words read +1; the products there are
+        // zero only because the activation pad words are zeros -- writing zero weights instead changes
+        // nothing and lets the tensor-copy form skip those K positions.  (BNN keeps +1: its epilogue
+        // constant counts the padded +1 x +1 products.)
+        const int zero_from = (f4 && w->type == TBN) ? w->Kw : -1;
         expand_weights_kernel<<<blocks, 128>>>(reinterpret_cast<const uint4*>(w->d_packed), reinterpret_cast<unsigned char*>(img), w->KN,
-                                                w->Kp, BN, two ? 1 : 0, f4);
+                                                w->Kp, BN, two ? 1 : 0, f4, zero_from);
         tnns_count_launch();
         TNNS_CUDA_TRY(cudaGetLastError());
     }
@@ -900,7 +959,7 @@ bool tnns_im2col_supported(const tnns_cuda_weights* w, const TnnsGeom& g) {
     if (!(w->type == TNN || w->type == TBN)) return false;   // outside the image the copy engine writes 0, a ternary zero
     if (!w->d_f4 || !w->d_jtab || w->Kp >= 65536) return false;
     if (tnns_i8_tile_n(w->KN) != 256 && tnns_i8_tile_n(w->KN) != 128 && tnns_i8_tile_n(w->KN) != 64) return false;
-    if (g.Cp % 4 != 0) return false;                         // a stage = 256 channels of one tap = one 128-byte box row
+    if (g.Cp != 1 && g.Cp != 2 && g.Cp % 4 != 0) return false;  // a 128-byte stage row = 1 tap of 256 channels, 2 of 128 or 4 of 64
     if (g.KH > 255 || g.KW > 255 || g.SH > 8 || g.SW > 8) return false;          // filter offsets are 8 bits, traversal strides <= 8
     if (g.PH > 128 || g.PW > 128 || g.PH - (g.KH - 1) < -128 || g.PW - (g.KW - 1) < -128) return false;  // box corners are 8 bits
     return true;
@@ -928,9 +987,11 @@ int encode_im2col_map(CUtensorMap* map, const void* d_image, const TnnsGeom& g) 
     const int lower[2] = {-g.PW, -g.PH};
     const int upper[2] = {g.PW - (g.KW - 1), g.PH - (g.KH - 1)};
     const cuuint32_t estr[4] = {1, (cuuint32_t)g.SW, (cuuint32_t)g.SH, 1};
-    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(d_image), dims, strides, lower, upper, 128, BM, estr,
-                              CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
-                              CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    // channels per pixel and copy: 128 bytes (256 channels), or the whole pixel when it has 64 or 32 bytes
+    const int taps = g.Cp == 1 ? 4 : (g.Cp == 2 ? 2 : 1);
+    const CUtensorMapSwizzle swz = taps == 1 ? CU_TENSOR_MAP_SWIZZLE_128B : (taps == 2 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_32B);
+    const CUresult r = encode(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 4, const_cast<void*>(d_image), dims, strides, lower, upper, 128 / taps, BM, estr,
+                              CU_TENSOR_MAP_INTERLEAVE_NONE, swz, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) return tnns_fail(TNNS_ERR_CUDA, "cuTensorMapEncodeIm2col failed with driver error %d", (int)r);
     // Drivers up to 13.1 set a flag in im2col maps of tensors below 128 KiB that must be clear
     // (the correction CUTLASS applies to its im2col descriptors, cute/atom/copy_traits_sm90_im2col.hpp).
@@ -979,21 +1040,26 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     a.img = nullptr;
     a.jtab = w->d_jtab;
     a.H = g.H; a.W = g.W; a.OW = g.OW; a.Cp = g.Cp; a.SH = g.SH; a.SW = g.SW; a.PH = g.PH; a.PW = g.PW;
+    const int taps = g.Cp == 1 ? 4 : (g.Cp == 2 ? 2 : 1);
     const int bn = tnns_i8_tile_n(w->KN);
     if (pairs == 2 && bn != 256) return tnns_fail(TNNS_ERR_UNSUPPORTED, "block pairs need more than 128 kernels");
     // Block pairs once there are enough 256-row tiles to occupy every SM pair.
     const long long pair_tiles = ((M + 2 * BM - 1) / (2 * BM)) * ((w->KN + bn - 1) / bn);
-    if (bn == 256 && (pairs == 2 || (pairs == 0 && pair_tiles >= ctx->sm_count / 2))) {
-        CUtensorMap map_b;
-        rc = encode_weight_map(&map_b, w, bn);
-        if (rc) return rc;
-        return launch_cfg<256, 1, true, true, 2>(ctx, a, stream, &map, &map_b);
-    }
-    switch (bn) {
-        case 64: return launch_cfg<64, 1, true, true>(ctx, a, stream, &map);
-        case 128: return launch_cfg<128, 1, true, true>(ctx, a, stream, &map);
-        default: return launch_cfg<256, 1, true, true>(ctx, a, stream, &map);
-    }
+    const bool use_pairs = bn == 256 && (pairs == 2 || (pairs == 0 && pair_tiles >= ctx->sm_count / 2));
+    CUtensorMap map_b;
+    if (use_pairs && (rc = encode_weight_map(&map_b, w, bn))) return rc;
+    auto go = [&](auto taps_c) -> int {
+        constexpr int T = decltype(taps_c)::value;
+        if (use_pairs) return launch_cfg<256, 1, true, true, 2, T>(ctx, a, stream, &map, &map_b);
+        switch (bn) {
+            case 64: return launch_cfg<64, 1, true, true, 1, T>(ctx, a, stream, &map);
+            case 128: return launch_cfg<128, 1, true, true, 1, T>(ctx, a, stream, &map);
+            default: return launch_cfg<256, 1, true, true, 1, T>(ctx, a, stream, &map);
+        }
+    };
+    if (taps == 4) return go(std::integral_constant<int, 4>());
+    if (taps == 2) return go(std::integral_constant<int, 2>());
+    return go(std::integral_constant<int, 1>());
 }
 
 // Launches the issue-bound MMA loop on every SM; `ops` receives the 2*M*N*K operations it performs.

@@ -452,6 +452,12 @@ IM2COL_LAYERS = [
     (TNN, Layer(512, 1, 1, 512, 1, 1, 0, 1), 8),       # fully connected
     (TNN, Layer(250, 9, 11, 64, 3, 3, 2, 3), 3),       # channel tail, padding 2, stride 3
     (TBN, Layer(512, 9, 11, 300, 3, 3, 0, 1), 3),      # no padding, ragged kernel tile
+    (TNN, Layer(64, 9, 9, 200, 3, 3, 1, 1), 5),        # C_pack = 1: four taps per stage row (32-byte swizzle), three pad taps
+    (TBN, Layer(64, 9, 9, 200, 3, 3, 1, 1), 5),        # the same against binary weights (pad words must not count)
+    (TNN, Layer(128, 14, 14, 256, 5, 3, 1, 2), 4),     # C_pack = 2: two taps per stage row (64-byte swizzle), one pad tap
+    (TBN, Layer(128, 10, 10, 100, 3, 3, 1, 2), 3),
+    (TNN, Layer(100, 9, 11, 64, 3, 3, 2, 3), 3),       # C_pack = 2 with a channel tail
+    (TNN, Layer(64, 12, 12, 32, 1, 1, 0, 1), 3),       # C_pack = 1, 1x1: one real tap, three pad taps
 ]
 
 
@@ -514,9 +520,10 @@ def test_e2m1_image_and_im2col_tensor_copy_gemm(type_, layer, N, gpu_ctx, checke
 @pytest.mark.gpu
 def test_im2col_route_declines_what_it_cannot_do(gpu_ctx, checker):
     """Binary activations (padding is +1, which a zero-filling copy cannot produce) and channel counts
-    that do not fill 128-byte chunks stay on the gathering GEMM; asking for the route anyway is an error."""
+    whose pixels are neither 32, 64 nor a multiple of 128 bytes stay on the gathering GEMM; asking for
+    the route anyway is an error."""
     ctx = gpu_ctx
-    for type_, layer in ((BTN, Layer(256, 8, 8, 64, 3, 3, 1, 1)), (TNN, Layer(128, 8, 8, 64, 3, 3, 1, 1))):
+    for type_, layer in ((BTN, Layer(256, 8, 8, 64, 3, 3, 1, 1)), (TNN, Layer(192, 8, 8, 64, 3, 3, 1, 1))):
         case = make_case(type_, layer, 2, 77, "uniform")
         wp = checker.pack_weights(wgt_ternary(type_), case.w, case.w_thr)
         w = ctx.upload_weights(type_, wp, layer.C, layer.KH, layer.KW)
