@@ -80,7 +80,8 @@ struct TcCfg {
     static constexpr int NG = ATMA ? 0 : ((MT == 1) ? (EPW == 2 ? 3 : 4) : 2);
     static constexpr int WARP_EPI0 = WARP_EXP0 + 4 * MT * NG;
     static constexpr int NTHREADS = 32 * (2 + 4 * MT * NG + 4 * MT * EPW);
-    static constexpr size_t SMEM = 1024 + (size_t)NSTG * (A_STAGE + B_STAGE) + 256;
+    static constexpr int TAPMAX = 1024;  // entries of the tap table kept in shared memory
+    static constexpr size_t SMEM = 1024 + (size_t)NSTG * (A_STAGE + B_STAGE) + 256 + TAPMAX * sizeof(uint32_t);
 };
 
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
@@ -305,6 +306,10 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                    bar_tempty = smem_u32(bars + 2 * NSTG + 2);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * NSTG + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    // The tap table (plane word -> kh, kw, ic) sits on the producer's critical path once per stage,
+    // so its first TAPMAX entries are copied to shared memory; longer tables fall back to global loads.
+    uint32_t* s_taps = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(bars) + 256);
+    auto tap_at = [&](int j) -> uint32_t { return j < Cfg::TAPMAX ? s_taps[j] : __ldg(p.jtab + j); };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nchunks = F4 ? p.Kp / 4 : p.Kp / 2;  // stages per tile
@@ -315,6 +320,8 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
     const uint32_t rank = (CG == 2) ? cluster_ctarank() : 0u;
     const long long unit = blockIdx.x / CG, nunits = gridDim.x / CG;
 
+    if (p.jtab)
+        for (int j = threadIdx.x; j < min(p.Kp, Cfg::TAPMAX); j += blockDim.x) s_taps[j] = __ldg(p.jtab + j);
     if (tid == 0) {
         for (int s = 0; s < NSTG; s++) {
             mbar_init(bar_full + 8 * s, ATMA ? 1 : 1 + 4 * MT);  // weight producer + the expander warps
@@ -364,7 +371,7 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
 
     if (warp == WARP_TMA) {
         if (lane == 0) {
-            uint32_t it = 0;
+            uint32_t s = 0, ph = 1;  // ring slot and the parity its "empty" barrier is waited with
             // pair: both blocks' copies report to the first block's barrier
             const uint32_t bar_full_lead = (CG == 2) ? mapa_shared(bar_full, 0) : bar_full;
             for (long long t = unit; t < ntiles; t += nunits) {
@@ -375,15 +382,15 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                 if (ATMA) {
                     long long row0 = (t / ntn) * TILE_M + (long long)rank * BMT;
                     if (row0 >= p.M) row0 = 0;  // second block of a pair past the last row: any valid pixels, never stored
-                    a_n = (int)(row0 / p.OHW);
+                    // 32-bit divisions where the row index allows it (64-bit ones cost this thread hundreds of cycles per tile)
+                    a_n = row0 < 0x7FFFFFFFLL ? (int)((uint32_t)row0 / (uint32_t)p.OHW) : (int)(row0 / p.OHW);
                     const int rem = (int)(row0 - (long long)a_n * p.OHW);
                     const int oh = rem / p.OW;
                     a_h = oh * p.SH - p.PH;
                     a_w = (rem - oh * p.OW) * p.SW - p.PW;
                 }
-                for (int c = 0; c < nchunks; c++, it++) {
-                    const int s = it % NSTG;
-                    if (!mbar_wait(bar_empty + 8 * s, ((it / NSTG) & 1) ^ 1, abort_flag, p.status, 1)) goto done;
+                for (int c = 0; c < nchunks; c++, s = (s + 1 == NSTG) ? 0 : s + 1, ph ^= (s == 0)) {
+                    if (!mbar_wait(bar_empty + 8 * s, ph, abort_flag, p.status, 1)) goto done;
                     // tensor-copy activations: the stage's four plane words are TAPS filter taps
                     // (TAPS: one tap of 256 channels, two of 128 or four of 64), one copy and one sub-tile
                     // each; words added by the pad-to-four have no tap: their sub-tile keeps what
@@ -394,7 +401,7 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                     if (ATMA) {
 #pragma unroll
                         for (int q = 0; q < TAPS; q++) {
-                            tap[q] = __ldg(p.jtab + 4 * c + q * wpt);
+                            tap[q] = tap_at(4 * c + q * wpt);
                             if (tap[q] != 0xFFFFFFFFu) a_bytes += sub;
                         }
                     }
@@ -502,7 +509,7 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                     uint64_t sw[4], zw[4];
                     if ((p.Cp & 3) == 0) {
                         // the four words of a stage are four neighbouring channel groups of one tap
-                        const uint32_t e = __ldg(p.jtab + 4 * pf_c);
+                        const uint32_t e = tap_at(4 * pf_c);
                         const int ih = im_ih0 + (int)(e >> 24), iw = im_iw0 + (int)((e >> 16) & 0xFF);
                         if (ih >= 0 && ih < p.H && iw >= 0 && iw < p.W) {
                             const uint4* src = reinterpret_cast<const uint4*>(base + ((size_t)ih * p.W + iw) * p.Cp + (e & 0xFFFF));
@@ -522,7 +529,7 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                     } else {
 #pragma unroll
                         for (int q = 0; q < 4; q++) {
-                            const uint32_t e = __ldg(p.jtab + 4 * pf_c + q);
+                            const uint32_t e = tap_at(4 * pf_c + q);
                             const int ih = im_ih0 + (int)(e >> 24), iw = im_iw0 + (int)((e >> 16) & 0xFF);
                             sw[q] = 0;
                             zw[q] = p.a_two_planes ? ~0ull : 0ull;
