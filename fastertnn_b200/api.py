@@ -300,6 +300,13 @@ class Context:
         pairs: 0 = by size, 1 = single blocks, 2 = block pairs (tcgen05.mma.cta_group::2)."""
         _check(self.lib.tnns_cuda_gemm_im2col(self.handle, w.handle, d_image, d_y, C.byref(shape), alpha, layout, pairs, stream))
 
+    def gemm_im2col_packed_out(self, w: Weights, d_image: int, d_image_out: int, d_thr_next: int, next_format: int, shape: Shape,
+                               alpha: float, stream=0, pairs=0):
+        """The copy-engine GEMM with the quantising epilogue: writes the next layer's activations as binary (0) or
+        ternary (1) bit planes or as a ternary 4-bit operand image (2) instead of fp32."""
+        _check(self.lib.tnns_cuda_gemm_im2col_packed_out(self.handle, w.handle, d_image, d_image_out, d_thr_next, next_format,
+                                                         C.byref(shape), alpha, pairs, stream))
+
     def im2col_supported(self, w: Weights, shape: Shape) -> bool:
         return bool(self.lib.tnns_cuda_im2col_supported(w.handle, C.byref(shape)))
 

@@ -371,8 +371,27 @@ int tnns_cuda_gemm_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, co
     if ((reinterpret_cast<uintptr_t>(d_a) & 15) || (reinterpret_cast<uintptr_t>(d_image) & 15))
         return tnns_fail(TNNS_ERR_INVALID, "packed operand and image must be 16-byte aligned");
     if (!w->d_f4 || w->Kp >= 65536) return tnns_fail(TNNS_ERR_UNSUPPORTED, "packed output needs the tensor-core GEMM");
+    if (next_ternary < 0 || next_ternary > 2) return tnns_fail(TNNS_ERR_INVALID, "output format must be 0, 1 or 2");
     return tnns_launch_gemm_tc(ctx, w, d_a, nullptr, (long long)N * OH * OW, OH * OW, alpha, TNNS_NCHW, true, (cudaStream_t)stream,
-                               d_image, d_thr_next, next_ternary != 0);
+                               d_image, d_thr_next, next_ternary);
+}
+
+int tnns_cuda_gemm_im2col_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, void* d_image_out,
+                                     const float* d_thr_next, int next_format, const tnns_shape_t* s, float alpha, int pairs,
+                                     void* stream) {
+    if (!ctx || !w || !d_image || !d_image_out || !d_thr_next) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    TnnsGeom g;
+    int rc = tnns_make_geom(s, &g);
+    if (rc) return rc;
+    if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW)
+        return tnns_fail(TNNS_ERR_INVALID, "shape does not match the uploaded weights");
+    if (w->device != ctx->device) return tnns_fail(TNNS_ERR_INVALID, "weights live on device %d, context on %d", w->device, ctx->device);
+    if ((reinterpret_cast<uintptr_t>(d_image) & 31) || (reinterpret_cast<uintptr_t>(d_image_out) & 15))
+        return tnns_fail(TNNS_ERR_INVALID, "input image must be 32-byte, output image 16-byte aligned");
+    if (pairs < 0 || pairs > 2) return tnns_fail(TNNS_ERR_INVALID, "pairs must be 0, 1 or 2");
+    if (next_format < 0 || next_format > 2) return tnns_fail(TNNS_ERR_INVALID, "output format must be 0, 1 or 2");
+    return tnns_launch_gemm_im2col(ctx, w, d_image, nullptr, g, alpha, TNNS_NCHW, (cudaStream_t)stream, pairs, d_image_out, d_thr_next,
+                                   next_format);
 }
 
 int tnns_cuda_im2row_packed(tnns_cuda_ctx* ctx, int ternary, const void* d_image, int64_t* d_packed, const tnns_shape_t* s,

@@ -9,7 +9,15 @@
 // Both are exact: |acc| <= 64*Kp < 2^22, so the int32 and the fp32 sums are the same integers
 // and the fp32 output is bit-identical to the popcount kernels.
 //
-// One persistent block per SM, 22 warps in four roles:
+// The activation operand reaches shared memory in one of two ways:
+//   expander-fed (ATMA = false)  warps gather the packed planes (an explicit im2row matrix or, for the
+//                       implicit form, the bit-plane image of the layer input) and expand them
+//   tensor-copy fed (ATMA = true)  the layer input was quantised straight into 4-bit operands and
+//                       the copy engine delivers each stage as im2col tensor copies; no expander
+//                       warps, optionally on block pairs (CG = 2, tcgen05.mma.cta_group::2)
+//
+// Expander-fed form: one persistent block per SM, 22 warps in four roles (the tensor-copy form
+// keeps warps 0, 1 and eight epilogue warps):
 //   warp 0      weight producer: one bulk async copy (TMA engine, no multicast, no tensor map)
 //               per stage of a pre-expanded, pre-swizzled weight tile (built once per layer)
 //   warp 1      MMA issuer: one thread issues four tcgen05.mma per stage and commits to the
@@ -272,6 +280,7 @@ struct GemmArgs {
     uint32_t* pimg;
     const float* thr_next;      // one threshold per image for that quantisation
     int next_ternary, cp_next;  // planes of the next layer's activations, its 64-channel groups
+    int pimg_e2m1;              // write that output as a 4-bit operand image [n][pixel][ic][32 B] instead of bit planes
     // optional implicit im2row (4-bit form): A is not a packed im2row matrix but the quantised
     // image [n][plane][pixel][ic] of the layer input; row r, plane word j are gathered on the fly
     const uint64_t* img;
@@ -677,11 +686,20 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                             }
                             const int have = p.KN - c0;
                             const uint32_t valid = have >= 32 ? 0xFFFFFFFFu : (have > 0 ? (1u << have) - 1u : 0u);
-                            const int planes = p.next_ternary ? 2 : 1;
-                            const size_t lanes = (size_t)p.cp_next * 2;  // 32-bit lanes per pixel and plane
-                            uint32_t* px = p.pimg + ((size_t)n_img * planes * p.OHW + rem) * lanes + (c0 >> 5);
-                            px[0] = sg & valid;
-                            if (p.next_ternary) px[(size_t)p.OHW * lanes] = ~(nz & valid);
+                            if (p.pimg_e2m1) {
+                                // the 32 channels as 16 bytes of e2m1 operands, where the copy-engine GEMM
+                                // of the next layer expects them (same expansion routine as everywhere)
+                                uint32_t w4[4];
+                                tnns_expand32_f4(sg & valid, ~(nz & valid), w4);
+                                uint4* px = reinterpret_cast<uint4*>(p.pimg) + ((size_t)n_img * p.OHW + rem) * ((size_t)p.cp_next * 2) + (c0 >> 5);
+                                *px = make_uint4(w4[0], w4[1], w4[2], w4[3]);
+                            } else {
+                                const int planes = p.next_ternary ? 2 : 1;
+                                const size_t lanes = (size_t)p.cp_next * 2;  // 32-bit lanes per pixel and plane
+                                uint32_t* px = p.pimg + ((size_t)n_img * planes * p.OHW + rem) * lanes + (c0 >> 5);
+                                px[0] = sg & valid;
+                                if (p.next_ternary) px[(size_t)p.OHW * lanes] = ~(nz & valid);
+                            }
                         }
                     } else if (p.layout == TNNS_NHWC) {
                         if (full && (p.KN & 3) == 0) {
@@ -931,7 +949,8 @@ int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const vo
     a.status = ctx->d_status;
     a.pimg = reinterpret_cast<uint32_t*>(d_pimg);
     a.thr_next = d_thr_next;
-    a.next_ternary = next_ternary;
+    a.next_ternary = next_ternary != 0;
+    a.pimg_e2m1 = next_ternary == 2;
     a.cp_next = (w->KN + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS;
     a.img = nullptr;
     a.jtab = nullptr;
@@ -1019,7 +1038,7 @@ int encode_weight_map(CUtensorMap* map, const tnns_cuda_weights* w, int BN) {
 
 // pairs: 0 = decide by size, 1 = single blocks, 2 = block pairs (kernel tile of 256 only)
 int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const TnnsGeom& g, float alpha,
-                            int layout, cudaStream_t stream, int pairs) {
+                            int layout, cudaStream_t stream, int pairs, void* d_pimg, const float* d_thr_next, int next_format) {
     const long long M = (long long)g.N * g.OH * g.OW;
     if (M == 0) return TNNS_OK;
     if (!tnns_im2col_supported(w, g)) return tnns_fail(TNNS_ERR_UNSUPPORTED, "layer shape or type outside the tensor-copy activation path");
@@ -1040,9 +1059,10 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     a.acc_bias = 0;
     a.alpha = alpha;
     a.status = ctx->d_status;
-    a.pimg = nullptr;
-    a.thr_next = nullptr;
-    a.next_ternary = 1;
+    a.pimg = reinterpret_cast<uint32_t*>(d_pimg);
+    a.thr_next = d_thr_next;
+    a.next_ternary = next_format != 0;
+    a.pimg_e2m1 = next_format == 2;
     a.cp_next = (w->KN + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS;
     a.img = nullptr;
     a.jtab = w->d_jtab;

@@ -103,8 +103,11 @@ int tnns_tensor_map_2d(void* map, int elem_bytes, const void* base, unsigned lon
 // 4-bit GEMM + PReLU whose activation tiles the copy engine gathers (im2col tensor copies) from
 // an e2m1 image; needs ternary activations and a channel count that fills 128-byte chunks
 bool tnns_im2col_supported(const tnns_cuda_weights* w, const TnnsGeom& g);
+// d_pimg != NULL: write the next layer's quantised activations instead of fp32 (next_format 0: binary
+// bit planes, 1: ternary bit planes, 2: ternary 4-bit operand image)
 int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const TnnsGeom& g,
-                            float alpha, int layout, cudaStream_t stream, int pairs = 0);
+                            float alpha, int layout, cudaStream_t stream, int pairs = 0, void* d_pimg = nullptr,
+                            const float* d_thr_next = nullptr, int next_format = 1);
 
 int tnns_launch_pack_weights(tnns_cuda_ctx* ctx, bool ternary, const float* d_w, const float* d_thr, void* d_packed, int KN, int C,
                              int KH, int KW, cudaStream_t stream);

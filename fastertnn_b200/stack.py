@@ -5,7 +5,14 @@ in the chosen layout; every layer re-quantises its input with its own thresholds
 
 ``chain="packed"`` removes that fp32 round trip: every layer but the last runs its GEMM with
 the quantising epilogue (``tnns_cuda_gemm_packed_out``) and the next layer starts from the bit
-planes (``tnns_cuda_im2row_packed``); the final fp32 output is bit-identical."""
+planes (``tnns_cuda_im2row_packed``); the final fp32 output is bit-identical.
+
+``chain="image"`` goes one step further where the layers qualify for the copy-engine route:
+the input is quantised once into a 4-bit operand image, every layer is ONE kernel -- the GEMM fed
+by im2col tensor copies, whose epilogue writes the next layer's 4-bit image
+(``tnns_cuda_gemm_im2col_packed_out``) -- and only the last layer writes fp32.  A layer that does
+not qualify takes the bit-plane steps of the packed chain; the format between two layers is
+chosen by what the consumer reads.  The final output is again bit-identical."""
 from __future__ import annotations
 
 import numpy as np
@@ -39,6 +46,20 @@ class ConvStack:
             self.d_img = ctx.malloc(img)
             self.d_a = ctx.malloc(a)
             self.extra = [self.d_img, self.d_a]
+        elif chain == "image":
+            if layout != api.NCHW:
+                raise ValueError("the image chain is defined for NCHW input and output")
+            if not self.act_ternary:
+                raise ValueError("4-bit operand images hold ternary activations")
+            self.fast = [ctx.im2col_supported(w, L.shape(batch)) for w, L in zip(self.weights, layers)]
+            img = max([api.e2m1_image_bytes(batch, layers[0].C, layers[0].H, layers[0].W)] +
+                      [api.e2m1_image_bytes(batch, L.KN, L.OH, L.OW) for L in layers])
+            self.d_imgs = [ctx.malloc(img), ctx.malloc(img)]  # ping-pong quantised activations (either format fits)
+            self.extra = list(self.d_imgs)
+            self.d_a = None
+            if not all(self.fast):
+                self.d_a = ctx.malloc(max(api.packed_bytes(type_, L.shape(batch)) for L, f in zip(layers, self.fast) if not f))
+                self.extra.append(self.d_a)
         elif chain != "fp32":
             raise ValueError(chain)
 
@@ -46,7 +67,7 @@ class ConvStack:
         return self.buf[0]
 
     def output_ptr(self) -> int:
-        return self.buf[1] if self.chain == "packed" else self.buf[len(self.layers) % 2]
+        return self.buf[1] if self.chain in ("packed", "image") else self.buf[len(self.layers) % 2]
 
     def run(self, stream: int = 0):
         """Enqueue all layers; input must already be in input_ptr()."""
@@ -63,6 +84,30 @@ class ConvStack:
                                              stream=stream)
                 else:
                     self.ctx.gemm(w, self.d_a, self.buf[1], self.batch, L.OH, L.OW, self.alpha, self.layout, stream=stream)
+            return
+        if self.chain == "image":
+            last = len(self.layers) - 1
+            L0 = self.layers[0]
+            # the input, in the format the first layer reads
+            if self.fast[0]:
+                self.ctx.quantise_e2m1(self.buf[0], self.d_thr, self.d_imgs[0], self.batch, L0.C, L0.H, L0.W, self.layout, stream)
+            else:
+                self.ctx.quantise(True, self.buf[0], self.d_thr, self.d_imgs[0], self.batch, L0.C, L0.H, L0.W, self.layout, stream)
+            for i, (L, w) in enumerate(zip(self.layers, self.weights)):
+                shape = L.shape(self.batch)
+                src, dst = self.d_imgs[i % 2], self.d_imgs[(i + 1) % 2]
+                nxt = 2 if (i < last and self.fast[i + 1]) else 1  # 4-bit image or ternary bit planes for the consumer
+                if self.fast[i]:
+                    if i < last:
+                        self.ctx.gemm_im2col_packed_out(w, src, dst, self.d_thr, nxt, shape, self.alpha, stream)
+                    else:
+                        self.ctx.gemm_im2col(w, src, self.buf[1], shape, self.alpha, self.layout, stream)
+                else:
+                    self.ctx.im2row_packed(True, src, self.d_a, shape, stream=stream)
+                    if i < last:
+                        self.ctx.gemm_packed_out(w, self.d_a, dst, self.d_thr, nxt, self.batch, L.OH, L.OW, self.alpha, stream=stream)
+                    else:
+                        self.ctx.gemm(w, self.d_a, self.buf[1], self.batch, L.OH, L.OW, self.alpha, self.layout, stream=stream)
             return
         for i, (L, w) in enumerate(zip(self.layers, self.weights)):
             self.ctx.conv(w, self.buf[i % 2], self.d_thr, self.buf[(i + 1) % 2], L.shape(self.batch), self.alpha, self.layout,

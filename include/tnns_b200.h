@@ -254,11 +254,11 @@ int tnns_cuda_quantise(tnns_cuda_ctx* ctx, int ternary, const float* d_x, const 
  * Same result as tnns_cuda_pack + tnns_cuda_gemm.  tnns_cuda_conv takes this route by default. */
 int tnns_cuda_gemm_implicit(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const tnns_shape_t* s,
                             float alpha, int layout, void* stream);
-/* The same route with the copy engine doing the gather (ternary activations, C a multiple of 256;
- * tnns_cuda_im2col_supported says whether a layer qualifies).  tnns_cuda_quantise_e2m1 writes the
+/* The same route with the copy engine doing the gather (ternary activations; 64-channel groups per
+ * pixel: 1, 2 or a multiple of 4; tnns_cuda_im2col_supported says whether a layer qualifies).  tnns_cuda_quantise_e2m1 writes the
  * quantised input as a 4-bit operand image, [n][pixel][C/2 bytes] with {-1,0,+1} as e2m1 nibbles
  * (tnns_e2m1_image_bytes() bytes, 32-byte aligned); tnns_cuda_gemm_im2col then receives every
- * 128-pixel x 256-channel activation tile of a filter tap as one im2col tensor copy (zero fill
+ * 128-pixel activation tile of a filter tap (256, 128 or 64 channels) as one im2col tensor copy (zero fill
  * outside the image = the reference's padding value, src/tnns/ternarize2row_avx2.c:438-452)
  * straight into the layout the tensor core reads: no warp expands or gathers anything.  Same
  * result as tnns_cuda_pack + tnns_cuda_gemm; tnns_cuda_conv prefers this route where it applies.
@@ -271,6 +271,15 @@ int tnns_cuda_quantise_e2m1(tnns_cuda_ctx* ctx, const float* d_x, const float* d
                             int layout, void* stream);
 int tnns_cuda_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const tnns_shape_t* s,
                           float alpha, int layout, int pairs, void* stream);
+/* Chaining on the copy-engine route: the same GEMM with the quantising epilogue of
+ * tnns_cuda_gemm_packed_out.  next_format (also accepted as `next_ternary` by
+ * tnns_cuda_gemm_packed_out): 0 = binary bit planes, 1 = ternary bit planes, 2 = ternary 4-bit
+ * operand image (tnns_e2m1_image_bytes(N, KN, OH, OW) bytes) -- what tnns_cuda_gemm_im2col of the
+ * next layer reads, so a stack of qualifying layers runs as one GEMM per layer with nothing but
+ * 4-bit images in between. */
+int tnns_cuda_gemm_im2col_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, void* d_image_out,
+                                     const float* d_thr_next, int next_format, const tnns_shape_t* s, float alpha, int pairs,
+                                     void* stream);
 int tnns_cuda_gemm_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const int64_t* d_a, void* d_image,
                               const float* d_thr_next, int next_ternary, int N, int OH, int OW, float alpha, void* stream);
 int tnns_cuda_im2row_packed(tnns_cuda_ctx* ctx, int ternary, const void* d_image, int64_t* d_packed, const tnns_shape_t* s,

@@ -251,7 +251,7 @@ def test_resnet18_style_stack_chained_on_device(gpu_ctx, checker):
     want = x
     for L, pw in zip(RESNET18_STACK, pws):
         want = checker.conv(TNN, want, thr, pw, (L.KH, L.KW), (L.P, L.P), (L.S, L.S), 0.5)
-    for chain in ("fp32", "packed"):
+    for chain in ("fp32", "packed", "image"):
         st = ConvStack(gpu_ctx, TNN, RESNET18_STACK, pws, N, 0.25, chain=chain)
         gpu_ctx.lib.tnns_cuda_memcpy_h2d(gpu_ctx.handle, st.input_ptr(), x.ctypes.data, x.nbytes)
         st.run()
@@ -260,6 +260,39 @@ def test_resnet18_style_stack_chained_on_device(gpu_ctx, checker):
         st.close()
         assert got.tobytes() == want.tobytes(), chain
         assert np.count_nonzero(got) > 0
+
+
+@pytest.mark.parametrize("type_", [TNN, TBN])
+def test_image_chain_switches_formats_between_layers(type_, gpu_ctx, checker):
+    """A stack whose layers alternate between the copy-engine route (4-bit image in) and the gathering
+    route (bit planes in): 64 -> 192 channels (three 64-channel groups: not eligible) -> 256 -> 100
+    (ragged) -> 128.  Every producer writes the format its consumer reads; final output bit-identical
+    to the checker chained on the host, for ternary and for binary weights."""
+    from fastertnn_b200 import synth
+    from fastertnn_b200.stack import ConvStack
+    layers = [Layer(64, 12, 12, 192, 3, 3, 1, 1), Layer(192, 12, 12, 256, 3, 3, 1, 2), Layer(256, 6, 6, 100, 3, 3, 1, 1),
+              Layer(100, 6, 6, 128, 1, 1, 0, 1), Layer(128, 6, 6, 40, 3, 3, 1, 1)]
+    N = 3
+    x = synth.uniform_pm1(31, (N, 64, 12, 12))
+    thr = np.full(N, 0.25, np.float32)
+    tern_w = wgt_ternary(type_)
+    pws = []
+    for i, L in enumerate(layers):
+        shape_w = (L.KN, L.C, L.KH, L.KW)
+        w = synth.ternary_values(900 + i, shape_w) if tern_w else synth.binary_values(900 + i, shape_w)
+        pws.append(checker.pack_weights(tern_w, w, np.full(L.KN, 0.5 if tern_w else 0.0, np.float32)))
+    want = x
+    for L, pw in zip(layers, pws):
+        want = checker.conv(type_, want, thr, pw, (L.KH, L.KW), (L.P, L.P), (L.S, L.S), 0.5)
+    st = ConvStack(gpu_ctx, type_, layers, pws, N, 0.25, chain="image")
+    assert st.fast == [True, False, True, True, True]
+    gpu_ctx.fill(st.input_ptr(), x)
+    st.run()
+    gpu_ctx.sync()
+    got = gpu_ctx.to_host(st.output_ptr(), want.shape, np.float32)
+    st.close()
+    assert got.tobytes() == want.tobytes()
+    assert np.count_nonzero(got) > 0
 
 
 @pytest.mark.parametrize("type_", [TNN, TBN, BTN, BNN])
