@@ -435,7 +435,8 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
         line = {
             "metric": METRIC, "value": ops / (ms_step * 1e-3) / 1e9, "unit": "GOPS", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_step, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
-            "dtype": ("e2m1 operands expanded from 2-bit planes, unit block scales, fp32 accumulate (exact), fp32 PReLU" if args.gemm in ("auto", "f4tc") else "int8 operands expanded from 2-bit planes, int32 accumulate, fp32 PReLU") if args.gemm != "popc" else "u32 bit-plane lanes, int32 popcount accumulate, fp32 PReLU",
+            "dtype": (("e2m1 (4-bit) operands quantised from fp32, unit block scales, fp32 accumulate (exact), fp32 PReLU" if im2col else
+                       "e2m1 operands expanded from 2-bit planes, unit block scales, fp32 accumulate (exact), fp32 PReLU") if args.gemm in ("auto", "f4tc") else "int8 operands expanded from 2-bit planes, int32 accumulate, fp32 PReLU") if args.gemm != "popc" else "u32 bit-plane lanes, int32 popcount accumulate, fp32 PReLU",
             "data": "synthetic",
             "config": {"workload": name, "batch": N_total, "batch_per_gpu": nloc, "layer": str(layer), "layout": "NCHW",
                        "M": N_total * OH * OW, "K": layer.C * layer.KH * layer.KW, "N": layer.KN, "gemm": args.gemm,
