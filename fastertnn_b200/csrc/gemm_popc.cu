@@ -16,9 +16,14 @@
 
 namespace {
 
+// The reference has two PReLU expressions, which differ in the sign of a zero sum under a negative
+// alpha: mm_tnn scales every non-positive value (src/tnns/mm_p2_final_tnn_avx2.c:90-93, 204-208: 0*alpha),
+// mm_tbn / mm_btn / mm_bnn pass zero through (result >= 0 ? result : alpha*result,
+// src/tnns/mm_p2_final_tbn_avx2.c:73, _btn_:73, _bnn_:60).
+template <int TYPE>
 __device__ __forceinline__ float prelu_i(int acc, float alpha) {
-    // src/tnns/mm_p2_final_tnn_avx2.c:204-208 ; acc == 0 gives +0.0f
-    return acc > 0 ? (float)acc : (float)acc * alpha;
+    if (TYPE == TNN) return acc > 0 ? (float)acc : (float)acc * alpha;
+    return acc >= 0 ? (float)acc : alpha * (float)acc;
 }
 
 __device__ __forceinline__ size_t out_index(long long r, int kn, int KN, int OHW, int layout) {
@@ -66,7 +71,7 @@ __global__ void __launch_bounds__(256) gemm_popc_simple_kernel(const uint32_t* _
             }
         }
         const int acc = (TYPE == BNN) ? K_unpack - 2 * cn : 64 * Kp - cz - 2 * cn;
-        y[out_index(r, kn, KN, OHW, layout)] = prelu_i(acc, alpha);
+        y[out_index(r, kn, KN, OHW, layout)] = prelu_i<TYPE>(acc, alpha);
     }
 }
 
@@ -227,7 +232,7 @@ __global__ void __launch_bounds__(NTHREADS) gemm_popc_tiled_kernel(const uint32_
             else if (TYPE == TBN) acc = 64 * Kp - az_cnt[i] - 2 * csa_total_w1(st[i][j]);
             else if (TYPE == BTN) acc = 64 * Kp - bz_cnt[j] - 2 * csa_total_w1(st[i][j]);
             else acc = K_unpack - 2 * csa_total_w1(st[i][j]);
-            v[j] = prelu_i(acc, alpha);
+            v[j] = prelu_i<TYPE>(acc, alpha);
         }
         const int c0 = n0 + warp * 8 + ln * 4;
         if (layout == TNNS_NHWC) {

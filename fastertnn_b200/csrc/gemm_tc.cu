@@ -281,6 +281,9 @@ struct GemmArgs {
     const float* thr_next;      // one threshold per image for that quantisation
     int next_ternary, cp_next;  // planes of the next layer's activations, its 64-channel groups
     int pimg_e2m1;              // write that output as a 4-bit operand image [n][pixel][ic][32 B] instead of bit planes
+    // PReLU of a zero sum: mm_tnn scales it (0*alpha, -0 for a negative alpha), mm_tbn / mm_btn / mm_bnn pass
+    // +0 through (src/tnns/mm_p2_final_tnn_avx2.c:90-93 against mm_p2_final_tbn_avx2.c:73)
+    int zero_passes;
     // optional implicit im2row (4-bit form): A is not a packed im2row matrix but the quantised
     // image [n][plane][pixel][ic] of the layer input; row r, plane word j are gathered on the fly
     const uint64_t* img;
@@ -604,6 +607,7 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
         const int sub = ((warp - WARP_EPI0) >> 2) % MT;   // which 128-row sub-tile (accumulator) it drains
         const int ecol = ((warp - WARP_EPI0) >> 2) / MT;  // which share of the columns
         constexpr int ECOLS = BN / EPW;
+        const bool alpha_in_unit = p.alpha > 0.f && p.alpha <= 1.f;
         const int bias_magic = 0x4B400000 + p.acc_bias;
         const float bias_f = (float)p.acc_bias;  // +0.0f when there is none: a + 0.0f also turns a -0 sum into +0
         uint32_t lt = 0;
@@ -652,19 +656,30 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                     }
                 }
                 if (row_ok) {
-                    // int -> float without the conversion unit: for |a| < 2^22 the float with bit
-                    // pattern 0x4B400000 + a is 1.5*2^23 + a exactly, so subtracting 1.5*2^23 gives a.
                     float f[32];
+                    if (F4 && alpha_in_unit) {
+                        // 0 < alpha <= 1: PReLU(a) = max(a, alpha*a), two instructions per output.  The
+                        // product is formed as fma(a, alpha, +0): one rounding like the reference's
+                        // acc*alpha, and a -0 sum (all products -0) gives +0, which max(-0, +0) returns.
 #pragma unroll
-                    for (int j = 0; j < 32; j++) {
-                        if (F4) {
-                            // max(a,0) + alpha*min(a,0): exact (one rounding, of alpha*a), and a -0 sum
-                            // comes out as +0 because max(-0,+0) is +0
+                        for (int j = 0; j < 32; j++) {
                             const float a = p.acc_bias ? __uint_as_float(v[j]) + bias_f : __uint_as_float(v[j]);
-                            f[j] = fmaf(p.alpha, fminf(a, 0.f), fmaxf(a, 0.f));
-                        } else {
+                            f[j] = fmaxf(a, fmaf(a, p.alpha, 0.0f));
+                        }
+                    } else if (F4) {
+                        // any alpha: the reference's expression on the canonical +0, a > 0 ? a : a*alpha
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const float ac = (p.acc_bias ? __uint_as_float(v[j]) + bias_f : __uint_as_float(v[j])) + 0.0f;
+                            f[j] = ac * ((p.zero_passes ? ac >= 0.f : ac > 0.f) ? 1.0f : p.alpha);
+                        }
+                    } else {
+                        // int -> float without the conversion unit: for |a| < 2^22 the float with bit
+                        // pattern 0x4B400000 + a is 1.5*2^23 + a exactly, so subtracting 1.5*2^23 gives a.
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
                             const float a = __int_as_float((int)v[j] + bias_magic) - 12582912.0f;
-                            f[j] = a * (a > 0.f ? 1.0f : p.alpha);  // PReLU; a == 0 stays +0
+                            f[j] = a * ((p.zero_passes ? a >= 0.f : a > 0.f) ? 1.0f : p.alpha);  // a == 0 is +0 here
                         }
                     }
                     const int c0 = n0 + cb;
@@ -945,6 +960,7 @@ int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const vo
     a.layout = layout;
     a.a_two_planes = (w->type == TNN || w->type == TBN) ? 1 : 0;
     a.acc_bias = (w->type == BNN) ? w->K_unpack - 64 * w->Kp : 0;
+    a.zero_passes = w->type != TNN;
     a.alpha = alpha;
     a.status = ctx->d_status;
     a.pimg = reinterpret_cast<uint32_t*>(d_pimg);
@@ -1057,6 +1073,7 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     a.layout = layout;
     a.a_two_planes = 1;
     a.acc_bias = 0;
+    a.zero_passes = w->type != TNN;
     a.alpha = alpha;
     a.status = ctx->d_status;
     a.pimg = reinterpret_cast<uint32_t*>(d_pimg);

@@ -183,11 +183,14 @@ int64_t* orc_pack_w_binary(const float* w, const float* thr, int KN, int C, int 
     return (int64_t*)out;
 }
 
-/* PReLU as the reference applies it to the integer accumulator: positive values
- * pass, non-positive are scaled (src/tnns/mm_p2_final_tnn_avx2.c:204-208,
- * src/tnns/mm_p2_final_tbn_avx2.c:73).  acc == 0 gives +0.0f either way for
- * finite alpha >= 0. */
+/* PReLU as mm_tnn applies it to the integer accumulator: positive values pass, non-positive
+ * are scaled (src/tnns/mm_p2_final_tnn_avx2.c:90-93, 204-208), so a zero sum is 0*alpha: +0 for
+ * alpha >= 0, -0 for a negative alpha. */
 static inline float prelu_i(int acc, float alpha) { return acc > 0 ? (float)acc : (float)acc * alpha; }
+/* mm_tbn / mm_btn / mm_bnn write `result >= 0 ? (float) result : prelu_alpha * result`
+ * (src/tnns/mm_p2_final_tbn_avx2.c:73, _btn_:73, _bnn_:60): a zero sum stays +0 whatever the sign
+ * of alpha, whereas mm_tnn multiplies it (prelu_i above; src/tnns/mm_p2_final_tnn_avx2.c:90-93). */
+static inline float prelu_i_ge(int acc, float alpha) { return acc >= 0 ? (float)acc : alpha * (float)acc; }
 
 static inline size_t nchw_at(size_t r, int kn, int KN, size_t OHW) {
     return ((r / OHW) * KN + kn) * OHW + r % OHW; /* include/tnns/mm.h:30 */
@@ -239,7 +242,7 @@ float* orc_mm_tbn(const int64_t* a, const int64_t* b, int N, int OH, int OW, int
                 const size_t p = p2_sign_at(j);
                 cn += __builtin_popcountll((ar[p] ^ br[j]) & ~ar[p + 4]);
             }
-            y[nchw_at((size_t)r, kn, KN, OHW)] = prelu_i(64 * Kp - cz - 2 * cn, alpha);
+            y[nchw_at((size_t)r, kn, KN, OHW)] = prelu_i_ge(64 * Kp - cz - 2 * cn, alpha);
         }
     }
     return y;
@@ -262,7 +265,7 @@ float* orc_mm_btn(const int64_t* a, const int64_t* b, int N, int OH, int OW, int
                 cz += __builtin_popcountll(br[p + 4]);
                 cn += __builtin_popcountll((ar[j] ^ br[p]) & ~br[p + 4]);
             }
-            y[nchw_at((size_t)r, kn, KN, OHW)] = prelu_i(64 * Kp - cz - 2 * cn, alpha);
+            y[nchw_at((size_t)r, kn, KN, OHW)] = prelu_i_ge(64 * Kp - cz - 2 * cn, alpha);
         }
     }
     return y;
@@ -282,7 +285,7 @@ float* orc_mm_bnn(const int64_t* a, const int64_t* b, int N, int OH, int OW, int
             int cn = 0;
             for (int j = 0; j < Kp; j++)
                 cn += __builtin_popcountll(A[(size_t)r * Kp + j] ^ B[(size_t)kn * Kp + j]);
-            y[nchw_at((size_t)r, kn, KN, OHW)] = prelu_i(K_unpack - 2 * cn, alpha);
+            y[nchw_at((size_t)r, kn, KN, OHW)] = prelu_i_ge(K_unpack - 2 * cn, alpha);
         }
     return y;
 }

@@ -569,3 +569,24 @@ def test_im2col_route_declines_what_it_cannot_do(gpu_ctx, checker):
         want = checker.conv(type_, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
         assert device_conv(ctx, case, wp, ft.NCHW, ft.PACK_AUTO, ft.GEMM_AUTO).tobytes() == want.tobytes()
         w.free()
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("alpha", [0.0, 1.0, 0.3, -0.25, 2.5])
+def test_prelu_slopes_other_than_one_half(alpha, gpu_ctx, checker):
+    """PReLU is acc > 0 ? acc : acc*alpha in fp32 (include/tnns/mm.h:60-66 of the reference).  Every GEMM
+    kernel must give the reference's bits for any slope, including the sign of zero (alpha = 0 turns
+    negative sums into -0, a negative alpha turns zero sums into -0).  Sparse activations (threshold
+    0.9) make zero sums common."""
+    ctx = gpu_ctx
+    for type_, layer in ((TNN, Layer(256, 6, 6, 40, 3, 3, 1, 1)), (TBN, Layer(64, 6, 6, 72, 3, 3, 1, 1)), (BNN, Layer(70, 5, 5, 33, 2, 2, 1, 1))):
+        case = make_case(type_, layer, 3, 1234, "uniform")
+        case.thr[:] = 0.9 if act_ternary(type_) else 0.0
+        wp = checker.pack_weights(wgt_ternary(type_), case.w, case.w_thr)
+        want = checker.conv(type_, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, alpha)
+        assert (want == 0).any()
+        case.alpha = alpha
+        for galgo in (ft.GEMM_AUTO, ft.GEMM_I8_TC, ft.GEMM_F4_TC, ft.GEMM_POPC_TILED, ft.GEMM_POPC_SIMPLE):
+            got = device_conv(ctx, case, wp, ft.NCHW, ft.PACK_AUTO, galgo)
+            bad = np.flatnonzero(got.view(np.uint32).ravel() != want.view(np.uint32).ravel())
+            assert bad.size == 0, (type_, alpha, galgo, bad.size, got.ravel()[bad[:3]], want.ravel()[bad[:3]])

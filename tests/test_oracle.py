@@ -9,7 +9,7 @@ from pathlib import Path
 import numpy as np
 import pytest
 
-from cases import act_ternary, extra_cases, reference_test_cases, special_value_case, wgt_ternary
+from cases import act_ternary, extra_cases, make_case, reference_test_cases, special_value_case, wgt_ternary
 
 GOLDEN = Path(__file__).resolve().parent / "golden"
 DIGESTS = json.loads((GOLDEN / "digests.json").read_text())
@@ -107,3 +107,19 @@ def test_special_values_port_equals_reference_objects(type_, port_oracle, ref_or
     a_p = port_oracle.pack(t, c.x, c.thr, c.kernel_hw, c.padding, c.stride)
     a_r = ref_oracle.pack(t, c.x, c.thr, c.kernel_hw, c.padding, c.stride)
     assert np.array_equal(a_p, a_r)
+
+
+@pytest.mark.parametrize("alpha", [0.0, 1.0, 0.3, -0.25, 2.5])
+@pytest.mark.parametrize("type_", [0, 1, 2, 3])
+def test_prelu_slopes_port_equals_reference_objects(type_, alpha, port_oracle, ref_oracle):
+    """The reference has two PReLU expressions (mm_tnn scales every non-positive sum, the other three
+    pass a zero sum through), which differ in the sign of zero for a negative slope; the restatement
+    follows both.  Sparse activations make zero sums common."""
+    from fastertnn_b200.workloads import Layer
+    layer = Layer(70, 5, 5, 33, 2, 2, 1, 1)
+    c = make_case(type_, layer, 2, 4321, "uniform")
+    c.thr[:] = 0.9 if act_ternary(type_) else 0.0
+    wp = ref_oracle.pack_weights(wgt_ternary(type_), c.w, c.w_thr)
+    y_r = ref_oracle.conv(type_, c.x, c.thr, wp, c.kernel_hw, c.padding, c.stride, alpha)
+    y_p = port_oracle.conv(type_, c.x, c.thr, wp, c.kernel_hw, c.padding, c.stride, alpha)
+    assert y_p.tobytes() == y_r.tobytes()
