@@ -41,6 +41,7 @@ METRIC = "ternary conv GOPS (2*M*N*K/s)"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
 # profiles/ (large layer, 64 images per launch), kept per image so that a rank's share scales.
 NCU_TRAFFIC_PER_IMAGE = {
+    ("tnn_conv_large", "f4_fused"): None,          # quantise + GEMM in one launch (filled in from the capture under profiles/)
     ("tnn_conv_large", "f4_im2col"): 91.5e6 / 64,  # im2col tensor copies from the 16.8 MB 4-bit image (block pairs)
     ("tnn_conv_large", "quantise_e2m1"): 143.1e6 / 64,
     ("tnn_conv_large", "f4"): 85.2e6 / 64,        # implicit im2row: reads the 8.4 MB image, not the im2row matrix
@@ -248,11 +249,22 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
     # rows itself; --route explicit: pack to the im2row matrix (t2r_p2_opt's job), then GEMM
     # "auto" is what tnns_cuda_conv picks: the copy-engine (im2col tensor copy) form where the layer qualifies
     tc4 = args.gemm in ("auto", "f4tc")
-    im2col = tc4 and args.route in ("auto", "im2col") and ctx.im2col_supported(w, shape)
-    if args.route == "im2col" and not im2col:
+    im2col = tc4 and args.route in ("auto", "im2col", "fused") and ctx.im2col_supported(w, shape)
+    if args.route in ("im2col", "fused") and not im2col:
         raise SystemExit("bench: this workload does not qualify for the im2col tensor-copy route")
     implicit = tc4 and (im2col or args.route in ("auto", "implicit"))
-    pack_bytes = (ft.api.e2m1_image_bytes(nloc, layer.C, layer.H, layer.W) if im2col else
+    sm_count = torch.cuda.get_device_properties(local).multi_processor_count
+
+    def fused_for(n):
+        """The library's own rule (tnns_cuda_conv): one launch with the quantise step inside the GEMM
+        kernel where the layer qualifies and every SM has at least four 128-row tiles."""
+        if not (im2col and args.route in ("auto", "fused")):
+            return False
+        tiles = -(-n * layer.OH * layer.OW // 128) * -(-layer.KN // 256)
+        return args.route == "fused" or tiles >= 4 * sm_count
+
+    fused = fused_for(nloc)
+    pack_bytes = (ft.api.fused_workspace_bytes(nloc, layer.C, layer.H, layer.W) if im2col else
                   ft.api.packed_image_bytes(True, nloc, layer.C, layer.H, layer.W) if implicit else ft.packed_bytes(ft.TNN, shape))
 
     def run_quantise(xp, pp, n, strm):
@@ -260,6 +272,9 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
             ctx.quantise_e2m1(xp, thr_d.data_ptr(), pp, n, layer.C, layer.H, layer.W, layout, strm)
         else:
             ctx.quantise(True, xp, thr_d.data_ptr(), pp, n, layer.C, layer.H, layer.W, layout, strm)
+
+    def run_fused(xp, pp, yp, shp, strm):
+        ctx.conv_fused(w, xp, thr_d.data_ptr(), yp, pp, pack_bytes, shp, 0.5, 0, strm)
 
     def run_gemm_image(pp, yp, shp, strm):
         if im2col:
@@ -280,24 +295,31 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
             xd.copy_(torch.roll(xd, shifts=r, dims=0))
         xs.append(xd)
         ys.append(torch.empty((nloc, layer.KN, OH, OW), dtype=torch.float32, device="cuda"))
-        ps.append(torch.empty(pack_bytes // 8 + 2, dtype=torch.int64, device="cuda"))
+        ps.append(torch.empty(pack_bytes // 8 + 32, dtype=torch.int64, device="cuda"))
     thr_d = torch.from_numpy(thr_h).cuda()
     stream = torch.cuda.Stream()
     sp = stream.cuda_stream
     layout = ft.NCHW
     gemm_algo = {"auto": ft.GEMM_AUTO, "popc": ft.GEMM_POPC_TILED, "i8tc": ft.GEMM_I8_TC, "f4tc": ft.GEMM_F4_TC}[args.gemm]
 
+    def aligned(t):
+        return (t.data_ptr() + 127) & ~127
+
     def step(i, ev=None):
         r = i % ring
         if ev:
             ev[0].record(stream)
-        if implicit:
+        if fused:
+            pass
+        elif implicit:
             run_quantise(xs[r].data_ptr(), ps[r].data_ptr(), nloc, sp)
         else:
             ctx.pack(True, xs[r].data_ptr(), thr_d.data_ptr(), ps[r].data_ptr(), shape, layout, ft.PACK_AUTO, sp)
         if ev:
             ev[1].record(stream)
-        if implicit:
+        if fused:
+            run_fused(xs[r].data_ptr(), aligned(ps[r]), ys[r].data_ptr(), shape, sp)
+        elif implicit:
             run_gemm_image(ps[r].data_ptr(), ys[r].data_ptr(), shape, sp)
         else:
             ctx.gemm(w, ps[r].data_ptr(), ys[r].data_ptr(), nloc, OH, OW, 0.5, layout, gemm_algo, sp)
@@ -345,7 +367,9 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
 
         def fstep(i):
             r = i % ring
-            if implicit:
+            if fused_for(nfix):
+                run_fused(xs[r].data_ptr(), aligned(ps[r]), ys[r].data_ptr(), fshape, sp)
+            elif implicit:
                 run_quantise(xs[r].data_ptr(), ps[r].data_ptr(), nfix, sp)
                 run_gemm_image(ps[r].data_ptr(), ys[r].data_ptr(), fshape, sp)
             else:
@@ -410,9 +434,10 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
         pk = peaks()
         ops = layer.ops(N_total)
         ops_loc = layer.ops(nloc)
-        pack_alg_bytes = in_bytes + pack_bytes
+        pack_alg_bytes = in_bytes + (ft.api.e2m1_image_bytes(nloc, layer.C, layer.H, layer.W) if im2col else pack_bytes)
+        t_pack_eff = t_pack_alone if fused else t_pack
         gemm_tops = ops_loc / (t_gemm * 1e-3) / 1e12
-        per_img = NCU_TRAFFIC_PER_IMAGE.get((name, {"popc": "popc", "i8tc": "tc"}.get(args.gemm, "f4_im2col" if im2col else "f4" if implicit else "f4_explicit")))
+        per_img = NCU_TRAFFIC_PER_IMAGE.get((name, {"popc": "popc", "i8tc": "tc"}.get(args.gemm, "f4_fused" if fused else "f4_im2col" if im2col else "f4" if implicit else "f4_explicit")))
         gemm_traffic = per_img * nloc if per_img else None
         per_img = NCU_TRAFFIC_PER_IMAGE.get((name, "quantise_e2m1" if im2col else "quantise" if implicit else "pack"))
         pack_traffic = per_img * nloc if per_img else None
@@ -428,7 +453,8 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
             gemm_peak = 2.0 * pk["bf16_tflops"]
             gemm_peak_source = f"2 x {pk['source']} bf16 burst figure (int8 dense rate = 2 x bf16)"
         else:
-            gemm_kernel_name, gemm_bound = ("gemm_tc_kernel<F4=true, ATMA=true> (tcgen05.mma kind::mxf4 GEMM fed by im2col tensor copies, unit scales, + PReLU)" if im2col else
+            gemm_kernel_name, gemm_bound = ("gemm_tc_kernel<F4=true, ATMA=true, QF=true> (whole layer in one launch: quantiser warps write the 4-bit image, tcgen05.mma kind::mxf4 GEMM fed by im2col tensor copies, unit scales, + PReLU)" if fused else
+                                            "gemm_tc_kernel<F4=true, ATMA=true> (tcgen05.mma kind::mxf4 GEMM fed by im2col tensor copies, unit scales, + PReLU)" if im2col else
                                             "gemm_tc_kernel<F4=true> (tcgen05.mma kind::mxf4 GEMM, unit scales, + PReLU)"), "tensor"
             gemm_peak = 4.0 * pk["bf16_tflops"]
             gemm_peak_source = f"4 x {pk['source']} bf16 burst figure (4-bit dense rate = 4 x bf16)"
@@ -440,12 +466,13 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
             "data": "synthetic",
             "config": {"workload": name, "batch": N_total, "batch_per_gpu": nloc, "layer": str(layer), "layout": "NCHW",
                        "M": N_total * OH * OW, "K": layer.C * layer.KH * layer.KW, "N": layer.KN, "gemm": args.gemm,
-                       "route": ("quantise to a 4-bit image -> GEMM fed by im2col tensor copies" if im2col else
+                       "route": ("one launch: quantise to a 4-bit image inside the GEMM kernel, GEMM fed by im2col tensor copies" if fused else
+                                 "quantise to a 4-bit image -> GEMM fed by im2col tensor copies" if im2col else
                                  "quantise to bit planes -> GEMM with implicit im2row" if implicit else "pack (im2row matrix) -> GEMM"),
                        "l2": f"ring of {ring} distinct input/workspace/output buffer sets ({ring * step_bytes >> 20} MiB) cycled "
                              f"between steps; one set alone is {step_bytes >> 20} MiB"},
             "gpu_launches": int(launches * world),
-            "kernels_ms": {("quantise" if implicit else "pack"): t_pack, "gemm": t_gemm},
+            "kernels_ms": ({"quantise+gemm (one launch)": t_gemm} if fused else {("quantise" if implicit else "pack"): t_pack, "gemm": t_gemm}),
             # dominant kernel: the GEMM.  Its roof is the tensor pipe; the int8 rate of this part is
             # twice its bf16 rate, and bf16 is what MEASURED_PEAKS.json holds (cuBLAS, burst figure
             # for a kernel timed alone), so peak = 2 x measured bf16.
@@ -456,13 +483,18 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
                 # second denominator, measured live: the rate of a bare tcgen05.mma loop of the same
                 # kind and tile shape (operands resident in shared memory, no loads, no epilogue)
                 "pipe_peak": ctx_mma_rate / 1e3 if ctx_mma_rate else None,
-                "frac_of_pipe_peak": gemm_tops / (ctx_mma_rate / 1e3) if ctx_mma_rate else None},
+                "frac_of_pipe_peak": gemm_tops / (ctx_mma_rate / 1e3) if ctx_mma_rate else None,
+                # the fused launch also streams the fp32 input and output through HBM
+                "hbm_algorithmic_bytes_per_launch": (in_bytes + out_bytes) if fused else None,
+                "hbm_frac": ((in_bytes + out_bytes) / (t_gemm * 1e-3) / 1e9 / pk["hbm_gbs"]) if fused else None},
             "roofline_pack": {
                 "kernel": ("quantise_tma_kernel<e2m1> (tensor-copy fed quantise to a 4-bit operand image)" if im2col else
                            "pack_staged_kernel<IMG_OUT> (quantise + bit-pack to a packed image)" if implicit else "pack_staged_kernel (quantise + bit-pack + im2row)"), "bound": "hbm",
-                "achieved": pack_alg_bytes / (t_pack * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": pack_alg_bytes / (t_pack * 1e-3) / 1e9 / pk["hbm_gbs"], "traffic": pack_traffic, "peak_source": pk["source"],
-                "algorithmic_bytes_per_launch": pack_alg_bytes, "ms_per_launch": t_pack,
+                "achieved": pack_alg_bytes / (t_pack_eff * 1e-3) / 1e9, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": pack_alg_bytes / (t_pack_eff * 1e-3) / 1e9 / pk["hbm_gbs"], "traffic": pack_traffic, "peak_source": pk["source"],
+                "algorithmic_bytes_per_launch": pack_alg_bytes, "ms_per_launch": t_pack_eff,
+                "note": ("not launched in the timed step (the quantise step runs inside the GEMM launch there); timed back to back by itself"
+                         if fused else None),
                 # the same kernel launched back to back without the GEMM in between
                 "ms_per_launch_alone": t_pack_alone,
                 "frac_alone": (pack_alg_bytes / (t_pack_alone * 1e-3) / 1e9 / pk["hbm_gbs"]) if t_pack_alone else None},
@@ -490,8 +522,10 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="tnn_conv_large")
     ap.add_argument("--gemm", choices=["auto", "popc", "i8tc", "f4tc"], default="auto")
-    ap.add_argument("--route", choices=["auto", "im2col", "implicit", "explicit"], default="auto",
-                    help="auto: the library's default layer route (im2col where the layer qualifies, else implicit); "
+    ap.add_argument("--route", choices=["auto", "fused", "im2col", "implicit", "explicit"], default="auto",
+                    help="auto: the library's default layer route (fused where the layer qualifies and is large enough, "
+                         "else im2col where it qualifies, else implicit); "
+                         "fused: quantise + GEMM fed by im2col tensor copies in ONE launch; "
                          "im2col: quantise to a 4-bit image + GEMM fed by im2col tensor copies; "
                          "implicit: quantise to bit planes + GEMM whose warps gather and expand their im2row rows; "
                          "explicit: pack to the im2row matrix, then GEMM")

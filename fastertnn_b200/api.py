@@ -17,7 +17,7 @@ from ._lib import GemmTestcase, Shape, Testcase, load_library
 TNN, TBN, BTN, BNN = 0, 1, 2, 3
 NCHW, NHWC = 0, 1
 PACK_AUTO, PACK_GATHER, PACK_STAGED = 0, 1, 2
-GEMM_AUTO, GEMM_POPC_SIMPLE, GEMM_POPC_TILED, GEMM_I8_TC, GEMM_F4_TC = 0, 1, 2, 3, 4
+GEMM_AUTO, GEMM_POPC_SIMPLE, GEMM_POPC_TILED, GEMM_I8_TC, GEMM_F4_TC, GEMM_F4_FUSED = 0, 1, 2, 3, 4, 5
 
 
 class TnnsError(RuntimeError):
@@ -300,6 +300,16 @@ class Context:
         pairs: 0 = by size, 1 = single blocks, 2 = block pairs (tcgen05.mma.cta_group::2)."""
         _check(self.lib.tnns_cuda_gemm_im2col(self.handle, w.handle, d_image, d_y, C.byref(shape), alpha, layout, pairs, stream))
 
+    def conv_fused_supported(self, w: Weights, shape: Shape, d_x: int, layout=NCHW) -> bool:
+        return bool(self.lib.tnns_cuda_conv_fused_supported(w.handle, C.byref(shape), d_x, layout))
+
+    def conv_fused(self, w: Weights, d_x: int, d_thr: int, d_y: int, d_ws: int, ws_bytes: int, shape: Shape, alpha: float,
+                   pairs=0, stream=0):
+        """Whole layer in ONE launch: quantiser warps beside the tensor-copy fed GEMM (NCHW input).
+        d_ws: fused_workspace_bytes() bytes, 128-byte aligned."""
+        _check(self.lib.tnns_cuda_conv_fused(self.handle, w.handle, d_x, d_thr, d_y, d_ws, ws_bytes, C.byref(shape), alpha, pairs,
+                                             stream))
+
     def gemm_im2col_packed_out(self, w: Weights, d_image: int, d_image_out: int, d_thr_next: int, next_format: int, shape: Shape,
                                alpha: float, stream=0, pairs=0):
         """The copy-engine GEMM with the quantising epilogue: writes the next layer's activations as binary (0) or
@@ -373,6 +383,10 @@ def conv_noalloc(type_: int, d_packed_weights: int, d_x: int, d_thr: int, d_y: i
 
 def packed_image_bytes(ternary: bool, N: int, C_: int, H: int, W: int) -> int:
     return load_library().tnns_packed_image_bytes(int(ternary), N, C_, H, W)
+
+
+def fused_workspace_bytes(N: int, C_: int, H: int, W: int) -> int:
+    return int(load_library().tnns_fused_workspace_bytes(N, C_, H, W))
 
 
 def e2m1_image_bytes(N: int, C_: int, H: int, W: int) -> int:

@@ -358,6 +358,39 @@ int tnns_cuda_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const 
 }
 
 // --- chained layers without the fp32 round trip ------------------------------------------------
+static inline size_t fused_image_bytes(int N, int C, int H, int W) { return (tnns_e2m1_image_bytes(N, C, H, W) + 127) & ~(size_t)127; }
+
+size_t tnns_fused_workspace_bytes(int N, int C, int H, int W) {
+    if (N < 0 || C <= 0 || H <= 0 || W <= 0) return 0;
+    return fused_image_bytes(N, C, H, W) + tnns_fused_sync_bytes(N);
+}
+
+int tnns_cuda_conv_fused_supported(const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout) {
+    TnnsGeom g;
+    if (!w || !s || tnns_make_geom(s, &g)) return 0;
+    if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW) return 0;
+    return tnns_fused_supported(w, g, d_x, layout) ? 1 : 0;
+}
+
+int tnns_cuda_conv_fused(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y,
+                         void* d_workspace, size_t workspace_bytes, const tnns_shape_t* s, float alpha, int pairs, void* stream) {
+    if (!ctx || !w || !d_x || !d_thr || !d_y || !d_workspace) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    TnnsGeom g;
+    int rc = tnns_make_geom(s, &g);
+    if (rc) return rc;
+    if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW)
+        return tnns_fail(TNNS_ERR_INVALID, "shape does not match the uploaded weights");
+    if (g.N == 0) return TNNS_OK;
+    if (reinterpret_cast<uintptr_t>(d_workspace) & 127) return tnns_fail(TNNS_ERR_INVALID, "workspace must be 128-byte aligned");
+    const size_t need = tnns_fused_workspace_bytes(g.N, g.C, g.H, g.W);
+    if (workspace_bytes < need) return tnns_fail(TNNS_ERR_INVALID, "workspace of %zu bytes, need %zu", workspace_bytes, need);
+    TnnsFusedInput f;
+    f.d_x = d_x;
+    f.d_thr = d_thr;
+    f.d_sync = reinterpret_cast<unsigned int*>(static_cast<char*>(d_workspace) + fused_image_bytes(g.N, g.C, g.H, g.W));
+    return tnns_launch_gemm_im2col(ctx, w, d_workspace, d_y, g, alpha, TNNS_NCHW, (cudaStream_t)stream, pairs, nullptr, nullptr, 1, &f);
+}
+
 size_t tnns_packed_image_bytes(int ternary, int N, int C, int H, int W) {
     if (N < 0 || C <= 0 || H <= 0 || W <= 0) return 0;
     return (size_t)N * (ternary ? 2 : 1) * H * W * ((C + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS) * 8;
@@ -425,6 +458,23 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
     // route (pack to the im2row matrix, then GEMM).
     // Where the layer qualifies (ternary activations, C a multiple of 256) the image is written as
     // 4-bit operands and the copy engine delivers the GEMM's activation tiles (im2col tensor copies).
+    if (gemm_algo == TNNS_GEMM_F4_FUSED || (pack_algo == TNNS_PACK_AUTO && gemm_algo == TNNS_GEMM_AUTO)) {
+        // one launch: the quantise step runs inside the GEMM kernel.  Taken on request, and by
+        // default where every SM has several tiles, so that the quantisation of later images hides
+        // under the MMAs of earlier ones (with one or two tiles per SM the two steps mostly run one
+        // after the other anyway, and the stand-alone quantise kernel is the faster of the two).
+        // Measured on B200, fused / two launches in us: 64 x 512x32x32 -> 512 (6.9 tiles per SM)
+        // 81 / 95, 256 x 128x28x28 -> 128 (10.6) 58 / 66, 256 x 64x56x56 -> 64 (42) 130 / 142;
+        // 256 x 256x14x14 -> 256 (2.6) 43 / 40, 16 x 512x32x32 -> 512 (1.7) 37 / 37.
+        const bool can = pack_algo == TNNS_PACK_AUTO && tnns_fused_supported(w, g, d_x, layout) &&
+                         (reinterpret_cast<uintptr_t>(d_workspace) & 127) == 0 &&
+                         tnns_fused_workspace_bytes(g.N, g.C, g.H, g.W) <= workspace_bytes;
+        if (gemm_algo == TNNS_GEMM_F4_FUSED && !can)
+            return tnns_fail(TNNS_ERR_UNSUPPORTED, "layer, layout, workspace size or alignment outside the fused quantise + GEMM route");
+        const long long tiles = (((long long)g.N * g.OH * g.OW + 127) / 128) * ((g.KN + 255) / 256);
+        if (can && (gemm_algo == TNNS_GEMM_F4_FUSED || tiles >= 4LL * ctx->sm_count))
+            return tnns_cuda_conv_fused(ctx, w, d_x, d_thr, d_y, d_workspace, workspace_bytes, s, alpha, 0, stream);
+    }
     const bool auto_route = pack_algo == TNNS_PACK_AUTO && (gemm_algo == TNNS_GEMM_AUTO || gemm_algo == TNNS_GEMM_F4_TC);
     if (auto_route && tnns_im2col_supported(w, g) && tnns_e2m1_image_bytes(g.N, g.C, g.H, g.W) <= workspace_bytes) {
         if (reinterpret_cast<uintptr_t>(d_workspace) & 31) return tnns_fail(TNNS_ERR_INVALID, "workspace must be 32-byte aligned");
@@ -455,7 +505,7 @@ int tnns_cuda_conv(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* 
     // room for the im2row matrix (explicit route) and, where the layer qualifies, for the 4-bit
     // image of the copy-engine route, which is larger than the matrix for 1x1 kernels
     size_t need = std::max<size_t>(tnns_packed_bytes(w->type, s), 16);
-    if (tnns_im2col_supported(w, g)) need = std::max(need, tnns_e2m1_image_bytes(g.N, g.C, g.H, g.W));
+    if (tnns_im2col_supported(w, g)) need = std::max(need, tnns_fused_workspace_bytes(g.N, g.C, g.H, g.W));
     if (ctx->workspace_bytes < need) {
         TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
         // earlier launches may still read the old workspace
@@ -512,7 +562,7 @@ int tnns_cuda_conv_host(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const fl
     tnns_shape_t ss = *s;
     ss.N = nb;
     size_t pack_slice = std::max<size_t>(tnns_packed_bytes(w->type, &ss), 16);
-    if (tnns_im2col_supported(w, g)) pack_slice = std::max(pack_slice, tnns_e2m1_image_bytes(nb, g.C, g.H, g.W));
+    if (tnns_im2col_supported(w, g)) pack_slice = std::max(pack_slice, tnns_fused_workspace_bytes(nb, g.C, g.H, g.W));
 
     // staging buffers are shared by both slots' sizes; growing needs the device idle
     bool must_grow = ctx->stage_in_bytes < in_img * nb || ctx->stage_out_bytes < out_img * nb ||

@@ -43,12 +43,19 @@
 #include "internal.h"
 #include "mbar.cuh"
 
+
+
 namespace {
 
 constexpr int BM = 128;        // rows per accumulator (tensor-memory lanes)
 constexpr int KCH = 128;       // K elements = bytes per row and stage (one swizzle atom)
 constexpr int A_SUB = BM * KCH;  // bytes of one 128-row activation sub-tile per stage
 constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_EXP0 = 2;
+// fused quantisation (QF)
+constexpr int Q_FLAG0 = 32;   // the per-image words start one 128-byte line after the item counter
+constexpr int Q_PIX = 128;    // pixels per quantise item = quantiser threads per block
+constexpr int Q_STG = 2;      // stages of the quantiser warps' ring
+constexpr int Q_PUBN = 8;     // items the quantiser warps may be ahead of the publisher
 // A block owns MT stacked 128-row sub-tiles (MT*128 rows) and BN kernels: every weight stage
 // that arrives from L2 feeds MT MMAs, which is what keeps the L2 -> SM weight traffic below
 // the tensor pipe's appetite.  Roles: warp 0 weight producer, warp 1 MMA issuer, NG groups of
@@ -71,12 +78,24 @@ constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_EXP0 = 2;
 // half.  A block then receives 32 KB instead of 48 KB per stage from L2 and the ring is six deep.
 // Both blocks' tensor copies report to the first block's "full" barrier; its commits release the
 // stage and publish the accumulator in both blocks (multicast arrive).
-template <int BN, int MT, bool F4, bool ATMA = false, int CG = 1, int TAPS = 1>
+// QF (tensor-copy form only) fuses the quantise step into the same launch: four more warps turn the
+// layer's fp32 input into the 4-bit image, item by item (128 pixels x 64 channels, claimed from a
+// global counter, fetched as one 32 KB tensor copy into a two-stage ring of their own -- the GEMM
+// ring is one or two stages shallower to make room), and count every finished item on its image's
+// word in global memory; the producer thread starts a tile's tensor copies once the images its
+// rows belong to are complete.  The quantisation (HBM-bound) then runs underneath the MMAs
+// (tensor-bound) of earlier tiles.
+template <int BN, int MT, bool F4, bool ATMA = false, int CG = 1, int TAPS = 1, bool QF = false>
 struct TcCfg {
+    static_assert(!QF || ATMA, "fused quantisation: tensor-copy form only");
+    static constexpr int NQ = QF ? 5 : 0;  // four quantiser warps (thread = pixel of a 128-pixel item) and the publisher's warp
     static_assert(TAPS == 1 || (ATMA && (TAPS == 2 || TAPS == 4)), "taps per stage row: tensor-copy form only");
     static_assert(!ATMA || (F4 && MT == 1), "tensor-copy activations: 4-bit form, one accumulator per block");
     static_assert(CG == 1 || (CG == 2 && ATMA), "block pairs: tensor-copy form only");
-    static constexpr int NSTG = (CG == 2) ? 6 : ((MT == 1) ? 4 : 3);  // smem ring depth
+    static constexpr int QSTG = Q_STG, Q_STAGE = 128 * 64 * 4;  // quantiser ring: stages, bytes per stage
+    // smem ring depth
+    static constexpr int NSTG_QF = (CG == 2) ? 5 : (BN == 256 ? 3 : 4);
+    static constexpr int NSTG = QF ? NSTG_QF : ((CG == 2) ? 6 : ((MT == 1) ? 4 : 3));
     static constexpr int A_STAGE = MT * A_SUB, B_STAGE = (BN / CG) * KCH;
     static constexpr bool OVL = F4 && MT == 1 && BN == 256;        // overlapping accumulator sets
     static constexpr int NBUF = (OVL || MT * BN <= (F4 ? 128 : 256)) ? 2 : 1;  // accumulator sets in tensor memory
@@ -87,9 +106,12 @@ struct TcCfg {
     // expander groups (stages expanded concurrently); 22 warps per block in every MT = 1 form
     static constexpr int NG = ATMA ? 0 : ((MT == 1) ? (EPW == 2 ? 3 : 4) : 2);
     static constexpr int WARP_EPI0 = WARP_EXP0 + 4 * MT * NG;
-    static constexpr int NTHREADS = 32 * (2 + 4 * MT * NG + 4 * MT * EPW);
-    static constexpr int TAPMAX = 1024;  // entries of the tap table kept in shared memory
-    static constexpr size_t SMEM = 1024 + (size_t)NSTG * (A_STAGE + B_STAGE) + 256 + TAPMAX * sizeof(uint32_t);
+    static constexpr int WARP_Q0 = WARP_EPI0 + 4 * MT * EPW;
+    static constexpr int NTHREADS = 32 * (2 + 4 * MT * NG + 4 * MT * EPW + NQ);
+    static constexpr int TAPMAX = QF ? 256 : 1024;  // entries of the tap table kept in shared memory
+    static constexpr size_t Q_OFF = (size_t)NSTG * (A_STAGE + B_STAGE) + 256 + TAPMAX * sizeof(uint32_t);  // quantiser ring, then its barriers
+    static constexpr size_t SMEM = 1024 + Q_OFF + (QF ? QSTG * Q_STAGE + 128 : 0);
+    static_assert(SMEM <= 232448, "shared memory per block");
 };
 
 __device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
@@ -289,15 +311,228 @@ struct GemmArgs {
     const uint64_t* img;
     const uint32_t* jtab;       // per plane word j: kh<<24 | kw<<16 | ic, 0xFFFFFFFF for pad words
     int H, W, OW, Cp, SH, SW, PH, PW;
+    // fused quantisation (QF): the layer's fp32 NCHW input and per-image thresholds, the 4-bit image
+    // the quantiser warps write (the tensor the activation copies read), and the launch's
+    // synchronisation words, zeroed before the launch: q_sync[0] = next item to claim,
+    // q_sync[Q_FLAG0 + n] = finished items of image n
+    const float* qx;
+    const float* qthr;
+    uint4* qimg;
+    unsigned int* q_sync;
+    int qN, qC, q_nbands;
 };
+
+__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
+    unsigned int v;
+    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+// Bounded wait for a counter in global memory that other blocks advance.
+__device__ __forceinline__ bool counter_wait(const unsigned int* ctr, unsigned int target, volatile int* abort_flag, unsigned int* status,
+                                             unsigned code) {
+    if (ld_acquire_gpu(ctr) >= target) return true;
+    const long long t0 = clock64();
+    for (;;) {
+#pragma unroll 1
+        for (int i = 0; i < 64; i++) {
+            if (ld_acquire_gpu(ctr) >= target) return true;
+            __nanosleep(40);
+        }
+        if (*abort_flag) return false;
+        if (clock64() - t0 > 2000000000LL) {
+            *abort_flag = 1;
+            atomicOr(status, STATUS_WAIT_EXPIRED | code);
+            return false;
+        }
+    }
+}
+__device__ __forceinline__ uint32_t push_sign(uint32_t acc, float d) { return __funnelshift_l(__float_as_uint(d), acc, 1); }
+
+// Quantiser role of the fused form, called by the four quantiser warps together (thread = pixel).
+// An item = 128 neighbouring pixels x 64 channels of one image (NCHW, a row of the 2-D tensor
+// (image, channel) x pixels per channel).  The first lane claims items in image order from a
+// global counter -- so the images the first tiles need are finished first, whichever blocks
+// run -- and requests each as ONE tensor copy into a two-stage ring; every thread then reads its
+// pixel's 64 channels from shared memory (conflict-free), pushes the sign bits of (v + t) and
+// (t - |v|) into the plane words (src/tnns/ternarize2row_avx2.c:438-452 read off sign bits),
+// hands the stage back and stores the pixel's 64 channels as 32 bytes of e2m1 operands.  A warp
+// that has stored its part of item k sets its progress word to k + 1; the publisher (below) turns
+// that into counts on the images' words in global memory.
+struct QuantArgs {
+    const float* qthr;
+    uint4* qimg;
+    unsigned int* q_sync;
+    int qN, qC, q_nbands, Cp, HW;
+    unsigned int* status;
+};
+// Control words of the quantiser warps and the publisher, behind the quantiser ring's barriers.
+struct QuantCtl {
+    unsigned int item[Q_STG];   // item held by each stage (>= items: end mark)
+    unsigned int done[4];        // per quantiser warp: items whose stores it has issued
+    unsigned int published;      // items the publisher has counted
+    unsigned int total;          // items this block processed, ~0u while the quantiser warps run
+    int pub_n[Q_PUBN];           // image of item k at k % Q_PUBN
+};
+static_assert(sizeof(QuantCtl) + 2 * Q_STG * sizeof(uint64_t) <= 128, "control words behind the quantiser ring");
+__device__ __noinline__ void quantise_items(const QuantArgs p, const CUtensorMap* tmap_q, unsigned char* stage0, uint64_t* qbars,
+                                            volatile int* abort_flag, const int qtid) {
+    constexpr int QSTG = Q_STG, Q_STAGE = Q_PIX * 64 * 4;
+    const int lane = qtid & 31, qwarp = qtid >> 5;
+    const uint32_t bar_full = smem_u32(qbars), bar_empty = smem_u32(qbars + QSTG);
+    volatile QuantCtl* ctl = reinterpret_cast<volatile QuantCtl*>(qbars + 2 * QSTG);
+    const unsigned int items = (unsigned int)p.qN * (unsigned int)p.q_nbands * (unsigned int)p.Cp;
+    // issue: the claimed item goes into stage s (or the end mark, completing the barrier without bytes)
+    auto issue = [&](int s, unsigned int i) {
+        ctl->item[s] = i;
+        if (i < items) {
+            const int ic = (int)(i % (unsigned int)p.Cp);
+            const unsigned int nb = i / (unsigned int)p.Cp;
+            const int band = (int)(nb % (unsigned int)p.q_nbands), n = (int)(nb / (unsigned int)p.q_nbands);
+            mbar_arrive_expect_tx(bar_full + 8 * s, Q_STAGE);  // the whole box, edges zero-filled
+            tma_tile2d_g2s(smem_u32(stage0 + s * Q_STAGE), tmap_q, band * Q_PIX, n * p.qC + ic * 64, bar_full + 8 * s);
+        } else {
+            mbar_arrive(bar_full + 8 * s);
+        }
+    };
+    unsigned int next = 0;  // issuer only: the item claimed ahead
+    if (qtid == 0) {
+#pragma unroll
+        for (int s = 0; s < QSTG; s++) issue(s, atomicAdd(p.q_sync, 1u));
+        next = atomicAdd(p.q_sync, 1u);
+    }
+    // the image's threshold is fetched one item ahead (a peek at the item the other stage holds,
+    // checked when its turn comes), so its load latency is not paid in front of the first compare
+    int pf_n = -1;
+    float pf_t = 0.f;
+    unsigned int k = 0;
+    for (;; k++) {
+        const int s = (int)(k % QSTG);
+        const uint32_t ph = (k / QSTG) & 1;
+        if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 7)) break;
+        const unsigned int i = ctl->item[s];
+        if (i >= items) break;  // every later claim is past the end as well
+        const int ic = (int)(i % (unsigned int)p.Cp);
+        const unsigned int nb = i / (unsigned int)p.Cp;
+        const int band = (int)(nb % (unsigned int)p.q_nbands), n = (int)(nb / (unsigned int)p.q_nbands);
+        const int nch = min(64, p.qC - ic * 64);
+        const float t = ((n == pf_n) ? pf_t : __ldg(p.qthr + n)) + 0.0f;  // + 0.0f: a threshold of -0 behaves as +0
+        {
+            // the loaded value is not touched before the next iteration: an instruction that used it
+            // here would hold this warp until the load returned
+            const unsigned int i2 = ctl->item[(s + 1) % QSTG];  // may be stale: only ever used after the check above
+            if (i2 < items) {
+                pf_n = (int)(i2 / ((unsigned int)p.Cp * (unsigned int)p.q_nbands));
+                pf_t = __ldg(p.qthr + pf_n);
+            }
+        }
+        const float* sp = reinterpret_cast<const float*>(stage0 + s * Q_STAGE) + qtid;
+        uint32_t sg[2] = {0, 0}, nz[2] = {0, 0};
+        // channel b of a half ends at bit b: visit 31 .. 0 and shift left (four independent chains)
+        if (nch == 64) {
+#pragma unroll
+            for (int b = 31; b >= 0; b--) {
+#pragma unroll
+                for (int h = 0; h < 2; h++) {
+                    const float v = sp[(32 * h + b) * Q_PIX];
+                    sg[h] = push_sign(sg[h], v + t);
+                    nz[h] = push_sign(nz[h], t - fabsf(v));
+                }
+            }
+        } else {
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+#pragma unroll 1
+                for (int b = 31; b >= 0; b--) {
+                    if (32 * h + b < nch) {
+                        const float v = sp[(32 * h + b) * Q_PIX];
+                        sg[h] = push_sign(sg[h], v + t);
+                        nz[h] = push_sign(nz[h], t - fabsf(v));
+                    } else {  // absent channel: sign 0, non-zero 0
+                        sg[h] <<= 1;
+                        nz[h] <<= 1;
+                    }
+                }
+            }
+        }
+        // every value is in registers: hand the stage back; the issuer refills it at once
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_empty + 8 * s);
+        if (qtid == 0) {
+            if (!mbar_wait(bar_empty + 8 * s, ph, abort_flag, p.status, 8)) break;
+            issue(s, next);
+            next = atomicAdd(p.q_sync, 1u);
+            // the publisher's ring of image indices: never more than Q_PUBN items ahead of it
+            if (k >= Q_PUBN && ctl->published + Q_PUBN <= k) {
+                const long long t0 = clock64();
+                while (ctl->published + Q_PUBN <= k && !*abort_flag) {
+                    if (clock64() - t0 > 2000000000LL) {
+                        *abort_flag = 1;
+                        atomicOr(p.status, STATUS_WAIT_EXPIRED | 9);
+                    }
+                }
+            }
+            ctl->pub_n[k % Q_PUBN] = n;
+        }
+        const int pix = band * Q_PIX + qtid;
+        if (pix < p.HW) {
+            uint32_t lo[4], hi[4];
+            tnns_expand32_f4(sg[0], ~nz[0], lo);
+            tnns_expand32_f4(sg[1], ~nz[1], hi);
+            uint4* dst = p.qimg + (((size_t)n * p.HW + pix) * p.Cp + ic) * 2;
+            dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
+            dst[1] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
+        }
+        // progress word of this warp: release at block scope, so that the publisher, having read it,
+        // may publish the warp's stores (and, for the first warp, the image index) further
+        __syncwarp();
+        if (lane == 0) {
+            __threadfence_block();
+            ctl->done[qwarp] = k + 1;
+        }
+    }
+    __syncwarp();
+    if (qtid == 0) ctl->total = k;
+}
+
+// Publisher of the fused form (one thread).  Counting a finished item on its image's word needs a
+// gpu-scope release fence in front -- the item's plain stores must be visible to whoever sees the
+// count -- and under the GEMM's store traffic that fence takes longer than quantising the item.
+// So the quantiser warps never fence at gpu scope: this thread watches their progress words,
+// and whenever all four have moved on it issues ONE fence and counts every newly finished item
+// (four warps per item) with relaxed adds.  The producer threads of all blocks poll those counts.
+__device__ __noinline__ void publish_items(unsigned int* q_sync, unsigned int* status, uint64_t* qbars, volatile int* abort_flag) {
+    volatile QuantCtl* ctl = reinterpret_cast<volatile QuantCtl*>(qbars + 2 * Q_STG);
+    unsigned int published = 0;
+    long long t0 = clock64();
+    for (;;) {
+        const unsigned int m = min(min(ctl->done[0], ctl->done[1]), min(ctl->done[2], ctl->done[3]));
+        if (m > published) {
+            __threadfence();  // acquire of the progress words at block scope, release of the warps' stores at gpu scope
+            for (unsigned int j = published; j < m; j++)
+                asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(q_sync + Q_FLAG0 + ctl->pub_n[j % Q_PUBN]), "r"(4u) : "memory");
+            published = m;
+            ctl->published = m;
+            t0 = clock64();
+        } else {
+            if (ctl->total == published || *abort_flag) break;
+            if (clock64() - t0 > 4000000000LL) {
+                *abort_flag = 1;
+                atomicOr(status, STATUS_WAIT_EXPIRED | 10);
+                break;
+            }
+            __nanosleep(64);
+        }
+    }
+}
 
 // TAPS (tensor-copy form): filter taps per 128-byte stage row -- 1: a tap's 256 channels fill the
 // row (C_pack % 4 == 0); 2: C_pack = 2, two taps of 128 channels in two 64-byte-swizzled sub-tiles;
 // 4: C_pack = 1, four taps of 64 channels in four 32-byte-swizzled sub-tiles.
-template <int BN, int MT, bool F4, bool ATMA, int CG, int TAPS>
-__global__ void __launch_bounds__(TcCfg<BN, MT, F4, ATMA, CG, TAPS>::NTHREADS, 1)
-gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b) {
-    using Cfg = TcCfg<BN, MT, F4, ATMA, CG, TAPS>;
+template <int BN, int MT, bool F4, bool ATMA, int CG, int TAPS, bool QF>
+__global__ void __launch_bounds__(TcCfg<BN, MT, F4, ATMA, CG, TAPS, QF>::NTHREADS, 1)
+gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __grid_constant__ CUtensorMap tmap_b,
+               const __grid_constant__ CUtensorMap tmap_q) {
+    using Cfg = TcCfg<BN, MT, F4, ATMA, CG, TAPS, QF>;
     constexpr int NSTG = Cfg::NSTG, A_STAGE = Cfg::A_STAGE, B_STAGE = Cfg::B_STAGE, NBUF = Cfg::NBUF, WARP_EPI0 = Cfg::WARP_EPI0, NG = Cfg::NG, EPW = Cfg::EPW;
     constexpr int BMT = MT * BM;      // rows per block
     constexpr int TILE_M = CG * BMT;  // rows per tile (a block pair shares one 256-row tile)
@@ -342,6 +577,17 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
         for (int b = 0; b < 2; b++) {
             mbar_init(bar_tfull + 8 * b, 1);
             mbar_init(bar_tempty + 8 * b, CG * 4 * MT * EPW);  // the epilogue warps (of both blocks of a pair)
+        }
+        if (QF) {
+            uint64_t* qbars = reinterpret_cast<uint64_t*>(smem + Cfg::Q_OFF + Cfg::QSTG * Cfg::Q_STAGE);
+            for (int s = 0; s < Cfg::QSTG; s++) {
+                mbar_init(smem_u32(qbars + s), 1);               // the issuer's arrive with the expected bytes
+                mbar_init(smem_u32(qbars + Cfg::QSTG + s), 4);   // the four quantiser warps
+            }
+            volatile QuantCtl* ctl = reinterpret_cast<volatile QuantCtl*>(qbars + 2 * Cfg::QSTG);
+            ctl->done[0] = ctl->done[1] = ctl->done[2] = ctl->done[3] = 0;
+            ctl->published = 0;
+            ctl->total = 0xFFFFFFFFu;
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -400,6 +646,17 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                     const int oh = rem / p.OW;
                     a_h = oh * p.SH - p.PH;
                     a_w = (rem - oh * p.OW) * p.SW - p.PW;
+                    if (QF) {
+                        // the copies of this tile read the images of its rows: wait until the
+                        // quantiser warps (of any block) have finished them
+                        const long long last = min(row0 + BMT, p.M) - 1;
+                        const int n_last = (int)(last / p.OHW);
+                        const unsigned int per_image = (unsigned int)(p.q_nbands * p.Cp) * 4u;  // every quantiser warp counts itself
+                        for (int n = a_n; n <= n_last; n++)
+                            if (!counter_wait(p.q_sync + Q_FLAG0 + n, per_image, abort_flag, p.status, 6)) goto done;
+                        // their plain stores, now visible to this thread, before the copy engine's reads
+                        asm volatile("fence.proxy.async.global;" ::: "memory");
+                    }
                 }
                 for (int c = 0; c < nchunks; c++, s = (s + 1 == NSTG) ? 0 : s + 1, ph ^= (s == 0)) {
                     if (!mbar_wait(bar_empty + 8 * s, ph, abort_flag, p.status, 1)) goto done;
@@ -601,6 +858,13 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                 }
             }
         }
+    } else if (QF && warp >= Cfg::WARP_Q0) {
+        uint64_t* qbars = reinterpret_cast<uint64_t*>(smem + Cfg::Q_OFF + Cfg::QSTG * Cfg::Q_STAGE);
+        if (warp < Cfg::WARP_Q0 + 4)
+            quantise_items(QuantArgs{p.qthr, p.qimg, p.q_sync, p.qN, p.qC, p.q_nbands, p.Cp, p.H * p.W, p.status}, &tmap_q, smem + Cfg::Q_OFF, qbars,
+                           abort_flag, tid - Cfg::WARP_Q0 * 32);
+        else if (lane == 0)
+            publish_items(p.q_sync, p.status, qbars, abort_flag);
     } else {
         // ---------------- epilogue ----------------
         const int q = warp & 3;                 // tensor-memory lane quadrant this warp may access
@@ -847,17 +1111,17 @@ __global__ void __launch_bounds__(128, 1) mma_rate_kernel(int iters, unsigned in
     }
 }
 
-template <int BN, int MT, bool F4, bool ATMA = false, int CG = 1, int TAPS = 1>
+template <int BN, int MT, bool F4, bool ATMA = false, int CG = 1, int TAPS = 1, bool QF = false>
 int launch_cfg(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream, const CUtensorMap* tmap_a = nullptr,
-               const CUtensorMap* tmap_b = nullptr) {
-    using Cfg = TcCfg<BN, MT, F4, ATMA, CG, TAPS>;
-    auto kern = gemm_tc_kernel<BN, MT, F4, ATMA, CG, TAPS>;
+               const CUtensorMap* tmap_b = nullptr, const CUtensorMap* tmap_q = nullptr) {
+    using Cfg = TcCfg<BN, MT, F4, ATMA, CG, TAPS, QF>;
+    auto kern = gemm_tc_kernel<BN, MT, F4, ATMA, CG, TAPS, QF>;
     static const CUtensorMap no_map = {};
     TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
     const long long tiles = ((a.M + CG * MT * BM - 1) / (CG * MT * BM)) * ((a.KN + BN - 1) / BN);
     if (CG == 1) {
         const int grid = (int)std::min<long long>(tiles, ctx->sm_count);
-        kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, stream>>>(a, tmap_a ? *tmap_a : no_map, no_map);
+        kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, stream>>>(a, tmap_a ? *tmap_a : no_map, no_map, tmap_q ? *tmap_q : no_map);
     } else {
         // block pairs: clusters of two consecutive blocks, as many as can be resident at once (the
         // kernel is persistent; a pair that had to wait for a free TPC would start its whole tile
@@ -883,7 +1147,7 @@ int launch_cfg(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream, const
             mp = std::min(n, ctx->sm_count / CG);
         }
         cfg.gridDim = dim3(CG * (int)std::min<long long>(tiles, mp));
-        TNNS_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a, tmap_a ? *tmap_a : no_map, tmap_b ? *tmap_b : no_map));
+        TNNS_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a, tmap_a ? *tmap_a : no_map, tmap_b ? *tmap_b : no_map, tmap_q ? *tmap_q : no_map));
     }
     tnns_count_launch();
     TNNS_CUDA_TRY(cudaGetLastError());
@@ -971,6 +1235,7 @@ int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const vo
     a.img = nullptr;
     a.jtab = nullptr;
     a.H = a.W = a.OW = a.Cp = a.SH = a.SW = a.PH = a.PW = 0;
+    a.qx = a.qthr = nullptr; a.qimg = nullptr; a.q_sync = nullptr; a.qN = a.qC = a.q_nbands = 0;
     if (implicit_geom) {
         // d_a is the quantised image of the layer input, not an im2row matrix
         if (!f4 || !w->d_jtab) return tnns_fail(TNNS_ERR_UNSUPPORTED, "implicit im2row needs the 4-bit tensor-core GEMM and layer geometry");
@@ -1053,12 +1318,31 @@ int encode_weight_map(CUtensorMap* map, const tnns_cuda_weights* w, int BN) {
 }  // namespace
 
 // pairs: 0 = decide by size, 1 = single blocks, 2 = block pairs (kernel tile of 256 only)
+size_t tnns_fused_sync_bytes(int N) { return ((size_t)(Q_FLAG0 + N) * sizeof(unsigned int) + 127) & ~(size_t)127; }
+
+bool tnns_fused_supported(const tnns_cuda_weights* w, const TnnsGeom& g, const float* d_x, int layout) {
+    if (!tnns_im2col_supported(w, g)) return false;
+    const long long HW = (long long)g.H * g.W;
+    // the quantiser warps receive 128 pixels x 64 channels per tensor copy: rows of H*W floats, 16-byte pitch and base
+    if (!tnns_quantise_tma_supported(d_x, g.H, g.W, layout)) return false;
+    const long long items = (long long)g.N * ((HW + Q_PIX - 1) / Q_PIX) * g.Cp;
+    return items < 0x7FFFFFFFLL;
+}
+
 int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const TnnsGeom& g, float alpha,
-                            int layout, cudaStream_t stream, int pairs, void* d_pimg, const float* d_thr_next, int next_format) {
+                            int layout, cudaStream_t stream, int pairs, void* d_pimg, const float* d_thr_next, int next_format,
+                            const TnnsFusedInput* fused) {
     const long long M = (long long)g.N * g.OH * g.OW;
     if (M == 0) return TNNS_OK;
     if (!tnns_im2col_supported(w, g)) return tnns_fail(TNNS_ERR_UNSUPPORTED, "layer shape or type outside the tensor-copy activation path");
     if (reinterpret_cast<uintptr_t>(d_image) & 15) return tnns_fail(TNNS_ERR_INVALID, "image must be 16-byte aligned");
+    if (fused) {
+        if (!fused->d_x || !fused->d_thr || !fused->d_sync) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+        if (!tnns_fused_supported(w, g, fused->d_x, layout))
+            return tnns_fail(TNNS_ERR_UNSUPPORTED, "fused quantisation needs NCHW input with H*W a multiple of four and a 16-byte aligned base");
+        if (reinterpret_cast<uintptr_t>(fused->d_sync) & 127) return tnns_fail(TNNS_ERR_INVALID, "synchronisation words must be 128-byte aligned");
+        TNNS_CUDA_TRY(cudaMemsetAsync(fused->d_sync, 0, tnns_fused_sync_bytes(g.N), stream));
+    }
     CUtensorMap map;
     int rc = encode_im2col_map(&map, d_image, g);
     if (rc) return rc;
@@ -1083,7 +1367,21 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     a.cp_next = (w->KN + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS;
     a.img = nullptr;
     a.jtab = w->d_jtab;
+    a.qx = a.qthr = nullptr; a.qimg = nullptr; a.q_sync = nullptr; a.qN = a.qC = a.q_nbands = 0;
     a.H = g.H; a.W = g.W; a.OW = g.OW; a.Cp = g.Cp; a.SH = g.SH; a.SW = g.SW; a.PH = g.PH; a.PW = g.PW;
+    alignas(64) CUtensorMap map_q;
+    if (fused) {
+        // the fp32 input as a 2-D tensor: one row of H*W floats per (image, channel); box = 128 pixels x 64 channels
+        const unsigned long long HW = (unsigned long long)g.H * g.W;
+        if ((rc = tnns_tensor_map_2d(&map_q, 4, fused->d_x, HW, (unsigned long long)g.N * g.C, HW * 4, Q_PIX, 64))) return rc;
+        a.qx = fused->d_x;
+        a.qthr = fused->d_thr;
+        a.qimg = reinterpret_cast<uint4*>(const_cast<void*>(d_image));
+        a.q_sync = fused->d_sync;
+        a.qN = g.N;
+        a.qC = g.C;
+        a.q_nbands = (g.H * g.W + Q_PIX - 1) / Q_PIX;
+    }
     const int taps = g.Cp == 1 ? 4 : (g.Cp == 2 ? 2 : 1);
     const int bn = tnns_i8_tile_n(w->KN);
     if (pairs == 2 && bn != 256) return tnns_fail(TNNS_ERR_UNSUPPORTED, "block pairs need more than 128 kernels");
@@ -1094,6 +1392,14 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     if (use_pairs && (rc = encode_weight_map(&map_b, w, bn))) return rc;
     auto go = [&](auto taps_c) -> int {
         constexpr int T = decltype(taps_c)::value;
+        if (fused) {
+            if (use_pairs) return launch_cfg<256, 1, true, true, 2, T, true>(ctx, a, stream, &map, &map_b, &map_q);
+            switch (bn) {
+                case 64: return launch_cfg<64, 1, true, true, 1, T, true>(ctx, a, stream, &map, nullptr, &map_q);
+                case 128: return launch_cfg<128, 1, true, true, 1, T, true>(ctx, a, stream, &map, nullptr, &map_q);
+                default: return launch_cfg<256, 1, true, true, 1, T, true>(ctx, a, stream, &map, nullptr, &map_q);
+            }
+        }
         if (use_pairs) return launch_cfg<256, 1, true, true, 2, T>(ctx, a, stream, &map, &map_b);
         switch (bn) {
             case 64: return launch_cfg<64, 1, true, true, 1, T>(ctx, a, stream, &map);

@@ -105,9 +105,19 @@ int tnns_tensor_map_2d(void* map, int elem_bytes, const void* base, unsigned lon
 bool tnns_im2col_supported(const tnns_cuda_weights* w, const TnnsGeom& g);
 // d_pimg != NULL: write the next layer's quantised activations instead of fp32 (next_format 0: binary
 // bit planes, 1: ternary bit planes, 2: ternary 4-bit operand image)
+// fused != NULL: the same launch also quantises the layer's fp32 input into d_image (quantiser
+// warps beside the GEMM's, tiles wait for their images); d_sync = tnns_fused_sync_bytes(N) bytes
+// of device memory, 128-byte aligned, cleared by the launcher on `stream`
+struct TnnsFusedInput {
+    const float* d_x;
+    const float* d_thr;
+    unsigned int* d_sync;
+};
+size_t tnns_fused_sync_bytes(int N);
+bool tnns_fused_supported(const tnns_cuda_weights* w, const TnnsGeom& g, const float* d_x, int layout);
 int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const TnnsGeom& g,
                             float alpha, int layout, cudaStream_t stream, int pairs = 0, void* d_pimg = nullptr,
-                            const float* d_thr_next = nullptr, int next_format = 1);
+                            const float* d_thr_next = nullptr, int next_format = 1, const TnnsFusedInput* fused = nullptr);
 
 int tnns_launch_pack_weights(tnns_cuda_ctx* ctx, bool ternary, const float* d_w, const float* d_thr, void* d_packed, int KN, int C,
                              int KH, int KW, cudaStream_t stream);

@@ -163,7 +163,8 @@ enum tnns_gemm_algo {
     TNNS_GEMM_POPC_SIMPLE = 1, /* one thread per output, integer pipe            */
     TNNS_GEMM_POPC_TILED = 2,  /* tiled carry-save popcount GEMM, integer pipe   */
     TNNS_GEMM_I8_TC = 3,       /* tcgen05 int8 tensor-core GEMM                  */
-    TNNS_GEMM_F4_TC = 4        /* tcgen05 4-bit (e2m1, unit scales) tensor-core GEMM */
+    TNNS_GEMM_F4_TC = 4,       /* tcgen05 4-bit (e2m1, unit scales) tensor-core GEMM */
+    TNNS_GEMM_F4_FUSED = 5     /* whole layers only: the 4-bit GEMM fed by tensor copies with the quantise step in the same launch */
 };
 
 /* Error codes returned by every tnns_cuda_* function (0 = success). */
@@ -271,6 +272,21 @@ int tnns_cuda_quantise_e2m1(tnns_cuda_ctx* ctx, const float* d_x, const float* d
                             int layout, void* stream);
 int tnns_cuda_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const tnns_shape_t* s,
                           float alpha, int layout, int pairs, void* stream);
+/* The copy-engine route as ONE launch (t2r_p2_opt's thresholding, src/tnns/ternarize2row_avx2.c:438-452,
+ * and mm_tnn / mm_tbn, src/tnns/mm_p2_final_tnn_avx2.c:384-387, in one kernel): beside the GEMM's
+ * warps every block runs quantiser warps that turn the fp32 input into the 4-bit operand image,
+ * 128 pixels x 64 channels at a time in image order, and count finished pieces per image in global
+ * memory; a tile's tensor copies start once the images of its rows are complete, so the
+ * HBM-bound quantisation runs underneath the tensor-bound MMAs of earlier tiles.  Needs what
+ * tnns_cuda_gemm_im2col needs plus NCHW input with H*W a multiple of four and a 16-byte aligned
+ * d_x (tnns_cuda_conv_fused_supported).  d_workspace: tnns_fused_workspace_bytes() bytes, 128-byte
+ * aligned (image + synchronisation words; the words are cleared on `stream` by the call).  Same
+ * result as every other route.  tnns_cuda_conv / _conv_ws take it with gemm_algo
+ * TNNS_GEMM_F4_FUSED, and with TNNS_GEMM_AUTO where the layer has several tiles per SM. */
+size_t tnns_fused_workspace_bytes(int N, int C, int H, int W);
+int tnns_cuda_conv_fused_supported(const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout);
+int tnns_cuda_conv_fused(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y,
+                         void* d_workspace, size_t workspace_bytes, const tnns_shape_t* s, float alpha, int pairs, void* stream);
 /* Chaining on the copy-engine route: the same GEMM with the quantising epilogue of
  * tnns_cuda_gemm_packed_out.  next_format (also accepted as `next_ternary` by
  * tnns_cuda_gemm_packed_out): 0 = binary bit planes, 1 = ternary bit planes, 2 = ternary 4-bit

@@ -550,6 +550,98 @@ def test_e2m1_image_and_im2col_tensor_copy_gemm(type_, layer, N, gpu_ctx, checke
         w.free()
 
 
+FUSED_LAYERS = [
+    (TNN, Layer(256, 14, 14, 256, 3, 3, 1, 1), 4),     # 196 pixels per image: a ragged second band of pixels
+    (TNN, Layer(256, 14, 14, 256, 5, 3, 1, 2), 8),     # 5 x 3 kernel, stride 2
+    (TBN, Layer(256, 10, 10, 100, 3, 3, 1, 2), 3),     # binary weights, images below one band
+    (TNN, Layer(1024, 14, 14, 1024, 5, 5, 1, 2), 2),   # 16 channel groups, four kernel tiles
+    (TNN, Layer(250, 10, 12, 64, 3, 3, 2, 3), 3),      # channel tail in the last group, padding 2, stride 3
+    (TNN, Layer(64, 12, 12, 200, 3, 3, 1, 1), 5),      # C_pack = 1
+    (TBN, Layer(128, 10, 10, 100, 3, 3, 1, 2), 3),     # C_pack = 2
+    (TNN, Layer(100, 8, 8, 64, 3, 3, 1, 1), 7),        # C_pack = 2 with a channel tail
+    (TNN, Layer(512, 6, 6, 512, 1, 1, 0, 1), 40),      # 36 pixels per image: a tile waits for several images
+    (TNN, Layer(256, 16, 16, 320, 3, 3, 1, 1), 80),    # more tiles than SMs: tiles of later images wait while earlier ones multiply
+]
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("type_,layer,N", FUSED_LAYERS, ids=lambda v: str(v).replace(" ", ""))
+def test_fused_quantise_and_tensor_copy_gemm(type_, layer, N, gpu_ctx, checker):
+    """One launch for the whole layer: quantiser warps write the 4-bit image while the GEMM's tensor
+    copies wait per image.  Output and image equal the two-kernel route and the reference bit for
+    bit, with single blocks and block pairs, on two calls in a row (the synchronisation words are
+    cleared by every call) and through the layer entry point."""
+    ctx = gpu_ctx
+    case = make_case(type_, layer, N, 6300 + layer.C + layer.KN, "uniform")
+    wp = checker.pack_weights(wgt_ternary(type_), case.w, case.w_thr)
+    want = checker.conv(type_, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
+    w = ctx.upload_weights(type_, wp, layer.C, layer.KH, layer.KW)
+    shape = layer.shape(N)
+    nb_e = ft.api.e2m1_image_bytes(N, layer.C, layer.H, layer.W)
+    nb_ws = ft.api.fused_workspace_bytes(N, layer.C, layer.H, layer.W)
+    assert nb_ws >= nb_e + 4 * N
+    d_t = ctx.to_device(case.thr)
+    d_x = ctx.to_device(case.x)
+    d_y = ctx.malloc(want.nbytes)
+    d_e = ctx.malloc(nb_e)
+    d_ws = ctx.malloc(nb_ws)
+    try:
+        assert ctx.conv_fused_supported(w, shape, d_x, ft.NCHW)
+        assert not ctx.conv_fused_supported(w, shape, d_x, ft.NHWC)
+        assert not ctx.conv_fused_supported(w, shape, d_x + 4, ft.NCHW)
+        ctx.quantise_e2m1(d_x, d_t, d_e, N, layer.C, layer.H, layer.W, ft.NCHW)
+        ctx.sync()
+        image = ctx.to_host(d_e, (nb_e // 4,), np.uint32)
+        for pairs in (1, 2, 0):
+            if pairs == 2 and layer.KN <= 128:
+                continue
+            for rep in range(2):
+                ctx.fill(d_y, np.full(want.size, np.nan, np.float32))
+                ctx.fill(d_ws, np.full(nb_ws // 4, 0xFFFFFFFF, np.uint32))   # stale image and stale counters
+                ctx.conv_fused(w, d_x, d_t, d_y, d_ws, nb_ws, shape, case.alpha, pairs)
+                ctx.sync()
+                assert ctx.to_host(d_y, want.shape, np.float32).tobytes() == want.tobytes()
+                assert np.array_equal(ctx.to_host(d_ws, (nb_e // 4,), np.uint32), image)
+        with pytest.raises(ft.TnnsError):
+            ctx.conv_fused(w, d_x, d_t, d_y, d_ws, nb_ws - 128, shape, case.alpha)
+        # the layer entry point on request
+        ctx.fill(d_y, np.full(want.size, np.nan, np.float32))
+        ctx.conv(w, d_x, d_t, d_y, shape, case.alpha, ft.NCHW, ft.PACK_AUTO, ft.GEMM_F4_FUSED)
+        ctx.sync()
+        assert ctx.to_host(d_y, want.shape, np.float32).tobytes() == want.tobytes()
+    finally:
+        for p in (d_t, d_x, d_y, d_e, d_ws):
+            ctx.free(p)
+        w.free()
+
+
+@pytest.mark.gpu
+def test_fused_route_declines_what_it_cannot_do(gpu_ctx, checker):
+    """Pixel counts that are not a multiple of four (the rows of the input tensor must be 16-byte
+    multiples for the copy engine) and NHWC input stay on the two-kernel route; asking for the fused
+    one is an error."""
+    ctx = gpu_ctx
+    layer = Layer(256, 7, 7, 64, 3, 3, 1, 1)
+    case = make_case(TNN, layer, 3, 91, "uniform")
+    wp = checker.pack_weights(True, case.w, case.w_thr)
+    want = checker.conv(TNN, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
+    w = ctx.upload_weights(TNN, wp, layer.C, layer.KH, layer.KW)
+    shape = layer.shape(3)
+    d_x, d_t = ctx.to_device(case.x), ctx.to_device(case.thr)
+    d_y = ctx.malloc(want.nbytes)
+    try:
+        assert ctx.im2col_supported(w, shape) and not ctx.conv_fused_supported(w, shape, d_x, ft.NCHW)
+        with pytest.raises(ft.TnnsError):
+            ctx.conv(w, d_x, d_t, d_y, shape, case.alpha, ft.NCHW, ft.PACK_AUTO, ft.GEMM_F4_FUSED)
+        ctx.conv(w, d_x, d_t, d_y, shape, case.alpha, ft.NCHW, ft.PACK_AUTO, ft.GEMM_AUTO)
+        ctx.sync()
+        assert ctx.to_host(d_y, want.shape, np.float32).tobytes() == want.tobytes()
+    finally:
+        for p in (d_x, d_t, d_y):
+            ctx.free(p)
+        w.free()
+
+
 @pytest.mark.gpu
 def test_im2col_route_declines_what_it_cannot_do(gpu_ctx, checker):
     """Binary activations (padding is +1, which a zero-filling copy cannot produce) and channel counts
