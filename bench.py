@@ -41,7 +41,7 @@ METRIC = "ternary conv GOPS (2*M*N*K/s)"
 # dram__bytes_read.sum + dram__bytes_write.sum per launch from the ncu captures summarised under
 # profiles/ (large layer, 64 images per launch), kept per image so that a rank's share scales.
 NCU_TRAFFIC_PER_IMAGE = {
-    ("tnn_conv_large", "f4_fused"): None,          # quantise + GEMM in one launch (filled in from the capture under profiles/)
+    ("tnn_conv_large", "f4_fused"): 226.1e6 / 64,  # quantise + GEMM in one launch: fp32 input read once, output partly still in L2
     ("tnn_conv_large", "f4_im2col"): 91.5e6 / 64,  # im2col tensor copies from the 16.8 MB 4-bit image (block pairs)
     ("tnn_conv_large", "quantise_e2m1"): 143.1e6 / 64,
     ("tnn_conv_large", "f4"): 85.2e6 / 64,        # implicit im2row: reads the 8.4 MB image, not the im2row matrix
