@@ -92,6 +92,8 @@ SIGNATURES = {
     "tnns_cuda_sync": (_i, [_vp]),
     "tnns_cuda_malloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "tnns_cuda_free": (None, [_vp, _vp]),
+    "tnns_cuda_malloc_host": (_i, [_vp, _sz, C.POINTER(_vp)]),
+    "tnns_cuda_free_host": (None, [_vp, _vp]),
     "tnns_e2m1_image_bytes": (_sz, [_i, _i, _i, _i]),
     "tnns_cuda_im2col_supported": (_i, [_vp, _vp]),
     "tnns_cuda_quantise_e2m1": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),

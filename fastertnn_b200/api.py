@@ -353,6 +353,15 @@ class Context:
     def free(self, p: int):
         self.lib.tnns_cuda_free(self.handle, p)
 
+    def malloc_host(self, nbytes: int) -> int:
+        """Page-locked host memory (tnns_cuda_conv_host moves it at full PCIe speed)."""
+        p = C.c_void_p()
+        _check(self.lib.tnns_cuda_malloc_host(self.handle, nbytes, C.byref(p)))
+        return p.value
+
+    def free_host(self, p: int):
+        self.lib.tnns_cuda_free_host(self.handle, p)
+
     def to_device(self, a: np.ndarray) -> int:
         a = np.ascontiguousarray(a)
         p = self.malloc(max(a.nbytes, 16))

@@ -1,5 +1,6 @@
 // Device-resident C ABI: contexts, weights, error reporting, layer entry points.
 #include <algorithm>
+#include <vector>
 #include <cstdarg>
 #include <cstdio>
 #include <cstdlib>
@@ -171,6 +172,19 @@ int tnns_cuda_malloc(tnns_cuda_ctx* ctx, size_t bytes, void** out) {
     TNNS_CUDA_TRY(cudaMalloc(out, bytes ? bytes : 16));
     return TNNS_OK;
 }
+int tnns_cuda_malloc_host(tnns_cuda_ctx* ctx, size_t bytes, void** out) {
+    if (!ctx || !out) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    *out = nullptr;
+    TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
+    TNNS_CUDA_TRY(cudaHostAlloc(out, std::max<size_t>(bytes, 16), cudaHostAllocPortable | cudaHostAllocMapped));
+    return TNNS_OK;
+}
+
+void tnns_cuda_free_host(tnns_cuda_ctx* ctx, void* p) {
+    (void)ctx;
+    if (p) cudaFreeHost(p);
+}
+
 void tnns_cuda_free(tnns_cuda_ctx* ctx, void* p) {
     if (!ctx || !p) return;
     cudaSetDevice(ctx->device);
@@ -554,8 +568,10 @@ int tnns_cuda_conv_host(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const fl
     if (g.N == 0) return TNNS_OK;
     TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
 
-    // slice the batch: about eight slices so copies and kernels overlap, at least one image each
-    // (sixteen slices measured slower: 3.48 ms against 3.30 ms on the large layer)
+    // (Letting the one-launch kernel work on page-locked host buffers directly -- tensor copies and
+    // epilogue stores over PCIe, no staging -- measured slower than the copy engines: 4.2 ms against
+    // 3.2 ms on the large layer; the SMs' reads of host memory reach about 32 GB/s.)
+    // slice the batch so that copies and kernels overlap; nb = images of a full slice
     const int nb = std::max(1, (g.N + 7) / 8);
     const size_t in_img = (size_t)g.C * g.H * g.W * sizeof(float);
     const size_t out_img = (size_t)g.KN * g.OH * g.OW * sizeof(float);
@@ -581,11 +597,27 @@ int tnns_cuda_conv_host(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const fl
         }
     }
 
+    // Slice plan: about eight slices of nb images, the first and the last of them cut in two (a
+    // quarter, then the rest): the download stream trails the upload stream by one slice, so small
+    // slices at both ends shorten what the slicing adds to the transfer time.  Slices larger than
+    // nb in the middle measured slower (the download stream then idles while a large slice
+    // uploads: 3.35 ms against 3.19 ms on the large layer), and so did sixteen equal slices (every
+    // slice costs event waits on three streams).
+    std::vector<int> plan;
+    {
+        const int quarter = std::max(1, nb / 4);
+        int left = g.N;
+        const bool taper = nb >= 2 && g.N >= 3 * nb;
+        if (taper) { plan.push_back(quarter); plan.push_back(nb - quarter); left -= 2 * nb; }
+        while (left > 0) { plan.push_back(std::min(nb, left)); left -= plan.back(); }
+        if (taper) { plan.push_back(nb - quarter); plan.push_back(quarter); }
+    }
+
     TNNS_CUDA_TRY(cudaMemcpyAsync(ctx->stage_thr, h_thr, (size_t)g.N * sizeof(float), cudaMemcpyHostToDevice, ctx->s_copy_in));
-    int k = 0;
-    for (int n0 = 0; n0 < g.N; n0 += nb, k++) {
+    int n0 = 0;
+    for (int k = 0; k < (int)plan.size(); n0 += plan[k], k++) {
         const int slot = k & 1;
-        const int cnt = std::min(nb, g.N - n0);
+        const int cnt = plan[k];
         ss.N = cnt;
         if (k >= 2) TNNS_CUDA_TRY(cudaStreamWaitEvent(ctx->s_copy_in, ctx->ev_done[slot], 0));  // kernels of slice k-2 done with stage_in
         TNNS_CUDA_TRY(cudaMemcpyAsync(ctx->stage_in[slot], (const char*)h_x + (size_t)n0 * in_img, in_img * cnt, cudaMemcpyHostToDevice,

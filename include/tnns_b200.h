@@ -301,9 +301,10 @@ int tnns_cuda_gemm_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, co
 int tnns_cuda_im2row_packed(tnns_cuda_ctx* ctx, int ternary, const void* d_image, int64_t* d_packed, const tnns_shape_t* s,
                             void* stream);
 
-/* Whole layer with HOST input / output buffers (pinned memory gives full PCIe speed):
- * the batch is cut into slices whose upload, kernels and download overlap on three
- * streams.  Synchronous: returns when h_y is complete. */
+/* Whole layer with HOST input / output buffers (the device-side half of tnns_conv,
+ * src/tnns/tnns_cpu_mm_p2.c:83-120): the batch is cut into slices whose upload, kernels and
+ * download overlap on three streams; page-locked buffers (tnns_cuda_malloc_host, cudaHostAlloc,
+ * cudaHostRegister) give full PCIe speed.  Synchronous: returns when h_y is complete. */
 int tnns_cuda_conv_host(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* h_x, const float* h_thr,
                         float* h_y, const tnns_shape_t* s, float alpha, int layout);
 
@@ -349,6 +350,10 @@ int tnns_cuda_selftest_wait_expiry(tnns_cuda_ctx* ctx);
 /* Plain device-memory helpers so that C callers need no CUDA headers.  Synchronous. */
 int tnns_cuda_malloc(tnns_cuda_ctx* ctx, size_t bytes, void** out);
 void tnns_cuda_free(tnns_cuda_ctx* ctx, void* p);
+/* Page-locked host memory (cudaHostAlloc, portable + mapped): the buffers tnns_cuda_conv_host
+ * moves at full PCIe speed. */
+int tnns_cuda_malloc_host(tnns_cuda_ctx* ctx, size_t bytes, void** out);
+void tnns_cuda_free_host(tnns_cuda_ctx* ctx, void* p);
 int tnns_cuda_memcpy_h2d(tnns_cuda_ctx* ctx, void* dst, const void* src, size_t bytes);
 int tnns_cuda_memcpy_d2h(tnns_cuda_ctx* ctx, void* dst, const void* src, size_t bytes);
 

@@ -169,6 +169,32 @@ def test_host_buffer_layer_matches_device_layer(gpu_ctx, checker):
     w.free()
 
 
+@pytest.mark.gpu
+def test_host_buffer_layer_on_page_locked_buffers(gpu_ctx, checker):
+    """Page-locked host buffers (tnns_cuda_malloc_host) through the host-buffer layer call: same
+    bytes as the reference on two calls in a row, for batches whose slices take the one-launch
+    route, 64-channel pixels, and a ragged last slice."""
+    import ctypes
+    ctx = gpu_ctx
+    for layer, N in ((Layer(256, 16, 16, 320, 3, 3, 1, 1), 160), (Layer(64, 48, 48, 64, 3, 3, 1, 1), 264), (Layer(128, 12, 12, 96, 3, 3, 1, 1), 19)):
+        case = make_case(TNN, layer, N, 4200 + N, "uniform")
+        wp = checker.pack_weights(True, case.w, case.w_thr)
+        want = checker.conv(TNN, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
+        w = ctx.upload_weights(TNN, wp, layer.C, layer.KH, layer.KW)
+        h_x, h_y = ctx.malloc_host(case.x.nbytes), ctx.malloc_host(want.nbytes)
+        try:
+            ctypes.memmove(h_x, case.x.ctypes.data, case.x.nbytes)
+            y = np.ctypeslib.as_array(ctypes.cast(h_y, ctypes.POINTER(ctypes.c_float)), shape=want.shape)
+            for _ in range(2):
+                y.fill(np.nan)
+                ctx.conv_host(w, h_x, case.thr.ctypes.data, h_y, layer.shape(N), case.alpha)
+                assert y.tobytes() == want.tobytes()
+        finally:
+            ctx.free_host(h_x)
+            ctx.free_host(h_y)
+            w.free()
+
+
 def test_empty_batch_is_a_no_op(gpu_ctx):
     layer = Layer(64, 4, 4, 8, 3, 3, 1, 1)
     shape = layer.shape(0)
