@@ -219,6 +219,7 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
         raise SystemExit("no CUDA device: this benchmark has no CPU fallback")
     torch.cuda.set_device(local)
     if world > 1:
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keeps NCCL's version banner off stdout (one JSON line there)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     def barrier():
