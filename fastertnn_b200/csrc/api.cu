@@ -136,6 +136,7 @@ void tnns_cuda_destroy(tnns_cuda_ctx* ctx) {
         if (ctx->ev_out[i]) cudaEventDestroy(ctx->ev_out[i]);
     }
     if (ctx->stage_thr) cudaFree(ctx->stage_thr);
+    if (ctx->fused_sync) cudaFree(ctx->fused_sync);
     if (ctx->s_copy_in) cudaStreamDestroy(ctx->s_copy_in);
     if (ctx->s_compute) cudaStreamDestroy(ctx->s_compute);
     if (ctx->s_copy_out) cudaStreamDestroy(ctx->s_copy_out);
@@ -150,6 +151,8 @@ int tnns_cuda_sync(tnns_cuda_ctx* ctx) {
     if (*ctx->h_status != 0) {
         const unsigned int code = *ctx->h_status;
         cudaMemset(ctx->d_status, 0, sizeof(unsigned int));
+        // a launch that gave up may have left before its words were consistent: start from zeros again
+        if (ctx->fused_sync) cudaMemset(ctx->fused_sync, 0, ctx->fused_sync_words * sizeof(unsigned int));
         return tnns_fail(TNNS_ERR_DEVICE_WAIT, "device status word = 0x%x (a bounded wait gave up)", code);
     }
     return TNNS_OK;

@@ -313,13 +313,14 @@ struct GemmArgs {
     int H, W, OW, Cp, SH, SW, PH, PW;
     // fused quantisation (QF): the layer's fp32 NCHW input and per-image thresholds, the 4-bit image
     // the quantiser warps write (the tensor the activation copies read), and the launch's
-    // synchronisation words, zeroed before the launch: q_sync[0] = next item to claim,
-    // q_sync[Q_FLAG0 + n] = finished items of image n
+    // synchronisation words, zero when the launch starts: q_sync[0] = next item to claim,
+    // q_sync[1] = blocks that have left, q_sync[Q_FLAG0 + n] = finished items of image n
     const float* qx;
     const float* qthr;
     uint4* qimg;
     unsigned int* q_sync;
     int qN, qC, q_nbands;
+    int q_self_clean;  // the last block to leave zeroes the words again (q_sync[1] counts the blocks that left)
 };
 
 __device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
@@ -559,6 +560,11 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
     auto tap_at = [&](int j) -> uint32_t { return j < Cfg::TAPMAX ? s_taps[j] : __ldg(p.jtab + j); };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    // Programmatic dependent launch (fused form): a following launch of this kind may place its
+    // blocks on SMs as the blocks of this one leave, run its set-up there, and wait (below, before
+    // it touches any global data) until this launch has completed.  All blocks of a launch are
+    // resident at once, so letting the dependents in early cannot starve this launch of SMs.
+    if (QF) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int nchunks = F4 ? p.Kp / 4 : p.Kp / 2;  // stages per tile
     const int ntn = (p.KN + BN - 1) / BN;
     const long long ntm = (p.M + TILE_M - 1) / TILE_M;
@@ -626,6 +632,10 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
         if (CG == 2) cluster_sync_all(); else __syncthreads();  // pair: the first block's MMAs read both blocks' scales
         tc_fence_after();
     }
+
+    // everything above touched only on-chip state and the layer's constant tables; what follows reads
+    // and writes tensors that the previous launch on the stream may still be working on
+    if (QF) asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == WARP_TMA) {
         if (lane == 0) {
@@ -1021,6 +1031,21 @@ done:
         if (CG == 2) asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
         else asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512u) : "memory");
     }
+    if (QF && p.q_self_clean && warp == WARP_TMA) {
+        // Every role of this block is past its last use of the synchronisation words.  The block
+        // that leaves last zeroes them, so the next launch on the stream finds them clean without
+        // a clearing operation in between (also after a wait that gave up: every block comes here).
+        unsigned int left = 0;
+        if (lane == 0) {
+            __threadfence();
+            left = atomicAdd(p.q_sync + 1, 1u);
+        }
+        left = __shfl_sync(0xFFFFFFFFu, left, 0);
+        if (left == gridDim.x - 1) {
+            __threadfence();
+            for (int i = lane; i < Q_FLAG0 + p.qN; i += 32) p.q_sync[i] = 0;
+        }
+    }
 }
 
 // Self-test of the bounded wait: one warp waits on an mbarrier that nothing ever completes.  The
@@ -1119,9 +1144,29 @@ int launch_cfg(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream, const
     static const CUtensorMap no_map = {};
     TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
     const long long tiles = ((a.M + CG * MT * BM - 1) / (CG * MT * BM)) * ((a.KN + BN - 1) / BN);
+    // fused form: the launch may be scheduled while its predecessor on the stream drains (the kernel
+    // waits for it, griddepcontrol.wait, before it touches global data)
+    cudaLaunchAttribute attr[2];
+    int nattr = 0;
+    if (QF) {
+        attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+        nattr++;
+    }
     if (CG == 1) {
         const int grid = (int)std::min<long long>(tiles, ctx->sm_count);
-        kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, stream>>>(a, tmap_a ? *tmap_a : no_map, no_map, tmap_q ? *tmap_q : no_map);
+        if (QF) {
+            cudaLaunchConfig_t cfg = {};
+            cfg.gridDim = dim3(grid);
+            cfg.blockDim = dim3(Cfg::NTHREADS);
+            cfg.dynamicSmemBytes = Cfg::SMEM;
+            cfg.stream = stream;
+            cfg.attrs = attr;
+            cfg.numAttrs = nattr;
+            TNNS_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a, tmap_a ? *tmap_a : no_map, no_map, tmap_q ? *tmap_q : no_map));
+        } else {
+            kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, stream>>>(a, tmap_a ? *tmap_a : no_map, no_map, tmap_q ? *tmap_q : no_map);
+        }
     } else {
         // block pairs: clusters of two consecutive blocks, as many as can be resident at once (the
         // kernel is persistent; a pair that had to wait for a free TPC would start its whole tile
@@ -1131,13 +1176,13 @@ int launch_cfg(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream, const
         cfg.blockDim = dim3(Cfg::NTHREADS);
         cfg.dynamicSmemBytes = Cfg::SMEM;
         cfg.stream = stream;
-        cudaLaunchAttribute attr[1];
-        attr[0].id = cudaLaunchAttributeClusterDimension;
-        attr[0].val.clusterDim.x = CG;
-        attr[0].val.clusterDim.y = 1;
-        attr[0].val.clusterDim.z = 1;
+        attr[nattr].id = cudaLaunchAttributeClusterDimension;
+        attr[nattr].val.clusterDim.x = CG;
+        attr[nattr].val.clusterDim.y = 1;
+        attr[nattr].val.clusterDim.z = 1;
+        nattr++;
         cfg.attrs = attr;
-        cfg.numAttrs = 1;
+        cfg.numAttrs = nattr;
         static int max_pairs[64] = {0};  // per device
         int& mp = max_pairs[ctx->device & 63];
         if (mp == 0) {
@@ -1235,7 +1280,7 @@ int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const vo
     a.img = nullptr;
     a.jtab = nullptr;
     a.H = a.W = a.OW = a.Cp = a.SH = a.SW = a.PH = a.PW = 0;
-    a.qx = a.qthr = nullptr; a.qimg = nullptr; a.q_sync = nullptr; a.qN = a.qC = a.q_nbands = 0;
+    a.qx = a.qthr = nullptr; a.qimg = nullptr; a.q_sync = nullptr; a.qN = a.qC = a.q_nbands = a.q_self_clean = 0;
     if (implicit_geom) {
         // d_a is the quantised image of the layer input, not an im2row matrix
         if (!f4 || !w->d_jtab) return tnns_fail(TNNS_ERR_UNSUPPORTED, "implicit im2row needs the 4-bit tensor-core GEMM and layer geometry");
@@ -1336,12 +1381,32 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     if (M == 0) return TNNS_OK;
     if (!tnns_im2col_supported(w, g)) return tnns_fail(TNNS_ERR_UNSUPPORTED, "layer shape or type outside the tensor-copy activation path");
     if (reinterpret_cast<uintptr_t>(d_image) & 15) return tnns_fail(TNNS_ERR_INVALID, "image must be 16-byte aligned");
+    bool own_words = false;
     if (fused) {
         if (!fused->d_x || !fused->d_thr || !fused->d_sync) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
         if (!tnns_fused_supported(w, g, fused->d_x, layout))
             return tnns_fail(TNNS_ERR_UNSUPPORTED, "fused quantisation needs NCHW input with H*W a multiple of four and a 16-byte aligned base");
         if (reinterpret_cast<uintptr_t>(fused->d_sync) & 127) return tnns_fail(TNNS_ERR_INVALID, "synchronisation words must be 128-byte aligned");
-        TNNS_CUDA_TRY(cudaMemsetAsync(fused->d_sync, 0, tnns_fused_sync_bytes(g.N), stream));
+        // The context keeps one set of synchronisation words of its own, bound to the first stream
+        // that launches the fused form: every launch leaves them zeroed (the last block out clears
+        // them), so launches on that stream need no clearing operation, and consecutive launches
+        // can overlap their set-up with the predecessor's tail (programmatic dependent launch).
+        // Launches on any other stream use the words in the caller's workspace, cleared here.
+        const size_t words = (size_t)Q_FLAG0 + (size_t)g.N;
+        if (ctx->fused_sync_words < words && (!ctx->fused_sync || ctx->fused_sync_stream == stream)) {
+            TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
+            TNNS_CUDA_TRY(cudaDeviceSynchronize());  // earlier launches may still use the old words
+            if (ctx->fused_sync) cudaFree(ctx->fused_sync);
+            ctx->fused_sync = nullptr;
+            ctx->fused_sync_words = 0;
+            const size_t cap = std::max<size_t>(words, 4096);
+            TNNS_CUDA_TRY(cudaMalloc(&ctx->fused_sync, cap * sizeof(unsigned int)));
+            TNNS_CUDA_TRY(cudaMemset(ctx->fused_sync, 0, cap * sizeof(unsigned int)));
+            ctx->fused_sync_words = cap;
+            ctx->fused_sync_stream = stream;
+        }
+        own_words = ctx->fused_sync && ctx->fused_sync_words >= words && ctx->fused_sync_stream == stream;
+        if (!own_words) TNNS_CUDA_TRY(cudaMemsetAsync(fused->d_sync, 0, tnns_fused_sync_bytes(g.N), stream));
     }
     CUtensorMap map;
     int rc = encode_im2col_map(&map, d_image, g);
@@ -1367,7 +1432,7 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     a.cp_next = (w->KN + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS;
     a.img = nullptr;
     a.jtab = w->d_jtab;
-    a.qx = a.qthr = nullptr; a.qimg = nullptr; a.q_sync = nullptr; a.qN = a.qC = a.q_nbands = 0;
+    a.qx = a.qthr = nullptr; a.qimg = nullptr; a.q_sync = nullptr; a.qN = a.qC = a.q_nbands = a.q_self_clean = 0;
     a.H = g.H; a.W = g.W; a.OW = g.OW; a.Cp = g.Cp; a.SH = g.SH; a.SW = g.SW; a.PH = g.PH; a.PW = g.PW;
     alignas(64) CUtensorMap map_q;
     if (fused) {
@@ -1377,7 +1442,8 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
         a.qx = fused->d_x;
         a.qthr = fused->d_thr;
         a.qimg = reinterpret_cast<uint4*>(const_cast<void*>(d_image));
-        a.q_sync = fused->d_sync;
+        a.q_sync = own_words ? ctx->fused_sync : fused->d_sync;
+        a.q_self_clean = own_words ? 1 : 0;
         a.qN = g.N;
         a.qC = g.C;
         a.q_nbands = (g.H * g.W + Q_PIX - 1) / Q_PIX;

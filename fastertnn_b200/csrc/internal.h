@@ -34,6 +34,11 @@ struct tnns_cuda_ctx {
     void* stage_pack[2];
     float* stage_thr;
     size_t stage_in_bytes, stage_out_bytes, stage_pack_bytes, stage_thr_count;
+    // synchronisation words of the one-launch layer kernel: zero between launches (the kernel clears
+    // them on its way out), used by launches on the one stream they are bound to
+    unsigned int* fused_sync;
+    size_t fused_sync_words;
+    cudaStream_t fused_sync_stream;
 };
 
 struct tnns_cuda_weights {
