@@ -642,6 +642,43 @@ def test_fused_quantise_and_tensor_copy_gemm(type_, layer, N, gpu_ctx, checker):
 
 
 @pytest.mark.gpu
+def test_fused_launches_on_two_streams(gpu_ctx, checker):
+    """The context's own synchronisation words serve the stream that used the fused form first (they
+    are left zeroed by every launch); launches on another stream use the words in the caller's
+    workspace, cleared per call.  Both give the reference's bytes, interleaved and back to back."""
+    import torch
+    ctx = gpu_ctx
+    layer = Layer(256, 12, 12, 300, 3, 3, 1, 1)
+    N = 9
+    case = make_case(TNN, layer, N, 7300, "uniform")
+    wp = checker.pack_weights(True, case.w, case.w_thr)
+    want = checker.conv(TNN, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
+    w = ctx.upload_weights(TNN, wp, layer.C, layer.KH, layer.KW)
+    shape = layer.shape(N)
+    nb_ws = ft.api.fused_workspace_bytes(N, layer.C, layer.H, layer.W)
+    d_x, d_t = ctx.to_device(case.x), ctx.to_device(case.thr)
+    d_y = [ctx.malloc(want.nbytes) for _ in range(2)]
+    d_ws = [ctx.malloc(nb_ws) for _ in range(2)]
+    streams = [0, torch.cuda.Stream().cuda_stream]
+    try:
+        ctx.conv_fused(w, d_x, d_t, d_y[0], d_ws[0], nb_ws, shape, case.alpha, 0, streams[0])   # binds the default stream
+        ctx.sync()
+        for rep in range(3):
+            for k in (0, 1):
+                ctx.fill(d_y[k], np.full(want.size, np.nan, np.float32))
+                ctx.fill(d_ws[k], np.full(nb_ws // 4, 0xFFFFFFFF, np.uint32))
+            for k in (1, 0, 1, 0):
+                ctx.conv_fused(w, d_x, d_t, d_y[k], d_ws[k], nb_ws, shape, case.alpha, 1 + (rep % 2), streams[k])
+            ctx.sync()
+            for k in (0, 1):
+                assert ctx.to_host(d_y[k], want.shape, np.float32).tobytes() == want.tobytes()
+    finally:
+        for p in (d_x, d_t, *d_y, *d_ws):
+            ctx.free(p)
+        w.free()
+
+
+@pytest.mark.gpu
 def test_fused_route_declines_what_it_cannot_do(gpu_ctx, checker):
     """Pixel counts that are not a multiple of four (the rows of the input tensor must be 16-byte
     multiples for the copy engine) and NHWC input stay on the two-kernel route; asking for the fused
