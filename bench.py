@@ -219,7 +219,6 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
         raise SystemExit("no CUDA device: this benchmark has no CPU fallback")
     torch.cuda.set_device(local)
     if world > 1:
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")  # keeps NCCL's version banner off stdout (one JSON line there)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
 
     def barrier():
@@ -528,6 +527,12 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
 
 
 def main():
+    # stdout carries exactly one JSON line: whatever libraries print there on the way (NCCL's version
+    # banner, for one) goes to stderr instead, and print() writes to the saved descriptor
+    sys.stdout.flush()
+    saved = os.dup(1)
+    os.dup2(2, 1)
+    sys.stdout = os.fdopen(saved, "w", buffering=1)
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=20)

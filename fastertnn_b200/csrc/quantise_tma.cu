@@ -74,13 +74,18 @@ quantise_tma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __res
         const int grp = (warp - 1) >> 2;
         const int p = tid - 32 - grp * QL;  // pixel of the band
         long long k = grp;
-        for (long long i = blockIdx.x + (long long)grp * gridDim.x; i < items; i += (long long)QGROUPS * gridDim.x, k += QGROUPS) {
+        // The threshold of an item's image is loaded one item ahead and not touched until its turn: an
+        // instruction that uses a just-issued load holds the (in-order) warp for the whole round trip.
+        const long long step = (long long)QGROUPS * gridDim.x, first = blockIdx.x + (long long)grp * gridDim.x;
+        float t_raw = first < items ? __ldg(thr + first / ((long long)Cp * nbands)) : 0.f;
+        for (long long i = first; i < items; i += step, k += QGROUPS) {
             const int s = (int)(k % QSTG);
             const int ic = (int)(i % Cp);
             const long long nb = i / Cp;
             const int band = (int)(nb % nbands), n = (int)(nb / nbands);
             const int nch = min(QC, C - ic * QC);  // channels present in this group
-            const float t = __ldg(thr + n) + 0.0f;  // + 0.0f: a threshold of -0 behaves as +0 in every compare
+            const float t = t_raw + 0.0f;  // + 0.0f: a threshold of -0 behaves as +0 in every compare
+            if (i + step < items) t_raw = __ldg(thr + (i + step) / ((long long)Cp * nbands));
             if (!mbar_wait(bar_full + 8 * s, (uint32_t)((k / QSTG) & 1), abort_flag, status, 0x22)) goto done;
             const float* sp = reinterpret_cast<const float*>(smem + s * QSTAGE_BYTES) + p;
             uint32_t sg[2] = {0, 0}, nz[2] = {0, 0};

@@ -280,7 +280,11 @@ int tnns_cuda_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const 
  * HBM-bound quantisation runs underneath the tensor-bound MMAs of earlier tiles.  Needs what
  * tnns_cuda_gemm_im2col needs plus NCHW input with H*W a multiple of four and a 16-byte aligned
  * d_x (tnns_cuda_conv_fused_supported).  d_workspace: tnns_fused_workspace_bytes() bytes, 128-byte
- * aligned (image + synchronisation words; the words are cleared on `stream` by the call).  Same
+ * aligned (image + synchronisation words).  The context owns a second set of synchronisation words,
+ * bound to the first stream that makes such a call and left zeroed by every launch; calls on that
+ * stream use them and may overlap their set-up with the previous such launch's tail, calls on any
+ * other stream use the words in the workspace, which the call clears on `stream` first.  The first
+ * call may allocate those words (and synchronise the device); keep it out of stream capture.  Same
  * result as every other route.  tnns_cuda_conv / _conv_ws take it with gemm_algo
  * TNNS_GEMM_F4_FUSED, and with TNNS_GEMM_AUTO where the layer has several tiles per SM. */
 size_t tnns_fused_workspace_bytes(int N, int C, int H, int W);
