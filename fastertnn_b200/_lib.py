@@ -100,6 +100,8 @@ SIGNATURES = {
     "tnns_cuda_gemm_im2col": (_i, [_vp, _vp, _vp, _vp, _vp, C.c_float, _i, _i, _vp]),
     "tnns_fused_workspace_bytes": (_sz, [_i, _i, _i, _i]),
     "tnns_cuda_conv_fused_supported": (_i, [_vp, _vp, _vp, _i]),
+    "tnns_cuda_conv_fused_preferred": (_i, [_vp, _vp, _vp, _vp, _i]),
+    "tnns_cuda_conv_fused_packed_out": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _sz, _pshape, C.c_float, _i, _vp]),
     "tnns_cuda_conv_fused": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _pshape, C.c_float, _i, _vp]),
     "tnns_cuda_gemm_im2col_packed_out": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _vp, C.c_float, _i, _vp]),
     "tnns_cuda_memcpy_h2d": (_i, [_vp, _vp, _vp, _sz]),

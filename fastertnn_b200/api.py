@@ -303,6 +303,16 @@ class Context:
     def conv_fused_supported(self, w: Weights, shape: Shape, d_x: int, layout=NCHW) -> bool:
         return bool(self.lib.tnns_cuda_conv_fused_supported(w.handle, C.byref(shape), d_x, layout))
 
+    def conv_fused_preferred(self, w: Weights, shape: Shape, d_x: int, layout=NCHW) -> bool:
+        """Whether conv() with GEMM_AUTO takes the one-launch route for this layer by itself."""
+        return bool(self.lib.tnns_cuda_conv_fused_preferred(self.handle, w.handle, C.byref(shape), d_x, layout))
+
+    def conv_fused_packed_out(self, w: Weights, d_x: int, d_thr: int, d_image_out: int, d_thr_next: int, next_format: int, d_ws: int,
+                              ws_bytes: int, shape: Shape, alpha: float, pairs=0, stream=0):
+        """conv_fused whose epilogue writes the next layer's quantised activations instead of fp32."""
+        _check(self.lib.tnns_cuda_conv_fused_packed_out(self.handle, w.handle, d_x, d_thr, d_image_out, d_thr_next, next_format, d_ws,
+                                                        ws_bytes, C.byref(shape), alpha, pairs, stream))
+
     def conv_fused(self, w: Weights, d_x: int, d_thr: int, d_y: int, d_ws: int, ws_bytes: int, shape: Shape, alpha: float,
                    pairs=0, stream=0):
         """Whole layer in ONE launch: quantiser warps beside the tensor-copy fed GEMM (NCHW input).

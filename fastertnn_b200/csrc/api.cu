@@ -389,15 +389,17 @@ int tnns_cuda_conv_fused_supported(const tnns_cuda_weights* w, const tnns_shape_
     return tnns_fused_supported(w, g, d_x, layout) ? 1 : 0;
 }
 
-int tnns_cuda_conv_fused(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y,
-                         void* d_workspace, size_t workspace_bytes, const tnns_shape_t* s, float alpha, int pairs, void* stream) {
-    if (!ctx || !w || !d_x || !d_thr || !d_y || !d_workspace) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+static int conv_fused_impl(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y,
+                           void* d_image_out, const float* d_thr_next, int next_format, void* d_workspace, size_t workspace_bytes,
+                           const tnns_shape_t* s, float alpha, int pairs, void* stream) {
+    if (!ctx || !w || !d_x || !d_thr || !d_workspace) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
     TnnsGeom g;
     int rc = tnns_make_geom(s, &g);
     if (rc) return rc;
     if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW)
         return tnns_fail(TNNS_ERR_INVALID, "shape does not match the uploaded weights");
     if (g.N == 0) return TNNS_OK;
+    if (pairs < 0 || pairs > 2) return tnns_fail(TNNS_ERR_INVALID, "pairs must be 0, 1 or 2");
     if (reinterpret_cast<uintptr_t>(d_workspace) & 127) return tnns_fail(TNNS_ERR_INVALID, "workspace must be 128-byte aligned");
     const size_t need = tnns_fused_workspace_bytes(g.N, g.C, g.H, g.W);
     if (workspace_bytes < need) return tnns_fail(TNNS_ERR_INVALID, "workspace of %zu bytes, need %zu", workspace_bytes, need);
@@ -405,7 +407,33 @@ int tnns_cuda_conv_fused(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const f
     f.d_x = d_x;
     f.d_thr = d_thr;
     f.d_sync = reinterpret_cast<unsigned int*>(static_cast<char*>(d_workspace) + fused_image_bytes(g.N, g.C, g.H, g.W));
-    return tnns_launch_gemm_im2col(ctx, w, d_workspace, d_y, g, alpha, TNNS_NCHW, (cudaStream_t)stream, pairs, nullptr, nullptr, 1, &f);
+    return tnns_launch_gemm_im2col(ctx, w, d_workspace, d_y, g, alpha, TNNS_NCHW, (cudaStream_t)stream, pairs, d_image_out, d_thr_next,
+                                   next_format, &f);
+}
+
+int tnns_cuda_conv_fused(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y,
+                         void* d_workspace, size_t workspace_bytes, const tnns_shape_t* s, float alpha, int pairs, void* stream) {
+    if (!d_y) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    return conv_fused_impl(ctx, w, d_x, d_thr, d_y, nullptr, nullptr, 1, d_workspace, workspace_bytes, s, alpha, pairs, stream);
+}
+
+int tnns_cuda_conv_fused_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr,
+                                    void* d_image_out, const float* d_thr_next, int next_format, void* d_workspace,
+                                    size_t workspace_bytes, const tnns_shape_t* s, float alpha, int pairs, void* stream) {
+    if (!d_image_out || !d_thr_next) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    if (reinterpret_cast<uintptr_t>(d_image_out) & 15) return tnns_fail(TNNS_ERR_INVALID, "output image must be 16-byte aligned");
+    if (next_format < 0 || next_format > 2) return tnns_fail(TNNS_ERR_INVALID, "output format must be 0, 1 or 2");
+    return conv_fused_impl(ctx, w, d_x, d_thr, nullptr, d_image_out, d_thr_next, next_format, d_workspace, workspace_bytes, s, alpha, pairs,
+                           stream);
+}
+
+// The rule tnns_cuda_conv applies with TNNS_GEMM_AUTO: the one-launch route where the layer qualifies
+// and every SM has at least four 128-row tiles.
+int tnns_cuda_conv_fused_preferred(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout) {
+    if (!ctx || !tnns_cuda_conv_fused_supported(w, s, d_x, layout)) return 0;
+    const long long tiles = (((long long)s->N * tnns_out_dim(s->H, s->PH, s->KH, s->SH) * tnns_out_dim(s->W, s->PW, s->KW, s->SW) + 127) / 128) *
+                            ((s->KN + 255) / 256);
+    return tiles >= 4LL * ctx->sm_count ? 1 : 0;
 }
 
 size_t tnns_packed_image_bytes(int ternary, int N, int C, int H, int W) {
@@ -488,8 +516,7 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
                          tnns_fused_workspace_bytes(g.N, g.C, g.H, g.W) <= workspace_bytes;
         if (gemm_algo == TNNS_GEMM_F4_FUSED && !can)
             return tnns_fail(TNNS_ERR_UNSUPPORTED, "layer, layout, workspace size or alignment outside the fused quantise + GEMM route");
-        const long long tiles = (((long long)g.N * g.OH * g.OW + 127) / 128) * ((g.KN + 255) / 256);
-        if (can && (gemm_algo == TNNS_GEMM_F4_FUSED || tiles >= 4LL * ctx->sm_count))
+        if (can && (gemm_algo == TNNS_GEMM_F4_FUSED || tnns_cuda_conv_fused_preferred(ctx, w, s, d_x, layout)))
             return tnns_cuda_conv_fused(ctx, w, d_x, d_thr, d_y, d_workspace, workspace_bytes, s, alpha, 0, stream);
     }
     const bool auto_route = pack_algo == TNNS_PACK_AUTO && (gemm_algo == TNNS_GEMM_AUTO || gemm_algo == TNNS_GEMM_F4_TC);

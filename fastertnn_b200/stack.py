@@ -10,7 +10,9 @@ planes (``tnns_cuda_im2row_packed``); the final fp32 output is bit-identical.
 ``chain="image"`` goes one step further where the layers qualify for the copy-engine route:
 the input is quantised once into a 4-bit operand image, every layer is ONE kernel -- the GEMM fed
 by im2col tensor copies, whose epilogue writes the next layer's 4-bit image
-(``tnns_cuda_gemm_im2col_packed_out``) -- and only the last layer writes fp32.  A layer that does
+(``tnns_cuda_gemm_im2col_packed_out``) -- and only the last layer writes fp32; where the first layer
+is large enough for the one-launch route, its kernel also quantises the input
+(``tnns_cuda_conv_fused_packed_out``).  A layer that does
 not qualify takes the bit-plane steps of the packed chain; the format between two layers is
 chosen by what the consumer reads.  The final output is again bit-identical."""
 from __future__ import annotations
@@ -56,6 +58,14 @@ class ConvStack:
                       [api.e2m1_image_bytes(batch, L.KN, L.OH, L.OW) for L in layers])
             self.d_imgs = [ctx.malloc(img), ctx.malloc(img)]  # ping-pong quantised activations (either format fits)
             self.extra = list(self.d_imgs)
+            # first layer in one launch (quantise step inside the GEMM kernel) where the library itself
+            # would choose that route; its workspace holds the input's 4-bit image
+            L0 = layers[0]
+            self.fuse_first = bool(self.fast[0]) and ctx.conv_fused_preferred(self.weights[0], L0.shape(batch), self.buf[0], layout)
+            self.ws0_bytes = api.fused_workspace_bytes(batch, L0.C, L0.H, L0.W)
+            if self.fuse_first:
+                self.d_ws0 = ctx.malloc(self.ws0_bytes)
+                self.extra.append(self.d_ws0)
             self.d_a = None
             if not all(self.fast):
                 self.d_a = ctx.malloc(max(api.packed_bytes(type_, L.shape(batch)) for L, f in zip(layers, self.fast) if not f))
@@ -89,7 +99,9 @@ class ConvStack:
             last = len(self.layers) - 1
             L0 = self.layers[0]
             # the input, in the format the first layer reads
-            if self.fast[0]:
+            if self.fuse_first:
+                pass
+            elif self.fast[0]:
                 self.ctx.quantise_e2m1(self.buf[0], self.d_thr, self.d_imgs[0], self.batch, L0.C, L0.H, L0.W, self.layout, stream)
             else:
                 self.ctx.quantise(True, self.buf[0], self.d_thr, self.d_imgs[0], self.batch, L0.C, L0.H, L0.W, self.layout, stream)
@@ -97,7 +109,13 @@ class ConvStack:
                 shape = L.shape(self.batch)
                 src, dst = self.d_imgs[i % 2], self.d_imgs[(i + 1) % 2]
                 nxt = 2 if (i < last and self.fast[i + 1]) else 1  # 4-bit image or ternary bit planes for the consumer
-                if self.fast[i]:
+                if i == 0 and self.fuse_first:
+                    if i < last:
+                        self.ctx.conv_fused_packed_out(w, self.buf[0], self.d_thr, dst, self.d_thr, nxt, self.d_ws0, self.ws0_bytes, shape,
+                                                       self.alpha, 0, stream)
+                    else:
+                        self.ctx.conv_fused(w, self.buf[0], self.d_thr, self.buf[1], self.d_ws0, self.ws0_bytes, shape, self.alpha, 0, stream)
+                elif self.fast[i]:
                     if i < last:
                         self.ctx.gemm_im2col_packed_out(w, src, dst, self.d_thr, nxt, shape, self.alpha, stream)
                     else:

@@ -291,6 +291,15 @@ size_t tnns_fused_workspace_bytes(int N, int C, int H, int W);
 int tnns_cuda_conv_fused_supported(const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout);
 int tnns_cuda_conv_fused(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y,
                          void* d_workspace, size_t workspace_bytes, const tnns_shape_t* s, float alpha, int pairs, void* stream);
+/* 1 where tnns_cuda_conv with TNNS_GEMM_AUTO takes that route by itself (the layer qualifies and
+ * every SM has at least four 128-row tiles), else 0. */
+int tnns_cuda_conv_fused_preferred(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout);
+/* The same launch as the first layer of a chain (src/timing_layers.c:188-201 chains layers through fp32
+ * buffers): fp32 input in, and instead of the fp32 output the next layer's quantised activations
+ * (d_image_out, d_thr_next, next_format as for tnns_cuda_gemm_im2col_packed_out below). */
+int tnns_cuda_conv_fused_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr,
+                                    void* d_image_out, const float* d_thr_next, int next_format, void* d_workspace,
+                                    size_t workspace_bytes, const tnns_shape_t* s, float alpha, int pairs, void* stream);
 /* Chaining on the copy-engine route: the same GEMM with the quantising epilogue of
  * tnns_cuda_gemm_packed_out.  next_format (also accepted as `next_ternary` by
  * tnns_cuda_gemm_packed_out): 0 = binary bit planes, 1 = ternary bit planes, 2 = ternary 4-bit

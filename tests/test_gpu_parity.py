@@ -642,6 +642,39 @@ def test_fused_quantise_and_tensor_copy_gemm(type_, layer, N, gpu_ctx, checker):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("next_format", [2, 1, 0])
+def test_fused_first_layer_of_a_chain(next_format, gpu_ctx, checker):
+    """The one-launch kernel with the quantising epilogue: fp32 input in, the next layer's quantised
+    activations out -- the same bytes as the quantise kernel followed by the GEMM with that epilogue."""
+    ctx = gpu_ctx
+    layer, N = Layer(128, 12, 12, 200, 3, 3, 1, 1), 6
+    case = make_case(TNN, layer, N, 8100 + next_format, "uniform")
+    wp = checker.pack_weights(True, case.w, case.w_thr)
+    w = ctx.upload_weights(TNN, wp, layer.C, layer.KH, layer.KW)
+    shape = layer.shape(N)
+    nb_in = ft.api.e2m1_image_bytes(N, layer.C, layer.H, layer.W)
+    nb_ws = ft.api.fused_workspace_bytes(N, layer.C, layer.H, layer.W)
+    nb_out = max(ft.api.e2m1_image_bytes(N, layer.KN, layer.OH, layer.OW), ft.api.packed_image_bytes(True, N, layer.KN, layer.OH, layer.OW))
+    thr_next = np.linspace(0.2, 3.0, N).astype(np.float32)
+    d_x, d_t, d_tn = ctx.to_device(case.x), ctx.to_device(case.thr), ctx.to_device(thr_next)
+    d_in, d_ws = ctx.malloc(nb_in), ctx.malloc(nb_ws)
+    d_o = [ctx.malloc(nb_out) for _ in range(2)]
+    try:
+        for p in d_o:
+            ctx.fill(p, np.zeros(nb_out // 4, np.uint32))
+        ctx.quantise_e2m1(d_x, d_t, d_in, N, layer.C, layer.H, layer.W, ft.NCHW)
+        ctx.gemm_im2col_packed_out(w, d_in, d_o[0], d_tn, next_format, shape, case.alpha)
+        ctx.conv_fused_packed_out(w, d_x, d_t, d_o[1], d_tn, next_format, d_ws, nb_ws, shape, case.alpha)
+        ctx.sync()
+        a, b = (ctx.to_host(p, (nb_out // 4,), np.uint32) for p in d_o)
+        assert a.any() and np.array_equal(a, b)
+    finally:
+        for p in (d_x, d_t, d_tn, d_in, d_ws, *d_o):
+            ctx.free(p)
+        w.free()
+
+
+@pytest.mark.gpu
 def test_fused_launches_on_two_streams(gpu_ctx, checker):
     """The context's own synchronisation words serve the stream that used the fused form first (they
     are left zeroed by every launch); launches on another stream use the words in the caller's
