@@ -253,15 +253,16 @@ def run_ours(args, layer: Layer, N_total: int, name: str):
     if args.route in ("im2col", "fused") and not im2col:
         raise SystemExit("bench: this workload does not qualify for the im2col tensor-copy route")
     implicit = tc4 and (im2col or args.route in ("auto", "implicit"))
-    sm_count = torch.cuda.get_device_properties(local).multi_processor_count
 
     def fused_for(n):
-        """The library's own rule (tnns_cuda_conv): one launch with the quantise step inside the GEMM
-        kernel where the layer qualifies and every SM has at least four 128-row tiles."""
+        """One launch with the quantise step inside the GEMM kernel: on request, else where the
+        library's own rule (tnns_cuda_conv with TNNS_GEMM_AUTO) takes that route.  The pointer only
+        stands for the input's alignment here (torch allocations are 512-byte aligned)."""
         if not (im2col and args.route in ("auto", "fused")):
             return False
-        tiles = -(-n * layer.OH * layer.OW // 128) * -(-layer.KN // 256)
-        return args.route == "fused" or tiles >= 4 * sm_count
+        if args.route == "fused":
+            return ctx.conv_fused_supported(w, layer.shape(n), 4096, ft.NCHW)
+        return ctx.conv_fused_preferred(w, layer.shape(n), 4096, ft.NCHW)
 
     fused = fused_for(nloc)
     pack_bytes = (ft.api.fused_workspace_bytes(nloc, layer.C, layer.H, layer.W) if im2col else
