@@ -675,6 +675,30 @@ def test_fused_first_layer_of_a_chain(next_format, gpu_ctx, checker):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("type_", [TNN, TBN])
+def test_fused_quantiser_on_special_values(type_, gpu_ctx, checker):
+    """+-0, values equal to and next to the thresholds, denormals, infinities, thresholds of 0 and -0:
+    the quantiser warps inside the GEMM launch decide exactly as the reference does (strict compares,
+    src/tnns/ternarize2row_avx2.c:444-449), seen through the layer output."""
+    ctx = gpu_ctx
+    case = special_value_case(type_)
+    layer, N = case.layer, case.N
+    wp = checker.pack_weights(wgt_ternary(type_), case.w, case.w_thr)
+    want = checker.conv(type_, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
+    w = ctx.upload_weights(type_, wp, layer.C, layer.KH, layer.KW)
+    d_x, d_t = ctx.to_device(case.x), ctx.to_device(case.thr)
+    d_y = ctx.malloc(want.nbytes)
+    try:
+        ctx.conv(w, d_x, d_t, d_y, layer.shape(N), case.alpha, ft.NCHW, ft.PACK_AUTO, ft.GEMM_F4_FUSED)
+        ctx.sync()
+        assert ctx.to_host(d_y, want.shape, np.float32).tobytes() == want.tobytes()
+    finally:
+        for p in (d_x, d_t, d_y):
+            ctx.free(p)
+        w.free()
+
+
+@pytest.mark.gpu
 def test_fused_launches_on_two_streams(gpu_ctx, checker):
     """The context's own synchronisation words serve the stream that used the fused form first (they
     are left zeroed by every launch); launches on another stream use the words in the caller's
