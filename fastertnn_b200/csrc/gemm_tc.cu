@@ -14,7 +14,10 @@
 //                       implicit form, the bit-plane image of the layer input) and expand them
 //   tensor-copy fed (ATMA = true)  the layer input was quantised straight into 4-bit operands and
 //                       the copy engine delivers each stage as im2col tensor copies; no expander
-//                       warps, optionally on block pairs (CG = 2, tcgen05.mma.cta_group::2)
+//                       warps, optionally on block pairs (CG = 2, tcgen05.mma.cta_group::2), and
+//                       optionally with the quantise step itself in the same launch (QF = true:
+//                       four quantiser warps and a publisher thread beside the GEMM's roles; a
+//                       tile's copies start once the images of its rows are complete)
 //
 // Expander-fed form: one persistent block per SM, 22 warps in four roles (the tensor-copy form
 // keeps warps 0, 1 and eight epilogue warps):
