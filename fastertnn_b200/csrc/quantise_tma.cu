@@ -46,6 +46,10 @@ quantise_tma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __res
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * QSTG);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const long long items = (long long)N * nbands * Cp;
+    // The GEMM that follows on the stream is launched as a programmatic dependent: its blocks may
+    // take SMs as the blocks of this launch leave and set themselves up there; it waits for this
+    // launch to complete before it reads the image.  All blocks of this launch are resident at once.
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
     if (tid == 0) {
         for (int s = 0; s < QSTG; s++) {
