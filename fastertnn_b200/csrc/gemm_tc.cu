@@ -563,11 +563,11 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
     auto tap_at = [&](int j) -> uint32_t { return j < Cfg::TAPMAX ? s_taps[j] : __ldg(p.jtab + j); };
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    // Programmatic dependent launch (tensor-copy forms): a following launch of this kind may place its
+    // Programmatic dependent launch: a following launch of this kind may place its
     // blocks on SMs as the blocks of this one leave, run its set-up there, and wait (below, before
     // it touches any global data) until this launch has completed.  All blocks of a launch are
     // resident at once, so letting the dependents in early cannot starve this launch of SMs.
-    if (ATMA) asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
     const int nchunks = F4 ? p.Kp / 4 : p.Kp / 2;  // stages per tile
     const int ntn = (p.KN + BN - 1) / BN;
     const long long ntm = (p.M + TILE_M - 1) / TILE_M;
@@ -638,7 +638,7 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
 
     // everything above touched only on-chip state and the layer's constant tables; what follows reads
     // and writes tensors that the previous launch on the stream may still be working on
-    if (ATMA) asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == WARP_TMA) {
         if (lane == 0) {
@@ -1147,29 +1147,23 @@ int launch_cfg(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream, const
     static const CUtensorMap no_map = {};
     TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
     const long long tiles = ((a.M + CG * MT * BM - 1) / (CG * MT * BM)) * ((a.KN + BN - 1) / BN);
-    // tensor-copy forms: the launch may be scheduled while its predecessor on the stream drains (the kernel
+    // the launch may be scheduled while its predecessor on the stream drains (the kernel
     // waits for it, griddepcontrol.wait, before it touches global data)
     cudaLaunchAttribute attr[2];
     int nattr = 0;
-    if (ATMA) {
-        attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-        attr[nattr].val.programmaticStreamSerializationAllowed = 1;
-        nattr++;
-    }
+    attr[nattr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[nattr].val.programmaticStreamSerializationAllowed = 1;
+    nattr++;
     if (CG == 1) {
         const int grid = (int)std::min<long long>(tiles, ctx->sm_count);
-        if (ATMA) {
-            cudaLaunchConfig_t cfg = {};
-            cfg.gridDim = dim3(grid);
-            cfg.blockDim = dim3(Cfg::NTHREADS);
-            cfg.dynamicSmemBytes = Cfg::SMEM;
-            cfg.stream = stream;
-            cfg.attrs = attr;
-            cfg.numAttrs = nattr;
-            TNNS_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a, tmap_a ? *tmap_a : no_map, no_map, tmap_q ? *tmap_q : no_map));
-        } else {
-            kern<<<grid, Cfg::NTHREADS, Cfg::SMEM, stream>>>(a, tmap_a ? *tmap_a : no_map, no_map, tmap_q ? *tmap_q : no_map);
-        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(Cfg::NTHREADS);
+        cfg.dynamicSmemBytes = Cfg::SMEM;
+        cfg.stream = stream;
+        cfg.attrs = attr;
+        cfg.numAttrs = nattr;
+        TNNS_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, a, tmap_a ? *tmap_a : no_map, no_map, tmap_q ? *tmap_q : no_map));
     } else {
         // block pairs: clusters of two consecutive blocks, as many as can be resident at once (the
         // kernel is persistent; a pair that had to wait for a free TPC would start its whole tile

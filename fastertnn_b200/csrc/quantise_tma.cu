@@ -60,6 +60,8 @@ quantise_tma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __res
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
+    // launched as a programmatic dependent itself: the input may be the output of the launch before
+    asm volatile("griddepcontrol.wait;" ::: "memory");
 
     if (warp == 0) {
         if (lane == 0) {
@@ -177,7 +179,17 @@ int tnns_launch_quantise_tma(tnns_cuda_ctx* ctx, bool ternary, const float* d_x,
     const int grid = (int)std::min<long long>(items, ctx->sm_count);
     auto launch = [&](auto kern) -> int {
         TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)QSMEM));
-        kern<<<grid, QTHREADS, QSMEM, stream>>>(map, d_thr, d_image, N, C, HW, Cp, nbands, ctx->d_status);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(QTHREADS);
+        cfg.dynamicSmemBytes = QSMEM;
+        cfg.stream = stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[0].val.programmaticStreamSerializationAllowed = 1;
+        cfg.attrs = attr;
+        cfg.numAttrs = 1;
+        TNNS_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, map, d_thr, d_image, N, C, HW, Cp, nbands, ctx->d_status));
         tnns_count_launch();
         TNNS_CUDA_TRY(cudaGetLastError());
         return TNNS_OK;
