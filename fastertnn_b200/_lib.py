@@ -54,9 +54,11 @@ class GemmTestcase(C.Structure):
 _vp, _i, _f, _sz = C.c_void_p, C.c_int, C.c_float, C.c_size_t
 _pf, _pi64 = C.POINTER(C.c_float), C.POINTER(C.c_int64)
 _pshape = C.POINTER(Shape)
+SHARD_FN = C.CFUNCTYPE(C.c_int, C.c_int, C.c_int, C.c_int, C.c_int, C.c_void_p)  # tnns_shard_fn
 SIGNATURES = {
     "tnns_conv": (None, [C.POINTER(Testcase)]),
     "tnns_gemm": (None, [C.POINTER(GemmTestcase)]),
+    "tnns_b200_thread_shutdown": (None, []),
     "mm_tnn": (_vp, [_vp, _vp, _i, _i, _i, _i, _i, _f]),
     "mm_tbn": (_vp, [_vp, _vp, _i, _i, _i, _i, _i, _f]),
     "mm_btn": (_vp, [_vp, _vp, _i, _i, _i, _i, _i, _f]),
@@ -85,6 +87,15 @@ SIGNATURES = {
     "tnns_cuda_gemm_packed_out": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _i, _f, _vp]),
     "tnns_cuda_im2row_packed": (_i, [_vp, _i, _vp, _vp, _pshape, _vp]),
     "tnns_cuda_conv_host": (_i, [_vp, _vp, _vp, _vp, _vp, _pshape, _f, _i]),
+    "tnns_shard_range": (None, [_i, _i, _i, C.POINTER(_i), C.POINTER(_i)]),
+    "tnns_shard_run": (_i, [_i, _i, SHARD_FN, _vp, C.POINTER(_i)]),
+    "tnns_cuda_multi_create": (_i, [C.POINTER(_i), _i, C.POINTER(_vp)]),
+    "tnns_cuda_multi_destroy": (None, [_vp]),
+    "tnns_cuda_multi_device_count": (_i, [_vp]),
+    "tnns_cuda_multi_context": (_vp, [_vp, _i]),
+    "tnns_cuda_multi_upload_weights": (_i, [_vp, _i, _vp, _i, _i, _i, _i, C.POINTER(_vp)]),
+    "tnns_cuda_multi_free_weights": (None, [_vp, _vp]),
+    "tnns_cuda_multi_conv_host": (_i, [_vp, _vp, _vp, _vp, _vp, _pshape, _f, _i, C.POINTER(_i)]),
     "tnns_cuda_noalloc_scratch_bytes": (_sz, []),
     "tnns_cuda_conv_noalloc": (_i, [_i, _vp, _vp, _vp, _vp, _pshape, _f, _i, _vp]),
     "tnns_cuda_pipe_rate": (_i, [_vp, _i, C.POINTER(C.c_double)]),
@@ -92,6 +103,7 @@ SIGNATURES = {
     "tnns_cuda_sync": (_i, [_vp]),
     "tnns_cuda_malloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "tnns_cuda_free": (None, [_vp, _vp]),
+    "tnns_cuda_mem_info": (_i, [_vp, C.POINTER(_sz), C.POINTER(_sz)]),
     "tnns_cuda_malloc_host": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "tnns_cuda_free_host": (None, [_vp, _vp]),
     "tnns_e2m1_image_bytes": (_sz, [_i, _i, _i, _i]),

@@ -363,6 +363,12 @@ class Context:
     def free(self, p: int):
         self.lib.tnns_cuda_free(self.handle, p)
 
+    def mem_info(self) -> tuple[int, int]:
+        """(free, total) bytes of device memory on this context's device."""
+        f, t = C.c_size_t(), C.c_size_t()
+        _check(self.lib.tnns_cuda_mem_info(self.handle, C.byref(f), C.byref(t)))
+        return f.value, t.value
+
     def malloc_host(self, nbytes: int) -> int:
         """Page-locked host memory (tnns_cuda_conv_host moves it at full PCIe speed)."""
         p = C.c_void_p()
@@ -387,6 +393,70 @@ class Context:
         out = np.empty(shape, dtype=dtype)
         _check(self.lib.tnns_cuda_memcpy_d2h(self.handle, _ptr(out), p, out.nbytes))
         return out
+
+
+def shard_range(N: int, shard: int, shards: int) -> tuple[int, int]:
+    """[n0, n1) of the images shard `shard` of `shards` owns (``tnns_shard_range``)."""
+    a, b = C.c_int(), C.c_int()
+    load_library().tnns_shard_range(N, shard, shards, C.byref(a), C.byref(b))
+    return a.value, b.value
+
+
+def shard_run(shards: int, N: int, fn) -> tuple[int, list[int]]:
+    """``tnns_shard_run``: fn(shard, shards, n0, n1) -> status on one host thread per shard behind a
+    start barrier.  Returns (overall status, status of every shard); never raises for a failed shard."""
+    from ._lib import SHARD_FN
+    cb = SHARD_FN(lambda g, G, n0, n1, _arg: int(fn(g, G, n0, n1)))
+    st = (C.c_int * shards)()
+    rc = load_library().tnns_shard_run(shards, N, cb, None, st)
+    return rc, list(st)
+
+
+class MultiWeights:
+    def __init__(self, group: "MultiContext", handle: int):
+        self.group, self.handle = group, handle
+
+    def free(self):
+        if self.handle:
+            load_library().tnns_cuda_multi_free_weights(self.group.handle, self.handle)
+            self.handle = None
+
+
+class MultiContext:
+    """A group of devices behind one call (``tnns_cuda_multi``): one host batch in, split by image
+    index over the devices, one host thread per device, weights replicated, no exchange between devices."""
+
+    def __init__(self, devices):
+        lib = load_library()
+        devs = (C.c_int * len(devices))(*devices)
+        h = C.c_void_p()
+        _check(lib.tnns_cuda_multi_create(devs, len(devices), C.byref(h)))
+        self.handle, self.devices, self.lib = h.value, list(devices), lib
+        self.shard_status: list[int] = []
+
+    def close(self):
+        if self.handle:
+            self.lib.tnns_cuda_multi_destroy(self.handle)
+            self.handle = None
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def upload_weights(self, type_: int, packed: np.ndarray, C_: int, KH: int, KW: int) -> MultiWeights:
+        pk = _i64(packed)
+        h = C.c_void_p()
+        _check(self.lib.tnns_cuda_multi_upload_weights(self.handle, type_, _ptr(pk), pk.shape[0], C_, KH, KW, C.byref(h)))
+        return MultiWeights(self, h.value)
+
+    def conv_host(self, w: MultiWeights, h_x: int, h_thr: int, h_y: int, shape: Shape, alpha: float, layout=NCHW):
+        """Host-pointer layer over all devices of the group; shard statuses are kept in ``shard_status``."""
+        st = (C.c_int * len(self.devices))()
+        rc = self.lib.tnns_cuda_multi_conv_host(self.handle, w.handle, h_x, h_thr, h_y, C.byref(shape), alpha, layout, st)
+        self.shard_status = list(st)
+        _check(rc)
 
 
 def noalloc_scratch_bytes() -> int:

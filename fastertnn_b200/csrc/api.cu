@@ -25,6 +25,7 @@ int tnns_fail(int status, const char* fmt, ...) {
     return status;
 }
 void tnns_count_launch(void) { tl_launches++; }
+void tnns_add_launches(unsigned long long n) { tl_launches += n; }
 
 extern "C" {
 
@@ -72,6 +73,24 @@ int tnns_make_geom(const tnns_shape_t* s, TnnsGeom* g) {
 
 static inline bool type_act_ternary(int type) { return type == TNN || type == TBN; }
 static inline bool type_wgt_ternary(int type) { return type == TNN || type == BTN; }
+
+// Every entry point that launches work opens with this: a context belongs to one device, but the
+// calling thread's current device is whatever its last CUDA call left it (a thread that holds two
+// contexts is on the second one's device after creating it).  Makes the context's device current,
+// and refuses weights that live on another device.
+static int enter(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w = nullptr) {
+    int cur = -1;
+    TNNS_CUDA_TRY(cudaGetDevice(&cur));
+    if (cur != ctx->device) TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
+    if (w && w->device != ctx->device)
+        return tnns_fail(TNNS_ERR_INVALID, "weights live on device %d, context on %d", w->device, ctx->device);
+    return TNNS_OK;
+}
+#define TNNS_ENTER(...)                   \
+    do {                                  \
+        int rc__ = enter(__VA_ARGS__);    \
+        if (rc__) return rc__;            \
+    } while (0)
 
 extern "C" {
 
@@ -175,6 +194,12 @@ int tnns_cuda_malloc(tnns_cuda_ctx* ctx, size_t bytes, void** out) {
     TNNS_CUDA_TRY(cudaMalloc(out, bytes ? bytes : 16));
     return TNNS_OK;
 }
+int tnns_cuda_mem_info(tnns_cuda_ctx* ctx, size_t* free_bytes, size_t* total_bytes) {
+    if (!ctx || !free_bytes || !total_bytes) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
+    TNNS_CUDA_TRY(cudaMemGetInfo(free_bytes, total_bytes));
+    return TNNS_OK;
+}
 int tnns_cuda_malloc_host(tnns_cuda_ctx* ctx, size_t bytes, void** out) {
     if (!ctx || !out) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
     *out = nullptr;
@@ -265,6 +290,7 @@ int tnns_cuda_pack_weights(tnns_cuda_ctx* ctx, int ternary, const float* d_w, co
                            int KH, int KW, void* stream) {
     if (!ctx || !d_w || !d_thr || !d_packed) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
     if (KN <= 0 || C <= 0 || KH <= 0 || KW <= 0) return tnns_fail(TNNS_ERR_INVALID, "non-positive weight dimension");
+    TNNS_ENTER(ctx);
     return tnns_launch_pack_weights(ctx, ternary != 0, d_w, d_thr, d_packed, KN, C, KH, KW, (cudaStream_t)stream);
 }
 
@@ -277,6 +303,7 @@ int tnns_cuda_pack(tnns_cuda_ctx* ctx, int ternary, const float* d_x, const floa
     if (rc) return rc;
     if (reinterpret_cast<uintptr_t>(d_packed) & 15) return tnns_fail(TNNS_ERR_INVALID, "packed buffer must be 16-byte aligned");
     if (algo < TNNS_PACK_AUTO || algo > TNNS_PACK_STAGED) return tnns_fail(TNNS_ERR_INVALID, "unknown pack algorithm %d", algo);
+    TNNS_ENTER(ctx);
     return tnns_launch_pack(ctx, ternary != 0, d_x, d_thr, d_packed, g, layout, algo, (cudaStream_t)stream);
 }
 
@@ -285,7 +312,7 @@ int tnns_cuda_gemm(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const int64_t
     if (!ctx || !w || !d_a || !d_y) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
     if (N < 0 || OH <= 0 || OW <= 0) return tnns_fail(TNNS_ERR_INVALID, "non-positive output dimension");
     if (layout != TNNS_NCHW && layout != TNNS_NHWC) return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
-    if (w->device != ctx->device) return tnns_fail(TNNS_ERR_INVALID, "weights live on device %d, context on %d", w->device, ctx->device);
+    TNNS_ENTER(ctx, w);
     if (reinterpret_cast<uintptr_t>(d_a) & 15) return tnns_fail(TNNS_ERR_INVALID, "packed operand must be 16-byte aligned");
     const long long M = (long long)N * OH * OW;
     const int K_unpack = w->K_unpack;
@@ -320,6 +347,7 @@ int tnns_cuda_quantise(tnns_cuda_ctx* ctx, int ternary, const float* d_x, const 
     if (!ctx || !d_x || !d_thr || !d_image) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
     if (N < 0 || C <= 0 || H <= 0 || W <= 0) return tnns_fail(TNNS_ERR_INVALID, "non-positive dimension");
     if (reinterpret_cast<uintptr_t>(d_image) & 31) return tnns_fail(TNNS_ERR_INVALID, "image must be 32-byte aligned");
+    TNNS_ENTER(ctx);
     return tnns_launch_quantise(ctx, ternary != 0, d_x, d_thr, d_image, N, C, H, W, layout, (cudaStream_t)stream);
 }
 
@@ -334,6 +362,7 @@ int tnns_cuda_gemm_implicit(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     if (layout != TNNS_NCHW && layout != TNNS_NHWC) return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
     if (reinterpret_cast<uintptr_t>(d_image) & 31) return tnns_fail(TNNS_ERR_INVALID, "image must be 32-byte aligned");
     if (!w->d_f4 || !w->d_jtab || w->Kp >= 65536) return tnns_fail(TNNS_ERR_UNSUPPORTED, "implicit im2row needs the 4-bit tensor-core GEMM");
+    TNNS_ENTER(ctx, w);
     return tnns_launch_gemm_tc(ctx, w, d_image, d_y, (long long)g.N * g.OH * g.OW, g.OH * g.OW, alpha, layout, true, (cudaStream_t)stream,
                                nullptr, nullptr, 1, &g);
 }
@@ -356,6 +385,7 @@ int tnns_cuda_quantise_e2m1(tnns_cuda_ctx* ctx, const float* d_x, const float* d
     if (!ctx || !d_x || !d_thr || !d_image) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
     if (N < 0 || C <= 0 || H <= 0 || W <= 0) return tnns_fail(TNNS_ERR_INVALID, "non-positive dimension");
     if (reinterpret_cast<uintptr_t>(d_image) & 31) return tnns_fail(TNNS_ERR_INVALID, "image must be 32-byte aligned");
+    TNNS_ENTER(ctx);
     return tnns_launch_quantise(ctx, true, d_x, d_thr, d_image, N, C, H, W, layout, (cudaStream_t)stream, TNNS_IMG_E2M1);
 }
 
@@ -369,7 +399,7 @@ int tnns_cuda_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const 
     if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW)
         return tnns_fail(TNNS_ERR_INVALID, "shape does not match the uploaded weights");
     if (layout != TNNS_NCHW && layout != TNNS_NHWC) return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
-    if (w->device != ctx->device) return tnns_fail(TNNS_ERR_INVALID, "weights live on device %d, context on %d", w->device, ctx->device);
+    TNNS_ENTER(ctx, w);
     if (reinterpret_cast<uintptr_t>(d_image) & 31) return tnns_fail(TNNS_ERR_INVALID, "image must be 32-byte aligned");
     return tnns_launch_gemm_im2col(ctx, w, d_image, d_y, g, alpha, layout, (cudaStream_t)stream, pairs);
 }
@@ -403,6 +433,7 @@ static int conv_fused_impl(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const
     if (reinterpret_cast<uintptr_t>(d_workspace) & 127) return tnns_fail(TNNS_ERR_INVALID, "workspace must be 128-byte aligned");
     const size_t need = tnns_fused_workspace_bytes(g.N, g.C, g.H, g.W);
     if (workspace_bytes < need) return tnns_fail(TNNS_ERR_INVALID, "workspace of %zu bytes, need %zu", workspace_bytes, need);
+    TNNS_ENTER(ctx, w);
     TnnsFusedInput f;
     f.d_x = d_x;
     f.d_thr = d_thr;
@@ -445,7 +476,7 @@ int tnns_cuda_gemm_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, co
                               const float* d_thr_next, int next_ternary, int N, int OH, int OW, float alpha, void* stream) {
     if (!ctx || !w || !d_a || !d_image || !d_thr_next) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
     if (N < 0 || OH <= 0 || OW <= 0) return tnns_fail(TNNS_ERR_INVALID, "non-positive output dimension");
-    if (w->device != ctx->device) return tnns_fail(TNNS_ERR_INVALID, "weights live on device %d, context on %d", w->device, ctx->device);
+    TNNS_ENTER(ctx, w);
     if ((reinterpret_cast<uintptr_t>(d_a) & 15) || (reinterpret_cast<uintptr_t>(d_image) & 15))
         return tnns_fail(TNNS_ERR_INVALID, "packed operand and image must be 16-byte aligned");
     if (!w->d_f4 || w->Kp >= 65536) return tnns_fail(TNNS_ERR_UNSUPPORTED, "packed output needs the tensor-core GEMM");
@@ -463,7 +494,7 @@ int tnns_cuda_gemm_im2col_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights
     if (rc) return rc;
     if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW)
         return tnns_fail(TNNS_ERR_INVALID, "shape does not match the uploaded weights");
-    if (w->device != ctx->device) return tnns_fail(TNNS_ERR_INVALID, "weights live on device %d, context on %d", w->device, ctx->device);
+    TNNS_ENTER(ctx, w);
     if ((reinterpret_cast<uintptr_t>(d_image) & 31) || (reinterpret_cast<uintptr_t>(d_image_out) & 15))
         return tnns_fail(TNNS_ERR_INVALID, "input image must be 32-byte, output image 16-byte aligned");
     if (pairs < 0 || pairs > 2) return tnns_fail(TNNS_ERR_INVALID, "pairs must be 0, 1 or 2");
@@ -480,6 +511,7 @@ int tnns_cuda_im2row_packed(tnns_cuda_ctx* ctx, int ternary, const void* d_image
     if (rc) return rc;
     if ((reinterpret_cast<uintptr_t>(d_packed) & 15) || (reinterpret_cast<uintptr_t>(d_image) & 15))
         return tnns_fail(TNNS_ERR_INVALID, "image and packed buffer must be 16-byte aligned");
+    TNNS_ENTER(ctx);
     return tnns_launch_pack(ctx, ternary != 0, reinterpret_cast<const float*>(d_image), reinterpret_cast<const float*>(d_image), d_packed, g,
                             TNNS_SRC_PACKED_IMAGE, TNNS_PACK_AUTO, (cudaStream_t)stream);
 }
@@ -496,6 +528,7 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
                          s->C, s->KH, s->KW, w->KN, w->C, w->KH, w->KW);
     const size_t need = tnns_packed_bytes(w->type, s);
     if (workspace_bytes < need) return tnns_fail(TNNS_ERR_INVALID, "workspace of %zu bytes, need %zu", workspace_bytes, need);
+    TNNS_ENTER(ctx, w);
     if (g.N == 0) return TNNS_OK;
     // Default route: quantise the input once into a packed image (1/16 of the fp32 bytes) and let
     // the 4-bit tensor-core GEMM gather its im2row rows from it, so the KH*KW-times larger im2row
@@ -546,12 +579,12 @@ int tnns_cuda_conv(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* 
     TnnsGeom g;
     int rc = tnns_make_geom(s, &g);
     if (rc) return rc;
+    TNNS_ENTER(ctx, w);
     // room for the im2row matrix (explicit route) and, where the layer qualifies, for the 4-bit
     // image of the copy-engine route, which is larger than the matrix for 1x1 kernels
     size_t need = std::max<size_t>(tnns_packed_bytes(w->type, s), 16);
     if (tnns_im2col_supported(w, g)) need = std::max(need, tnns_fused_workspace_bytes(g.N, g.C, g.H, g.W));
     if (ctx->workspace_bytes < need) {
-        TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
         // earlier launches may still read the old workspace
         TNNS_CUDA_TRY(cudaDeviceSynchronize());
         if (ctx->workspace) cudaFree(ctx->workspace);
@@ -595,8 +628,8 @@ int tnns_cuda_conv_host(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const fl
     if (rc) return rc;
     if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW)
         return tnns_fail(TNNS_ERR_INVALID, "shape does not match the uploaded weights");
+    TNNS_ENTER(ctx, w);
     if (g.N == 0) return TNNS_OK;
-    TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
 
     // (Letting the one-launch kernel work on page-locked host buffers directly -- tensor copies and
     // epilogue stores over PCIe, no staging -- measured slower than the copy engines: 4.2 ms against
@@ -643,31 +676,39 @@ int tnns_cuda_conv_host(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const fl
         if (taper) { plan.push_back(nb - quarter); plan.push_back(quarter); }
     }
 
-    TNNS_CUDA_TRY(cudaMemcpyAsync(ctx->stage_thr, h_thr, (size_t)g.N * sizeof(float), cudaMemcpyHostToDevice, ctx->s_copy_in));
+    // Every failure inside the loop leaves through one exit that drains the three streams first:
+    // copies and kernels of earlier slices are still queued, and the caller may free h_x / h_y (the
+    // drop-in tnns_conv frees its output buffer) as soon as this function returns.
+    cudaError_t e = cudaMemcpyAsync(ctx->stage_thr, h_thr, (size_t)g.N * sizeof(float), cudaMemcpyHostToDevice, ctx->s_copy_in);
+    rc = TNNS_OK;
     int n0 = 0;
-    for (int k = 0; k < (int)plan.size(); n0 += plan[k], k++) {
+    for (int k = 0; k < (int)plan.size() && e == cudaSuccess && rc == TNNS_OK; n0 += plan[k], k++) {
         const int slot = k & 1;
         const int cnt = plan[k];
         ss.N = cnt;
-        if (k >= 2) TNNS_CUDA_TRY(cudaStreamWaitEvent(ctx->s_copy_in, ctx->ev_done[slot], 0));  // kernels of slice k-2 done with stage_in
-        TNNS_CUDA_TRY(cudaMemcpyAsync(ctx->stage_in[slot], (const char*)h_x + (size_t)n0 * in_img, in_img * cnt, cudaMemcpyHostToDevice,
-                                      ctx->s_copy_in));
-        TNNS_CUDA_TRY(cudaEventRecord(ctx->ev_in[slot], ctx->s_copy_in));
-        TNNS_CUDA_TRY(cudaStreamWaitEvent(ctx->s_compute, ctx->ev_in[slot], 0));
-        if (k >= 2) TNNS_CUDA_TRY(cudaStreamWaitEvent(ctx->s_compute, ctx->ev_out[slot], 0));  // download of slice k-2 done with stage_out
+        if (k >= 2) e = cudaStreamWaitEvent(ctx->s_copy_in, ctx->ev_done[slot], 0);  // kernels of slice k-2 done with stage_in
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync(ctx->stage_in[slot], (const char*)h_x + (size_t)n0 * in_img, in_img * cnt, cudaMemcpyHostToDevice, ctx->s_copy_in);
+        if (e == cudaSuccess) e = cudaEventRecord(ctx->ev_in[slot], ctx->s_copy_in);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->s_compute, ctx->ev_in[slot], 0);
+        if (e == cudaSuccess && k >= 2) e = cudaStreamWaitEvent(ctx->s_compute, ctx->ev_out[slot], 0);  // download of slice k-2 done with stage_out
+        if (e != cudaSuccess) break;
         rc = tnns_cuda_conv_ws(ctx, w, (const float*)ctx->stage_in[slot], ctx->stage_thr + n0, (float*)ctx->stage_out[slot],
                                ctx->stage_pack[slot], ctx->stage_pack_bytes, &ss, alpha, layout, TNNS_PACK_AUTO, TNNS_GEMM_AUTO,
                                ctx->s_compute);
-        if (rc) { cudaDeviceSynchronize(); return rc; }
-        TNNS_CUDA_TRY(cudaEventRecord(ctx->ev_done[slot], ctx->s_compute));
-        TNNS_CUDA_TRY(cudaStreamWaitEvent(ctx->s_copy_out, ctx->ev_done[slot], 0));
-        TNNS_CUDA_TRY(cudaMemcpyAsync((char*)h_y + (size_t)n0 * out_img, ctx->stage_out[slot], out_img * cnt, cudaMemcpyDeviceToHost,
-                                      ctx->s_copy_out));
-        TNNS_CUDA_TRY(cudaEventRecord(ctx->ev_out[slot], ctx->s_copy_out));
+        if (rc) break;
+        e = cudaEventRecord(ctx->ev_done[slot], ctx->s_compute);
+        if (e == cudaSuccess) e = cudaStreamWaitEvent(ctx->s_copy_out, ctx->ev_done[slot], 0);
+        if (e == cudaSuccess)
+            e = cudaMemcpyAsync((char*)h_y + (size_t)n0 * out_img, ctx->stage_out[slot], out_img * cnt, cudaMemcpyDeviceToHost, ctx->s_copy_out);
+        if (e == cudaSuccess) e = cudaEventRecord(ctx->ev_out[slot], ctx->s_copy_out);
     }
-    TNNS_CUDA_TRY(cudaStreamSynchronize(ctx->s_copy_out));
-    TNNS_CUDA_TRY(cudaStreamSynchronize(ctx->s_compute));
-    TNNS_CUDA_TRY(cudaStreamSynchronize(ctx->s_copy_in));
+    const cudaError_t s0 = cudaStreamSynchronize(ctx->s_copy_out), s1 = cudaStreamSynchronize(ctx->s_compute),
+                      s2 = cudaStreamSynchronize(ctx->s_copy_in);
+    if (rc) return rc;  // tnns_cuda_conv_ws recorded its own error
+    if (e == cudaSuccess) e = s0 != cudaSuccess ? s0 : (s1 != cudaSuccess ? s1 : s2);
+    if (e != cudaSuccess)
+        return tnns_fail(e == cudaErrorMemoryAllocation ? TNNS_ERR_NOMEM : TNNS_ERR_CUDA, "host-buffer layer failed: %s", cudaGetErrorString(e));
     return TNNS_OK;
 }
 

@@ -7,8 +7,13 @@
 // packed im2row matrix -- the one piece of scratch memory a layer needs between its two
 // kernels -- lives in the fixed array below instead of a cudaMalloc'd workspace.
 //
-// Cost: every GPU whose context loads this library keeps TNNS_NOALLOC_SCRATCH_BYTES of
-// device memory reserved until the process exits, whether or not the entry point is used.
+// Cost: a GPU keeps TNNS_NOALLOC_SCRATCH_BYTES of device memory reserved from the moment the
+// part of the library that holds the array is loaded on it until the process exits.  With CUDA's
+// default lazy module loading that moment is the FIRST call of the entry point on the device (the
+// address look-up below loads the module); with CUDA_MODULE_LOADING=EAGER it is the creation of
+// the CUDA context.  Either way a host that hands all device memory to its own arena must make
+// one call -- an empty batch (N = 0) is enough -- BEFORE the arena takes the memory; afterwards
+// the array could no longer be placed and the call reports TNNS_ERR_NOMEM.
 #include <mutex>
 
 #include "internal.h"
@@ -41,6 +46,14 @@ int setup_device(int device, DeviceState** out) {
     if (!st.ready) {
         void* ptr = nullptr;
         cudaError_t e = cudaGetSymbolAddress(&ptr, g_noalloc_scratch);
+        if (e == cudaErrorMemoryAllocation) {
+            // loading the array's module needs TNNS_NOALLOC_SCRATCH_BYTES of free device memory
+            cudaGetLastError();
+            return tnns_fail(TNNS_ERR_NOMEM,
+                             "device %d has no room left for the %zu-byte scratch array: make the first call (an empty batch is "
+                             "enough) before other allocators take the device's memory, or set CUDA_MODULE_LOADING=EAGER",
+                             device, (size_t)TNNS_NOALLOC_SCRATCH_BYTES);
+        }
         if (e != cudaSuccess || !ptr)
             return tnns_fail(TNNS_ERR_CUDA, "cudaGetSymbolAddress(scratch) failed on device %d: %s", device, cudaGetErrorString(e));
         int sms = 0, smem = 0, major = 0;
@@ -77,13 +90,14 @@ extern "C" int tnns_cuda_conv_noalloc(int type, const int64_t* d_packed_weights,
                          "packed im2row matrix needs %zu bytes but the built-in scratch holds %zu: split the batch into smaller "
                          "calls or use tnns_cuda_conv_ws with your own workspace",
                          need, (size_t)TNNS_NOALLOC_SCRATCH_BYTES);
-    if (g.N == 0) return TNNS_OK;
-
     int device = 0;
     TNNS_CUDA_TRY(cudaGetDevice(&device));
     if (device < 0 || device >= kMaxDevices) return tnns_fail(TNNS_ERR_UNSUPPORTED, "device index %d beyond %d", device, kMaxDevices);
+    // before the empty-batch return: a start-up call with N = 0 is how a host resolves (and thereby
+    // reserves) the scratch array on this device while memory is still free
     DeviceState* st = nullptr;
     if ((rc = setup_device(device, &st))) return rc;
+    if (g.N == 0) return TNNS_OK;
 
     // The launchers only read these three fields of a context; nothing here owns memory.
     tnns_cuda_ctx view = {};

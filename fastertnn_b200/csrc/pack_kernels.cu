@@ -357,7 +357,11 @@ int launch_staged(tnns_cuda_ctx* ctx, const float* d_x, const float* d_thr, void
     const int LV = std::max(Lmax / VEC, 1);
     const bool pair = (g.Cp % 2) == 0;
     auto launch = [&](auto kern) -> int {
-        if (smem > 48 * 1024) TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
+        // the attribute belongs to (function, device), not to a context: every caller sets the same
+        // value, the device's opt-in maximum, so host threads packing layers of different band
+        // sizes cannot lower each other's limit between this call and the launch
+        if (smem > 48 * 1024)
+            TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)std::max(smem, ctx->smem_optin)));
         kern<<<g.N * nbands, kPackThreads, smem, stream>>>(d_x, d_thr, reinterpret_cast<uint4*>(d_packed), g, BOH, nbands, Lmax,
                                                            tnns_fastdiv(UP), tnns_fastdiv(g.OW), tnns_fastdiv(LV));
         tnns_count_launch();

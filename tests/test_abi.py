@@ -19,6 +19,7 @@ def declared_functions():
     text = (ROOT / "include" / "tnns_b200.h").read_text()
     text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
     text = re.sub(r"^\s*#.*$", "", text, flags=re.M)  # preprocessor lines declare no functions
+    text = re.sub(r"typedef[^;]*\(\s*\*[^;]*;", "", text)  # function-pointer typedefs declare no functions
     names = re.findall(r"\b([A-Za-z_][A-Za-z0-9_]*)\s*\([^;{}]*\)\s*;", text)
     return sorted(set(n for n in names if n not in ("defined",)))
 
