@@ -24,12 +24,22 @@ from .workloads import Layer
 
 
 class ConvStack:
+    """reinterpret_links: the reference's driver hands every layer's output BUFFER to the next layer
+    and reads it with the next layer's shape; in its model tables a few consecutive shapes do not
+    chain (a pooling step the tables leave out), and the next layer then reads the first
+    N*C*H*W floats of the larger buffer.  With reinterpret_links=True such links are accepted and
+    behave exactly so (the link goes through fp32; chain="image" starts a new run of 4-bit images
+    behind it); otherwise they are an error."""
+
     def __init__(self, ctx: api.Context, type_: int, layers: list[Layer], packed_weights: list[np.ndarray], batch: int,
-                 threshold: float, alpha: float = 0.5, layout: int = api.NCHW, chain: str = "fp32"):
+                 threshold: float, alpha: float = 0.5, layout: int = api.NCHW, chain: str = "fp32", reinterpret_links: bool = False):
         assert len(layers) == len(packed_weights)
+        self.link_ok = []
         for a, b in zip(layers, layers[1:]):
-            if (a.KN, a.OH, a.OW) != (b.C, b.H, b.W):
+            ok = (a.KN, a.OH, a.OW) == (b.C, b.H, b.W)
+            if not ok and not (reinterpret_links and b.C * b.H * b.W <= a.KN * a.OH * a.OW and chain in ("fp32", "image")):
                 raise ValueError(f"layer output {a.KN}x{a.OH}x{a.OW} does not feed {b.C}x{b.H}x{b.W}")
+            self.link_ok.append(ok)
         self.ctx, self.type, self.layers, self.batch, self.alpha, self.layout = ctx, type_, layers, batch, alpha, layout
         self.weights = [ctx.upload_weights(type_, pw, L.C, L.KH, L.KW) for L, pw in zip(layers, packed_weights)]
         sizes = [batch * layers[0].C * layers[0].H * layers[0].W] + [batch * L.KN * L.OH * L.OW for L in layers]
@@ -40,6 +50,7 @@ class ConvStack:
         self.chain = chain
         self.act_ternary = type_ in (api.TNN, api.TBN)
         self.extra = []
+        self._out = self.buf[len(layers) % 2]
         if chain == "packed":
             if layout != api.NCHW:
                 raise ValueError("the packed chain is defined for NCHW input and output")
@@ -48,28 +59,34 @@ class ConvStack:
             self.d_img = ctx.malloc(img)
             self.d_a = ctx.malloc(a)
             self.extra = [self.d_img, self.d_a]
+            self._out = self.buf[1]
         elif chain == "image":
             if layout != api.NCHW:
                 raise ValueError("the image chain is defined for NCHW input and output")
             if not self.act_ternary:
                 raise ValueError("4-bit operand images hold ternary activations")
             self.fast = [ctx.im2col_supported(w, L.shape(batch)) for w, L in zip(self.weights, layers)]
-            img = max([api.e2m1_image_bytes(batch, layers[0].C, layers[0].H, layers[0].W)] +
-                      [api.e2m1_image_bytes(batch, L.KN, L.OH, L.OW) for L in layers])
+            img = max([max(api.e2m1_image_bytes(batch, L.C, L.H, L.W), api.e2m1_image_bytes(batch, L.KN, L.OH, L.OW)) for L in layers])
             self.d_imgs = [ctx.malloc(img), ctx.malloc(img)]  # ping-pong quantised activations (either format fits)
             self.extra = list(self.d_imgs)
-            # first layer in one launch (quantise step inside the GEMM kernel) where the library itself
+            # a layer that starts a run (the first layer, and every layer behind a reinterpreted link)
+            # reads fp32: in one launch (quantise step inside the GEMM kernel) where the library itself
             # would choose that route; its workspace holds the input's 4-bit image
-            L0 = layers[0]
-            self.fuse_first = bool(self.fast[0]) and ctx.conv_fused_preferred(self.weights[0], L0.shape(batch), self.buf[0], layout)
-            self.ws0_bytes = api.fused_workspace_bytes(batch, L0.C, L0.H, L0.W)
-            if self.fuse_first:
+            n = len(layers)
+            self.run_first = [i == 0 or not self.link_ok[i - 1] for i in range(n)]
+            self.run_last = [i == n - 1 or not self.link_ok[i] for i in range(n)]
+            self.fuse = [bool(self.run_first[i] and self.fast[i] and ctx.conv_fused_preferred(self.weights[i], layers[i].shape(batch), self.buf[0], layout))
+                         for i in range(n)]
+            self.fuse_first = self.fuse[0]
+            self.ws0_bytes = max([api.fused_workspace_bytes(batch, L.C, L.H, L.W) for L, f in zip(layers, self.fuse) if f] + [0])
+            if self.ws0_bytes:
                 self.d_ws0 = ctx.malloc(self.ws0_bytes)
                 self.extra.append(self.d_ws0)
             self.d_a = None
             if not all(self.fast):
                 self.d_a = ctx.malloc(max(api.packed_bytes(type_, L.shape(batch)) for L, f in zip(layers, self.fast) if not f))
                 self.extra.append(self.d_a)
+            self._out = self.buf[sum(self.run_last) % 2]
         elif chain != "fp32":
             raise ValueError(chain)
 
@@ -77,7 +94,7 @@ class ConvStack:
         return self.buf[0]
 
     def output_ptr(self) -> int:
-        return self.buf[1] if self.chain in ("packed", "image") else self.buf[len(self.layers) % 2]
+        return self._out
 
     def run(self, stream: int = 0):
         """Enqueue all layers; input must already be in input_ptr()."""
@@ -96,36 +113,38 @@ class ConvStack:
                     self.ctx.gemm(w, self.d_a, self.buf[1], self.batch, L.OH, L.OW, self.alpha, self.layout, stream=stream)
             return
         if self.chain == "image":
-            last = len(self.layers) - 1
-            L0 = self.layers[0]
-            # the input, in the format the first layer reads
-            if self.fuse_first:
-                pass
-            elif self.fast[0]:
-                self.ctx.quantise_e2m1(self.buf[0], self.d_thr, self.d_imgs[0], self.batch, L0.C, L0.H, L0.W, self.layout, stream)
-            else:
-                self.ctx.quantise(True, self.buf[0], self.d_thr, self.d_imgs[0], self.batch, L0.C, L0.H, L0.W, self.layout, stream)
+            fp, k = self.buf[0], 0  # fp32 tensor the current run of layers starts from; runs finished so far
             for i, (L, w) in enumerate(zip(self.layers, self.weights)):
                 shape = L.shape(self.batch)
                 src, dst = self.d_imgs[i % 2], self.d_imgs[(i + 1) % 2]
-                nxt = 2 if (i < last and self.fast[i + 1]) else 1  # 4-bit image or ternary bit planes for the consumer
-                if i == 0 and self.fuse_first:
-                    if i < last:
-                        self.ctx.conv_fused_packed_out(w, self.buf[0], self.d_thr, dst, self.d_thr, nxt, self.d_ws0, self.ws0_bytes, shape,
+                last = self.run_last[i]
+                out_fp = self.buf[(k + 1) % 2]
+                nxt = 2 if (not last and self.fast[i + 1]) else 1  # 4-bit image or ternary bit planes for the consumer
+                if self.run_first[i] and not self.fuse[i]:
+                    # the run's input, in the format its first layer reads
+                    if self.fast[i]:
+                        self.ctx.quantise_e2m1(fp, self.d_thr, src, self.batch, L.C, L.H, L.W, self.layout, stream)
+                    else:
+                        self.ctx.quantise(True, fp, self.d_thr, src, self.batch, L.C, L.H, L.W, self.layout, stream)
+                if self.fuse[i]:
+                    if not last:
+                        self.ctx.conv_fused_packed_out(w, fp, self.d_thr, dst, self.d_thr, nxt, self.d_ws0, self.ws0_bytes, shape,
                                                        self.alpha, 0, stream)
                     else:
-                        self.ctx.conv_fused(w, self.buf[0], self.d_thr, self.buf[1], self.d_ws0, self.ws0_bytes, shape, self.alpha, 0, stream)
+                        self.ctx.conv_fused(w, fp, self.d_thr, out_fp, self.d_ws0, self.ws0_bytes, shape, self.alpha, 0, stream)
                 elif self.fast[i]:
-                    if i < last:
+                    if not last:
                         self.ctx.gemm_im2col_packed_out(w, src, dst, self.d_thr, nxt, shape, self.alpha, stream)
                     else:
-                        self.ctx.gemm_im2col(w, src, self.buf[1], shape, self.alpha, self.layout, stream)
+                        self.ctx.gemm_im2col(w, src, out_fp, shape, self.alpha, self.layout, stream)
                 else:
                     self.ctx.im2row_packed(True, src, self.d_a, shape, stream=stream)
-                    if i < last:
+                    if not last:
                         self.ctx.gemm_packed_out(w, self.d_a, dst, self.d_thr, nxt, self.batch, L.OH, L.OW, self.alpha, stream=stream)
                     else:
-                        self.ctx.gemm(w, self.d_a, self.buf[1], self.batch, L.OH, L.OW, self.alpha, self.layout, stream=stream)
+                        self.ctx.gemm(w, self.d_a, out_fp, self.batch, L.OH, L.OW, self.alpha, self.layout, stream=stream)
+                if last:
+                    fp, k = out_fp, k + 1
             return
         for i, (L, w) in enumerate(zip(self.layers, self.weights)):
             self.ctx.conv(w, self.buf[i % 2], self.d_thr, self.buf[(i + 1) % 2], L.shape(self.batch), self.alpha, self.layout,

@@ -8,6 +8,9 @@ from __future__ import annotations
 
 from dataclasses import dataclass
 
+import json
+from pathlib import Path
+
 from ._lib import Shape
 
 
@@ -71,3 +74,27 @@ RESNET18_STACK = [
     Layer(256, 14, 14, 512, 3, 3, 1, 2),
     Layer(512, 7, 7, 512, 3, 3, 1, 1), Layer(512, 7, 7, 512, 3, 3, 1, 1),
 ]
+
+
+# Layer tables of the reference's end-to-end timing mode (its include/timing/shapes_e2e.h: ResNet18/34/152,
+# VGG16/19, DarkNet19/53), kept as numbers in model_tables.json; batch 8 there (src/timing_layers.c:46).
+_MODEL_TABLES = None
+
+
+def model_tables() -> dict:
+    global _MODEL_TABLES
+    if _MODEL_TABLES is None:
+        _MODEL_TABLES = json.loads((Path(__file__).resolve().parent / "model_tables.json").read_text())
+    return _MODEL_TABLES
+
+
+def model_names() -> list[str]:
+    return sorted(model_tables()["models"])
+
+
+def model_layers(name: str) -> list[Layer]:
+    """The layers of one of the reference's model tables, in the order its driver runs them."""
+    return [Layer(*row) for row in model_tables()["models"][name]]
+
+
+REFERENCE_MODEL_BATCH = 8

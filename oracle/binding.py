@@ -23,9 +23,21 @@ _vp, _i, _f = C.c_void_p, C.c_int, C.c_float
 TNN, TBN, BTN, BNN = 0, 1, 2, 3
 
 
-def build():
+def reference_checkout() -> str:
+    """Where the reference's sources lie: the environment variable TNNS_REFERENCE_DIR, else a
+    checkout named ``reference`` beside this repository; empty when there is none."""
+    import os
+    env = os.environ.get("TNNS_REFERENCE_DIR")
+    if env:
+        return env
+    cand = HERE.parent.parent / "reference"
+    return str(cand) if (cand / "src" / "tnns" / "tnns_cpu_mm_p2.c").exists() else ""
+
+
+def build(reference: str | None = None):
     """(Re)build the checkers; the _ref targets are skipped when the reference sources are absent."""
-    subprocess.run(["make", "-s", "-C", str(HERE)], check=True)
+    ref = reference_checkout() if reference is None else reference
+    subprocess.run(["make", "-s", "-C", str(HERE), f"REF={ref}"], check=True)
 
 
 def _f32(a):
