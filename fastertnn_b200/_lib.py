@@ -111,6 +111,15 @@ SIGNATURES = {
     "tnns_cuda_quantise_e2m1": (_i, [_vp, _vp, _vp, _vp, _i, _i, _i, _i, _i, _vp]),
     "tnns_cuda_gemm_im2col": (_i, [_vp, _vp, _vp, _vp, _vp, C.c_float, _i, _i, _vp]),
     "tnns_fused_workspace_bytes": (_sz, [_i, _i, _i, _i]),
+    "tnns_e2m1_bordered_image_bytes": (_sz, [_i] * 6),
+    "tnns_slab_workspace_bytes": (_sz, [_i] * 6),
+    "tnns_cuda_slab_supported": (_i, [_vp, _vp, _vp]),
+    "tnns_cuda_conv_slab_supported": (_i, [_vp, _vp, _vp, _vp, _i]),
+    "tnns_cuda_quantise_e2m1_bordered": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
+    "tnns_cuda_gemm_slab": (_i, [_vp, _vp, _vp, _vp, _pshape, C.c_float, _i, _i, _vp]),
+    "tnns_cuda_gemm_slab_packed_out": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _pshape, C.c_float, _i, _vp]),
+    "tnns_cuda_conv_slab": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _pshape, C.c_float, _i, _vp]),
+    "tnns_cuda_conv_slab_packed_out": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _pshape, C.c_float, _i, _vp]),
     "tnns_cuda_conv_fused_supported": (_i, [_vp, _vp, _vp, _i]),
     "tnns_cuda_conv_fused_preferred": (_i, [_vp, _vp, _vp, _vp, _i]),
     "tnns_cuda_conv_fused_packed_out": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _sz, _pshape, C.c_float, _i, _vp]),

@@ -17,7 +17,7 @@ from ._lib import GemmTestcase, Shape, Testcase, load_library
 TNN, TBN, BTN, BNN = 0, 1, 2, 3
 NCHW, NHWC = 0, 1
 PACK_AUTO, PACK_GATHER, PACK_STAGED = 0, 1, 2
-GEMM_AUTO, GEMM_POPC_SIMPLE, GEMM_POPC_TILED, GEMM_I8_TC, GEMM_F4_TC, GEMM_F4_FUSED = 0, 1, 2, 3, 4, 5
+GEMM_AUTO, GEMM_POPC_SIMPLE, GEMM_POPC_TILED, GEMM_I8_TC, GEMM_F4_TC, GEMM_F4_FUSED, GEMM_F4_SLAB, GEMM_F4_SLAB_FUSED = 0, 1, 2, 3, 4, 5, 6, 7
 
 
 class TnnsError(RuntimeError):
@@ -327,6 +327,38 @@ class Context:
         _check(self.lib.tnns_cuda_gemm_im2col_packed_out(self.handle, w.handle, d_image, d_image_out, d_thr_next, next_format,
                                                          C.byref(shape), alpha, pairs, stream))
 
+    # -- stride-1 layers from a bordered 4-bit image (slab-fed GEMM)
+    def slab_supported(self, w: Weights, shape: Shape) -> bool:
+        return bool(self.lib.tnns_cuda_slab_supported(self.handle, w.handle, C.byref(shape)))
+
+    def conv_slab_supported(self, w: Weights, shape: Shape, d_x: int, layout=NCHW) -> bool:
+        return bool(self.lib.tnns_cuda_conv_slab_supported(self.handle, w.handle, C.byref(shape), d_x, layout))
+
+    def quantise_e2m1_bordered(self, ternary: bool, d_x: int, d_thr: int, d_image: int, N: int, C_: int, H: int, W: int, PH: int, PW: int,
+                               layout=NCHW, stream=0):
+        """fp32 NCHW tensor -> 4-bit operand image with the layer's padding stored around every image."""
+        _check(self.lib.tnns_cuda_quantise_e2m1_bordered(self.handle, int(ternary), d_x, d_thr, d_image, N, C_, H, W, PH, PW, layout, stream))
+
+    def gemm_slab(self, w: Weights, d_image: int, d_y: int, shape: Shape, alpha: float, layout=NCHW, stream=0, pairs=0):
+        """GEMM + PReLU from a bordered 4-bit image: one slab of pixels per tile serves every filter tap."""
+        _check(self.lib.tnns_cuda_gemm_slab(self.handle, w.handle, d_image, d_y, C.byref(shape), alpha, layout, pairs, stream))
+
+    def gemm_slab_packed_out(self, w: Weights, d_image: int, d_image_out: int, d_thr_next: int, next_format: int, next_pad, shape: Shape,
+                             alpha: float, stream=0, pairs=0):
+        """next_format: 0 / 1 bit planes (binary / ternary), 2 plain 4-bit image, 3 / 5 bordered 4-bit image for a
+        ternary / binary next layer with padding next_pad = (PH, PW)."""
+        _check(self.lib.tnns_cuda_gemm_slab_packed_out(self.handle, w.handle, d_image, d_image_out, d_thr_next, next_format, next_pad[0],
+                                                       next_pad[1], C.byref(shape), alpha, pairs, stream))
+
+    def conv_slab(self, w: Weights, d_x: int, d_thr: int, d_y: int, d_ws: int, ws_bytes: int, shape: Shape, alpha: float, pairs=0, stream=0):
+        """Whole stride-1 layer in ONE launch: quantiser warps write the bordered image beside the slab-fed GEMM."""
+        _check(self.lib.tnns_cuda_conv_slab(self.handle, w.handle, d_x, d_thr, d_y, d_ws, ws_bytes, C.byref(shape), alpha, pairs, stream))
+
+    def conv_slab_packed_out(self, w: Weights, d_x: int, d_thr: int, d_image_out: int, d_thr_next: int, next_format: int, next_pad, d_ws: int,
+                             ws_bytes: int, shape: Shape, alpha: float, pairs=0, stream=0):
+        _check(self.lib.tnns_cuda_conv_slab_packed_out(self.handle, w.handle, d_x, d_thr, d_image_out, d_thr_next, next_format, next_pad[0],
+                                                       next_pad[1], d_ws, ws_bytes, C.byref(shape), alpha, pairs, stream))
+
     def im2col_supported(self, w: Weights, shape: Shape) -> bool:
         return bool(self.lib.tnns_cuda_im2col_supported(w.handle, C.byref(shape)))
 
@@ -476,6 +508,14 @@ def packed_image_bytes(ternary: bool, N: int, C_: int, H: int, W: int) -> int:
 
 def fused_workspace_bytes(N: int, C_: int, H: int, W: int) -> int:
     return int(load_library().tnns_fused_workspace_bytes(N, C_, H, W))
+
+
+def bordered_image_bytes(N: int, C_: int, H: int, W: int, PH: int, PW: int) -> int:
+    return int(load_library().tnns_e2m1_bordered_image_bytes(N, C_, H, W, PH, PW))
+
+
+def slab_workspace_bytes(N: int, C_: int, H: int, W: int, PH: int, PW: int) -> int:
+    return int(load_library().tnns_slab_workspace_bytes(N, C_, H, W, PH, PW))
 
 
 def e2m1_image_bytes(N: int, C_: int, H: int, W: int) -> int:

@@ -404,6 +404,128 @@ int tnns_cuda_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const 
     return tnns_launch_gemm_im2col(ctx, w, d_image, d_y, g, alpha, layout, (cudaStream_t)stream, pairs);
 }
 
+// --- bordered 4-bit images and the slab-fed GEMM (stride-1 layers) ----------------------------------
+size_t tnns_e2m1_bordered_image_bytes(int N, int C, int H, int W, int PH, int PW) { return tnns_bordered_image_bytes(N, C, H, W, PH, PW); }
+
+static inline size_t slab_image_bytes(int N, int C, int H, int W, int PH, int PW) {
+    return (tnns_bordered_image_bytes(N, C, H, W, PH, PW) + 127) & ~(size_t)127;
+}
+size_t tnns_slab_workspace_bytes(int N, int C, int H, int W, int PH, int PW) {
+    if (N < 0 || C <= 0 || H <= 0 || W <= 0 || PH < 0 || PW < 0) return 0;
+    return slab_image_bytes(N, C, H, W, PH, PW) + tnns_fused_sync_bytes(N);
+}
+
+int tnns_cuda_quantise_e2m1_bordered(tnns_cuda_ctx* ctx, int ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
+                                     int W, int PH, int PW, int layout, void* stream) {
+    if (!ctx || !d_x || !d_thr || !d_image) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    if (N < 0 || C <= 0 || H <= 0 || W <= 0 || PH < 0 || PW < 0) return tnns_fail(TNNS_ERR_INVALID, "non-positive dimension");
+    if (reinterpret_cast<uintptr_t>(d_image) & 127) return tnns_fail(TNNS_ERR_INVALID, "bordered image must be 128-byte aligned");
+    if (!tnns_quantise_tma_supported(d_x, H, W, layout))
+        return tnns_fail(TNNS_ERR_UNSUPPORTED, "the bordered image is written from NCHW input with H*W a multiple of four (at least 32) and a 16-byte aligned base");
+    TNNS_ENTER(ctx);
+    return tnns_launch_quantise_tma(ctx, ternary != 0, d_x, d_thr, d_image, N, C, H, W, (cudaStream_t)stream, TNNS_IMG_E2M1, PH, PW);
+}
+
+static int slab_geom(const tnns_cuda_weights* w, const tnns_shape_t* s, TnnsGeom* g) {
+    int rc = tnns_make_geom(s, g);
+    if (rc) return rc;
+    if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW)
+        return tnns_fail(TNNS_ERR_INVALID, "shape does not match the uploaded weights");
+    return TNNS_OK;
+}
+
+int tnns_cuda_slab_supported(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s) {
+    TnnsGeom g;
+    if (!ctx || !w || !s || tnns_make_geom(s, &g)) return 0;
+    if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW) return 0;
+    return tnns_slab_supported(ctx, w, g, false) ? 1 : 0;
+}
+
+// next_format of the public slab entry points -> (format, binary) of the launcher
+static int slab_next(int next_format, int* fmt, int* binary) {
+    switch (next_format) {
+        case 0: *fmt = 0; *binary = 1; return TNNS_OK;
+        case 1: *fmt = 1; *binary = 0; return TNNS_OK;
+        case 2: *fmt = 2; *binary = 0; return TNNS_OK;
+        case 3: *fmt = 3; *binary = 0; return TNNS_OK;
+        case 5: *fmt = 3; *binary = 1; return TNNS_OK;
+        default: return tnns_fail(TNNS_ERR_INVALID, "output format must be 0, 1, 2, 3 or 5");
+    }
+}
+
+int tnns_cuda_gemm_slab(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const tnns_shape_t* s, float alpha,
+                        int layout, int pairs, void* stream) {
+    if (!ctx || !w || !d_image || !d_y) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    if (pairs < 0 || pairs > 2) return tnns_fail(TNNS_ERR_INVALID, "pairs must be 0, 1 or 2");
+    if (layout != TNNS_NCHW && layout != TNNS_NHWC) return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
+    TnnsGeom g;
+    int rc = slab_geom(w, s, &g);
+    if (rc) return rc;
+    TNNS_ENTER(ctx, w);
+    return tnns_launch_gemm_slab(ctx, w, d_image, d_y, g, alpha, layout, (cudaStream_t)stream, pairs);
+}
+
+int tnns_cuda_gemm_slab_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, void* d_image_out, const float* d_thr_next,
+                                   int next_format, int next_PH, int next_PW, const tnns_shape_t* s, float alpha, int pairs, void* stream) {
+    if (!ctx || !w || !d_image || !d_image_out || !d_thr_next) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    if (pairs < 0 || pairs > 2) return tnns_fail(TNNS_ERR_INVALID, "pairs must be 0, 1 or 2");
+    if (reinterpret_cast<uintptr_t>(d_image_out) & 15) return tnns_fail(TNNS_ERR_INVALID, "output image must be 16-byte aligned");
+    int fmt, bin;
+    int rc = slab_next(next_format, &fmt, &bin);
+    if (rc) return rc;
+    TnnsGeom g;
+    if ((rc = slab_geom(w, s, &g))) return rc;
+    TNNS_ENTER(ctx, w);
+    return tnns_launch_gemm_slab(ctx, w, d_image, nullptr, g, alpha, TNNS_NCHW, (cudaStream_t)stream, pairs, d_image_out, d_thr_next, fmt, bin,
+                                 next_PH, next_PW);
+}
+
+static int conv_slab_impl(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y, void* d_image_out,
+                          const float* d_thr_next, int fmt, int bin, int next_PH, int next_PW, void* d_workspace, size_t workspace_bytes,
+                          const tnns_shape_t* s, float alpha, int pairs, void* stream) {
+    if (!ctx || !w || !d_x || !d_thr || !d_workspace) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    if (pairs < 0 || pairs > 2) return tnns_fail(TNNS_ERR_INVALID, "pairs must be 0, 1 or 2");
+    TnnsGeom g;
+    int rc = slab_geom(w, s, &g);
+    if (rc) return rc;
+    if (g.N == 0) return TNNS_OK;
+    if (reinterpret_cast<uintptr_t>(d_workspace) & 127) return tnns_fail(TNNS_ERR_INVALID, "workspace must be 128-byte aligned");
+    const size_t need = tnns_slab_workspace_bytes(g.N, g.C, g.H, g.W, g.PH, g.PW);
+    if (workspace_bytes < need) return tnns_fail(TNNS_ERR_INVALID, "workspace of %zu bytes, need %zu", workspace_bytes, need);
+    TNNS_ENTER(ctx, w);
+    TnnsFusedInput f;
+    f.d_x = d_x;
+    f.d_thr = d_thr;
+    f.d_sync = reinterpret_cast<unsigned int*>(static_cast<char*>(d_workspace) + slab_image_bytes(g.N, g.C, g.H, g.W, g.PH, g.PW));
+    return tnns_launch_gemm_slab(ctx, w, d_workspace, d_y, g, alpha, TNNS_NCHW, (cudaStream_t)stream, pairs, d_image_out, d_thr_next, fmt, bin, next_PH,
+                                 next_PW, &f);
+}
+
+int tnns_cuda_conv_slab(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y, void* d_workspace,
+                        size_t workspace_bytes, const tnns_shape_t* s, float alpha, int pairs, void* stream) {
+    if (!d_y) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    return conv_slab_impl(ctx, w, d_x, d_thr, d_y, nullptr, nullptr, 2, 0, 0, 0, d_workspace, workspace_bytes, s, alpha, pairs, stream);
+}
+
+int tnns_cuda_conv_slab_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, void* d_image_out,
+                                   const float* d_thr_next, int next_format, int next_PH, int next_PW, void* d_workspace, size_t workspace_bytes,
+                                   const tnns_shape_t* s, float alpha, int pairs, void* stream) {
+    if (!d_image_out || !d_thr_next) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    if (reinterpret_cast<uintptr_t>(d_image_out) & 15) return tnns_fail(TNNS_ERR_INVALID, "output image must be 16-byte aligned");
+    int fmt, bin;
+    int rc = slab_next(next_format, &fmt, &bin);
+    if (rc) return rc;
+    return conv_slab_impl(ctx, w, d_x, d_thr, nullptr, d_image_out, d_thr_next, fmt, bin, next_PH, next_PW, d_workspace, workspace_bytes, s, alpha, pairs,
+                          stream);
+}
+
+int tnns_cuda_conv_slab_supported(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout) {
+    TnnsGeom g;
+    if (!ctx || !w || !s || tnns_make_geom(s, &g)) return 0;
+    if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW) return 0;
+    return (tnns_slab_supported(ctx, w, g, true) && tnns_quantise_tma_supported(d_x, g.H, g.W, layout)) ? 1 : 0;
+}
+
 // --- chained layers without the fp32 round trip ------------------------------------------------
 static inline size_t fused_image_bytes(int N, int C, int H, int W) { return (tnns_e2m1_image_bytes(N, C, H, W) + 127) & ~(size_t)127; }
 
@@ -530,6 +652,20 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
     if (workspace_bytes < need) return tnns_fail(TNNS_ERR_INVALID, "workspace of %zu bytes, need %zu", workspace_bytes, need);
     TNNS_ENTER(ctx, w);
     if (g.N == 0) return TNNS_OK;
+    if (gemm_algo == TNNS_GEMM_F4_SLAB || gemm_algo == TNNS_GEMM_F4_SLAB_FUSED) {
+        // stride-1 layers from a bordered 4-bit image: one slab of pixels per tile serves every filter tap
+        const bool one_launch = gemm_algo == TNNS_GEMM_F4_SLAB_FUSED;
+        const size_t ws_need = one_launch ? tnns_slab_workspace_bytes(g.N, g.C, g.H, g.W, g.PH, g.PW)
+                                          : tnns_bordered_image_bytes(g.N, g.C, g.H, g.W, g.PH, g.PW);
+        if (pack_algo != TNNS_PACK_AUTO || layout != TNNS_NCHW || !tnns_slab_supported(ctx, w, g, one_launch) ||
+            !tnns_quantise_tma_supported(d_x, g.H, g.W, layout) || (reinterpret_cast<uintptr_t>(d_workspace) & 127) || ws_need > workspace_bytes)
+            return tnns_fail(TNNS_ERR_UNSUPPORTED, "layer, layout, workspace size or alignment outside the slab-fed route");
+        if (one_launch) return tnns_cuda_conv_slab(ctx, w, d_x, d_thr, d_y, d_workspace, workspace_bytes, s, alpha, 0, stream);
+        rc = tnns_launch_quantise_tma(ctx, type_act_ternary(w->type), d_x, d_thr, d_workspace, g.N, g.C, g.H, g.W, (cudaStream_t)stream, TNNS_IMG_E2M1,
+                                      g.PH, g.PW);
+        if (rc) return rc;
+        return tnns_launch_gemm_slab(ctx, w, d_workspace, d_y, g, alpha, layout, (cudaStream_t)stream);
+    }
     // Default route: quantise the input once into a packed image (1/16 of the fp32 bytes) and let
     // the 4-bit tensor-core GEMM gather its im2row rows from it, so the KH*KW-times larger im2row
     // matrix is never written.  Forcing a pack or GEMM algorithm selects the explicit two-kernel
@@ -584,6 +720,7 @@ int tnns_cuda_conv(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* 
     // image of the copy-engine route, which is larger than the matrix for 1x1 kernels
     size_t need = std::max<size_t>(tnns_packed_bytes(w->type, s), 16);
     if (tnns_im2col_supported(w, g)) need = std::max(need, tnns_fused_workspace_bytes(g.N, g.C, g.H, g.W));
+    if (tnns_slab_supported(ctx, w, g, false)) need = std::max(need, tnns_slab_workspace_bytes(g.N, g.C, g.H, g.W, g.PH, g.PW));
     if (ctx->workspace_bytes < need) {
         // earlier launches may still read the old workspace
         TNNS_CUDA_TRY(cudaDeviceSynchronize());

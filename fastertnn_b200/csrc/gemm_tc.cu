@@ -43,22 +43,12 @@
 #include <type_traits>
 #include <vector>
 
-#include "internal.h"
-#include "mbar.cuh"
+#include "gemm_tc_common.cuh"
 
 
 
 namespace {
 
-constexpr int BM = 128;        // rows per accumulator (tensor-memory lanes)
-constexpr int KCH = 128;       // K elements = bytes per row and stage (one swizzle atom)
-constexpr int A_SUB = BM * KCH;  // bytes of one 128-row activation sub-tile per stage
-constexpr int WARP_TMA = 0, WARP_MMA = 1, WARP_EXP0 = 2;
-// fused quantisation (QF)
-constexpr int Q_FLAG0 = 32;   // the per-image words start one 128-byte line after the item counter
-constexpr int Q_PIX = 128;    // pixels per quantise item = quantiser threads per block
-constexpr int Q_STG = 2;      // stages of the quantiser warps' ring
-constexpr int Q_PUBN = 8;     // items the quantiser warps may be ahead of the publisher
 // A block owns MT stacked 128-row sub-tiles (MT*128 rows) and BN kernels: every weight stage
 // that arrives from L2 feeds MT MMAs, which is what keeps the L2 -> SM weight traffic below
 // the tensor pipe's appetite.  Roles: warp 0 weight producer, warp 1 MMA issuer, NG groups of
@@ -117,99 +107,6 @@ struct TcCfg {
     static_assert(SMEM <= 232448, "shared memory per block");
 };
 
-__device__ __forceinline__ void bulk_g2s(uint32_t dst_smem, const void* src, uint32_t bytes, uint32_t bar) {
-    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];" ::"r"(dst_smem), "l"(src),
-                 "r"(bytes), "r"(bar)
-                 : "memory");
-}
-// im2col tensor copy: `pixels per column` base pixels starting at (w, h, n), walking the layer's
-// output lattice (stride, padding box are in the tensor map), each read at filter offset (kw, kh),
-// channels from byte c on; outside the image the copy engine writes zeros.
-__device__ __forceinline__ void tma_im2col_g2s(uint32_t dst_smem, const void* tmap, int c, int w, int h, int n, unsigned short kw,
-                                               unsigned short kh, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
-        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(kw), "h"(kh)
-        : "memory");
-}
-// Block-pair forms of the tensor copies: the data lands in the executing block's shared memory,
-// the bytes are reported to `bar`, which may live in the other block of the pair (an address in
-// the shared::cluster window).  No multicast: every block fetches its own tile.
-__device__ __forceinline__ void tma_im2col_g2s_pair(uint32_t dst_smem, const void* tmap, int c, int w, int h, int n, unsigned short kw,
-                                                    unsigned short kh, uint32_t bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.4d.im2col.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
-        ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(c), "r"(w), "r"(h), "r"(n), "h"(kw), "h"(kh)
-        : "memory");
-}
-__device__ __forceinline__ void tma_tile2d_g2s_pair(uint32_t dst_smem, const void* tmap, int x, int y, uint32_t bar) {
-    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst_smem), "l"(reinterpret_cast<uint64_t>(tmap)), "r"(bar), "r"(x), "r"(y)
-                 : "memory");
-}
-__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tc_mma_f4(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
-                                          uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %6, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
-        : "memory");
-}
-// Block-pair forms, issued by the first block of the pair for both: the commit arrives on the
-// barrier at the same shared-memory offset in both blocks.
-__device__ __forceinline__ void tc_commit_pair(uint32_t bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
-                 "h"((unsigned short)3)
-                 : "memory");
-}
-__device__ __forceinline__ void tc_mma_f4_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t sfa, uint32_t sfb,
-                                               uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %6, 0;\n\t"
-        "tcgen05.mma.cta_group::2.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
-        : "memory");
-}
-__device__ __forceinline__ void tc_mma_i8(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\t"
-        "setp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
-        : "memory");
-}
-
-// Shared-memory matrix descriptor: K-major operand, 128-byte swizzle, rows 128 B apart, 8-row
-// groups 1024 B apart (stride byte offset), descriptor version 1 (sm_100).
-// The same for a sub-tile whose rows are 64 or 32 bytes long (64- / 32-byte swizzle; eight-row
-// groups 512 / 256 bytes apart): taps = 2 or 4 filter taps share a 128-byte stage row, each tap in
-// a sub-tile of its own.  taps = 1 is the 128-byte form of make_desc.
-__device__ __forceinline__ uint64_t make_desc_taps(uint32_t smem_addr, int taps) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-    d |= (uint64_t)1 << 16;
-    d |= (uint64_t)((1024 / taps) >> 4) << 32;                       // stride byte offset
-    d |= (uint64_t)1 << 46;                                          // version
-    d |= (uint64_t)(taps == 1 ? 2 : (taps == 2 ? 4 : 6)) << 61;      // SWIZZLE_128B / _64B / _32B
-    return d;
-}
-__device__ __forceinline__ uint64_t make_desc(uint32_t smem_addr) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
-    d |= (uint64_t)1 << 16;              // leading byte offset (unused with swizzle)
-    d |= (uint64_t)(1024 >> 4) << 32;    // stride byte offset
-    d |= (uint64_t)1 << 46;              // version
-    d |= (uint64_t)2 << 61;              // SWIZZLE_128B
-    return d;
-}
 
 // 32 elements (one 32-bit lane per plane) -> 32 int8 in a fixed permuted order, as eight words.
 // code = zero<<1 | sign : 0 -> +1, 1 -> -1, 2 or 3 -> 0 (a set zero bit wins, as az|bz does).
@@ -326,208 +223,7 @@ struct GemmArgs {
     int q_self_clean;  // the last block to leave zeroes the words again (q_sync[1] counts the blocks that left)
 };
 
-__device__ __forceinline__ unsigned int ld_acquire_gpu(const unsigned int* p) {
-    unsigned int v;
-    asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-// Bounded wait for a counter in global memory that other blocks advance.
-__device__ __forceinline__ bool counter_wait(const unsigned int* ctr, unsigned int target, volatile int* abort_flag, unsigned int* status,
-                                             unsigned code) {
-    if (ld_acquire_gpu(ctr) >= target) return true;
-    const long long t0 = clock64();
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 64; i++) {
-            if (ld_acquire_gpu(ctr) >= target) return true;
-            __nanosleep(40);
-        }
-        if (*abort_flag) return false;
-        if (clock64() - t0 > 2000000000LL) {
-            *abort_flag = 1;
-            atomicOr(status, STATUS_WAIT_EXPIRED | code);
-            return false;
-        }
-    }
-}
-__device__ __forceinline__ uint32_t push_sign(uint32_t acc, float d) { return __funnelshift_l(__float_as_uint(d), acc, 1); }
 
-// Quantiser role of the fused form, called by the four quantiser warps together (thread = pixel).
-// An item = 128 neighbouring pixels x 64 channels of one image (NCHW, a row of the 2-D tensor
-// (image, channel) x pixels per channel).  The first lane claims items in image order from a
-// global counter -- so the images the first tiles need are finished first, whichever blocks
-// run -- and requests each as ONE tensor copy into a two-stage ring; every thread then reads its
-// pixel's 64 channels from shared memory (conflict-free), pushes the sign bits of (v + t) and
-// (t - |v|) into the plane words (src/tnns/ternarize2row_avx2.c:438-452 read off sign bits),
-// hands the stage back and stores the pixel's 64 channels as 32 bytes of e2m1 operands.  A warp
-// that has stored its part of item k sets its progress word to k + 1; the publisher (below) turns
-// that into counts on the images' words in global memory.
-struct QuantArgs {
-    const float* qthr;
-    uint4* qimg;
-    unsigned int* q_sync;
-    int qN, qC, q_nbands, Cp, HW;
-    unsigned int* status;
-};
-// Control words of the quantiser warps and the publisher, behind the quantiser ring's barriers.
-struct QuantCtl {
-    unsigned int item[Q_STG];   // item held by each stage (>= items: end mark)
-    unsigned int done[4];        // per quantiser warp: items whose stores it has issued
-    unsigned int published;      // items the publisher has counted
-    unsigned int total;          // items this block processed, ~0u while the quantiser warps run
-    int pub_n[Q_PUBN];           // image of item k at k % Q_PUBN
-};
-static_assert(sizeof(QuantCtl) + 2 * Q_STG * sizeof(uint64_t) <= 128, "control words behind the quantiser ring");
-__device__ __noinline__ void quantise_items(const QuantArgs p, const CUtensorMap* tmap_q, unsigned char* stage0, uint64_t* qbars,
-                                            volatile int* abort_flag, const int qtid) {
-    constexpr int QSTG = Q_STG, Q_STAGE = Q_PIX * 64 * 4;
-    const int lane = qtid & 31, qwarp = qtid >> 5;
-    const uint32_t bar_full = smem_u32(qbars), bar_empty = smem_u32(qbars + QSTG);
-    volatile QuantCtl* ctl = reinterpret_cast<volatile QuantCtl*>(qbars + 2 * QSTG);
-    const unsigned int items = (unsigned int)p.qN * (unsigned int)p.q_nbands * (unsigned int)p.Cp;
-    // issue: the claimed item goes into stage s (or the end mark, completing the barrier without bytes)
-    auto issue = [&](int s, unsigned int i) {
-        ctl->item[s] = i;
-        if (i < items) {
-            const int ic = (int)(i % (unsigned int)p.Cp);
-            const unsigned int nb = i / (unsigned int)p.Cp;
-            const int band = (int)(nb % (unsigned int)p.q_nbands), n = (int)(nb / (unsigned int)p.q_nbands);
-            mbar_arrive_expect_tx(bar_full + 8 * s, Q_STAGE);  // the whole box, edges zero-filled
-            tma_tile2d_g2s(smem_u32(stage0 + s * Q_STAGE), tmap_q, band * Q_PIX, n * p.qC + ic * 64, bar_full + 8 * s);
-        } else {
-            mbar_arrive(bar_full + 8 * s);
-        }
-    };
-    unsigned int next = 0;  // issuer only: the item claimed ahead
-    if (qtid == 0) {
-#pragma unroll
-        for (int s = 0; s < QSTG; s++) issue(s, atomicAdd(p.q_sync, 1u));
-        next = atomicAdd(p.q_sync, 1u);
-    }
-    // the image's threshold is fetched one item ahead (a peek at the item the other stage holds,
-    // checked when its turn comes), so its load latency is not paid in front of the first compare
-    int pf_n = -1;
-    float pf_t = 0.f;
-    unsigned int k = 0;
-    for (;; k++) {
-        const int s = (int)(k % QSTG);
-        const uint32_t ph = (k / QSTG) & 1;
-        if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 7)) break;
-        const unsigned int i = ctl->item[s];
-        if (i >= items) break;  // every later claim is past the end as well
-        const int ic = (int)(i % (unsigned int)p.Cp);
-        const unsigned int nb = i / (unsigned int)p.Cp;
-        const int band = (int)(nb % (unsigned int)p.q_nbands), n = (int)(nb / (unsigned int)p.q_nbands);
-        const int nch = min(64, p.qC - ic * 64);
-        const float t = ((n == pf_n) ? pf_t : __ldg(p.qthr + n)) + 0.0f;  // + 0.0f: a threshold of -0 behaves as +0
-        {
-            // the loaded value is not touched before the next iteration: an instruction that used it
-            // here would hold this warp until the load returned
-            const unsigned int i2 = ctl->item[(s + 1) % QSTG];  // may be stale: only ever used after the check above
-            if (i2 < items) {
-                pf_n = (int)(i2 / ((unsigned int)p.Cp * (unsigned int)p.q_nbands));
-                pf_t = __ldg(p.qthr + pf_n);
-            }
-        }
-        const float* sp = reinterpret_cast<const float*>(stage0 + s * Q_STAGE) + qtid;
-        uint32_t sg[2] = {0, 0}, nz[2] = {0, 0};
-        // channel b of a half ends at bit b: visit 31 .. 0 and shift left (four independent chains)
-        if (nch == 64) {
-#pragma unroll
-            for (int b = 31; b >= 0; b--) {
-#pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const float v = sp[(32 * h + b) * Q_PIX];
-                    sg[h] = push_sign(sg[h], v + t);
-                    nz[h] = push_sign(nz[h], t - fabsf(v));
-                }
-            }
-        } else {
-#pragma unroll
-            for (int h = 0; h < 2; h++) {
-#pragma unroll 1
-                for (int b = 31; b >= 0; b--) {
-                    if (32 * h + b < nch) {
-                        const float v = sp[(32 * h + b) * Q_PIX];
-                        sg[h] = push_sign(sg[h], v + t);
-                        nz[h] = push_sign(nz[h], t - fabsf(v));
-                    } else {  // absent channel: sign 0, non-zero 0
-                        sg[h] <<= 1;
-                        nz[h] <<= 1;
-                    }
-                }
-            }
-        }
-        // every value is in registers: hand the stage back; the issuer refills it at once
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_empty + 8 * s);
-        if (qtid == 0) {
-            if (!mbar_wait(bar_empty + 8 * s, ph, abort_flag, p.status, 8)) break;
-            issue(s, next);
-            next = atomicAdd(p.q_sync, 1u);
-            // the publisher's ring of image indices: never more than Q_PUBN items ahead of it
-            if (k >= Q_PUBN && ctl->published + Q_PUBN <= k) {
-                const long long t0 = clock64();
-                while (ctl->published + Q_PUBN <= k && !*abort_flag) {
-                    if (clock64() - t0 > 2000000000LL) {
-                        *abort_flag = 1;
-                        atomicOr(p.status, STATUS_WAIT_EXPIRED | 9);
-                    }
-                }
-            }
-            ctl->pub_n[k % Q_PUBN] = n;
-        }
-        const int pix = band * Q_PIX + qtid;
-        if (pix < p.HW) {
-            uint32_t lo[4], hi[4];
-            tnns_expand32_f4(sg[0], ~nz[0], lo);
-            tnns_expand32_f4(sg[1], ~nz[1], hi);
-            uint4* dst = p.qimg + (((size_t)n * p.HW + pix) * p.Cp + ic) * 2;
-            dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
-            dst[1] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
-        }
-        // progress word of this warp: release at block scope, so that the publisher, having read it,
-        // may publish the warp's stores (and, for the first warp, the image index) further
-        __syncwarp();
-        if (lane == 0) {
-            __threadfence_block();
-            ctl->done[qwarp] = k + 1;
-        }
-    }
-    __syncwarp();
-    if (qtid == 0) ctl->total = k;
-}
-
-// Publisher of the fused form (one thread).  Counting a finished item on its image's word needs a
-// gpu-scope release fence in front -- the item's plain stores must be visible to whoever sees the
-// count -- and under the GEMM's store traffic that fence takes longer than quantising the item.
-// So the quantiser warps never fence at gpu scope: this thread watches their progress words,
-// and whenever all four have moved on it issues ONE fence and counts every newly finished item
-// (four warps per item) with relaxed adds.  The producer threads of all blocks poll those counts.
-__device__ __noinline__ void publish_items(unsigned int* q_sync, unsigned int* status, uint64_t* qbars, volatile int* abort_flag) {
-    volatile QuantCtl* ctl = reinterpret_cast<volatile QuantCtl*>(qbars + 2 * Q_STG);
-    unsigned int published = 0;
-    long long t0 = clock64();
-    for (;;) {
-        const unsigned int m = min(min(ctl->done[0], ctl->done[1]), min(ctl->done[2], ctl->done[3]));
-        if (m > published) {
-            __threadfence();  // acquire of the progress words at block scope, release of the warps' stores at gpu scope
-            for (unsigned int j = published; j < m; j++)
-                asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(q_sync + Q_FLAG0 + ctl->pub_n[j % Q_PUBN]), "r"(4u) : "memory");
-            published = m;
-            ctl->published = m;
-            t0 = clock64();
-        } else {
-            if (ctl->total == published || *abort_flag) break;
-            if (clock64() - t0 > 4000000000LL) {
-                *abort_flag = 1;
-                atomicOr(status, STATUS_WAIT_EXPIRED | 10);
-                break;
-            }
-            __nanosleep(64);
-        }
-    }
-}
 
 // TAPS (tensor-copy form): filter taps per 128-byte stage row -- 1: a tap's 256 channels fill the
 // row (C_pack % 4 == 0); 2: C_pack = 2, two taps of 128 channels in two 64-byte-swizzled sub-tiles;
@@ -874,7 +570,7 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
     } else if (QF && warp >= Cfg::WARP_Q0) {
         uint64_t* qbars = reinterpret_cast<uint64_t*>(smem + Cfg::Q_OFF + Cfg::QSTG * Cfg::Q_STAGE);
         if (warp < Cfg::WARP_Q0 + 4)
-            quantise_items(QuantArgs{p.qthr, p.qimg, p.q_sync, p.qN, p.qC, p.q_nbands, p.Cp, p.H * p.W, p.status}, &tmap_q, smem + Cfg::Q_OFF, qbars,
+            quantise_items(plain_quant_args(p.qthr, p.qimg, p.q_sync, p.qN, p.qC, p.q_nbands, p.Cp, p.H, p.W, p.status), &tmap_q, smem + Cfg::Q_OFF, qbars,
                            abort_flag, tid - Cfg::WARP_Q0 * 32);
         else if (lane == 0)
             publish_items(p.q_sync, p.status, qbars, abort_flag);
@@ -1371,6 +1067,33 @@ bool tnns_fused_supported(const tnns_cuda_weights* w, const TnnsGeom& g, const f
     return items < 0x7FFFFFFFLL;
 }
 
+// Synchronisation words of a one-launch layer (item counter, count of blocks that have left, one word
+// per image).  The context keeps one set of its own, bound to the first stream that launches a fused
+// form: every launch leaves them zeroed (the last block out clears them), so launches on that stream
+// need no clearing operation, and consecutive launches can overlap their set-up with the
+// predecessor's tail (programmatic dependent launch).  Launches on any other stream use the words
+// in the caller's workspace, cleared here on `stream`.
+int tnns_fused_sync_prepare(tnns_cuda_ctx* ctx, int N, cudaStream_t stream, unsigned int* caller_words, unsigned int** words_out, int* self_clean) {
+    const size_t words = (size_t)Q_FLAG0 + (size_t)N;
+    if (ctx->fused_sync_words < words && (!ctx->fused_sync || ctx->fused_sync_stream == stream)) {
+        TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
+        TNNS_CUDA_TRY(cudaDeviceSynchronize());  // earlier launches may still use the old words
+        if (ctx->fused_sync) cudaFree(ctx->fused_sync);
+        ctx->fused_sync = nullptr;
+        ctx->fused_sync_words = 0;
+        const size_t cap = std::max<size_t>(words, 4096);
+        TNNS_CUDA_TRY(cudaMalloc(&ctx->fused_sync, cap * sizeof(unsigned int)));
+        TNNS_CUDA_TRY(cudaMemset(ctx->fused_sync, 0, cap * sizeof(unsigned int)));
+        ctx->fused_sync_words = cap;
+        ctx->fused_sync_stream = stream;
+    }
+    const bool own = ctx->fused_sync && ctx->fused_sync_words >= words && ctx->fused_sync_stream == stream;
+    if (!own) TNNS_CUDA_TRY(cudaMemsetAsync(caller_words, 0, tnns_fused_sync_bytes(N), stream));
+    *words_out = own ? ctx->fused_sync : caller_words;
+    *self_clean = own ? 1 : 0;
+    return TNNS_OK;
+}
+
 int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const TnnsGeom& g, float alpha,
                             int layout, cudaStream_t stream, int pairs, void* d_pimg, const float* d_thr_next, int next_format,
                             const TnnsFusedInput* fused) {
@@ -1378,32 +1101,15 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     if (M == 0) return TNNS_OK;
     if (!tnns_im2col_supported(w, g)) return tnns_fail(TNNS_ERR_UNSUPPORTED, "layer shape or type outside the tensor-copy activation path");
     if (reinterpret_cast<uintptr_t>(d_image) & 15) return tnns_fail(TNNS_ERR_INVALID, "image must be 16-byte aligned");
-    bool own_words = false;
+    unsigned int* fused_words = nullptr;
+    int fused_self_clean = 0;
     if (fused) {
         if (!fused->d_x || !fused->d_thr || !fused->d_sync) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
         if (!tnns_fused_supported(w, g, fused->d_x, layout))
             return tnns_fail(TNNS_ERR_UNSUPPORTED, "fused quantisation needs NCHW input with H*W a multiple of four and a 16-byte aligned base");
         if (reinterpret_cast<uintptr_t>(fused->d_sync) & 127) return tnns_fail(TNNS_ERR_INVALID, "synchronisation words must be 128-byte aligned");
-        // The context keeps one set of synchronisation words of its own, bound to the first stream
-        // that launches the fused form: every launch leaves them zeroed (the last block out clears
-        // them), so launches on that stream need no clearing operation, and consecutive launches
-        // can overlap their set-up with the predecessor's tail (programmatic dependent launch).
-        // Launches on any other stream use the words in the caller's workspace, cleared here.
-        const size_t words = (size_t)Q_FLAG0 + (size_t)g.N;
-        if (ctx->fused_sync_words < words && (!ctx->fused_sync || ctx->fused_sync_stream == stream)) {
-            TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
-            TNNS_CUDA_TRY(cudaDeviceSynchronize());  // earlier launches may still use the old words
-            if (ctx->fused_sync) cudaFree(ctx->fused_sync);
-            ctx->fused_sync = nullptr;
-            ctx->fused_sync_words = 0;
-            const size_t cap = std::max<size_t>(words, 4096);
-            TNNS_CUDA_TRY(cudaMalloc(&ctx->fused_sync, cap * sizeof(unsigned int)));
-            TNNS_CUDA_TRY(cudaMemset(ctx->fused_sync, 0, cap * sizeof(unsigned int)));
-            ctx->fused_sync_words = cap;
-            ctx->fused_sync_stream = stream;
-        }
-        own_words = ctx->fused_sync && ctx->fused_sync_words >= words && ctx->fused_sync_stream == stream;
-        if (!own_words) TNNS_CUDA_TRY(cudaMemsetAsync(fused->d_sync, 0, tnns_fused_sync_bytes(g.N), stream));
+        int rc0 = tnns_fused_sync_prepare(ctx, g.N, stream, fused->d_sync, &fused_words, &fused_self_clean);
+        if (rc0) return rc0;
     }
     CUtensorMap map;
     int rc = encode_im2col_map(&map, d_image, g);
@@ -1439,8 +1145,8 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
         a.qx = fused->d_x;
         a.qthr = fused->d_thr;
         a.qimg = reinterpret_cast<uint4*>(const_cast<void*>(d_image));
-        a.q_sync = own_words ? ctx->fused_sync : fused->d_sync;
-        a.q_self_clean = own_words ? 1 : 0;
+        a.q_sync = fused_words;
+        a.q_self_clean = fused_self_clean;
         a.qN = g.N;
         a.qC = g.C;
         a.q_nbands = (g.H * g.W + Q_PIX - 1) / Q_PIX;

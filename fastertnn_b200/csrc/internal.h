@@ -100,11 +100,13 @@ int tnns_launch_quantise(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, con
 // the same for NCHW input whose rows the copy engine can fetch (H*W a multiple of four floats,
 // 16-byte aligned base): tensor copies into a shared-memory ring instead of register loads
 bool tnns_quantise_tma_supported(const float* d_x, int H, int W, int layout);
+// PH, PW (4-bit image only): store the image bordered, i.e. every image framed by PH rows / PW columns of
+// the padding value (ternary 0, binary +1), [n][H + 2*PH][W + 2*PW][C/2 bytes]
 int tnns_launch_quantise_tma(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
-                             int W, cudaStream_t stream, int format);
+                             int W, cudaStream_t stream, int format, int PH = 0, int PW = 0);
 // driver-encoded descriptor of a two-dimensional tensor for the copy engine (128 bytes at `map`)
 int tnns_tensor_map_2d(void* map, int elem_bytes, const void* base, unsigned long long dim0, unsigned long long dim1,
-                       unsigned long long stride1_bytes, unsigned box0, unsigned box1);
+                       unsigned long long stride1_bytes, unsigned box0, unsigned box1, int swizzle_bytes = 0);
 // 4-bit GEMM + PReLU whose activation tiles the copy engine gathers (im2col tensor copies) from
 // an e2m1 image; needs ternary activations and a channel count that fills 128-byte chunks
 bool tnns_im2col_supported(const tnns_cuda_weights* w, const TnnsGeom& g);
@@ -123,6 +125,21 @@ bool tnns_fused_supported(const tnns_cuda_weights* w, const TnnsGeom& g, const f
 int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const TnnsGeom& g,
                             float alpha, int layout, cudaStream_t stream, int pairs = 0, void* d_pimg = nullptr,
                             const float* d_thr_next = nullptr, int next_format = 1, const TnnsFusedInput* fused = nullptr);
+
+int tnns_fused_sync_prepare(tnns_cuda_ctx* ctx, int N, cudaStream_t stream, unsigned int* caller_words, unsigned int** words_out, int* self_clean);
+
+// Slab-fed 4-bit GEMM + PReLU for stride-1 layers (gemm_slab.cu): d_image is the BORDERED 4-bit image of
+// the layer input, [n][H + 2*PH][W + 2*PW][C/2 bytes] with the padding value in the border, and one
+// slab of pixels per tile serves every filter tap.  All four network types (binary activations: the
+// border holds +1).  d_pimg != NULL: quantised output for the next layer instead of fp32 --
+// next_format 0 / 1 bit planes, 2 plain 4-bit image, 3 bordered 4-bit image for a next layer with
+// padding (next_PH, next_PW) whose padded size equals this layer's; next_binary: that layer's
+// activations are binary.  fused != NULL: the same launch quantises the fp32 input into d_image.
+bool tnns_slab_supported(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const TnnsGeom& g, bool fused);
+size_t tnns_bordered_image_bytes(int N, int C, int H, int W, int PH, int PW);
+int tnns_launch_gemm_slab(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const TnnsGeom& g, float alpha, int layout,
+                          cudaStream_t stream, int pairs = 0, void* d_pimg = nullptr, const float* d_thr_next = nullptr, int next_format = 2,
+                          int next_binary = 0, int next_PH = 0, int next_PW = 0, const TnnsFusedInput* fused = nullptr);
 
 int tnns_launch_pack_weights(tnns_cuda_ctx* ctx, bool ternary, const float* d_w, const float* d_thr, void* d_packed, int KN, int C,
                              int KH, int KW, cudaStream_t stream);

@@ -38,7 +38,7 @@ __device__ __forceinline__ uint32_t push_sign_bit(uint32_t acc, float d) { retur
 template <bool TERNARY, int IMG>
 __global__ void __launch_bounds__(QTHREADS, 1)
 quantise_tma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __restrict__ thr, void* __restrict__ out, int N, int C, int HW,
-                    int Cp, int nbands, unsigned int* status) {
+                    int Cp, int nbands, unsigned int* status, int W, int Wp, int HpWp, int off0) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + QSTG * QSTAGE_BYTES);
@@ -63,6 +63,23 @@ quantise_tma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __res
     // launched as a programmatic dependent itself: the input may be the output of the launch before
     asm volatile("griddepcontrol.wait;" ::: "memory");
 
+    if (IMG == TNNS_IMG_E2M1 && HpWp != HW && warp > 0) {
+        // bordered image (4-bit form): pixel (y, x) of image n sits at n*HpWp + y*Wp + x + off0 and the
+        // frame of PH rows / PW columns around every image holds the layer's padding value -- ternary 0,
+        // binary +1 -- so that a consumer reads padding like any other pixel.  Written here, before the
+        // items, by all consumer threads of the grid.
+        const uint32_t padw = TERNARY ? 0u : 0x22222222u;
+        const uint4 pad4 = make_uint4(padw, padw, padw, padw);
+        const int PH = off0 / Wp, PW = off0 - PH * Wp, H = HW / W;
+        const long long total = (long long)N * HpWp;
+        for (long long t = (long long)blockIdx.x * (QGROUPS * QL) + (tid - 32); t < total; t += (long long)gridDim.x * (QGROUPS * QL)) {
+            const int r = (int)(t % HpWp), y = r / Wp, x = r - y * Wp;
+            if (y < PH || y >= PH + H || x < PW || x >= PW + W) {
+                uint4* dst = reinterpret_cast<uint4*>(out) + (size_t)t * Cp * 2;
+                for (int u = 0; u < 2 * Cp; u++) dst[u] = pad4;
+            }
+        }
+    }
     if (warp == 0) {
         if (lane == 0) {
             long long k = 0;
@@ -129,6 +146,7 @@ quantise_tma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __res
                     }
                 }
             }
+            if (!TERNARY) nz[0] = nz[1] = 0xFFFFFFFFu;  // the binary alphabet has no zero; absent channels read +1
             // every value is in registers: hand the stage back before storing
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + 8 * s);
@@ -138,7 +156,8 @@ quantise_tma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __res
                     uint32_t lo[4], hi[4];
                     tnns_expand32_f4(sg[0], ~nz[0], lo);
                     tnns_expand32_f4(sg[1], ~nz[1], hi);
-                    uint4* dst = reinterpret_cast<uint4*>(out) + (((size_t)n * HW + pix) * Cp + ic) * 2;
+                    const int y = pix / W, x = pix - y * W;
+                    uint4* dst = reinterpret_cast<uint4*>(out) + (((size_t)n * HpWp + (size_t)y * Wp + x + off0) * Cp + ic) * 2;
                     dst[0] = make_uint4(lo[0], lo[1], lo[2], lo[3]);
                     dst[1] = make_uint4(hi[0], hi[1], hi[2], hi[3]);
                 } else {
@@ -168,8 +187,11 @@ bool tnns_quantise_tma_supported(const float* d_x, int H, int W, int layout) {
 }
 
 int tnns_launch_quantise_tma(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
-                             int W, cudaStream_t stream, int format) {
+                             int W, cudaStream_t stream, int format, int PH, int PW) {
     const int HW = H * W;
+    if (N == 0) return TNNS_OK;
+    if ((PH || PW) && format != TNNS_IMG_E2M1) return tnns_fail(TNNS_ERR_INVALID, "only the 4-bit image has a bordered form");
+    const int Wp = W + 2 * PW, HpWp = (H + 2 * PH) * Wp, off0 = PH * Wp + PW;
     const int Cp = (C + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS;
     const int nbands = (HW + QL - 1) / QL;
     alignas(64) CUtensorMap map;
@@ -189,11 +211,11 @@ int tnns_launch_quantise_tma(tnns_cuda_ctx* ctx, bool ternary, const float* d_x,
         attr[0].val.programmaticStreamSerializationAllowed = 1;
         cfg.attrs = attr;
         cfg.numAttrs = 1;
-        TNNS_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, map, d_thr, d_image, N, C, HW, Cp, nbands, ctx->d_status));
+        TNNS_CUDA_TRY(cudaLaunchKernelEx(&cfg, kern, map, d_thr, d_image, N, C, HW, Cp, nbands, ctx->d_status, W, Wp, HpWp, off0));
         tnns_count_launch();
         TNNS_CUDA_TRY(cudaGetLastError());
         return TNNS_OK;
     };
-    if (format == TNNS_IMG_E2M1) return launch(quantise_tma_kernel<true, TNNS_IMG_E2M1>);
+    if (format == TNNS_IMG_E2M1) return ternary ? launch(quantise_tma_kernel<true, TNNS_IMG_E2M1>) : launch(quantise_tma_kernel<false, TNNS_IMG_E2M1>);
     return ternary ? launch(quantise_tma_kernel<true, TNNS_IMG_PLANES>) : launch(quantise_tma_kernel<false, TNNS_IMG_PLANES>);
 }

@@ -170,7 +170,9 @@ enum tnns_gemm_algo {
     TNNS_GEMM_POPC_TILED = 2,  /* tiled carry-save popcount GEMM, integer pipe   */
     TNNS_GEMM_I8_TC = 3,       /* tcgen05 int8 tensor-core GEMM                  */
     TNNS_GEMM_F4_TC = 4,       /* tcgen05 4-bit (e2m1, unit scales) tensor-core GEMM */
-    TNNS_GEMM_F4_FUSED = 5     /* whole layers only: the 4-bit GEMM fed by tensor copies with the quantise step in the same launch */
+    TNNS_GEMM_F4_FUSED = 5,    /* whole layers only: the 4-bit GEMM fed by tensor copies with the quantise step in the same launch */
+    TNNS_GEMM_F4_SLAB = 6,     /* whole stride-1 layers only: bordered 4-bit image, then the slab-fed 4-bit GEMM */
+    TNNS_GEMM_F4_SLAB_FUSED = 7 /* the same as one launch */
 };
 
 /* Error codes returned by every tnns_cuda_* function (0 = success). */
@@ -306,6 +308,45 @@ int tnns_cuda_conv_fused_preferred(tnns_cuda_ctx* ctx, const tnns_cuda_weights* 
 int tnns_cuda_conv_fused_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr,
                                     void* d_image_out, const float* d_thr_next, int next_format, void* d_workspace,
                                     size_t workspace_bytes, const tnns_shape_t* s, float alpha, int pairs, void* stream);
+/* Stride-1 layers from a BORDERED 4-bit image (t2r_p2_opt / b2r scatter every packed pixel to the
+ * KH*KW windows that use it, src/tnns/ternarize2row_avx2.c:285-313, src/tnns/binarize2row_avx2.c:131-199;
+ * here no window is ever materialised).  The image keeps the layer's padding around every image:
+ * [n][H + 2*PH][W + 2*PW][C/2 bytes] (tnns_e2m1_bordered_image_bytes), border pixels = the padding
+ * value -- ternary 0, binary +1 (b2r pads with zero bits, src/tnns/binarize2row_avx2.c:146-151) -- so all
+ * four network types qualify.  Output rows are laid over the padded lattice, and the 128 rows of a
+ * tile read, for filter tap (kh, kw), 128 consecutive pixels of the image starting kh*(W+2*PW) + kw
+ * further on: ONE tiled tensor copy of 128 + (KH-1)*(W+2*PW) + KW-1 pixels per tile and 256-channel
+ * group serves every tap, the tensor core reading each tap as a row-shifted view of that slab
+ * (rows on border positions are computed and not stored).  Needs stride 1 and 64, 128 or a multiple
+ * of 256 channels (after rounding to 64): tnns_cuda_slab_supported.
+ *   tnns_cuda_quantise_e2m1_bordered  fp32 NCHW (H*W a multiple of four) -> bordered image, 128-byte aligned
+ *   tnns_cuda_gemm_slab               bordered image -> fp32 output (same result as every other route)
+ *   tnns_cuda_gemm_slab_packed_out    the same with the quantising epilogue: next_format 0 / 1 bit planes
+ *                                     (binary / ternary), 2 plain 4-bit image, 3 bordered 4-bit image for a
+ *                                     ternary next layer with padding (next_PH, next_PW), 5 the same for a
+ *                                     binary next layer.  Formats 3 / 5 need the next layer's padded size to
+ *                                     equal this layer's (a same-size stride-1 chain); the rows on border
+ *                                     positions then write the next image's border, so the whole image is
+ *                                     rewritten by every launch.
+ *   tnns_cuda_conv_slab(_packed_out)  ONE launch: quantiser warps write the bordered image inside the GEMM
+ *                                     kernel (workspace: tnns_slab_workspace_bytes, 128-byte aligned; the
+ *                                     synchronisation words follow the rules of tnns_cuda_conv_fused).
+ * tnns_cuda_conv / _conv_ws take these routes with gemm_algo TNNS_GEMM_F4_SLAB / _SLAB_FUSED. */
+size_t tnns_e2m1_bordered_image_bytes(int N, int C, int H, int W, int PH, int PW);
+size_t tnns_slab_workspace_bytes(int N, int C, int H, int W, int PH, int PW);
+int tnns_cuda_slab_supported(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s);
+int tnns_cuda_conv_slab_supported(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout);
+int tnns_cuda_quantise_e2m1_bordered(tnns_cuda_ctx* ctx, int ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
+                                     int W, int PH, int PW, int layout, void* stream);
+int tnns_cuda_gemm_slab(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const tnns_shape_t* s, float alpha,
+                        int layout, int pairs, void* stream);
+int tnns_cuda_gemm_slab_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, void* d_image_out, const float* d_thr_next,
+                                   int next_format, int next_PH, int next_PW, const tnns_shape_t* s, float alpha, int pairs, void* stream);
+int tnns_cuda_conv_slab(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y, void* d_workspace,
+                        size_t workspace_bytes, const tnns_shape_t* s, float alpha, int pairs, void* stream);
+int tnns_cuda_conv_slab_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, void* d_image_out,
+                                   const float* d_thr_next, int next_format, int next_PH, int next_PW, void* d_workspace, size_t workspace_bytes,
+                                   const tnns_shape_t* s, float alpha, int pairs, void* stream);
 /* Chaining on the copy-engine route: the same GEMM with the quantising epilogue of
  * tnns_cuda_gemm_packed_out.  next_format (also accepted as `next_ternary` by
  * tnns_cuda_gemm_packed_out): 0 = binary bit planes, 1 = ternary bit planes, 2 = ternary 4-bit
