@@ -424,16 +424,23 @@ class LayerRun:
         self.in_bytes = nloc * layer.C * layer.H * layer.W * 4
         self.out_bytes = nloc * layer.KN * OH * OW * 4
         tc4 = args.gemm in ("auto", "f4tc")
-        self.im2col = tc4 and args.route in ("auto", "im2col", "fused") and ctx.im2col_supported(w, self.shape)
+        # the slab-fed route (stride-1 layers from a bordered 4-bit image): on request, or where the library's own rule takes it
+        self.slab = tc4 and (args.route in ("slab", "slab_fused") or (args.route == "auto" and ctx.slab_auto(w, self.shape, 4096, ft.NCHW) > 0))
+        if self.slab and not ctx.slab_supported(w, self.shape):
+            raise SystemExit("bench: this workload does not qualify for the slab-fed route")
+        self.im2col = tc4 and not self.slab and args.route in ("auto", "im2col", "fused") and ctx.im2col_supported(w, self.shape)
         if args.route in ("im2col", "fused") and not self.im2col:
             raise SystemExit("bench: this workload does not qualify for the im2col tensor-copy route")
-        self.implicit = tc4 and (self.im2col or args.route in ("auto", "implicit"))
+        self.implicit = tc4 and (self.slab or self.im2col or args.route in ("auto", "implicit"))
         self.fused = False
-        if self.im2col and args.route in ("auto", "fused"):
+        if self.slab:
+            self.fused = args.route == "slab_fused" or (args.route == "auto" and ctx.slab_auto(w, self.shape, 4096, ft.NCHW) == 2)
+        elif self.im2col and args.route in ("auto", "fused"):
             # the pointer only stands for the input's alignment here (torch allocations are 512-byte aligned)
             self.fused = (ctx.conv_fused_supported(w, self.shape, 4096, ft.NCHW) if args.route == "fused"
                           else ctx.conv_fused_preferred(w, self.shape, 4096, ft.NCHW))
-        self.pack_bytes = (ft.api.fused_workspace_bytes(nloc, layer.C, layer.H, layer.W) if self.im2col else
+        self.pack_bytes = (ft.api.slab_workspace_bytes(nloc, layer.C, layer.H, layer.W, layer.P, layer.P) if self.slab else
+                           ft.api.fused_workspace_bytes(nloc, layer.C, layer.H, layer.W) if self.im2col else
                            ft.api.packed_image_bytes(self.tern, nloc, layer.C, layer.H, layer.W) if self.implicit
                            else ft.packed_bytes(type_, self.shape))
         self.step_bytes = self.in_bytes + self.out_bytes + self.pack_bytes
@@ -457,7 +464,10 @@ class LayerRun:
 
     def quantise(self, r):
         ft, L = self.ft, self.layer
-        if self.im2col:
+        if self.slab:
+            self.ctx.quantise_e2m1_bordered(self.tern, self.xs[r].data_ptr(), self.thr_d.data_ptr(), self._aligned(self.ps[r]), self.nloc, L.C, L.H, L.W,
+                                            L.P, L.P, ft.NCHW, self.sp)
+        elif self.im2col:
             self.ctx.quantise_e2m1(self.xs[r].data_ptr(), self.thr_d.data_ptr(), self._aligned(self.ps[r]), self.nloc, L.C, L.H, L.W, ft.NCHW, self.sp)
         else:
             self.ctx.quantise(self.tern, self.xs[r].data_ptr(), self.thr_d.data_ptr(), self._aligned(self.ps[r]), self.nloc, L.C, L.H, L.W, ft.NCHW, self.sp)
@@ -475,7 +485,11 @@ class LayerRun:
             self.ctx.pack(self.tern, x, self.thr_d.data_ptr(), p, self.shape, ft.NCHW, ft.PACK_AUTO, self.sp)
         if ev:
             ev[1].record(self.stream)
-        if self.fused:
+        if self.slab and self.fused:
+            self.ctx.conv_slab(self.w, x, self.thr_d.data_ptr(), y, p, self.pack_bytes, self.shape, 0.5, 0, self.sp)
+        elif self.slab:
+            self.ctx.gemm_slab(self.w, p, y, self.shape, 0.5, ft.NCHW, self.sp)
+        elif self.fused:
             self.ctx.conv_fused(self.w, x, self.thr_d.data_ptr(), y, p, self.pack_bytes, self.shape, 0.5, 0, self.sp)
         elif self.im2col:
             self.ctx.gemm_im2col(self.w, p, y, self.shape, 0.5, ft.NCHW, self.sp)
@@ -487,11 +501,16 @@ class LayerRun:
             ev[2].record(self.stream)
 
     def route_name(self):
+        if self.slab:
+            return ("one launch: quantise to a bordered 4-bit image inside the GEMM kernel, GEMM fed by one slab of pixels per tile for all filter taps"
+                    if self.fused else "quantise to a bordered 4-bit image -> GEMM fed by one slab of pixels per tile for all filter taps")
         return ("one launch: quantise to a 4-bit image inside the GEMM kernel, GEMM fed by im2col tensor copies" if self.fused else
                 "quantise to a 4-bit image -> GEMM fed by im2col tensor copies" if self.im2col else
                 "quantise to bit planes -> GEMM with implicit im2row" if self.implicit else "pack (im2row matrix) -> GEMM")
 
     def kernel_key(self):
+        if self.slab and self.args.gemm in ("auto", "f4tc"):
+            return "f4_slab_fused" if self.fused else "f4_slab"
         return {"popc": "popc", "i8tc": "tc"}.get(self.args.gemm, "f4_fused" if self.fused else "f4_im2col" if self.im2col else
                                                  "f4" if self.implicit else "f4_explicit")
 
@@ -588,7 +607,7 @@ def run_layer(args, name, type_, N_cfg, layer: Layer):
     # issue-bound tcgen05.mma loop (no loads, no epilogue) on this GPU, 1e9 operations per second
     ctx_mma_rate = ctx.pipe_rate(3 if args.gemm == "i8tc" else 4) if args.gemm != "popc" else 0.0
     ctx.sync()
-    info = {"route": run.route_name(), "key": run.kernel_key(), "fused": run.fused, "im2col": run.im2col, "implicit": run.implicit,
+    info = {"route": run.route_name(), "key": run.kernel_key(), "fused": run.fused, "im2col": run.im2col, "implicit": run.implicit, "slab": run.slab,
             "ring": run.ring, "step_bytes": run.step_bytes, "in_bytes": run.in_bytes, "out_bytes": run.out_bytes,
             "pack_bytes": run.pack_bytes}
     y0_dev = run.ys[0][:1].cpu()
@@ -668,13 +687,14 @@ def run_layer(args, name, type_, N_cfg, layer: Layer):
         ops = layer.ops(N_total)
         ops_loc = layer.ops(nloc)
         in_bytes, out_bytes, pack_bytes = info["in_bytes"], info["out_bytes"], info["pack_bytes"]
-        fused, im2col, implicit = info["fused"], info["im2col"], info["implicit"]
-        pack_alg_bytes = in_bytes + (ft.api.e2m1_image_bytes(nloc, layer.C, layer.H, layer.W) if im2col else pack_bytes)
+        fused, im2col, implicit, slab = info["fused"], info["im2col"], info["implicit"], info["slab"]
+        pack_alg_bytes = in_bytes + (ft.api.bordered_image_bytes(nloc, layer.C, layer.H, layer.W, layer.P, layer.P) if slab else
+                                     ft.api.e2m1_image_bytes(nloc, layer.C, layer.H, layer.W) if im2col else pack_bytes)
         t_pack_eff = t_pack_alone if fused else t_pack
         gemm_tops = ops_loc / (t_gemm * 1e-3) / 1e12
         per_img = ncu_traffic(name, info["key"])
         gemm_traffic = per_img * nloc if per_img else None
-        per_img = ncu_traffic(name, "quantise_e2m1" if im2col else "quantise" if implicit else "pack")
+        per_img = ncu_traffic(name, "quantise_e2m1_bordered" if slab else "quantise_e2m1" if im2col else "quantise" if implicit else "pack")
         pack_traffic = per_img * nloc if per_img else None
         if args.gemm == "popc":
             # integer-pipe kernel: 5.5 LOP3 per 32-bit lane and output, LOP3 issues 64 lanes/clk/SM
@@ -686,7 +706,9 @@ def run_layer(args, name, type_, N_cfg, layer: Layer):
             gemm_peak = 2.0 * pk["bf16_tflops"]
             gemm_peak_source = f"2 x {pk['source']} bf16 burst figure (int8 dense rate = 2 x bf16)"
         else:
-            gemm_kernel_name, gemm_bound = ("gemm_tc_kernel<F4=true, ATMA=true, QF=true> (whole layer in one launch: quantiser warps write the 4-bit image, tcgen05.mma kind::mxf4 GEMM fed by im2col tensor copies, unit scales, + PReLU)" if fused else
+            gemm_kernel_name, gemm_bound = ("gemm_slab_kernel<QF=true> (whole layer in one launch: quantiser warps write the bordered 4-bit image, tcgen05.mma kind::mxf4 GEMM fed by one slab of pixels per tile, unit scales, + PReLU)" if slab and fused else
+                                            "gemm_slab_kernel (tcgen05.mma kind::mxf4 GEMM fed by one slab of pixels per tile from a bordered 4-bit image, unit scales, + PReLU)" if slab else
+                                            "gemm_tc_kernel<F4=true, ATMA=true, QF=true> (whole layer in one launch: quantiser warps write the 4-bit image, tcgen05.mma kind::mxf4 GEMM fed by im2col tensor copies, unit scales, + PReLU)" if fused else
                                             "gemm_tc_kernel<F4=true, ATMA=true> (tcgen05.mma kind::mxf4 GEMM fed by im2col tensor copies, unit scales, + PReLU)" if im2col else
                                             "gemm_tc_kernel<F4=true> (tcgen05.mma kind::mxf4 GEMM, unit scales, + PReLU)"), "tensor"
             gemm_peak = 4.0 * pk["bf16_tflops"]
@@ -721,7 +743,8 @@ def run_layer(args, name, type_, N_cfg, layer: Layer):
                 "hbm_algorithmic_bytes_per_launch": (in_bytes + out_bytes) if fused else None,
                 "hbm_frac": ((in_bytes + out_bytes) / (t_gemm * 1e-3) / 1e9 / pk["hbm_gbs"]) if fused else None},
             "roofline_pack": {
-                "kernel": ("quantise_tma_kernel<e2m1> (tensor-copy fed quantise to a 4-bit operand image)" if im2col else
+                "kernel": ("quantise_tma_kernel<e2m1> (tensor-copy fed quantise to a bordered 4-bit operand image)" if slab else
+                           "quantise_tma_kernel<e2m1> (tensor-copy fed quantise to a 4-bit operand image)" if im2col else
                            "pack_staged_kernel<IMG_OUT> (quantise + bit-pack to a packed image)" if implicit else "pack_staged_kernel (quantise + bit-pack + im2row)"), "bound": "hbm",
                 "achieved": pack_alg_bytes / (t_pack_eff * 1e-3) / 1e9 if t_pack_eff else None, "peak": pk["hbm_gbs"], "unit": "GB/s",
                 "frac": pack_alg_bytes / (t_pack_eff * 1e-3) / 1e9 / pk["hbm_gbs"] if t_pack_eff else None, "traffic": pack_traffic, "peak_source": pk["source"],
@@ -909,9 +932,10 @@ def main():
     ap.add_argument("--impl", choices=["ours", "reference"], default="ours")
     ap.add_argument("--workload", choices=sorted(WORKLOADS), default="tnn_conv_large")
     ap.add_argument("--gemm", choices=["auto", "popc", "i8tc", "f4tc"], default="auto")
-    ap.add_argument("--route", choices=["auto", "fused", "im2col", "implicit", "explicit"], default="auto",
+    ap.add_argument("--route", choices=["auto", "slab", "slab_fused", "fused", "im2col", "implicit", "explicit"], default="auto",
                     help="auto: the library's default layer route (fused where the layer qualifies and is large enough, "
                          "else im2col where it qualifies, else implicit); "
+                         "slab / slab_fused: stride-1 layers from a bordered 4-bit image, one slab of pixels per tile for all taps (two launches / one); "
                          "fused: quantise + GEMM fed by im2col tensor copies in ONE launch; "
                          "im2col: quantise to a 4-bit image + GEMM fed by im2col tensor copies; "
                          "implicit: quantise to bit planes + GEMM whose warps gather and expand their im2row rows; "

@@ -115,6 +115,9 @@ SIGNATURES = {
     "tnns_slab_workspace_bytes": (_sz, [_i] * 6),
     "tnns_cuda_slab_supported": (_i, [_vp, _vp, _vp]),
     "tnns_cuda_conv_slab_supported": (_i, [_vp, _vp, _vp, _vp, _i]),
+    "tnns_cuda_slab_preferred": (_i, [_vp, _vp, _vp]),
+    "tnns_cuda_conv_auto_algo": (_i, [_vp, _vp, _vp, _vp, _i]),
+    "tnns_cuda_conv_slab_one_launch_preferred": (_i, [_vp, _vp, _vp, _vp, _i]),
     "tnns_cuda_quantise_e2m1_bordered": (_i, [_vp, _i, _vp, _vp, _vp, _i, _i, _i, _i, _i, _i, _i, _vp]),
     "tnns_cuda_gemm_slab": (_i, [_vp, _vp, _vp, _vp, _pshape, C.c_float, _i, _i, _vp]),
     "tnns_cuda_gemm_slab_packed_out": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _i, _pshape, C.c_float, _i, _vp]),

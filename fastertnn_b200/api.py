@@ -331,6 +331,21 @@ class Context:
     def slab_supported(self, w: Weights, shape: Shape) -> bool:
         return bool(self.lib.tnns_cuda_slab_supported(self.handle, w.handle, C.byref(shape)))
 
+    def slab_preferred(self, w: Weights, shape: Shape) -> bool:
+        """Whether the library's own rule takes the slab-fed route for this layer."""
+        return bool(self.lib.tnns_cuda_slab_preferred(self.handle, w.handle, C.byref(shape)))
+
+    def conv_auto_algo(self, w: Weights, shape: Shape, d_x: int, layout=NCHW) -> int:
+        """The GEMM_* value conv() with GEMM_AUTO resolves to for this layer and input."""
+        return int(self.lib.tnns_cuda_conv_auto_algo(self.handle, w.handle, C.byref(shape), d_x, layout))
+
+    def slab_auto(self, w: Weights, shape: Shape, d_x: int, layout=NCHW) -> int:
+        """0: conv() with GEMM_AUTO does not take the slab-fed route; 1: it does, as two launches; 2: as one launch."""
+        return {GEMM_F4_SLAB: 1, GEMM_F4_SLAB_FUSED: 2}.get(self.conv_auto_algo(w, shape, d_x, layout), 0)
+
+    def conv_slab_one_launch_preferred(self, w: Weights, shape: Shape, d_x: int, layout=NCHW) -> bool:
+        return bool(self.lib.tnns_cuda_conv_slab_one_launch_preferred(self.handle, w.handle, C.byref(shape), d_x, layout))
+
     def conv_slab_supported(self, w: Weights, shape: Shape, d_x: int, layout=NCHW) -> bool:
         return bool(self.lib.tnns_cuda_conv_slab_supported(self.handle, w.handle, C.byref(shape), d_x, layout))
 

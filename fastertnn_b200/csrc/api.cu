@@ -441,6 +441,17 @@ int tnns_cuda_slab_supported(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* 
     return tnns_slab_supported(ctx, w, g, false) ? 1 : 0;
 }
 
+// Where the library itself prefers the slab-fed route (tnns_cuda_conv with TNNS_GEMM_AUTO, ConvStack):
+// the layer qualifies and the padded lattice does not add too many rows that are computed and thrown away.
+int tnns_cuda_slab_preferred(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s) {
+    TnnsGeom g;
+    if (!ctx || !w || !s || tnns_make_geom(s, &g)) return 0;
+    if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW) return 0;
+    if (!tnns_slab_supported(ctx, w, g, false)) return 0;
+    const double useful = (double)g.OH * g.OW / ((double)(g.H + 2 * g.PH) * (g.W + 2 * g.PW));
+    return useful >= 0.75 ? 1 : 0;
+}
+
 // next_format of the public slab entry points -> (format, binary) of the launcher
 static int slab_next(int next_format, int* fmt, int* binary) {
     switch (next_format) {
@@ -524,6 +535,24 @@ int tnns_cuda_conv_slab_supported(const tnns_cuda_ctx* ctx, const tnns_cuda_weig
     if (!ctx || !w || !s || tnns_make_geom(s, &g)) return 0;
     if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW) return 0;
     return (tnns_slab_supported(ctx, w, g, true) && tnns_quantise_tma_supported(d_x, g.H, g.W, layout)) ? 1 : 0;
+}
+
+// The one-launch slab form is preferred under the same rule as the one-launch im2col form: every SM has
+// at least four 128-row tiles, so that the quantisation of later images hides under earlier tiles.
+int tnns_cuda_conv_slab_one_launch_preferred(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout) {
+    if (!tnns_cuda_conv_slab_supported(ctx, w, s, d_x, layout)) return 0;
+    const long long rows = (long long)s->N * (s->H + 2 * s->PH) * (s->W + 2 * s->PW);
+    const long long tiles = ((rows + 127) / 128) * ((s->KN + 255) / 256);
+    return tiles >= 4LL * ctx->sm_count ? 1 : 0;
+}
+
+// The algorithm tnns_cuda_conv / _conv_ws resolve TNNS_GEMM_AUTO (with TNNS_PACK_AUTO) to, workspace permitting.
+int tnns_cuda_conv_auto_algo(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout) {
+    if (!ctx || !w || !s) return TNNS_GEMM_AUTO;
+    if (layout == TNNS_NCHW && tnns_cuda_slab_preferred(ctx, w, s) && tnns_cuda_conv_slab_supported(ctx, w, s, d_x, layout))
+        return tnns_cuda_conv_slab_one_launch_preferred(ctx, w, s, d_x, layout) ? TNNS_GEMM_F4_SLAB_FUSED : TNNS_GEMM_F4_SLAB;
+    if (tnns_cuda_conv_fused_preferred(const_cast<tnns_cuda_ctx*>(ctx), w, s, d_x, layout)) return TNNS_GEMM_F4_FUSED;
+    return TNNS_GEMM_F4_TC;
 }
 
 // --- chained layers without the fp32 round trip ------------------------------------------------
@@ -652,6 +681,16 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
     if (workspace_bytes < need) return tnns_fail(TNNS_ERR_INVALID, "workspace of %zu bytes, need %zu", workspace_bytes, need);
     TNNS_ENTER(ctx, w);
     if (g.N == 0) return TNNS_OK;
+    const bool auto_both = pack_algo == TNNS_PACK_AUTO && gemm_algo == TNNS_GEMM_AUTO;
+    if (auto_both) {
+        // the library's own choice; a slab-fed form is taken only when the caller's workspace holds its bordered image
+        const int pick = tnns_cuda_conv_auto_algo(ctx, w, s, d_x, layout);
+        if (pick == TNNS_GEMM_F4_SLAB || pick == TNNS_GEMM_F4_SLAB_FUSED) {
+            const size_t ws_need = pick == TNNS_GEMM_F4_SLAB_FUSED ? tnns_slab_workspace_bytes(g.N, g.C, g.H, g.W, g.PH, g.PW)
+                                                                   : tnns_bordered_image_bytes(g.N, g.C, g.H, g.W, g.PH, g.PW);
+            if ((reinterpret_cast<uintptr_t>(d_workspace) & 127) == 0 && ws_need <= workspace_bytes) gemm_algo = pick;
+        }
+    }
     if (gemm_algo == TNNS_GEMM_F4_SLAB || gemm_algo == TNNS_GEMM_F4_SLAB_FUSED) {
         // stride-1 layers from a bordered 4-bit image: one slab of pixels per tile serves every filter tap
         const bool one_launch = gemm_algo == TNNS_GEMM_F4_SLAB_FUSED;
@@ -672,7 +711,7 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
     // route (pack to the im2row matrix, then GEMM).
     // Where the layer qualifies (ternary activations, C a multiple of 256) the image is written as
     // 4-bit operands and the copy engine delivers the GEMM's activation tiles (im2col tensor copies).
-    if (gemm_algo == TNNS_GEMM_F4_FUSED || (pack_algo == TNNS_PACK_AUTO && gemm_algo == TNNS_GEMM_AUTO)) {
+    if (gemm_algo == TNNS_GEMM_F4_FUSED || auto_both) {
         // one launch: the quantise step runs inside the GEMM kernel.  Taken on request, and by
         // default where every SM has several tiles, so that the quantisation of later images hides
         // under the MMAs of earlier ones (with one or two tiles per SM the two steps mostly run one

@@ -35,7 +35,7 @@ namespace {
 
 constexpr int SL_MAXSLAB = 4;    // slab buffers at most
 constexpr int SL_MAXSTG = 12;    // weight ring depth at most
-constexpr int SL_TAPMAX = 256;   // filter taps at most
+constexpr int SL_TAPMAX = 4096;  // filter taps at most
 constexpr int SL_BAR_BYTES = 512;
 
 struct SlabArgs {
@@ -101,9 +101,7 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
                    bar_tempty = smem_u32(bars + 2 * SL_MAXSLAB + 2 * SL_MAXSTG + 2);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * SL_MAXSLAB + 2 * SL_MAXSTG + 4);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-    // per tap: what to add to a slab's descriptor to start at the tap's first row (units of 16 bytes)
-    uint32_t* s_tapoff = reinterpret_cast<uint32_t*>(reinterpret_cast<unsigned char*>(bars) + SL_BAR_BYTES);
-    unsigned char* q_ring = reinterpret_cast<unsigned char*>(s_tapoff) + SL_TAPMAX * 4;
+    unsigned char* q_ring = reinterpret_cast<unsigned char*>(bars) + SL_BAR_BYTES;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -114,7 +112,6 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
     const int unit = blockIdx.x / CG, nunits = gridDim.x / CG;
     const int SPG = (TAPS == 1) ? p.T : p.nchunks;  // weight stages per slab
 
-    for (int t = tid; t < p.T; t += blockDim.x) s_tapoff[t] = (uint32_t)(((t / p.KW) * p.Wp + (t % p.KW)) * (RB / 16));
     if (tid == 0) {
         for (int s = 0; s < SL_MAXSLAB; s++) {
             mbar_init(bar_sfull + 8 * s, 1);
@@ -224,14 +221,71 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
             }
         }
     } else if (warp == WARP_MMA) {
-        if (lane == 0 && rank == 0) {
+        if (lane == 0 && rank == 0) {  // pair: the first block issues for both
+            // This one thread's instruction stream paces the tensor pipe.  Two things measured on this loop:
+            // nothing that touches shared memory may stand between two MMAs (a table look-up per tap, queued
+            // behind the MMAs just issued, cost 60 clocks per MMA: tap offsets are running counters), and the
+            // MMAs of a tile must sit in ONE divergent region (issued one by one from `if (leader)` branches of
+            // a warp-wide loop, every reconvergence waited for the MMA before it: three times slower).
             uint32_t lt = 0, sl = 0, slph = 0, s = 0, ph = 0;
             bool first_tile = true;
             const uint64_t da0 = make_desc_taps(smem_u32(sA), TAPS), db0 = make_desc(smem_u32(sB));
             const uint32_t slab16 = (uint32_t)(p.slab_bytes >> 4);
+            const uint32_t row16 = (uint32_t)(p.Wp * (RB / 16));  // one image row further down the slab, in descriptor units
+            const uint32_t a_lo0 = (uint32_t)da0, a_hi = (uint32_t)(da0 >> 32), b_lo0 = (uint32_t)db0, b_hi = (uint32_t)(db0 >> 32);
+            const uint32_t sfa = tmem_base + SF_COL, sfb = tmem_base + SF_COL + 16;
+            if (p.T == 9 && p.KW == 3) {
+                // 3x3 filters: the nine tap offsets live in registers and every MMA of a slab is issued from straight-line
+                // code -- one 32-bit add per operand and MMA.  (The generic loop below spends a dozen dependent
+                // instructions between two MMAs; with the epilogue warps competing for the same scheduler that cost
+                // 250 clocks per MMA on 64-kernel tiles against 85 for the instruction alone.)
+                uint32_t aoff[9];
+#pragma unroll
+                for (int j = 0; j < 9; j++) aoff[j] = (uint32_t)((j / 3) * p.Wp + (j % 3)) * (RB / 16);
+                constexpr int KPT = 4 / TAPS;               // K steps (32 bytes) per tap: 1, 2 or 4
+                for (int t = unit; t < ntiles; t += nunits, lt++, first_tile = false) {
+                    const int buf = lt & 1;
+                    if (!mbar_wait(OVL ? bar_tempty : bar_tempty + 8 * buf, (OVL ? (lt & 1) : ((lt >> 1) & 1)) ^ 1, abort_flag, p.status, 2)) goto done;
+                    tc_fence_after();
+                    const uint32_t d_tmem = tmem_base + buf * ACC_OFF;
+                    uint32_t acc = 0;
+                    for (int cg = 0; cg < p.G; cg++) {
+                        if (!mbar_wait(bar_sfull + 8 * sl, slph, abort_flag, p.status, 0x13)) goto done;
+                        tc_fence_after();
+                        const uint32_t slab_lo = a_lo0 + sl * slab16;
+                        uint32_t b_lo = 0;
+#pragma unroll
+                        for (int q = 0; q < 9 * KPT; q++) {   // K step q: tap q / KPT, stage q / 4
+                            const int k = q & 3;
+                            if (k == 0) {
+                                const int j = q >> 2;
+                                const int c = (TAPS == 1) ? j * p.G + cg : j;
+                                const uint32_t slot = p.b_resident ? (uint32_t)c : s;
+                                if (!p.b_resident || first_tile) {
+                                    if (!mbar_wait(bar_bfull + 8 * slot, p.b_resident ? 0u : ph, abort_flag, p.status, 3)) goto done;
+                                    tc_fence_after();
+                                }
+                                b_lo = b_lo0 + slot * (uint32_t)(B_STAGE >> 4);
+                            }
+                            const uint32_t a_lo = slab_lo + aoff[q / KPT] + 2u * (uint32_t)(q % KPT);
+                            if (CG == 2) tc_mma_f4_pair_lh(d_tmem, a_lo, a_hi, b_lo + 2u * k, b_hi, IDESC, sfa, sfb, acc);
+                            else tc_mma_f4_lh(d_tmem, a_lo, a_hi, b_lo + 2u * k, b_hi, IDESC, sfa, sfb, acc);
+                            acc = 1;
+                            if ((k == 3 || q == 9 * KPT - 1) && !p.b_resident) {
+                                if (CG == 2) tc_commit_pair(bar_bempty + 8 * s); else tc_commit(bar_bempty + 8 * s);
+                                if (++s == (uint32_t)p.nstg) { s = 0; ph ^= 1; }
+                            }
+                        }
+                        if (CG == 2) tc_commit_pair(bar_sempty + 8 * sl); else tc_commit(bar_sempty + 8 * sl);
+                        if (++sl == (uint32_t)p.nslab) { sl = 0; slph ^= 1; }
+                    }
+                    if (CG == 2) tc_commit_pair(bar_tfull + 8 * buf); else tc_commit(bar_tfull + 8 * buf);
+                }
+            } else
             for (int t = unit; t < ntiles; t += nunits, lt++, first_tile = false) {
                 const int buf = lt & 1;
-                if (!mbar_wait(OVL ? bar_tempty : bar_tempty + 8 * buf, (OVL ? (lt & 1) : ((lt >> 1) & 1)) ^ 1, abort_flag, p.status, 2)) goto done;
+                if (!mbar_wait(OVL ? bar_tempty : bar_tempty + 8 * buf, (OVL ? (lt & 1) : ((lt >> 1) & 1)) ^ 1, abort_flag, p.status, 2))
+                    goto done;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * ACC_OFF;
                 uint32_t acc = 0;
@@ -239,6 +293,10 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
                     if (!mbar_wait(bar_sfull + 8 * sl, slph, abort_flag, p.status, 0x13)) goto done;
                     tc_fence_after();
                     const uint64_t da = da0 + (uint64_t)(sl * slab16);
+                    // tap (kh, kw) starts kh*Wp + kw rows into the slab: kept as running counters -- a table in
+                    // shared memory would put a load, queued behind the MMAs just issued, in front of every MMA
+                    uint32_t kwc = 0, rowoff = 0, tapoff = 0;
+                    int tap = 0;
                     for (int j = 0; j < SPG; j++) {
                         const int c = (TAPS == 1) ? j * p.G + cg : j;
                         const uint32_t slot = p.b_resident ? (uint32_t)c : s;
@@ -250,13 +308,19 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
 #pragma unroll
                         for (int k = 0; k < 4; k++) {
                             // K step k of the stage = 64 elements = 32 bytes of one tap's pixel row
-                            const int tap = (TAPS == 1) ? j : (TAPS == 2 ? 2 * c + (k >> 1) : 4 * c + k);
                             const uint32_t koff = (TAPS == 1) ? 2u * k : (TAPS == 2 ? 2u * (k & 1) : 0u);
                             if (TAPS == 1 || tap < p.T) {
-                                const uint64_t dak = da + (uint64_t)(s_tapoff[tap] + koff);
+                                const uint64_t dak = da + (uint64_t)(tapoff + koff);
                                 if (CG == 2) tc_mma_f4_pair(d_tmem, dak, db + 2 * k, IDESC, tmem_base + SF_COL, tmem_base + SF_COL + 16, acc);
                                 else tc_mma_f4(d_tmem, dak, db + 2 * k, IDESC, tmem_base + SF_COL, tmem_base + SF_COL + 16, acc);
                                 acc = 1;
+                            }
+                            // the next K step belongs to the next tap: after every step (32-byte pixels), every second
+                            // (64-byte pixels) or the stage's last (128-byte pixels)
+                            if (TAPS == 4 || (TAPS == 2 && (k & 1)) || (TAPS == 1 && k == 3)) {
+                                tap++;
+                                if (++kwc == (uint32_t)p.KW) { kwc = 0; rowoff += row16; tapoff = rowoff; }
+                                else tapoff += RB / 16;
                             }
                         }
                         if (!p.b_resident) {
@@ -560,7 +624,7 @@ bool choose_form(int sm_count, const tnns_cuda_weights* w, const TnnsGeom& g, in
     if (pairs_req == 2 && pl.bn != 256) return false;
     ch->pairs = pl.bn == 256 && (pairs_req == 2 || (pairs_req == 0 && pair_tiles >= sm_count / 2));
     ch->b_stage = (pl.bn / (ch->pairs ? 2 : 1)) * KCH;
-    ch->fixed = 1024 + SL_BAR_BYTES + SL_TAPMAX * 4 + (fused ? Q_STG * Q_PIX * 64 * 4 + 128 : 0);
+    ch->fixed = 1024 + SL_BAR_BYTES + (fused ? Q_STG * Q_PIX * 64 * 4 + 128 : 0);
     if (!ring_depths(pl, ch->b_stage, ch->fixed, w->Kp / 4, ch->ntn == 1, &ch->nslab, &ch->nstg, &ch->resident)) return false;
     ch->smem = (size_t)ch->fixed + (size_t)ch->nslab * pl.slab_bytes + (size_t)ch->nstg * ch->b_stage;
     return true;

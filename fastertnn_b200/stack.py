@@ -32,7 +32,7 @@ class ConvStack:
     behind it); otherwise they are an error."""
 
     def __init__(self, ctx: api.Context, type_: int, layers: list[Layer], packed_weights: list[np.ndarray], batch: int,
-                 threshold: float, alpha: float = 0.5, layout: int = api.NCHW, chain: str = "fp32", reinterpret_links: bool = False):
+                 threshold: float, alpha: float = 0.5, layout: int = api.NCHW, chain: str = "fp32", reinterpret_links: bool = False, use_slab: bool = True):
         assert len(layers) == len(packed_weights)
         self.link_ok = []
         for a, b in zip(layers, layers[1:]):
@@ -63,28 +63,50 @@ class ConvStack:
         elif chain == "image":
             if layout != api.NCHW:
                 raise ValueError("the image chain is defined for NCHW input and output")
-            if not self.act_ternary:
-                raise ValueError("4-bit operand images hold ternary activations")
-            self.fast = [ctx.im2col_supported(w, L.shape(batch)) for w, L in zip(self.weights, layers)]
-            img = max([max(api.e2m1_image_bytes(batch, L.C, L.H, L.W), api.e2m1_image_bytes(batch, L.KN, L.OH, L.OW)) for L in layers])
-            self.d_imgs = [ctx.malloc(img), ctx.malloc(img)]  # ping-pong quantised activations (either format fits)
+            n = len(layers)
+            shapes = [L.shape(batch) for L in layers]
+            self.fast = [self.act_ternary and ctx.im2col_supported(w, sh) for w, sh in zip(self.weights, shapes)]
+            self.run_first = [i == 0 or not self.link_ok[i - 1] for i in range(n)]
+            self.run_last = [i == n - 1 or not self.link_ok[i] for i in range(n)]
+            # mode of every layer = the format its input arrives in:
+            #   "slab"    bordered 4-bit image (stride-1 layers; the only 4-bit form of binary activations).  Its
+            #             producer is the quantise step of a run's first layer, or a slab-fed predecessor whose
+            #             padded lattice is this layer's (its epilogue then writes this image with its border)
+            #   "im2col"  plain 4-bit image read through im2col tensor copies
+            #   "planes"  bit planes + im2row from planes
+            want_slab = [use_slab and ctx.slab_preferred(w, sh) for w, sh in zip(self.weights, shapes)]
+            self.mode = []
+            for i, L in enumerate(layers):
+                ok = want_slab[i] and (self.run_first[i] or (self.mode[i - 1] == "slab" and
+                                                            (layers[i - 1].H + 2 * layers[i - 1].P, layers[i - 1].W + 2 * layers[i - 1].P) ==
+                                                            (L.H + 2 * L.P, L.W + 2 * L.P)))
+                self.mode.append("slab" if ok else "im2col" if self.fast[i] else "planes")
+            if not self.act_ternary and any(m != "slab" for m in self.mode):
+                raise ValueError("binary activations travel as 4-bit images only between slab-fed (stride-1, same-size) layers; use chain='packed'")
+            img = max([max(api.bordered_image_bytes(batch, L.C, L.H, L.W, L.P, L.P), api.e2m1_image_bytes(batch, L.KN, L.OH, L.OW),
+                           api.bordered_image_bytes(batch, L.KN, L.OH, L.OW, L.P, L.P)) for L in layers])
+            self.d_imgs = [ctx.malloc(img), ctx.malloc(img)]  # ping-pong quantised activations (any format fits)
             self.extra = list(self.d_imgs)
             # a layer that starts a run (the first layer, and every layer behind a reinterpreted link)
             # reads fp32: in one launch (quantise step inside the GEMM kernel) where the library itself
-            # would choose that route; its workspace holds the input's 4-bit image
-            n = len(layers)
-            self.run_first = [i == 0 or not self.link_ok[i - 1] for i in range(n)]
-            self.run_last = [i == n - 1 or not self.link_ok[i] for i in range(n)]
-            self.fuse = [bool(self.run_first[i] and self.fast[i] and ctx.conv_fused_preferred(self.weights[i], layers[i].shape(batch), self.buf[0], layout))
-                         for i in range(n)]
+            # would choose that form; its workspace holds the input's 4-bit image
+            self.fuse = []
+            for i, (L, w, sh) in enumerate(zip(layers, self.weights, shapes)):
+                if not self.run_first[i]:
+                    self.fuse.append(False)
+                elif self.mode[i] == "slab":
+                    self.fuse.append(bool(ctx.conv_slab_one_launch_preferred(w, sh, self.buf[0], layout)))
+                else:
+                    self.fuse.append(bool(self.mode[i] == "im2col" and ctx.conv_fused_preferred(w, sh, self.buf[0], layout)))
             self.fuse_first = self.fuse[0]
-            self.ws0_bytes = max([api.fused_workspace_bytes(batch, L.C, L.H, L.W) for L, f in zip(layers, self.fuse) if f] + [0])
+            self.ws0_bytes = max([max(api.fused_workspace_bytes(batch, L.C, L.H, L.W), api.slab_workspace_bytes(batch, L.C, L.H, L.W, L.P, L.P))
+                                  for L, f in zip(layers, self.fuse) if f] + [0])
             if self.ws0_bytes:
                 self.d_ws0 = ctx.malloc(self.ws0_bytes)
                 self.extra.append(self.d_ws0)
             self.d_a = None
-            if not all(self.fast):
-                self.d_a = ctx.malloc(max(api.packed_bytes(type_, L.shape(batch)) for L, f in zip(layers, self.fast) if not f))
+            if any(m == "planes" for m in self.mode):
+                self.d_a = ctx.malloc(max(api.packed_bytes(type_, L.shape(batch)) for L, m in zip(layers, self.mode) if m == "planes"))
                 self.extra.append(self.d_a)
             self._out = self.buf[sum(self.run_last) % 2]
         elif chain != "fp32":
@@ -114,31 +136,51 @@ class ConvStack:
             return
         if self.chain == "image":
             fp, k = self.buf[0], 0  # fp32 tensor the current run of layers starts from; runs finished so far
+            tern = self.act_ternary
             for i, (L, w) in enumerate(zip(self.layers, self.weights)):
                 shape = L.shape(self.batch)
                 src, dst = self.d_imgs[i % 2], self.d_imgs[(i + 1) % 2]
                 last = self.run_last[i]
                 out_fp = self.buf[(k + 1) % 2]
-                nxt = 2 if (not last and self.fast[i + 1]) else 1  # 4-bit image or ternary bit planes for the consumer
+                mode = self.mode[i]
+                # what the consumer reads: bordered 4-bit image (3 ternary / 5 binary), plain 4-bit image (2), bit planes (1 / 0)
+                nxt, nxt_pad = 1 if tern else 0, (0, 0)
+                if not last:
+                    Ln = self.layers[i + 1]
+                    if self.mode[i + 1] == "slab":
+                        nxt, nxt_pad = (3 if tern else 5), (Ln.P, Ln.P)
+                    elif self.mode[i + 1] == "im2col":
+                        nxt = 2
                 if self.run_first[i] and not self.fuse[i]:
                     # the run's input, in the format its first layer reads
-                    if self.fast[i]:
+                    if mode == "slab":
+                        self.ctx.quantise_e2m1_bordered(tern, fp, self.d_thr, src, self.batch, L.C, L.H, L.W, L.P, L.P, self.layout, stream)
+                    elif mode == "im2col":
                         self.ctx.quantise_e2m1(fp, self.d_thr, src, self.batch, L.C, L.H, L.W, self.layout, stream)
                     else:
-                        self.ctx.quantise(True, fp, self.d_thr, src, self.batch, L.C, L.H, L.W, self.layout, stream)
-                if self.fuse[i]:
-                    if not last:
-                        self.ctx.conv_fused_packed_out(w, fp, self.d_thr, dst, self.d_thr, nxt, self.d_ws0, self.ws0_bytes, shape,
-                                                       self.alpha, 0, stream)
+                        self.ctx.quantise(tern, fp, self.d_thr, src, self.batch, L.C, L.H, L.W, self.layout, stream)
+                if mode == "slab":
+                    if self.fuse[i]:
+                        if not last:
+                            self.ctx.conv_slab_packed_out(w, fp, self.d_thr, dst, self.d_thr, nxt, nxt_pad, self.d_ws0, self.ws0_bytes, shape, self.alpha, 0, stream)
+                        else:
+                            self.ctx.conv_slab(w, fp, self.d_thr, out_fp, self.d_ws0, self.ws0_bytes, shape, self.alpha, 0, stream)
+                    elif not last:
+                        self.ctx.gemm_slab_packed_out(w, src, dst, self.d_thr, nxt, nxt_pad, shape, self.alpha, stream)
                     else:
-                        self.ctx.conv_fused(w, fp, self.d_thr, out_fp, self.d_ws0, self.ws0_bytes, shape, self.alpha, 0, stream)
-                elif self.fast[i]:
-                    if not last:
+                        self.ctx.gemm_slab(w, src, out_fp, shape, self.alpha, self.layout, stream)
+                elif mode == "im2col":
+                    if self.fuse[i]:
+                        if not last:
+                            self.ctx.conv_fused_packed_out(w, fp, self.d_thr, dst, self.d_thr, nxt, self.d_ws0, self.ws0_bytes, shape, self.alpha, 0, stream)
+                        else:
+                            self.ctx.conv_fused(w, fp, self.d_thr, out_fp, self.d_ws0, self.ws0_bytes, shape, self.alpha, 0, stream)
+                    elif not last:
                         self.ctx.gemm_im2col_packed_out(w, src, dst, self.d_thr, nxt, shape, self.alpha, stream)
                     else:
                         self.ctx.gemm_im2col(w, src, out_fp, shape, self.alpha, self.layout, stream)
                 else:
-                    self.ctx.im2row_packed(True, src, self.d_a, shape, stream=stream)
+                    self.ctx.im2row_packed(tern, src, self.d_a, shape, stream=stream)
                     if not last:
                         self.ctx.gemm_packed_out(w, self.d_a, dst, self.d_thr, nxt, self.batch, L.OH, L.OW, self.alpha, stream=stream)
                     else:

@@ -335,6 +335,12 @@ int tnns_cuda_conv_fused_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights*
 size_t tnns_e2m1_bordered_image_bytes(int N, int C, int H, int W, int PH, int PW);
 size_t tnns_slab_workspace_bytes(int N, int C, int H, int W, int PH, int PW);
 int tnns_cuda_slab_supported(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s);
+/* 1 where the library's own rule (tnns_cuda_conv with TNNS_GEMM_AUTO) takes the slab-fed route for this layer. */
+int tnns_cuda_slab_preferred(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s);
+/* The tnns_gemm_algo that tnns_cuda_conv / _conv_ws resolve TNNS_GEMM_AUTO to for this layer and input
+ * (workspace permitting): _F4_SLAB_FUSED, _F4_SLAB, _F4_FUSED, or _F4_TC for the two-launch forms. */
+int tnns_cuda_conv_auto_algo(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout);
+int tnns_cuda_conv_slab_one_launch_preferred(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout);
 int tnns_cuda_conv_slab_supported(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout);
 int tnns_cuda_quantise_e2m1_bordered(tnns_cuda_ctx* ctx, int ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
                                      int W, int PH, int PW, int layout, void* stream);
