@@ -889,7 +889,7 @@ def run_stack(args, name, type_, N_cfg, layers):
             "data": "synthetic",
             "config": common_config(name, "stack", type_, N_total, layers, args.scaling),
             "impl_config": {"batch_per_gpu": nloc, "chain": chain,
-                            "routes": (["fused" if f else "im2col" if a else "planes" for f, a in zip(st.fuse, st.fast)] if chain == "image" else None),
+                            "routes": ([m + (" (one launch with its quantise step)" if f else "") for m, f in zip(st.mode, st.fuse)] if chain == "image" else None),
                             "l2": "the chain's activations (hundreds of MB at this batch) pass through the same ping-pong buffers every step; "
                                   "each layer's input was written by its predecessor, as in any chained run",
                             "check": "skipped" if args.no_check else "every rank compared its chain output with the CPU checker chained on the host before timing"},

@@ -441,15 +441,22 @@ int tnns_cuda_slab_supported(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* 
     return tnns_slab_supported(ctx, w, g, false) ? 1 : 0;
 }
 
-// Where the library itself prefers the slab-fed route (tnns_cuda_conv with TNNS_GEMM_AUTO, ConvStack):
-// the layer qualifies and the padded lattice does not add too many rows that are computed and thrown away.
+// Where the library itself prefers the slab-fed route (tnns_cuda_conv with TNNS_GEMM_AUTO, ConvStack).
+// Measured on B200, quantise + GEMM in us, slab-fed / im2col-fed (or, binary activations, gathering warps):
+//   256 x 64x56x56 -> 64      GEMM alone 55 / 93          256 x 128x28x28 -> 128   55 / 58
+//   1 x 256x56x56 -> 256 BTN  13.1 / 14.0                 64 x 512x32x32 -> 512 BTN  95 / 102
+//   64 x 512x32x32 -> 512     95 / 79 (one launch)        256 x 256x14x14 -> 256   37 / 35
+// The slab removes the per-tap copy requests, which is what bounds 32- and 64-byte pixels, and it is the only
+// copy-engine form of binary activations; on 128-byte pixels the tensor pipe bounds both forms and the padded
+// lattice's extra rows (13 % at 32x32, 31 % at 14x14) decide for the im2col form.
 int tnns_cuda_slab_preferred(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s) {
     TnnsGeom g;
     if (!ctx || !w || !s || tnns_make_geom(s, &g)) return 0;
     if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW) return 0;
     if (!tnns_slab_supported(ctx, w, g, false)) return 0;
     const double useful = (double)g.OH * g.OW / ((double)(g.H + 2 * g.PH) * (g.W + 2 * g.PW));
-    return useful >= 0.75 ? 1 : 0;
+    if (useful < 0.75) return 0;
+    return (!type_act_ternary(w->type) || g.Cp <= 2) ? 1 : 0;
 }
 
 // next_format of the public slab entry points -> (format, binary) of the launcher
@@ -537,13 +544,12 @@ int tnns_cuda_conv_slab_supported(const tnns_cuda_ctx* ctx, const tnns_cuda_weig
     return (tnns_slab_supported(ctx, w, g, true) && tnns_quantise_tma_supported(d_x, g.H, g.W, layout)) ? 1 : 0;
 }
 
-// The one-launch slab form is preferred under the same rule as the one-launch im2col form: every SM has
-// at least four 128-row tiles, so that the quantisation of later images hides under earlier tiles.
+// The one-launch slab form (quantiser warps inside the GEMM kernel) measured slower than its two launches on
+// every shape tried (64 x 512x32x32 -> 512: 98 against 95 us; 256 x 128x28x28 -> 128: 86 against 55), so the
+// library never picks it by itself; it stays available on request (TNNS_GEMM_F4_SLAB_FUSED, tnns_cuda_conv_slab).
 int tnns_cuda_conv_slab_one_launch_preferred(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout) {
-    if (!tnns_cuda_conv_slab_supported(ctx, w, s, d_x, layout)) return 0;
-    const long long rows = (long long)s->N * (s->H + 2 * s->PH) * (s->W + 2 * s->PW);
-    const long long tiles = ((rows + 127) / 128) * ((s->KN + 255) / 256);
-    return tiles >= 4LL * ctx->sm_count ? 1 : 0;
+    (void)ctx; (void)w; (void)s; (void)d_x; (void)layout;
+    return 0;
 }
 
 // The algorithm tnns_cuda_conv / _conv_ws resolve TNNS_GEMM_AUTO (with TNNS_PACK_AUTO) to, workspace permitting.

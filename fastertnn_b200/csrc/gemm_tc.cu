@@ -415,6 +415,13 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
             uint32_t lt = 0, s = 0, ph = 0;
             constexpr int KPS = 4 / TAPS;                       // 32-byte K steps per sub-tile
             const uint64_t da0 = make_desc_taps(smem_u32(sA), TAPS), db0 = make_desc(smem_u32(sB));
+            // Only a descriptor's low word (the address, in 16-byte units) changes from stage to stage and from K
+            // step to K step: the loop does 32-bit adds on running low words and nothing else between two MMAs.
+            // Measured on the slab-fed twin of this loop: every dependent instruction in front of an MMA costs
+            // this thread, which shares its scheduler with two epilogue warps, about ten clocks of issue time.
+            const uint32_t a_lo0 = (uint32_t)da0, a_hi = (uint32_t)(da0 >> 32), b_lo0 = (uint32_t)db0, b_hi = (uint32_t)(db0 >> 32);
+            const uint32_t sfa = tmem_base + SF_COL, sfb = tmem_base + SF_COL + 16;
+            uint32_t a_lo = a_lo0, b_lo = b_lo0;                // descriptors of ring slot s
             for (long long t = unit; t < ntiles; t += nunits, lt++) {
                 const int buf = lt % NBUF;
                 // overlapping sets: one barrier, completed once per tile when the columns shared
@@ -422,25 +429,27 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                 if (!mbar_wait(OVL ? bar_tempty : bar_tempty + 8 * buf, (OVL ? (lt & 1) : ((lt / NBUF) & 1)) ^ 1, abort_flag, p.status, 2)) goto done;
                 tc_fence_after();
                 const uint32_t d_tmem = tmem_base + buf * ACC_OFF;
+                uint32_t acc = 0;
                 for (int c = 0; c < nchunks; c++) {
                     if (!mbar_wait(bar_full + 8 * s, ph, abort_flag, p.status, 3)) goto done;
                     tc_fence_after();
-                    const uint64_t db = db0 + (uint64_t)(s * (B_STAGE >> 4));
 #pragma unroll
                     for (int mt = 0; mt < MT; mt++) {
-                        const uint64_t da = da0 + (uint64_t)(s * (A_STAGE >> 4) + mt * (A_SUB >> 4));
 #pragma unroll
                         for (int k = 0; k < KCH / 32; k++) {
                             // K step k: sub-tile k / KPS, 32 bytes x (k % KPS) into its rows
-                            const uint64_t dak = da + (uint64_t)((k / KPS) * ((A_STAGE / TAPS) >> 4) + 2 * (k % KPS));
-                            if (CG == 2) tc_mma_f4_pair(d_tmem, dak, db + 2 * k, IDESC, tmem_base + SF_COL, tmem_base + SF_COL + 16, (c | k) ? 1u : 0u);
-                            else if (F4) tc_mma_f4(d_tmem + mt * BN, dak, db + 2 * k, IDESC, tmem_base + SF_COL, tmem_base + SF_COL + 16, (c | k) ? 1u : 0u);
-                            else tc_mma_i8(d_tmem + mt * BN, dak, db + 2 * k, IDESC, (c | k) ? 1u : 0u);
+                            constexpr int SUB16 = (A_STAGE / TAPS) >> 4;
+                            const uint32_t ak = a_lo + (uint32_t)(mt * (A_SUB >> 4) + (k / KPS) * SUB16 + 2 * (k % KPS));
+                            if (CG == 2) tc_mma_f4_pair_lh(d_tmem, ak, a_hi, b_lo + 2 * k, b_hi, IDESC, sfa, sfb, acc | (uint32_t)k);
+                            else if (F4) tc_mma_f4_lh(d_tmem + mt * BN, ak, a_hi, b_lo + 2 * k, b_hi, IDESC, sfa, sfb, acc | (uint32_t)k);
+                            else tc_mma_i8(d_tmem + mt * BN, ((uint64_t)a_hi << 32) | ak, ((uint64_t)b_hi << 32) | (b_lo + 2 * k), IDESC, (c | k) ? 1u : 0u);
                         }
                     }
+                    acc = 1;
                     // stage reusable once these MMAs have read it (pair: in both blocks)
                     if (CG == 2) tc_commit_pair(bar_empty + 8 * s); else tc_commit(bar_empty + 8 * s);
-                    if (++s == NSTG) { s = 0; ph ^= 1; }
+                    if (++s == NSTG) { s = 0; ph ^= 1; a_lo = a_lo0; b_lo = b_lo0; }
+                    else { a_lo += A_STAGE >> 4; b_lo += B_STAGE >> 4; }
                 }
                 // accumulator complete (pair: each block's epilogue drains its own 128 rows)
                 if (CG == 2) tc_commit_pair(bar_tfull + 8 * buf); else tc_commit(bar_tfull + 8 * buf);

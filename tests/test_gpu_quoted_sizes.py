@@ -58,8 +58,8 @@ def test_large_layer_full_batch_on_the_default_route(type_, gpu_ctx, checker):
 def test_resnet18_style_stack_at_batch_256(gpu_ctx, checker):
     """The 11-layer ternary stack at the batch its figure is quoted on (256): all three ways of
     chaining on the device against the checker chained on the host, every byte of the final
-    256 x 512 x 7 x 7 output.  At this batch the first layers have thousands of tiles and take the
-    one-launch route, which a small batch never reaches."""
+    256 x 512 x 7 x 7 output.  At this batch every layer has thousands of tiles and block pairs and
+    the one-launch forms are reached, which a small batch never does."""
     from fastertnn_b200.stack import ConvStack
     N = RESNET18_STACK_BATCH
     L0 = RESNET18_STACK[0]
@@ -74,7 +74,7 @@ def test_resnet18_style_stack_at_batch_256(gpu_ctx, checker):
         st = ConvStack(gpu_ctx, TNN, RESNET18_STACK, pws, N, 0.25, chain=chain)
         try:
             if chain == "image":
-                assert st.fuse_first, "at batch 256 the first layer takes the one-launch route"
+                assert st.mode[:2] == ["slab", "slab"], "the two 64-channel layers take the slab-fed route"
             gpu_ctx.fill(st.input_ptr(), x)
             st.run()
             gpu_ctx.sync()
