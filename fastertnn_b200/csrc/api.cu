@@ -616,12 +616,13 @@ int tnns_cuda_conv_fused_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights*
 }
 
 // The rule tnns_cuda_conv applies with TNNS_GEMM_AUTO: the one-launch route where the layer qualifies
-// and every SM has at least four 128-row tiles.
+// and every SM has at least three 128-row tiles (measured, one launch / two launches in us: 32 images of
+// 512x32x32 -> 512, 3.5 tiles per SM: 49 / 54; 256 x 256x14x14 -> 256, 2.6: 43 / 40; 16 images, 1.7: 33 / 31.5).
 int tnns_cuda_conv_fused_preferred(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout) {
     if (!ctx || !tnns_cuda_conv_fused_supported(w, s, d_x, layout)) return 0;
     const long long tiles = (((long long)s->N * tnns_out_dim(s->H, s->PH, s->KH, s->SH) * tnns_out_dim(s->W, s->PW, s->KW, s->SW) + 127) / 128) *
                             ((s->KN + 255) / 256);
-    return tiles >= 4LL * ctx->sm_count ? 1 : 0;
+    return tiles >= 3LL * ctx->sm_count ? 1 : 0;
 }
 
 size_t tnns_packed_image_bytes(int ternary, int N, int C, int H, int W) {

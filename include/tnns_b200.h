@@ -294,13 +294,13 @@ int tnns_cuda_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const 
  * other stream use the words in the workspace, which the call clears on `stream` first.  The first
  * call may allocate those words (and synchronise the device); keep it out of stream capture.  Same
  * result as every other route.  tnns_cuda_conv / _conv_ws take it with gemm_algo
- * TNNS_GEMM_F4_FUSED, and with TNNS_GEMM_AUTO where the layer has several tiles per SM. */
+ * TNNS_GEMM_F4_FUSED, and with TNNS_GEMM_AUTO where the layer has at least three tiles per SM. */
 size_t tnns_fused_workspace_bytes(int N, int C, int H, int W);
 int tnns_cuda_conv_fused_supported(const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout);
 int tnns_cuda_conv_fused(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y,
                          void* d_workspace, size_t workspace_bytes, const tnns_shape_t* s, float alpha, int pairs, void* stream);
 /* 1 where tnns_cuda_conv with TNNS_GEMM_AUTO takes that route by itself (the layer qualifies and
- * every SM has at least four 128-row tiles), else 0. */
+ * every SM has at least three 128-row tiles), else 0. */
 int tnns_cuda_conv_fused_preferred(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout);
 /* The same launch as the first layer of a chain (src/timing_layers.c:188-201 chains layers through fp32
  * buffers): fp32 input in, and instead of the fp32 output the next layer's quantised activations
