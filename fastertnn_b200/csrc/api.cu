@@ -684,8 +684,6 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
     if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW)
         return tnns_fail(TNNS_ERR_INVALID, "shape (KN=%d C=%d %dx%d) does not match the uploaded weights (KN=%d C=%d %dx%d)", s->KN,
                          s->C, s->KH, s->KW, w->KN, w->C, w->KH, w->KW);
-    const size_t need = tnns_packed_bytes(w->type, s);
-    if (workspace_bytes < need) return tnns_fail(TNNS_ERR_INVALID, "workspace of %zu bytes, need %zu", workspace_bytes, need);
     TNNS_ENTER(ctx, w);
     if (g.N == 0) return TNNS_OK;
     const bool auto_both = pack_algo == TNNS_PACK_AUTO && gemm_algo == TNNS_GEMM_AUTO;
@@ -750,6 +748,10 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
         return tnns_launch_gemm_tc(ctx, w, d_workspace, d_y, (long long)g.N * g.OH * g.OW, g.OH * g.OW, alpha, layout, true,
                                    (cudaStream_t)stream, nullptr, nullptr, 1, &g);
     }
+    // the explicit route materialises the im2row matrix
+    const size_t need = tnns_packed_bytes(w->type, s);
+    if (workspace_bytes < need)
+        return tnns_fail(TNNS_ERR_INVALID, "workspace of %zu bytes; the packed im2row matrix this route writes needs %zu", workspace_bytes, need);
     rc = tnns_cuda_pack(ctx, type_act_ternary(w->type), d_x, d_thr, (int64_t*)d_workspace, s, layout, pack_algo, stream);
     if (rc) return rc;
     return tnns_cuda_gemm(ctx, w, (const int64_t*)d_workspace, d_y, g.N, g.OH, g.OW, alpha, layout, gemm_algo, stream);

@@ -520,7 +520,11 @@ int launch_slab(tnns_cuda_ctx* ctx, const SlabArgs& a, size_t smem, cudaStream_t
     using Cfg = SlabCfg<BN, CG, TAPS, QF>;
     auto kern = gemm_slab_kernel<BN, CG, TAPS, QF>;
     static const CUtensorMap no_map = {};
-    TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_MAX));
+    static bool smem_set[64] = {false};  // once per kernel and device
+    if (!smem_set[ctx->device & 63]) {
+        TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::SMEM_MAX));
+        smem_set[ctx->device & 63] = true;
+    }
     const long long tiles = (long long)((a.Mv + CG * BM - 1) / (CG * BM)) * ((a.KN + BN - 1) / BN);
     cudaLaunchAttribute attr[2];
     int nattr = 0;

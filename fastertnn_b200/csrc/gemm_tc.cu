@@ -850,7 +850,12 @@ int launch_cfg(tnns_cuda_ctx* ctx, const GemmArgs& a, cudaStream_t stream, const
     using Cfg = TcCfg<BN, MT, F4, ATMA, CG, TAPS, QF>;
     auto kern = gemm_tc_kernel<BN, MT, F4, ATMA, CG, TAPS, QF>;
     static const CUtensorMap no_map = {};
-    TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
+    // once per kernel and device: the attribute belongs to (function, device), and the call costs a microsecond per launch
+    static bool smem_set[64] = {false};
+    if (!smem_set[ctx->device & 63]) {
+        TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)Cfg::SMEM));
+        smem_set[ctx->device & 63] = true;
+    }
     const long long tiles = ((a.M + CG * MT * BM - 1) / (CG * MT * BM)) * ((a.KN + BN - 1) / BN);
     // the launch may be scheduled while its predecessor on the stream drains (the kernel
     // waits for it, griddepcontrol.wait, before it touches global data)

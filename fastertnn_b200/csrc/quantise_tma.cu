@@ -199,8 +199,11 @@ int tnns_launch_quantise_tma(tnns_cuda_ctx* ctx, bool ternary, const float* d_x,
     if (rc) return rc;
     const long long items = (long long)N * nbands * Cp;
     const int grid = (int)std::min<long long>(items, ctx->sm_count);
-    auto launch = [&](auto kern) -> int {
-        TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)QSMEM));
+    auto launch = [&](auto kern, bool* smem_set) -> int {
+        if (!smem_set[ctx->device & 63]) {  // once per kernel and device
+            TNNS_CUDA_TRY(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)QSMEM));
+            smem_set[ctx->device & 63] = true;
+        }
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(grid);
         cfg.blockDim = dim3(QTHREADS);
@@ -216,6 +219,8 @@ int tnns_launch_quantise_tma(tnns_cuda_ctx* ctx, bool ternary, const float* d_x,
         TNNS_CUDA_TRY(cudaGetLastError());
         return TNNS_OK;
     };
-    if (format == TNNS_IMG_E2M1) return ternary ? launch(quantise_tma_kernel<true, TNNS_IMG_E2M1>) : launch(quantise_tma_kernel<false, TNNS_IMG_E2M1>);
-    return ternary ? launch(quantise_tma_kernel<true, TNNS_IMG_PLANES>) : launch(quantise_tma_kernel<false, TNNS_IMG_PLANES>);
+    static bool set_te[64] = {false}, set_be[64] = {false}, set_tp[64] = {false}, set_bp[64] = {false};
+    if (format == TNNS_IMG_E2M1)
+        return ternary ? launch(quantise_tma_kernel<true, TNNS_IMG_E2M1>, set_te) : launch(quantise_tma_kernel<false, TNNS_IMG_E2M1>, set_be);
+    return ternary ? launch(quantise_tma_kernel<true, TNNS_IMG_PLANES>, set_tp) : launch(quantise_tma_kernel<false, TNNS_IMG_PLANES>, set_bp);
 }

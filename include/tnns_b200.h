@@ -234,7 +234,12 @@ int tnns_cuda_gemm(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const int64_t
 int tnns_cuda_conv(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y,
                    const tnns_shape_t* s, float alpha, int layout, int pack_algo, int gemm_algo, void* stream);
 
-/* Same with caller-owned workspace of at least tnns_packed_bytes() bytes. */
+/* Same with a caller-owned workspace.  Every route needs only what it writes there, and with
+ * TNNS_PACK_AUTO / TNNS_GEMM_AUTO the call takes the best route the workspace holds: the
+ * copy-engine routes keep a 4-bit image (tnns_fused_workspace_bytes, tnns_slab_workspace_bytes;
+ * 128-byte aligned), the gathering route bit planes (tnns_packed_image_bytes), the explicit route --
+ * the only one a forced pack or GEMM algorithm takes -- the packed im2row matrix
+ * (tnns_packed_bytes).  A workspace of the largest of these that applies never limits the choice. */
 int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr,
                       float* d_y, void* d_workspace, size_t workspace_bytes, const tnns_shape_t* s, float alpha,
                       int layout, int pack_algo, int gemm_algo, void* stream);
