@@ -99,10 +99,10 @@ def layer_inputs(type_: int, layer: Layer, n0: int, n1: int):
     return x, thr
 
 
-def common_config(name, kind, type_, batch, layers, scaling):
+def common_config(name, kind, type_, batch, layers, scaling, layout="nchw"):
     """The keys both arms print, with the same values: what is computed, not how."""
     L = layers[0]
-    cfg = {"workload": name, "type": TYPE_NAMES[type_], "batch": batch, "layout": "NCHW", "scaling": scaling}
+    cfg = {"workload": name, "type": TYPE_NAMES[type_], "batch": batch, "layout": layout.upper(), "scaling": scaling}
     if kind == "layer":
         cfg.update({"layer": str(L), "M": batch * L.OH * L.OW, "K": L.C * L.KH * L.KW, "N": L.KN})
     else:
@@ -283,7 +283,7 @@ def run_reference(args, name, kind, type_, batch, layers):
         "impl": "reference", "metric": METRIC, "value": val, "unit": "GOPS", "n_gpus": args.gpus, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": t * 1e3, "higher_is_better": True, "scaling": args.scaling, "vs_baseline": None,
         "dtype": "int (64-bit popcount lanes)", "data": "synthetic",
-        "config": common_config(name, kind, type_, N_job, layers, args.scaling),
+        "config": common_config(name, kind, type_, N_job, layers, args.scaling, args.layout if kind == "layer" else "nchw"),
         "impl_config": {"batch_timed_per_step": wl.N, "host_threads": used, "code": wl.chk.kind,
                         "note": "GOPS = operations of the images actually processed per step / time; the CPU path has no GPUs to "
                                 "shard over, so n_gpus only names the run it is compared with"},
@@ -421,11 +421,13 @@ class LayerRun:
         self.tern = act_ternary(type_)
         self.shape = layer.shape(nloc)
         OH, OW = layer.OH, layer.OW
+        self.nhwc = getattr(args, "layout", "nchw") == "nhwc"
+        self.layout = LO = ft.NHWC if self.nhwc else ft.NCHW
         self.in_bytes = nloc * layer.C * layer.H * layer.W * 4
         self.out_bytes = nloc * layer.KN * OH * OW * 4
         tc4 = args.gemm in ("auto", "f4tc")
         # the slab-fed route (stride-1 layers from a bordered 4-bit image): on request, or where the library's own rule takes it
-        self.slab = tc4 and (args.route in ("slab", "slab_fused") or (args.route == "auto" and ctx.slab_auto(w, self.shape, 4096, ft.NCHW) > 0))
+        self.slab = tc4 and (args.route in ("slab", "slab_fused") or (args.route == "auto" and ctx.slab_auto(w, self.shape, 4096, LO) > 0))
         if self.slab and not ctx.slab_supported(w, self.shape):
             raise SystemExit("bench: this workload does not qualify for the slab-fed route")
         self.im2col = tc4 and not self.slab and args.route in ("auto", "im2col", "fused") and ctx.im2col_supported(w, self.shape)
@@ -434,23 +436,27 @@ class LayerRun:
         self.implicit = tc4 and (self.slab or self.im2col or args.route in ("auto", "implicit"))
         self.fused = False
         if self.slab:
-            self.fused = args.route == "slab_fused" or (args.route == "auto" and ctx.slab_auto(w, self.shape, 4096, ft.NCHW) == 2)
+            self.fused = args.route == "slab_fused" or (args.route == "auto" and ctx.slab_auto(w, self.shape, 4096, LO) == 2)
         elif self.im2col and args.route in ("auto", "fused"):
             # the pointer only stands for the input's alignment here (torch allocations are 512-byte aligned)
-            self.fused = (ctx.conv_fused_supported(w, self.shape, 4096, ft.NCHW) if args.route == "fused"
-                          else ctx.conv_fused_preferred(w, self.shape, 4096, ft.NCHW))
+            self.fused = (ctx.conv_fused_supported(w, self.shape, 4096, LO) if args.route == "fused"
+                          else ctx.conv_fused_preferred(w, self.shape, 4096, LO))
         self.pack_bytes = (ft.api.slab_workspace_bytes(nloc, layer.C, layer.H, layer.W, layer.P, layer.P) if self.slab else
                            ft.api.fused_workspace_bytes(nloc, layer.C, layer.H, layer.W) if self.im2col else
                            ft.api.packed_image_bytes(self.tern, nloc, layer.C, layer.H, layer.W) if self.implicit
                            else ft.packed_bytes(type_, self.shape))
         self.step_bytes = self.in_bytes + self.out_bytes + self.pack_bytes
         self.ring = max(2, -(-3 * L2_BYTES // max(self.step_bytes, 1)))
+        if self.nhwc and (args.route in ("fused", "slab_fused") or not tc4):
+            raise SystemExit("bench: NHWC input is measured on the two-launch tensor-core routes")
         x0 = torch.from_numpy(x_h[:nloc]).cuda()
+        if self.nhwc:
+            x0 = x0.permute(0, 2, 3, 1).contiguous()
         self.xs, self.ys, self.ps = [], [], []
         for r in range(self.ring):
             # distinct data per ring slot: the images rotated
             self.xs.append(x0 if r == 0 else torch.roll(x0, shifts=r, dims=0))
-            self.ys.append(torch.empty((nloc, layer.KN, OH, OW), dtype=torch.float32, device="cuda"))
+            self.ys.append(torch.empty((nloc, OH, OW, layer.KN) if self.nhwc else (nloc, layer.KN, OH, OW), dtype=torch.float32, device="cuda"))
             self.ps.append(torch.empty(self.pack_bytes // 8 + 32, dtype=torch.int64, device="cuda"))
         self.thr_d = torch.from_numpy(thr_h[:nloc].copy()).cuda()
         self.stream = torch.cuda.Stream()
@@ -470,18 +476,18 @@ class LayerRun:
         ft, L = self.ft, self.layer
         if self.slab:
             self.ctx.quantise_e2m1_bordered(self.tern, self.xs[r].data_ptr(), self.thr_d.data_ptr(), self._aligned(self.ps[r]), self.nloc, L.C, L.H, L.W,
-                                            L.P, L.P, ft.NCHW, self.sp)
+                                            L.P, L.P, self.layout, self.sp)
         elif self.im2col:
-            self.ctx.quantise_e2m1(self.xs[r].data_ptr(), self.thr_d.data_ptr(), self._aligned(self.ps[r]), self.nloc, L.C, L.H, L.W, ft.NCHW, self.sp)
+            self.ctx.quantise_e2m1(self.xs[r].data_ptr(), self.thr_d.data_ptr(), self._aligned(self.ps[r]), self.nloc, L.C, L.H, L.W, self.layout, self.sp)
         else:
-            self.ctx.quantise(self.tern, self.xs[r].data_ptr(), self.thr_d.data_ptr(), self._aligned(self.ps[r]), self.nloc, L.C, L.H, L.W, ft.NCHW, self.sp)
+            self.ctx.quantise(self.tern, self.xs[r].data_ptr(), self.thr_d.data_ptr(), self._aligned(self.ps[r]), self.nloc, L.C, L.H, L.W, self.layout, self.sp)
 
     def step(self, i, ev=None):
         ft, L, r = self.ft, self.layer, i % self.ring
         x, y, p = self.xs[r].data_ptr(), self.ys[r].data_ptr(), self._aligned(self.ps[r])
         if ev is None and self.auto_call:
             # the library's own layer call: one call into the library per step, its own choice of route
-            self.ctx.conv_ws(self.w, x, self.thr_d.data_ptr(), y, p, self.pack_bytes, self.shape, 0.5, ft.NCHW, ft.PACK_AUTO, ft.GEMM_AUTO, self.sp)
+            self.ctx.conv_ws(self.w, x, self.thr_d.data_ptr(), y, p, self.pack_bytes, self.shape, 0.5, self.layout, ft.PACK_AUTO, ft.GEMM_AUTO, self.sp)
             return
         if ev:
             ev[0].record(self.stream)
@@ -490,21 +496,21 @@ class LayerRun:
         elif self.implicit:
             self.quantise(r)
         else:
-            self.ctx.pack(self.tern, x, self.thr_d.data_ptr(), p, self.shape, ft.NCHW, ft.PACK_AUTO, self.sp)
+            self.ctx.pack(self.tern, x, self.thr_d.data_ptr(), p, self.shape, self.layout, ft.PACK_AUTO, self.sp)
         if ev:
             ev[1].record(self.stream)
         if self.slab and self.fused:
             self.ctx.conv_slab(self.w, x, self.thr_d.data_ptr(), y, p, self.pack_bytes, self.shape, 0.5, 0, self.sp)
         elif self.slab:
-            self.ctx.gemm_slab(self.w, p, y, self.shape, 0.5, ft.NCHW, self.sp)
+            self.ctx.gemm_slab(self.w, p, y, self.shape, 0.5, self.layout, self.sp)
         elif self.fused:
             self.ctx.conv_fused(self.w, x, self.thr_d.data_ptr(), y, p, self.pack_bytes, self.shape, 0.5, 0, self.sp)
         elif self.im2col:
-            self.ctx.gemm_im2col(self.w, p, y, self.shape, 0.5, ft.NCHW, self.sp)
+            self.ctx.gemm_im2col(self.w, p, y, self.shape, 0.5, self.layout, self.sp)
         elif self.implicit:
-            self.ctx.gemm_implicit(self.w, p, y, self.shape, 0.5, ft.NCHW, self.sp)
+            self.ctx.gemm_implicit(self.w, p, y, self.shape, 0.5, self.layout, self.sp)
         else:
-            self.ctx.gemm(self.w, p, y, self.nloc, L.OH, L.OW, 0.5, ft.NCHW, self.gemm_algo, self.sp)
+            self.ctx.gemm(self.w, p, y, self.nloc, L.OH, L.OW, 0.5, self.layout, self.gemm_algo, self.sp)
         if ev:
             ev[2].record(self.stream)
 
@@ -536,7 +542,10 @@ def check_rank_slice(D: Dist, run: LayerRun, type_, layer, x_h, thr_h, wp):
     ok = True
     for n in sorted({0, run.nloc - 1}):
         want = chk.conv(type_, x_h[n:n + 1], thr_h[n:n + 1], wp, (layer.KH, layer.KW), (layer.P, layer.P), (layer.S, layer.S), 0.5)
-        ok = ok and run.ys[0][n:n + 1].cpu().numpy().tobytes() == want.tobytes()
+        got = run.ys[0][n:n + 1]
+        if run.nhwc:
+            got = got.permute(0, 3, 1, 2).contiguous()
+        ok = ok and got.cpu().numpy().tobytes() == want.tobytes()
     return ok
 
 
@@ -645,20 +654,22 @@ def run_layer(args, name, type_, N_cfg, layer: Layer):
     D.barrier()
     if rank == 0:
         xj, tj = layer_inputs(type_, layer, 0, N_total)
-        x_pin = torch.from_numpy(xj).pin_memory()
+        nhwc = args.layout == "nhwc"
+        LO = ft.NHWC if nhwc else ft.NCHW
+        x_pin = torch.from_numpy(np.ascontiguousarray(xj.transpose(0, 2, 3, 1)) if nhwc else xj).pin_memory()
         t_pin = torch.from_numpy(tj).pin_memory()
-        y_pin = torch.empty((N_total, layer.KN, OH, OW), dtype=torch.float32).pin_memory()
+        y_pin = torch.empty((N_total, OH, OW, layer.KN) if nhwc else (N_total, layer.KN, OH, OW), dtype=torch.float32).pin_memory()
         shape_job = layer.shape(N_total)
         if world == 1:
             def call():
-                ctx.conv_host(w, x_pin.data_ptr(), t_pin.data_ptr(), y_pin.data_ptr(), shape_job, 0.5, ft.NCHW)
+                ctx.conv_host(w, x_pin.data_ptr(), t_pin.data_ptr(), y_pin.data_ptr(), shape_job, 0.5, LO)
             grp = None
         else:
             grp = ft.MultiContext(list(range(world)))
             gw = grp.upload_weights(type_, wp, layer.C, layer.KH, layer.KW)
 
             def call():
-                grp.conv_host(gw, x_pin.data_ptr(), t_pin.data_ptr(), y_pin.data_ptr(), shape_job, 0.5, ft.NCHW)
+                grp.conv_host(gw, x_pin.data_ptr(), t_pin.data_ptr(), y_pin.data_ptr(), shape_job, 0.5, LO)
         for _ in range(3):
             call()
         e2e_steps = max(3, min(args.steps, 10))
@@ -727,7 +738,7 @@ def run_layer(args, name, type_, N_cfg, layer: Layer):
             "dtype": (("e2m1 (4-bit) operands quantised from fp32, unit block scales, fp32 accumulate (exact), fp32 PReLU" if im2col else
                        "e2m1 operands expanded from 2-bit planes, unit block scales, fp32 accumulate (exact), fp32 PReLU") if args.gemm in ("auto", "f4tc") else "int8 operands expanded from 2-bit planes, int32 accumulate, fp32 PReLU") if args.gemm != "popc" else "u32 bit-plane lanes, int32 popcount accumulate, fp32 PReLU",
             "data": "synthetic",
-            "config": common_config(name, "layer", type_, N_total, [layer], args.scaling),
+            "config": common_config(name, "layer", type_, N_total, [layer], args.scaling, args.layout),
             "impl_config": {"batch_per_gpu": nloc, "gemm": args.gemm, "route": info["route"],
                             "l2": f"ring of {info['ring']} distinct input/workspace/output buffer sets ({info['ring'] * info['step_bytes'] >> 20} MiB) cycled "
                                   f"between steps; one set alone is {info['step_bytes'] >> 20} MiB",
@@ -948,6 +959,7 @@ def main():
                          "im2col: quantise to a 4-bit image + GEMM fed by im2col tensor copies; "
                          "implicit: quantise to bit planes + GEMM whose warps gather and expand their im2row rows; "
                          "explicit: pack to the im2row matrix, then GEMM")
+    ap.add_argument("--layout", choices=["nchw", "nhwc"], default="nchw", help="layer workloads: memory layout of the fp32 input and output")
     ap.add_argument("--chain", choices=["image", "packed", "fp32"], default="image", help="stack workloads: what travels between two layers")
     ap.add_argument("--scaling", choices=["weak", "strong"], default="strong",
                     help="strong: the configured batch is split over the ranks; weak: every rank processes the configured batch")

@@ -102,8 +102,10 @@ int tnns_launch_quantise(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, con
 bool tnns_quantise_tma_supported(const float* d_x, int H, int W, int layout);
 // PH, PW (4-bit image only): store the image bordered, i.e. every image framed by PH rows / PW columns of
 // the padding value (ternary 0, binary +1), [n][H + 2*PH][W + 2*PW][C/2 bytes]
+// layout TNNS_NHWC: the input is (pixels) x (channels), fetched as 128-byte-swizzled boxes (tnns_quantise_tma_nhwc_supported)
+bool tnns_quantise_tma_nhwc_supported(const float* d_x, int N, int C, int H, int W);
 int tnns_launch_quantise_tma(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
-                             int W, cudaStream_t stream, int format, int PH = 0, int PW = 0);
+                             int W, cudaStream_t stream, int format, int PH = 0, int PW = 0, int layout = TNNS_NCHW);
 // driver-encoded descriptor of a two-dimensional tensor for the copy engine (128 bytes at `map`)
 int tnns_tensor_map_2d(void* map, int elem_bytes, const void* base, unsigned long long dim0, unsigned long long dim1,
                        unsigned long long stride1_bytes, unsigned box0, unsigned box1, int swizzle_bytes = 0);

@@ -470,6 +470,9 @@ int tnns_launch_quantise(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, con
     if (format == TNNS_IMG_E2M1 && !ternary) return tnns_fail(TNNS_ERR_UNSUPPORTED, "the 4-bit image holds ternary activations only");
     if (tnns_quantise_tma_supported(d_x, H, W, layout))
         return tnns_launch_quantise_tma(ctx, ternary, d_x, d_thr, d_image, N, C, H, W, stream, format);
+    // (a 1x1 image is the same memory in both layouts: fully connected layers take this form too)
+    if ((layout == TNNS_NHWC || H * W == 1) && tnns_quantise_tma_nhwc_supported(d_x, N, C, H, W))
+        return tnns_launch_quantise_tma(ctx, ternary, d_x, d_thr, d_image, N, C, H, W, stream, format, 0, 0, TNNS_NHWC);
     if (layout != TNNS_NCHW && layout != TNNS_NHWC) return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
     TnnsGeom g;
     g.N = N; g.C = C; g.H = H; g.W = W; g.KN = 1; g.KH = g.KW = 1; g.PH = g.PW = 0; g.SH = g.SW = 1;

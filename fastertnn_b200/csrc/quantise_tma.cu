@@ -11,6 +11,12 @@
 // consecutive floats), the sign and non-zero bits pushed into the plane words branch-free, the
 // stage handed back, then the pixel's 64 channels stored as one 64-bit word per plane or as
 // 32 bytes of e2m1 operands.  The kernel is bound by HBM traffic: 4 bytes read per input value.
+//
+// NHWC input (NHWC_IN) is the tensor (pixels of all images) x (channels): an item arrives as two
+// copies of 128 pixels x 32 channels, written in the 128-byte swizzle pattern, so that a thread
+// reads its pixel's channels as eight 16-byte loads per half whose physical chunk is rotated by the
+// pixel index: the 32 lanes of a warp then spread over all banks (a plain [pixel][channel] tile
+// would put every lane on the same bank).
 #include <cuda.h>
 
 #include <algorithm>
@@ -35,7 +41,36 @@ constexpr size_t QSMEM = 1024 + (size_t)QSTG * QSTAGE_BYTES + 128;
 
 __device__ __forceinline__ uint32_t push_sign_bit(uint32_t acc, float d) { return __funnelshift_l(__float_as_uint(d), acc, 1); }
 
-template <bool TERNARY, int IMG>
+// One pixel's row of a 128-byte-swizzled half-tile: 32 channels = eight 16-byte chunks, chunk c stored at
+// c ^ (p & 7).  Channel b ends at bit b (visit 31 .. 0 and shift left); channels at or past nch read as
+// absent (sign 0, non-zero 0).
+template <bool TERNARY>
+__device__ __forceinline__ void quantise_row32(const unsigned char* row, int p, int nch, float t, uint32_t& sg_out, uint32_t& nz_out) {
+    uint32_t sg = 0, nz = 0;
+#pragma unroll
+    for (int c = 7; c >= 0; c--) {
+        const float4 v4 = *reinterpret_cast<const float4*>(row + ((c ^ (p & 7)) << 4));
+#pragma unroll
+        for (int e = 3; e >= 0; e--) {
+            const float v = e == 3 ? v4.w : e == 2 ? v4.z : e == 1 ? v4.y : v4.x;
+            if (4 * c + e < nch) {
+                if (TERNARY) {
+                    sg = push_sign_bit(sg, v + t);
+                    nz = push_sign_bit(nz, t - fabsf(v));
+                } else {
+                    sg = push_sign_bit(sg, (v + 0.0f) - t);
+                }
+            } else {
+                sg <<= 1;
+                nz <<= 1;
+            }
+        }
+    }
+    sg_out = sg;
+    nz_out = nz;
+}
+
+template <bool TERNARY, int IMG, bool NHWC_IN>
 __global__ void __launch_bounds__(QTHREADS, 1)
 quantise_tma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __restrict__ thr, void* __restrict__ out, int N, int C, int HW,
                     int Cp, int nbands, unsigned int* status, int W, int Wp, int HpWp, int off0) {
@@ -45,7 +80,10 @@ quantise_tma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __res
     const uint32_t bar_full = smem_u32(bars), bar_empty = smem_u32(bars + QSTG);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bars + 2 * QSTG);
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-    const long long items = (long long)N * nbands * Cp;
+    // NCHW: an item is (image, band of 128 pixels of that image, channel group).  NHWC: the pixels of all
+    // images are the rows of one tensor, a band is 128 consecutive rows and may straddle images.
+    const long long items = NHWC_IN ? (long long)nbands * Cp : (long long)N * nbands * Cp;
+    const int rows_total = NHWC_IN ? N * HW : 0;
     // The GEMM that follows on the stream is launched as a programmatic dependent: its blocks may
     // take SMs as the blocks of this launch leave and set themselves up there; it waits for this
     // launch to complete before it reads the image.  All blocks of this launch are resident at once.
@@ -89,8 +127,14 @@ quantise_tma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __res
                 const long long nb = i / Cp;
                 const int band = (int)(nb % nbands), n = (int)(nb / nbands);
                 if (!mbar_wait(bar_empty + 8 * s, (uint32_t)((k / QSTG) & 1) ^ 1, abort_flag, status, 0x21)) goto done;
-                mbar_arrive_expect_tx(bar_full + 8 * s, QSTAGE_BYTES);  // the whole box, edges zero-filled
-                tma_tile2d_g2s(smem_u32(smem + s * QSTAGE_BYTES), &tmap, band * QL, n * C + ic * QC, bar_full + 8 * s);
+                mbar_arrive_expect_tx(bar_full + 8 * s, QSTAGE_BYTES);  // the whole box(es), edges zero-filled
+                if (NHWC_IN) {
+                    const int row0 = (int)nb * QL;  // pixel row of the (pixels x channels) tensor
+                    tma_tile2d_g2s(smem_u32(smem + s * QSTAGE_BYTES), &tmap, ic * QC, row0, bar_full + 8 * s);
+                    tma_tile2d_g2s(smem_u32(smem + s * QSTAGE_BYTES + QSTAGE_BYTES / 2), &tmap, ic * QC + 32, row0, bar_full + 8 * s);
+                } else {
+                    tma_tile2d_g2s(smem_u32(smem + s * QSTAGE_BYTES), &tmap, band * QL, n * C + ic * QC, bar_full + 8 * s);
+                }
             }
         }
     } else {
@@ -100,21 +144,42 @@ quantise_tma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __res
         // The threshold of an item's image is loaded one item ahead and not touched until its turn: an
         // instruction that uses a just-issued load holds the (in-order) warp for the whole round trip.
         const long long step = (long long)QGROUPS * gridDim.x, first = blockIdx.x + (long long)grp * gridDim.x;
-        float t_raw = first < items ? __ldg(thr + first / ((long long)Cp * nbands)) : 0.f;
+        auto threshold_of = [&](long long i) -> float {
+            if (NHWC_IN) {
+                const int row = (int)(i / Cp) * QL + p;
+                return row < rows_total ? __ldg(thr + row / HW) : 0.f;
+            }
+            return __ldg(thr + i / ((long long)Cp * nbands));
+        };
+        float t_raw = first < items ? threshold_of(first) : 0.f;
         for (long long i = first; i < items; i += step, k += QGROUPS) {
             const int s = (int)(k % QSTG);
             const int ic = (int)(i % Cp);
             const long long nb = i / Cp;
-            const int band = (int)(nb % nbands), n = (int)(nb / nbands);
+            int band, n, pix;
+            if (NHWC_IN) {
+                const int row = (int)nb * QL + p;
+                n = row / HW;
+                pix = row < rows_total ? row - n * HW : HW;  // rows past the tensor's end were zero-filled and are not stored
+                band = 0;
+            } else {
+                band = (int)(nb % nbands);
+                n = (int)(nb / nbands);
+                pix = band * QL + p;
+            }
             const int nch = min(QC, C - ic * QC);  // channels present in this group
             const float t = t_raw + 0.0f;  // + 0.0f: a threshold of -0 behaves as +0 in every compare
-            if (i + step < items) t_raw = __ldg(thr + (i + step) / ((long long)Cp * nbands));
+            if (i + step < items) t_raw = threshold_of(i + step);
             if (!mbar_wait(bar_full + 8 * s, (uint32_t)((k / QSTG) & 1), abort_flag, status, 0x22)) goto done;
             const float* sp = reinterpret_cast<const float*>(smem + s * QSTAGE_BYTES) + p;
             uint32_t sg[2] = {0, 0}, nz[2] = {0, 0};
             // channel b of a half ends at bit b: visit 31 .. 0 and shift left; predicates read
             // off sign bits (v < -t <=> signbit(v + t); |v| > t <=> signbit(t - |v|); v < t <=> signbit(v - t))
-            if (nch == QC) {
+            if (NHWC_IN) {
+                const unsigned char* row = smem + s * QSTAGE_BYTES + p * 128;
+                quantise_row32<TERNARY>(row, p, nch, t, sg[0], nz[0]);
+                quantise_row32<TERNARY>(row + QSTAGE_BYTES / 2, p, nch - 32, t, sg[1], nz[1]);
+            } else if (nch == QC) {
 #pragma unroll
                 for (int half = 0; half < 2; half++) {
 #pragma unroll
@@ -150,7 +215,6 @@ quantise_tma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __res
             // every value is in registers: hand the stage back before storing
             __syncwarp();
             if (lane == 0) mbar_arrive(bar_empty + 8 * s);
-            const int pix = band * QL + p;
             if (pix < HW) {
                 if (IMG == TNNS_IMG_E2M1) {
                     uint32_t lo[4], hi[4];
@@ -186,18 +250,25 @@ bool tnns_quantise_tma_supported(const float* d_x, int H, int W, int layout) {
     return layout == TNNS_NCHW && HW % 4 == 0 && HW >= 32 && (reinterpret_cast<uintptr_t>(d_x) & 15) == 0;
 }
 
+// NHWC: rows of C floats must be 16-byte multiples and the tensor large enough for a box of 128 pixel rows
+bool tnns_quantise_tma_nhwc_supported(const float* d_x, int N, int C, int H, int W) {
+    return C % 4 == 0 && (long long)N * H * W >= 128 && (long long)N * H * W < 0x7FFFFFFFLL && (reinterpret_cast<uintptr_t>(d_x) & 15) == 0;
+}
+
 int tnns_launch_quantise_tma(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
-                             int W, cudaStream_t stream, int format, int PH, int PW) {
+                             int W, cudaStream_t stream, int format, int PH, int PW, int layout) {
     const int HW = H * W;
     if (N == 0) return TNNS_OK;
     if ((PH || PW) && format != TNNS_IMG_E2M1) return tnns_fail(TNNS_ERR_INVALID, "only the 4-bit image has a bordered form");
     const int Wp = W + 2 * PW, HpWp = (H + 2 * PH) * Wp, off0 = PH * Wp + PW;
     const int Cp = (C + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS;
-    const int nbands = (HW + QL - 1) / QL;
+    const bool nhwc = layout == TNNS_NHWC;
+    const int nbands = nhwc ? (int)(((long long)N * HW + QL - 1) / QL) : (HW + QL - 1) / QL;
     alignas(64) CUtensorMap map;
-    int rc = tnns_tensor_map_2d(&map, 4, d_x, (unsigned long long)HW, (unsigned long long)N * C, (unsigned long long)HW * 4, QL, QC);
+    int rc = nhwc ? tnns_tensor_map_2d(&map, 4, d_x, (unsigned long long)C, (unsigned long long)N * HW, (unsigned long long)C * 4, 32, QL, 128)
+                  : tnns_tensor_map_2d(&map, 4, d_x, (unsigned long long)HW, (unsigned long long)N * C, (unsigned long long)HW * 4, QL, QC);
     if (rc) return rc;
-    const long long items = (long long)N * nbands * Cp;
+    const long long items = nhwc ? (long long)nbands * Cp : (long long)N * nbands * Cp;
     const int grid = (int)std::min<long long>(items, ctx->sm_count);
     auto launch = [&](auto kern, bool* smem_set) -> int {
         if (!smem_set[ctx->device & 63]) {  // once per kernel and device
@@ -219,8 +290,16 @@ int tnns_launch_quantise_tma(tnns_cuda_ctx* ctx, bool ternary, const float* d_x,
         TNNS_CUDA_TRY(cudaGetLastError());
         return TNNS_OK;
     };
-    static bool set_te[64] = {false}, set_be[64] = {false}, set_tp[64] = {false}, set_bp[64] = {false};
-    if (format == TNNS_IMG_E2M1)
-        return ternary ? launch(quantise_tma_kernel<true, TNNS_IMG_E2M1>, set_te) : launch(quantise_tma_kernel<false, TNNS_IMG_E2M1>, set_be);
-    return ternary ? launch(quantise_tma_kernel<true, TNNS_IMG_PLANES>, set_tp) : launch(quantise_tma_kernel<false, TNNS_IMG_PLANES>, set_bp);
+    static bool set_flags[8][64] = {};
+    const int which = (format == TNNS_IMG_E2M1 ? 0 : 2) + (ternary ? 0 : 1) + (nhwc ? 4 : 0);
+    switch (which) {
+        case 0: return launch(quantise_tma_kernel<true, TNNS_IMG_E2M1, false>, set_flags[0]);
+        case 1: return launch(quantise_tma_kernel<false, TNNS_IMG_E2M1, false>, set_flags[1]);
+        case 2: return launch(quantise_tma_kernel<true, TNNS_IMG_PLANES, false>, set_flags[2]);
+        case 3: return launch(quantise_tma_kernel<false, TNNS_IMG_PLANES, false>, set_flags[3]);
+        case 4: return launch(quantise_tma_kernel<true, TNNS_IMG_E2M1, true>, set_flags[4]);
+        case 5: return launch(quantise_tma_kernel<false, TNNS_IMG_E2M1, true>, set_flags[5]);
+        case 6: return launch(quantise_tma_kernel<true, TNNS_IMG_PLANES, true>, set_flags[6]);
+        default: return launch(quantise_tma_kernel<false, TNNS_IMG_PLANES, true>, set_flags[7]);
+    }
 }

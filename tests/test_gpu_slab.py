@@ -6,7 +6,7 @@ import numpy as np
 import pytest
 
 import fastertnn_b200 as ft
-from cases import BNN, BTN, TBN, TNN, act_ternary, make_case, to_nchw, wgt_ternary
+from cases import BNN, BTN, TBN, TNN, act_ternary, make_case, to_nchw, to_nhwc, wgt_ternary
 from fastertnn_b200 import synth
 from fastertnn_b200.workloads import Layer
 from test_gpu_parity import _expand32_f4_numpy, expected_image
@@ -71,6 +71,23 @@ def test_bordered_image_and_slab_gemm(type_, layer, N, gpu_ctx, checker):
         ctx.sync()
         image = ctx.to_host(d_img, (nb // 4,), np.uint32)
         assert np.array_equal(image, expected_bordered(checker, case).reshape(-1)), "bordered image"
+        # the same image from NHWC input (channel counts that are multiples of four)
+        d_xh = ctx.to_device(to_nhwc(case.x))
+        if layer.C % 4 == 0 and N * layer.H * layer.W >= 128:
+            ctx.fill(d_img, np.full(nb // 4, 0x5A5A5A5A, np.uint32))
+            ctx.quantise_e2m1_bordered(tern, d_xh, d_t, d_img, N, layer.C, layer.H, layer.W, layer.P, layer.P, ft.NHWC)
+            ctx.sync()
+            assert np.array_equal(ctx.to_host(d_img, (nb // 4,), np.uint32), image), "bordered image from NHWC input"
+            got = np.empty((N, layer.OH, layer.OW, layer.KN), np.float32)
+            ctx.fill(d_y, np.full(want.size, np.nan, np.float32))
+            assert ctx.conv_auto_algo(w, shape, d_xh, ft.NHWC) in (ft.GEMM_F4_SLAB, ft.GEMM_F4_TC, ft.GEMM_F4_FUSED)
+            ctx.conv(w, d_xh, d_t, d_y, shape, case.alpha, ft.NHWC, ft.PACK_AUTO, ft.GEMM_F4_SLAB)
+            ctx.sync()
+            assert to_nchw(ctx.to_host(d_y, got.shape, np.float32)).tobytes() == want.tobytes(), "slab route, NHWC in and out"
+        else:
+            with pytest.raises(ft.TnnsError):
+                ctx.quantise_e2m1_bordered(tern, d_xh, d_t, d_img, N, layer.C, layer.H, layer.W, layer.P, layer.P, ft.NHWC)
+        ctx.free(d_xh)
         for layout in (ft.NCHW, ft.NHWC):
             for pairs in (1, 2):
                 if pairs == 2 and layer.KN <= 128:
@@ -211,3 +228,34 @@ def test_slab_route_declines_what_it_cannot_do(gpu_ctx, checker):
     assert e.value.status == 4
     ctx.free(d)
     w.free()
+
+
+@pytest.mark.parametrize("tern", [True, False])
+@pytest.mark.parametrize("C,H,W,N", [(64, 12, 12, 3), (512, 9, 7, 5), (100, 13, 11, 2), (4, 16, 16, 1), (260, 5, 5, 6), (1024, 3, 3, 15),
+                                     (36, 1, 1, 130)])
+def test_quantise_from_nhwc_through_the_copy_engine(tern, C, H, W, N, gpu_ctx, checker):
+    """NHWC input arrives as 128-byte-swizzled boxes of 128 pixels x 32 channels; the bit planes and the
+    4-bit image must equal those made from the same tensor in NCHW (odd pixel counts, channel tails,
+    bands that straddle images, 1x1 images)."""
+    ctx = gpu_ctx
+    x = synth.uniform_pm1(9700 + C + H, (N, C, H, W))
+    thr = (synth.uniform_pm1(9701, (N,)) * 0.3 + (0.35 if tern else 0.0)).astype(np.float32)
+    d_x, d_xh, d_t = ctx.to_device(x), ctx.to_device(to_nhwc(x)), ctx.to_device(thr)
+    nbp = ft.api.packed_image_bytes(tern, N, C, H, W)
+    nbe = ft.api.e2m1_image_bytes(N, C, H, W)
+    d_a, d_b = ctx.malloc(max(nbp, nbe)), ctx.malloc(max(nbp, nbe))
+    try:
+        for d in (d_a, d_b):
+            ctx.fill(d, np.full(max(nbp, nbe) // 4, 0x3C3C3C3C, np.uint32))
+        ctx.quantise(tern, d_x, d_t, d_a, N, C, H, W, ft.NCHW)
+        ctx.quantise(tern, d_xh, d_t, d_b, N, C, H, W, ft.NHWC)
+        ctx.sync()
+        assert np.array_equal(ctx.to_host(d_a, (nbp // 4,), np.uint32), ctx.to_host(d_b, (nbp // 4,), np.uint32)), "bit planes"
+        if tern:
+            ctx.quantise_e2m1(d_x, d_t, d_a, N, C, H, W, ft.NCHW)
+            ctx.quantise_e2m1(d_xh, d_t, d_b, N, C, H, W, ft.NHWC)
+            ctx.sync()
+            assert np.array_equal(ctx.to_host(d_a, (nbe // 4,), np.uint32), ctx.to_host(d_b, (nbe // 4,), np.uint32)), "4-bit image"
+    finally:
+        for p in (d_x, d_xh, d_t, d_a, d_b):
+            ctx.free(p)
