@@ -100,6 +100,7 @@ SIGNATURES = {
     "tnns_cuda_conv_noalloc": (_i, [_i, _vp, _vp, _vp, _vp, _pshape, _f, _i, _vp]),
     "tnns_cuda_pipe_rate": (_i, [_vp, _i, C.POINTER(C.c_double)]),
     "tnns_cuda_selftest_wait_expiry": (_i, [_vp]),
+    "tnns_prelu_thresholds": (_i, [_f, _f, _f, _i, C.POINTER(_f), C.POINTER(_f)]),
     "tnns_cuda_sync": (_i, [_vp]),
     "tnns_cuda_malloc": (_i, [_vp, _sz, C.POINTER(_vp)]),
     "tnns_cuda_free": (None, [_vp, _vp]),

@@ -506,6 +506,15 @@ class MultiContext:
         _check(rc)
 
 
+def prelu_thresholds(t: float, alpha: float, bias: float = 0.0, ternary: bool = True) -> tuple[float, float]:
+    """The constants (n1, t2) of the quantising epilogues' threshold rule (tnns_prelu_thresholds): for an integer
+    accumulator v, sign = v + n1 < 0 and above = t2 - v < 0 reproduce PReLU(v + bias) followed by the next layer's
+    quantiser with threshold t.  Host code; needs no GPU."""
+    n1, t2 = C.c_float(), C.c_float()
+    _check(load_library().tnns_prelu_thresholds(t, alpha, bias, int(ternary), C.byref(n1), C.byref(t2)))
+    return n1.value, t2.value
+
+
 def noalloc_scratch_bytes() -> int:
     return load_library().tnns_cuda_noalloc_scratch_bytes()
 

@@ -8,6 +8,7 @@
 #include <new>
 
 #include "internal.h"
+#include "prelu_thresholds.cuh"
 
 // ---------------------------------------------------------------------------------------
 // thread-local error state
@@ -184,6 +185,17 @@ int tnns_cuda_selftest_wait_expiry(tnns_cuda_ctx* ctx) {
     if (!ctx) return tnns_fail(TNNS_ERR_INVALID, "ctx is NULL");
     TNNS_CUDA_TRY(cudaSetDevice(ctx->device));
     return tnns_launch_wait_selftest(ctx, 0);
+}
+
+// The constants of the threshold form of "PReLU, then the next layer's quantiser" (prelu_thresholds.cuh),
+// computed by the same code the kernels run.
+int tnns_prelu_thresholds(float t, float alpha, float bias, int ternary, float* n1, float* t2) {
+    if (!n1 || !t2) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    if (!(alpha > 0.f && alpha <= 1.f)) return tnns_fail(TNNS_ERR_INVALID, "the threshold form needs 0 < alpha <= 1 (got %g)", (double)alpha);
+    const tnns_thr::Pair r = tnns_thr::make(t + 0.0f, alpha, bias, ternary != 0);
+    *n1 = r.n1;
+    *t2 = r.t2;
+    return TNNS_OK;
 }
 
 // --- plain memory helpers so C callers need no CUDA headers -------------------------------
@@ -415,15 +427,23 @@ size_t tnns_slab_workspace_bytes(int N, int C, int H, int W, int PH, int PW) {
     return slab_image_bytes(N, C, H, W, PH, PW) + tnns_fused_sync_bytes(N);
 }
 
+// the stand-alone quantise kernel that writes the bordered image takes either layout
+static bool bordered_quantise_ok(const float* d_x, int N, int C, int H, int W, int layout) {
+    if (layout == TNNS_NHWC) return tnns_quantise_tma_nhwc_supported(d_x, N, C, H, W);
+    return tnns_quantise_tma_supported(d_x, H, W, layout);
+}
+
 int tnns_cuda_quantise_e2m1_bordered(tnns_cuda_ctx* ctx, int ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
                                      int W, int PH, int PW, int layout, void* stream) {
     if (!ctx || !d_x || !d_thr || !d_image) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
     if (N < 0 || C <= 0 || H <= 0 || W <= 0 || PH < 0 || PW < 0) return tnns_fail(TNNS_ERR_INVALID, "non-positive dimension");
     if (reinterpret_cast<uintptr_t>(d_image) & 127) return tnns_fail(TNNS_ERR_INVALID, "bordered image must be 128-byte aligned");
-    if (!tnns_quantise_tma_supported(d_x, H, W, layout))
-        return tnns_fail(TNNS_ERR_UNSUPPORTED, "the bordered image is written from NCHW input with H*W a multiple of four (at least 32) and a 16-byte aligned base");
+    if (!bordered_quantise_ok(d_x, N, C, H, W, layout))
+        return tnns_fail(TNNS_ERR_UNSUPPORTED,
+                         "the bordered image is written from a 16-byte aligned base: NCHW with H*W a multiple of four (at least 32), or NHWC "
+                         "with C a multiple of four and at least 128 pixels in all");
     TNNS_ENTER(ctx);
-    return tnns_launch_quantise_tma(ctx, ternary != 0, d_x, d_thr, d_image, N, C, H, W, (cudaStream_t)stream, TNNS_IMG_E2M1, PH, PW);
+    return tnns_launch_quantise_tma(ctx, ternary != 0, d_x, d_thr, d_image, N, C, H, W, (cudaStream_t)stream, TNNS_IMG_E2M1, PH, PW, layout);
 }
 
 static int slab_geom(const tnns_cuda_weights* w, const tnns_shape_t* s, TnnsGeom* g) {
@@ -557,6 +577,8 @@ int tnns_cuda_conv_auto_algo(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* 
     if (!ctx || !w || !s) return TNNS_GEMM_AUTO;
     if (layout == TNNS_NCHW && tnns_cuda_slab_preferred(ctx, w, s) && tnns_cuda_conv_slab_supported(ctx, w, s, d_x, layout))
         return tnns_cuda_conv_slab_one_launch_preferred(ctx, w, s, d_x, layout) ? TNNS_GEMM_F4_SLAB_FUSED : TNNS_GEMM_F4_SLAB;
+    if (layout == TNNS_NHWC && tnns_cuda_slab_preferred(ctx, w, s) && tnns_quantise_tma_nhwc_supported(d_x, s->N, s->C, s->H, s->W))
+        return TNNS_GEMM_F4_SLAB;  // two launches: the quantiser inside the GEMM kernel reads NCHW only
     if (tnns_cuda_conv_fused_preferred(const_cast<tnns_cuda_ctx*>(ctx), w, s, d_x, layout)) return TNNS_GEMM_F4_FUSED;
     return TNNS_GEMM_F4_TC;
 }
@@ -701,12 +723,12 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
         const bool one_launch = gemm_algo == TNNS_GEMM_F4_SLAB_FUSED;
         const size_t ws_need = one_launch ? tnns_slab_workspace_bytes(g.N, g.C, g.H, g.W, g.PH, g.PW)
                                           : tnns_bordered_image_bytes(g.N, g.C, g.H, g.W, g.PH, g.PW);
-        if (pack_algo != TNNS_PACK_AUTO || layout != TNNS_NCHW || !tnns_slab_supported(ctx, w, g, one_launch) ||
-            !tnns_quantise_tma_supported(d_x, g.H, g.W, layout) || (reinterpret_cast<uintptr_t>(d_workspace) & 127) || ws_need > workspace_bytes)
+        if (pack_algo != TNNS_PACK_AUTO || (layout != TNNS_NCHW && (one_launch || layout != TNNS_NHWC)) || !tnns_slab_supported(ctx, w, g, one_launch) ||
+            !bordered_quantise_ok(d_x, g.N, g.C, g.H, g.W, layout) || (reinterpret_cast<uintptr_t>(d_workspace) & 127) || ws_need > workspace_bytes)
             return tnns_fail(TNNS_ERR_UNSUPPORTED, "layer, layout, workspace size or alignment outside the slab-fed route");
         if (one_launch) return tnns_cuda_conv_slab(ctx, w, d_x, d_thr, d_y, d_workspace, workspace_bytes, s, alpha, 0, stream);
         rc = tnns_launch_quantise_tma(ctx, type_act_ternary(w->type), d_x, d_thr, d_workspace, g.N, g.C, g.H, g.W, (cudaStream_t)stream, TNNS_IMG_E2M1,
-                                      g.PH, g.PW);
+                                      g.PH, g.PW, layout);
         if (rc) return rc;
         return tnns_launch_gemm_slab(ctx, w, d_workspace, d_y, g, alpha, layout, (cudaStream_t)stream);
     }

@@ -75,7 +75,11 @@ struct SlabCfg {
     static constexpr int ACC_OFF = OVL ? BN - 32 : BN;
     static constexpr int EPW = 2;                     // epilogue warps per lane quadrant
     static constexpr int WARP_EPI0 = 2, WARP_Q0 = 2 + 4 * EPW;
-    static constexpr int NTHREADS = 32 * (2 + 4 * EPW + (QF ? 5 : 0));
+    // Two separate accumulator sets and single blocks: a second warp issues the MMAs of every other tile, so that one
+    // issuer's barrier waits and descriptor arithmetic run under the other's MMAs (see the MMA role).
+    static constexpr bool DUAL = !OVL && CG == 1;
+    static constexpr int WARP_MMA2 = 2 + 4 * EPW + (QF ? 5 : 0);
+    static constexpr int NTHREADS = 32 * (2 + 4 * EPW + (QF ? 5 : 0) + (DUAL ? 1 : 0));
     static constexpr int Q_STAGE = Q_PIX * 64 * 4;
     static constexpr int SMEM_MAX = 232448;
 };
@@ -220,7 +224,7 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
                 }
             }
         }
-    } else if (warp == WARP_MMA) {
+    } else if (warp == WARP_MMA || (Cfg::DUAL && warp == Cfg::WARP_MMA2)) {
         if (lane == 0 && rank == 0) {  // pair: the first block issues for both
             // This one thread's instruction stream paces the tensor pipe.  Two things measured on this loop:
             // nothing that touches shared memory may stand between two MMAs (a table look-up per tap, queued
@@ -234,16 +238,34 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
             const uint32_t row16 = (uint32_t)(p.Wp * (RB / 16));  // one image row further down the slab, in descriptor units
             const uint32_t a_lo0 = (uint32_t)da0, a_hi = (uint32_t)(da0 >> 32), b_lo0 = (uint32_t)db0, b_hi = (uint32_t)(db0 >> 32);
             const uint32_t sfa = tmem_base + SF_COL, sfb = tmem_base + SF_COL + 16;
-            if (p.T == 9 && p.KW == 3) {
+            const bool fast3x3 = p.T == 9 && p.KW == 3;
+            if (warp != WARP_MMA && !fast3x3) goto done;  // the generic loop has one issuer
+            if (fast3x3) {
                 // 3x3 filters: the nine tap offsets live in registers and every MMA of a slab is issued from straight-line
                 // code -- one 32-bit add per operand and MMA.  (The generic loop below spends a dozen dependent
                 // instructions between two MMAs; with the epilogue warps competing for the same scheduler that cost
                 // 250 clocks per MMA on 64-kernel tiles against 85 for the instruction alone.)
+                //
+                // Two issuers (DUAL): this thread takes every other tile of the block's sequence -- its accumulator set is
+                // always the same one -- and steps its ring positions over the other issuer's tiles.  Measured on
+                // 256 x 64x56x56 -> 64 with one issuer: 1560 clocks per tile of which 550 were this thread's two barrier
+                // waits with the tensor pipe idle, and 1010 the issue of nine MMAs that execute in 770.
                 uint32_t aoff[9];
 #pragma unroll
                 for (int j = 0; j < 9; j++) aoff[j] = (uint32_t)((j / 3) * p.Wp + (j % 3)) * (RB / 16);
                 constexpr int KPT = 4 / TAPS;               // K steps (32 bytes) per tap: 1, 2 or 4
-                for (int t = unit; t < ntiles; t += nunits, lt++, first_tile = false) {
+                constexpr int NISSUE = Cfg::DUAL ? 2 : 1;
+                const int me = (warp == WARP_MMA) ? 0 : 1;
+                const int stages_per_tile = p.G * ((9 * KPT + 3) / 4);
+                auto skip_tile = [&]() {  // ring positions over a tile the other issuer takes
+                    for (int i = 0; i < p.G; i++)
+                        if (++sl == (uint32_t)p.nslab) { sl = 0; slph ^= 1; }
+                    if (!p.b_resident)
+                        for (int i = 0; i < stages_per_tile; i++)
+                            if (++s == (uint32_t)p.nstg) { s = 0; ph ^= 1; }
+                };
+                if (me == 1) { skip_tile(); lt = 1; }
+                for (int t = unit + me * nunits; t < ntiles; t += NISSUE * nunits, lt += NISSUE, first_tile = false) {
                     const int buf = lt & 1;
                     if (!mbar_wait(OVL ? bar_tempty : bar_tempty + 8 * buf, (OVL ? (lt & 1) : ((lt >> 1) & 1)) ^ 1, abort_flag, p.status, 2)) goto done;
                     tc_fence_after();
@@ -280,6 +302,7 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
                         if (++sl == (uint32_t)p.nslab) { sl = 0; slph ^= 1; }
                     }
                     if (CG == 2) tc_commit_pair(bar_tfull + 8 * buf); else tc_commit(bar_tfull + 8 * buf);
+                    if (NISSUE == 2) skip_tile();
                 }
             } else
             for (int t = unit; t < ntiles; t += nunits, lt++, first_tile = false) {
@@ -345,7 +368,7 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
         } else if (lane == 0) {
             publish_items(p.q_sync, p.status, qbars, abort_flag);
         }
-    } else if (warp >= WARP_EPI0) {
+    } else if (warp >= WARP_EPI0 && warp < WARP_EPI0 + 4 * EPW) {
         // ---------------- epilogue ----------------
         const int q = warp & 3;                        // tensor-memory lane quadrant this warp may access
         const int ecol = (warp - WARP_EPI0) >> 2;      // which share of the columns
@@ -356,11 +379,19 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
         const int OHW = p.OH * p.OW;
         uint32_t lt = 0;
         const uint32_t bar_release = (CG == 2 && rank != 0) ? mapa_shared(bar_tempty, 0) : 0u;
+        // quantised output with 0 < alpha <= 1: PReLU and the next layer's rule collapse into thresholds on
+        // the accumulator (two instructions per output and plane instead of evaluating the PReLU first).
+        // Taken on 256-kernel tiles only: on narrower tiles, where the epilogue of one tile runs beside the few
+        // MMAs of the next, the shorter but denser instruction stream slowed the tensor pipe more than it
+        // saved (256 x 64x56x56 -> 64 with a bordered image out: 60 us against 49).
+        const bool next_tern = !p.next_binary && p.next_format != 0;
+        const bool by_thr = BN == 256 && p.pimg != nullptr && alpha_in_unit;
+        tnns_thr::Pair qt = {0.f, 0.f};
+        int qt_img = -1;
         for (int t = unit; t < ntiles; t += nunits, lt++) {
             const int buf = lt & 1;
             const int n0 = (t % ntn) * BN;
-            if (!mbar_wait(bar_tfull + 8 * buf, (lt >> 1) & 1, abort_flag, p.status, 5)) goto done;
-            tc_fence_after();
+            // where this thread's row sits in the lattice, and its image's threshold: worked out while the tile's MMAs run
             const int row = (t / ntn) * TILE_M + (int)rank * BM + q * 32 + lane;  // virtual row
             const bool row_ok = row < p.Mv;
             const int n_img = row_ok ? (int)p.div_hpwp.div((uint32_t)row) : 0;
@@ -370,6 +401,13 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
             const int opix = yy * p.OW + xx;
             float* ybase = (p.layout == TNNS_NHWC) ? p.y + ((size_t)n_img * OHW + opix) * p.KN : p.y + (size_t)n_img * p.KN * OHW + opix;
             const float tq = (p.pimg && valid) ? __ldg(p.thr_next + n_img) + 0.0f : 0.f;
+            if (by_thr && valid && n_img != qt_img) {
+                // the next layer's rule as thresholds on the raw accumulator, once per image this thread meets
+                qt = tnns_thr::make(tq, p.alpha, bias_f, next_tern);
+                qt_img = n_img;
+            }
+            if (!mbar_wait(bar_tfull + 8 * buf, (lt >> 1) & 1, abort_flag, p.status, 5)) goto done;
+            tc_fence_after();
             int start = 0;
             if (OVL && buf == 0 && ecol == EPW - 1) start = NSL - 1;
 #pragma unroll 1
@@ -399,10 +437,33 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
                 const int c0 = n0 + cb;
                 if (valid) {
                     float f[32];
-                    if (alpha_in_unit) {
+                    uint32_t sg = 0, nz = 0;
+                    if (by_thr) {
+                        if (next_tern) {
+                            uint32_t above = 0;
+#pragma unroll
+                            for (int j = 31; j >= 0; j--) {
+                                sg = push_sign(sg, __uint_as_float(v[j]) + qt.n1);
+                                above = push_sign(above, qt.t2 - __uint_as_float(v[j]));
+                            }
+                            nz = sg | above;
+                        } else {
+#pragma unroll
+                            for (int j = 31; j >= 0; j--) sg = push_sign(sg, __uint_as_float(v[j]) + qt.n1);
+                        }
+                    } else
+                    // (the run-time choices are taken outside the unrolled loops: left inside, every element pays for
+                    // both sides of each -- the epilogue warps share their schedulers with the MMA-issuing threads)
+                    if (alpha_in_unit && p.acc_bias) {
 #pragma unroll
                         for (int j = 0; j < 32; j++) {
-                            const float a = p.acc_bias ? __uint_as_float(v[j]) + bias_f : __uint_as_float(v[j]);
+                            const float a = __uint_as_float(v[j]) + bias_f;
+                            f[j] = fmaxf(a, fmaf(a, p.alpha, 0.0f));
+                        }
+                    } else if (alpha_in_unit) {
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const float a = __uint_as_float(v[j]);
                             f[j] = fmaxf(a, fmaf(a, p.alpha, 0.0f));
                         }
                     } else {
@@ -415,16 +476,10 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
                     const bool full = c0 + 32 <= p.KN;
                     if (p.pimg) {
                         if (c0 < p.cp_next * 64) {
-                            const bool tern = !p.next_binary && p.next_format != 0;
-                            uint32_t sg = 0, nz = 0;
-#pragma unroll
-                            for (int j = 31; j >= 0; j--) {
-                                if (tern) {
-                                    sg = __funnelshift_l(__float_as_uint(f[j] + tq), sg, 1);
-                                    nz = __funnelshift_l(__float_as_uint(tq - fabsf(f[j])), nz, 1);
-                                } else {
-                                    sg = __funnelshift_l(__float_as_uint((f[j] + 0.0f) - tq), sg, 1);
-                                }
+                            const bool tern = next_tern;
+                            if (!by_thr) {
+                                if (tern) quantise32_ternary(f, tq, sg, nz);
+                                else sg = quantise32_binary(f, tq);
                             }
                             const int have = p.KN - c0;
                             const uint32_t vmask = have >= 32 ? 0xFFFFFFFFu : (have > 0 ? (1u << have) - 1u : 0u);

@@ -594,18 +594,29 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
         const float bias_f = (float)p.acc_bias;  // +0.0f when there is none: a + 0.0f also turns a -0 sum into +0
         uint32_t lt = 0;
         const uint32_t bar_release = (CG == 2 && rank != 0) ? mapa_shared(bar_tempty, 0) : 0u;  // pair: the first block's barrier
+        // quantised output with 0 < alpha <= 1: PReLU and the next layer's rule collapse into thresholds on
+        // the accumulator (two instructions per output and plane instead of evaluating the PReLU first)
+        const bool by_thr = F4 && p.pimg != nullptr && alpha_in_unit;
+        tnns_thr::Pair qt = {0.f, 0.f};
+        long long qt_img = -1;
         for (long long t = unit; t < ntiles; t += nunits, lt++) {
             const int buf = lt % NBUF;
             const long long m0 = (t / ntn) * TILE_M + (long long)rank * BMT + sub * BM;
             const int n0 = (int)(t % ntn) * BN;
-            if (!mbar_wait(bar_tfull + 8 * buf, (lt / NBUF) & 1, abort_flag, p.status, 5)) goto done;
-            tc_fence_after();
+            // the row's image (a 64-bit division) and threshold: worked out while the tile's MMAs run
             const long long row = m0 + q * 32 + lane;
             const bool row_ok = row < p.M;
             const long long n_img = row_ok ? row / p.OHW : 0;
             const int rem = (int)(row - n_img * p.OHW);
             float* ybase = (p.layout == TNNS_NHWC) ? p.y + (size_t)row * p.KN : p.y + (size_t)n_img * p.KN * p.OHW + rem;
             const float tq = (p.pimg && row_ok) ? __ldg(p.thr_next + n_img) + 0.0f : 0.f;  // + 0.0f: -0 acts as +0
+            if (by_thr && row_ok && n_img != qt_img) {
+                // the next layer's rule as thresholds on the raw accumulator, once per image this thread meets
+                qt = tnns_thr::make(tq, p.alpha, bias_f, p.next_ternary != 0);
+                qt_img = n_img;
+            }
+            if (!mbar_wait(bar_tfull + 8 * buf, (lt / NBUF) & 1, abort_flag, p.status, 5)) goto done;
+            tc_fence_after();
             // overlapping sets: start with the 32 columns shared with the other set (the last of
             // set 0, the first of set 1) if this warp owns them, and release after the first slice
             constexpr int NSL = ECOLS / 32;
@@ -639,13 +650,35 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                 }
                 if (row_ok) {
                     float f[32];
-                    if (F4 && alpha_in_unit) {
+                    uint32_t sg = 0, nz = 0;
+                    if (by_thr) {
+                        if (p.next_ternary) {
+                            uint32_t above = 0;
+#pragma unroll
+                            for (int j = 31; j >= 0; j--) {
+                                sg = push_sign(sg, __uint_as_float(v[j]) + qt.n1);
+                                above = push_sign(above, qt.t2 - __uint_as_float(v[j]));
+                            }
+                            nz = sg | above;
+                        } else {
+#pragma unroll
+                            for (int j = 31; j >= 0; j--) sg = push_sign(sg, __uint_as_float(v[j]) + qt.n1);
+                        }
+                    } else if (F4 && alpha_in_unit && p.acc_bias) {
+                        // (the run-time choices are taken outside the unrolled loops: left inside, every element
+                        // pays for both sides of each)
+#pragma unroll
+                        for (int j = 0; j < 32; j++) {
+                            const float a = __uint_as_float(v[j]) + bias_f;
+                            f[j] = fmaxf(a, fmaf(a, p.alpha, 0.0f));
+                        }
+                    } else if (F4 && alpha_in_unit) {
                         // 0 < alpha <= 1: PReLU(a) = max(a, alpha*a), two instructions per output.  The
                         // product is formed as fma(a, alpha, +0): one rounding like the reference's
                         // acc*alpha, and a -0 sum (all products -0) gives +0, which max(-0, +0) returns.
 #pragma unroll
                         for (int j = 0; j < 32; j++) {
-                            const float a = p.acc_bias ? __uint_as_float(v[j]) + bias_f : __uint_as_float(v[j]);
+                            const float a = __uint_as_float(v[j]);
                             f[j] = fmaxf(a, fmaf(a, p.alpha, 0.0f));
                         }
                     } else if (F4) {
@@ -671,15 +704,9 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                         // 32-bit lane of the next layer's bit planes (same rules as the pack kernel:
                         // sign = f < -t, non-zero = |f| > t; binary: f < t), channels past KN absent.
                         if (c0 < p.cp_next * 64) {
-                            uint32_t sg = 0, nz = 0;
-#pragma unroll
-                            for (int j = 31; j >= 0; j--) {
-                                if (p.next_ternary) {
-                                    sg = __funnelshift_l(__float_as_uint(f[j] + tq), sg, 1);
-                                    nz = __funnelshift_l(__float_as_uint(tq - fabsf(f[j])), nz, 1);
-                                } else {
-                                    sg = __funnelshift_l(__float_as_uint((f[j] + 0.0f) - tq), sg, 1);
-                                }
+                            if (!by_thr) {
+                                if (p.next_ternary) quantise32_ternary(f, tq, sg, nz);
+                                else sg = quantise32_binary(f, tq);
                             }
                             const int have = p.KN - c0;
                             const uint32_t valid = have >= 32 ? 0xFFFFFFFFu : (have > 0 ? (1u << have) - 1u : 0u);

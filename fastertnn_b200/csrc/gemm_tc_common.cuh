@@ -6,6 +6,7 @@
 
 #include "internal.h"
 #include "mbar.cuh"
+#include "prelu_thresholds.cuh"
 
 namespace {
 
@@ -163,6 +164,27 @@ __device__ __forceinline__ bool counter_wait(const unsigned int* ctr, unsigned i
     }
 }
 __device__ __forceinline__ uint32_t push_sign(uint32_t acc, float d) { return __funnelshift_l(__float_as_uint(d), acc, 1); }
+
+// 32 layer outputs of one pixel -> one 32-bit lane of the next layer's sign plane and non-zero plane
+// (element j at bit j; same rules as the quantise kernels: sign = f < -t, non-zero = |f| > t; binary:
+// sign = f < t).  One shift chain per plane: splitting each into four chains joined at the end was
+// measured slower on 64-kernel tiles (55 against 49 us per layer), where the epilogue's instruction
+// count, not its dependency stalls, is what the tile rate hangs on.
+__device__ __forceinline__ void quantise32_ternary(const float (&f)[32], float tq, uint32_t& sg, uint32_t& nz) {
+    sg = 0;
+    nz = 0;
+#pragma unroll
+    for (int j = 31; j >= 0; j--) {
+        sg = push_sign(sg, f[j] + tq);
+        nz = push_sign(nz, tq - fabsf(f[j]));
+    }
+}
+__device__ __forceinline__ uint32_t quantise32_binary(const float (&f)[32], float tq) {
+    uint32_t sg = 0;
+#pragma unroll
+    for (int j = 31; j >= 0; j--) sg = push_sign(sg, (f[j] + 0.0f) - tq);  // + 0.0f: -0 reads as +0
+    return sg;
+}
 
 // Quantiser role of the fused form, called by the four quantiser warps together (thread = pixel).
 // An item = 128 neighbouring pixels x 64 channels of one image (NCHW, a row of the 2-D tensor

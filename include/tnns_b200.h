@@ -324,7 +324,8 @@ int tnns_cuda_conv_fused_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights*
  * group serves every tap, the tensor core reading each tap as a row-shifted view of that slab
  * (rows on border positions are computed and not stored).  Needs stride 1 and 64, 128 or a multiple
  * of 256 channels (after rounding to 64): tnns_cuda_slab_supported.
- *   tnns_cuda_quantise_e2m1_bordered  fp32 NCHW (H*W a multiple of four) -> bordered image, 128-byte aligned
+ *   tnns_cuda_quantise_e2m1_bordered  fp32 NCHW (H*W a multiple of four) or NHWC (C a multiple of four, at least
+ *                                     128 pixels in all) -> bordered image, 128-byte aligned
  *   tnns_cuda_gemm_slab               bordered image -> fp32 output (same result as every other route)
  *   tnns_cuda_gemm_slab_packed_out    the same with the quantising epilogue: next_format 0 / 1 bit planes
  *                                     (binary / ternary), 2 plain 4-bit image, 3 bordered 4-bit image for a
@@ -456,6 +457,16 @@ int tnns_cuda_sync(tnns_cuda_ctx* ctx);
  * the following tnns_cuda_sync returns TNNS_ERR_DEVICE_WAIT.  The kernel returns normally and the
  * context remains usable. */
 int tnns_cuda_selftest_wait_expiry(tnns_cuda_ctx* ctx);
+
+/* The rule of the quantising epilogues, on the host (no GPU needed; no reference counterpart).  A layer
+ * that writes the next layer's quantised activations applies, for 0 < alpha <= 1, thresholds to its raw
+ * integer accumulator v instead of evaluating PReLU(v + bias) first:
+ *     sign bit = (v + *n1 < 0)      above = (*t2 - v < 0)      ternary non-zero = sign | above
+ * which equals the reference's PReLU (src/tnns/mm_p2_final_tnn_avx2.c:90-93) followed by its quantisers
+ * (src/tnns/ternarize2row_avx2.c:438-452, src/tnns/binarize2row_avx2.c:19-21) for every integer v below
+ * 2^22 in magnitude.  This returns the two constants the kernels derive from a next-layer threshold t,
+ * so that the equivalence can be checked exhaustively on a CPU.  ternary = 0: *t2 is 0 and unused. */
+int tnns_prelu_thresholds(float t, float alpha, float bias, int ternary, float* n1, float* t2);
 
 /* Plain device-memory helpers so that C callers need no CUDA headers.  Synchronous. */
 int tnns_cuda_malloc(tnns_cuda_ctx* ctx, size_t bytes, void** out);
