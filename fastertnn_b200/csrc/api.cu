@@ -428,8 +428,10 @@ size_t tnns_slab_workspace_bytes(int N, int C, int H, int W, int PH, int PW) {
 }
 
 // the stand-alone quantise kernel that writes the bordered image takes either layout
+// (a 1x1 image is the same memory in both layouts and is read as pixel-major: fully connected layers)
+static int quantise_layout(int layout, int H, int W) { return (H == 1 && W == 1) ? TNNS_NHWC : layout; }
 static bool bordered_quantise_ok(const float* d_x, int N, int C, int H, int W, int layout) {
-    if (layout == TNNS_NHWC) return tnns_quantise_tma_nhwc_supported(d_x, N, C, H, W);
+    if (quantise_layout(layout, H, W) == TNNS_NHWC) return tnns_quantise_tma_nhwc_supported(d_x, N, C, H, W);
     return tnns_quantise_tma_supported(d_x, H, W, layout);
 }
 
@@ -443,7 +445,8 @@ int tnns_cuda_quantise_e2m1_bordered(tnns_cuda_ctx* ctx, int ternary, const floa
                          "the bordered image is written from a 16-byte aligned base: NCHW with H*W a multiple of four (at least 32), or NHWC "
                          "with C a multiple of four and at least 128 pixels in all");
     TNNS_ENTER(ctx);
-    return tnns_launch_quantise_tma(ctx, ternary != 0, d_x, d_thr, d_image, N, C, H, W, (cudaStream_t)stream, TNNS_IMG_E2M1, PH, PW, layout);
+    return tnns_launch_quantise_tma(ctx, ternary != 0, d_x, d_thr, d_image, N, C, H, W, (cudaStream_t)stream, TNNS_IMG_E2M1, PH, PW,
+                                    quantise_layout(layout, H, W));
 }
 
 static int slab_geom(const tnns_cuda_weights* w, const tnns_shape_t* s, TnnsGeom* g) {
@@ -728,7 +731,7 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
             return tnns_fail(TNNS_ERR_UNSUPPORTED, "layer, layout, workspace size or alignment outside the slab-fed route");
         if (one_launch) return tnns_cuda_conv_slab(ctx, w, d_x, d_thr, d_y, d_workspace, workspace_bytes, s, alpha, 0, stream);
         rc = tnns_launch_quantise_tma(ctx, type_act_ternary(w->type), d_x, d_thr, d_workspace, g.N, g.C, g.H, g.W, (cudaStream_t)stream, TNNS_IMG_E2M1,
-                                      g.PH, g.PW, layout);
+                                      g.PH, g.PW, quantise_layout(layout, g.H, g.W));
         if (rc) return rc;
         return tnns_launch_gemm_slab(ctx, w, d_workspace, d_y, g, alpha, layout, (cudaStream_t)stream);
     }

@@ -723,7 +723,7 @@ int tnns_launch_gemm_slab(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const 
     a.OH = g.OH; a.OW = g.OW; a.Wp = pl.Wp; a.HpWp = pl.Hp * pl.Wp;
     a.KW = g.KW; a.T = pl.T; a.G = pl.G;
     a.slab_bytes = pl.slab_bytes; a.copy_rows = pl.copy_rows; a.ncopies = pl.ncopies;
-    a.layout = layout;
+    a.layout = (g.OH * g.OW == 1) ? TNNS_NHWC : layout;  // one pixel per image: both layouts are the same memory, the pixel-major epilogue stores 16 bytes per lane
     a.zero_passes = w->type != TNN;
     // BNN counts its products: pad words are never multiplied here, absent channels (+1 x +1) are
     a.acc_bias = (w->type == BNN) ? w->K_unpack - 64 * w->Kw : 0;

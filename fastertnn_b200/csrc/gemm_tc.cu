@@ -597,6 +597,7 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
         // quantised output with 0 < alpha <= 1: PReLU and the next layer's rule collapse into thresholds on
         // the accumulator (two instructions per output and plane instead of evaluating the PReLU first)
         const bool by_thr = F4 && p.pimg != nullptr && alpha_in_unit;
+        const bool rows16 = F4 && p.pimg == nullptr && p.layout == TNNS_NHWC && (p.KN & 1) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 7) == 0;
         tnns_thr::Pair qt = {0.f, 0.f};
         long long qt_img = -1;
         for (long long t = unit; t < ntiles; t += nunits, lt++) {
@@ -627,6 +628,27 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                 const int cb = ecol * ECOLS + ((i + start) % NSL) * 32;
                 uint32_t v[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * ACC_OFF + sub * BN + cb);
+                if (rows16) {
+                    // pixel-major fp32 output: fetched in the shape that gives four lanes one 32-byte piece of a row
+                    tmem_ld_16x256b_x4(taddr, v);
+                    tmem_ld_16x256b_x4(taddr + (16u << 16), v + 16);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (OVL ? (i == 0) : (i == NSL - 1)) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (CG == 2 && rank != 0) mbar_arrive_cluster(bar_release + (OVL ? 0 : 8 * buf));
+                            else mbar_arrive(OVL ? bar_tempty : bar_tempty + 8 * buf);
+                        }
+                    }
+                    const long long row0 = m0 + q * 32;
+                    if (row0 < p.M) {
+                        float f[32];
+                        prelu32_f4(v, f, alpha_in_unit, p.acc_bias, bias_f, p.alpha, p.zero_passes);
+                        store_rows16(f, p.y + (size_t)row0 * p.KN + (n0 + cb), p.KN, p.M - row0, p.KN - (n0 + cb), lane);
+                    }
+                    continue;
+                }
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
@@ -664,30 +686,8 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
 #pragma unroll
                             for (int j = 31; j >= 0; j--) sg = push_sign(sg, __uint_as_float(v[j]) + qt.n1);
                         }
-                    } else if (F4 && alpha_in_unit && p.acc_bias) {
-                        // (the run-time choices are taken outside the unrolled loops: left inside, every element
-                        // pays for both sides of each)
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const float a = __uint_as_float(v[j]) + bias_f;
-                            f[j] = fmaxf(a, fmaf(a, p.alpha, 0.0f));
-                        }
-                    } else if (F4 && alpha_in_unit) {
-                        // 0 < alpha <= 1: PReLU(a) = max(a, alpha*a), two instructions per output.  The
-                        // product is formed as fma(a, alpha, +0): one rounding like the reference's
-                        // acc*alpha, and a -0 sum (all products -0) gives +0, which max(-0, +0) returns.
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const float a = __uint_as_float(v[j]);
-                            f[j] = fmaxf(a, fmaf(a, p.alpha, 0.0f));
-                        }
                     } else if (F4) {
-                        // any alpha: the reference's expression on the canonical +0, a > 0 ? a : a*alpha
-#pragma unroll
-                        for (int j = 0; j < 32; j++) {
-                            const float ac = (p.acc_bias ? __uint_as_float(v[j]) + bias_f : __uint_as_float(v[j])) + 0.0f;
-                            f[j] = ac * ((p.zero_passes ? ac >= 0.f : ac > 0.f) ? 1.0f : p.alpha);
-                        }
+                        prelu32_f4(v, f, alpha_in_unit, p.acc_bias, bias_f, p.alpha, p.zero_passes);
                     } else {
                         // int -> float without the conversion unit: for |a| < 2^22 the float with bit
                         // pattern 0x4B400000 + a is 1.5*2^23 + a exactly, so subtracting 1.5*2^23 gives a.
@@ -1000,7 +1000,9 @@ int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const vo
     a.KN = w->KN;
     a.Kp = w->Kp;
     a.OHW = OHW;
-    a.layout = layout;
+    // one output pixel per image (fully connected layers): both layouts are the same memory, and the pixel-major
+    // epilogue writes 16 bytes per lane where the channel-major one would write 4 (rows are KN floats apart either way)
+    a.layout = OHW == 1 ? TNNS_NHWC : layout;
     a.a_two_planes = (w->type == TNN || w->type == TBN) ? 1 : 0;
     a.acc_bias = (w->type == BNN) ? w->K_unpack - 64 * w->Kp : 0;
     a.zero_passes = w->type != TNN;
@@ -1163,7 +1165,7 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     a.KN = w->KN;
     a.Kp = w->Kp;
     a.OHW = g.OH * g.OW;
-    a.layout = layout;
+    a.layout = a.OHW == 1 ? TNNS_NHWC : layout;  // one pixel per image: same memory, wider stores (see above)
     a.a_two_planes = 1;
     a.acc_bias = 0;
     a.zero_passes = w->type != TNN;

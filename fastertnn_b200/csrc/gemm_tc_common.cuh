@@ -186,6 +186,68 @@ __device__ __forceinline__ uint32_t quantise32_binary(const float (&f)[32], floa
     return sg;
 }
 
+// PReLU of 32 fp32 accumulators (4-bit form), as the reference evaluates it on an integer sum
+// (src/tnns/mm_p2_final_tnn_avx2.c:90-93; zero_passes: the tbn / btn / bnn forms pass a zero sum through).
+// The run-time choices sit outside the unrolled loops: inside, every element pays for both sides of each.
+__device__ __forceinline__ void prelu32_f4(const uint32_t (&v)[32], float (&f)[32], bool alpha_in_unit, int acc_bias, float bias_f, float alpha,
+                                           int zero_passes) {
+    if (alpha_in_unit && acc_bias) {
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const float a = __uint_as_float(v[j]) + bias_f;
+            f[j] = fmaxf(a, fmaf(a, alpha, 0.0f));
+        }
+    } else if (alpha_in_unit) {
+        // 0 < alpha <= 1: PReLU(a) = max(a, alpha*a), two instructions per output.  The product is formed as
+        // fma(a, alpha, +0): one rounding like the reference's acc*alpha, and a -0 sum (all products -0) gives
+        // +0, which max(-0, +0) returns.
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const float a = __uint_as_float(v[j]);
+            f[j] = fmaxf(a, fmaf(a, alpha, 0.0f));
+        }
+    } else {
+        // any alpha: the reference's expression on the canonical +0, a > 0 ? a : a*alpha
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const float ac = (acc_bias ? __uint_as_float(v[j]) + bias_f : __uint_as_float(v[j])) + 0.0f;
+            f[j] = ac * ((zero_passes ? ac >= 0.f : ac > 0.f) ? 1.0f : alpha);
+        }
+    }
+}
+
+// Tensor-memory load of 16 lanes x 32 columns in the 16x256b shape: thread t of the warp receives, for each
+// group k of eight columns, w[4k], w[4k+1] = row t/4, columns 8k + 2(t%4) and + 1, and w[4k+2], w[4k+3] = the
+// same columns of row t/4 + 8.  Four neighbouring lanes thus hold 32 contiguous bytes of one row: the shape
+// for writing a pixel-major (NHWC) fp32 tile with full sectors per store.
+__device__ __forceinline__ void tmem_ld_16x256b_x4(uint32_t taddr, uint32_t* w) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.16x256b.x4.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7]), "=r"(w[8]), "=r"(w[9]),
+          "=r"(w[10]), "=r"(w[11]), "=r"(w[12]), "=r"(w[13]), "=r"(w[14]), "=r"(w[15])
+        : "r"(taddr)
+        : "memory");
+}
+
+// Stores what two such loads (lanes 0..15 and 16..31 of the warp's quadrant) delivered: f[16*hh + 4k + 2*b + {0,1}] is
+// row 16*hh + 8*b + lane/4 of the quadrant, columns 8k + 2(lane%4) and + 1 of the slice.  y_quad = the quadrant's first
+// row at the slice's first column; rows_left / cols_left = rows and columns that exist from there on; KN is even.
+__device__ __forceinline__ void store_rows16(const float (&f)[32], float* y_quad, int KN, long long rows_left, int cols_left, int lane) {
+    const int cc = 2 * (lane & 3);
+#pragma unroll
+    for (int h = 0; h < 4; h++) {
+        const int r = 8 * h + (lane >> 2);
+        if (r < rows_left) {
+            float* yr = y_quad + (size_t)r * KN + cc;
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                if (8 * k + cc < cols_left)
+                    __stcs(reinterpret_cast<float2*>(yr + 8 * k), make_float2(f[16 * (h >> 1) + 4 * k + 2 * (h & 1)], f[16 * (h >> 1) + 4 * k + 2 * (h & 1) + 1]));
+        }
+    }
+}
+
 // Quantiser role of the fused form, called by the four quantiser warps together (thread = pixel).
 // An item = 128 neighbouring pixels x 64 channels of one image (NCHW, a row of the 2-D tensor
 // (image, channel) x pixels per channel).  The first lane claims items in image order from a
