@@ -713,7 +713,8 @@ def run_layer(args, name, type_, N_cfg, layer: Layer):
         gemm_tops = ops_loc / (t_gemm * 1e-3) / 1e12
         per_img = ncu_traffic(name, info["key"])
         gemm_traffic = per_img * nloc if per_img else None
-        per_img = ncu_traffic(name, "quantise_e2m1_bordered" if slab else "quantise_e2m1" if im2col else "quantise" if implicit else "pack")
+        pack_key = "quantise_e2m1_bordered" if slab else "quantise_e2m1" if im2col else "quantise" if implicit else "pack"
+        per_img = (ncu_traffic(name, pack_key + "_nhwc") if args.layout == "nhwc" else None) or ncu_traffic(name, pack_key)
         pack_traffic = per_img * nloc if per_img else None
         if args.gemm == "popc":
             # integer-pipe kernel: 5.5 LOP3 per 32-bit lane and output, LOP3 issues 64 lanes/clk/SM
