@@ -447,8 +447,8 @@ class LayerRun:
                            else ft.packed_bytes(type_, self.shape))
         self.step_bytes = self.in_bytes + self.out_bytes + self.pack_bytes
         self.ring = max(2, -(-3 * L2_BYTES // max(self.step_bytes, 1)))
-        if self.nhwc and (args.route in ("fused", "slab_fused") or not tc4):
-            raise SystemExit("bench: NHWC input is measured on the two-launch tensor-core routes")
+        if self.nhwc and (args.route == "slab_fused" or not tc4):
+            raise SystemExit("bench: NHWC input is measured on the tensor-core routes (not the one-launch slab form)")
         x0 = torch.from_numpy(x_h[:nloc]).cuda()
         if self.nhwc:
             x0 = x0.permute(0, 2, 3, 1).contiguous()
@@ -504,7 +504,7 @@ class LayerRun:
         elif self.slab:
             self.ctx.gemm_slab(self.w, p, y, self.shape, 0.5, self.layout, self.sp)
         elif self.fused:
-            self.ctx.conv_fused(self.w, x, self.thr_d.data_ptr(), y, p, self.pack_bytes, self.shape, 0.5, 0, self.sp)
+            self.ctx.conv_ws(self.w, x, self.thr_d.data_ptr(), y, p, self.pack_bytes, self.shape, 0.5, self.layout, ft.PACK_AUTO, ft.GEMM_F4_FUSED, self.sp)
         elif self.im2col:
             self.ctx.gemm_im2col(self.w, p, y, self.shape, 0.5, self.layout, self.sp)
         elif self.implicit:

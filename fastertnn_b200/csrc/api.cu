@@ -603,7 +603,7 @@ int tnns_cuda_conv_fused_supported(const tnns_cuda_weights* w, const tnns_shape_
 
 static int conv_fused_impl(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y,
                            void* d_image_out, const float* d_thr_next, int next_format, void* d_workspace, size_t workspace_bytes,
-                           const tnns_shape_t* s, float alpha, int pairs, void* stream) {
+                           const tnns_shape_t* s, float alpha, int pairs, void* stream, int layout = TNNS_NCHW) {
     if (!ctx || !w || !d_x || !d_thr || !d_workspace) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
     TnnsGeom g;
     int rc = tnns_make_geom(s, &g);
@@ -620,7 +620,7 @@ static int conv_fused_impl(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const
     f.d_x = d_x;
     f.d_thr = d_thr;
     f.d_sync = reinterpret_cast<unsigned int*>(static_cast<char*>(d_workspace) + fused_image_bytes(g.N, g.C, g.H, g.W));
-    return tnns_launch_gemm_im2col(ctx, w, d_workspace, d_y, g, alpha, TNNS_NCHW, (cudaStream_t)stream, pairs, d_image_out, d_thr_next,
+    return tnns_launch_gemm_im2col(ctx, w, d_workspace, d_y, g, alpha, layout, (cudaStream_t)stream, pairs, d_image_out, d_thr_next,
                                    next_format, &f);
 }
 
@@ -755,7 +755,7 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
         if (gemm_algo == TNNS_GEMM_F4_FUSED && !can)
             return tnns_fail(TNNS_ERR_UNSUPPORTED, "layer, layout, workspace size or alignment outside the fused quantise + GEMM route");
         if (can && (gemm_algo == TNNS_GEMM_F4_FUSED || tnns_cuda_conv_fused_preferred(ctx, w, s, d_x, layout)))
-            return tnns_cuda_conv_fused(ctx, w, d_x, d_thr, d_y, d_workspace, workspace_bytes, s, alpha, 0, stream);
+            return conv_fused_impl(ctx, w, d_x, d_thr, d_y, nullptr, nullptr, 1, d_workspace, workspace_bytes, s, alpha, 0, stream, layout);
     }
     const bool auto_route = pack_algo == TNNS_PACK_AUTO && (gemm_algo == TNNS_GEMM_AUTO || gemm_algo == TNNS_GEMM_F4_TC);
     if (auto_route && tnns_im2col_supported(w, g) && tnns_e2m1_image_bytes(g.N, g.C, g.H, g.W) <= workspace_bytes) {

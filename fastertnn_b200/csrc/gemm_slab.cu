@@ -363,7 +363,7 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
             QuantArgs qa;
             qa.qthr = p.qthr; qa.qimg = p.qimg; qa.q_sync = p.q_sync; qa.qN = p.qN; qa.qC = p.qC; qa.q_nbands = p.q_nbands; qa.Cp = p.Cp;
             qa.HW = p.q_H * p.q_W; qa.status = p.status;
-            qa.W = p.q_W; qa.Wp = p.Wp; qa.HpWp = p.HpWp; qa.off0 = p.q_PH * p.Wp + p.q_PW; qa.border = 1; qa.binary = p.q_binary;
+            qa.W = p.q_W; qa.Wp = p.Wp; qa.HpWp = p.HpWp; qa.off0 = p.q_PH * p.Wp + p.q_PW; qa.border = 1; qa.binary = p.q_binary; qa.nhwc = 0;
             quantise_items(qa, &tmap_q, q_ring, qbars, abort_flag, tid - Cfg::WARP_Q0 * 32);
         } else if (lane == 0) {
             publish_items(p.q_sync, p.status, qbars, abort_flag);

@@ -101,8 +101,9 @@ struct TcCfg {
     static constexpr int WARP_EPI0 = WARP_EXP0 + 4 * MT * NG;
     static constexpr int WARP_Q0 = WARP_EPI0 + 4 * MT * EPW;
     static constexpr int NTHREADS = 32 * (2 + 4 * MT * NG + 4 * MT * EPW + NQ);
-    static constexpr int TAPMAX = QF ? 256 : 1024;  // entries of the tap table kept in shared memory
+    static constexpr int TAPMAX = QF ? 192 : 1024;  // entries of the tap table kept in shared memory (QF: 192 entries + the 256 bytes of barriers = 1 KB, see Q_OFF)
     static constexpr size_t Q_OFF = (size_t)NSTG * (A_STAGE + B_STAGE) + 256 + TAPMAX * sizeof(uint32_t);  // quantiser ring, then its barriers
+    static_assert(!QF || Q_OFF % 1024 == 0, "the quantiser ring receives 128-byte-swizzled boxes: its stages start on 1024-byte boundaries");
     static constexpr size_t SMEM = 1024 + Q_OFF + (QF ? QSTG * Q_STAGE + 128 : 0);
     static_assert(SMEM <= 232448, "shared memory per block");
 };
@@ -220,6 +221,7 @@ struct GemmArgs {
     uint4* qimg;
     unsigned int* q_sync;
     int qN, qC, q_nbands;
+    int q_nhwc;        // that input is pixel-major (NHWC)
     int q_self_clean;  // the last block to leave zeroes the words again (q_sync[1] counts the blocks that left)
 };
 
@@ -579,7 +581,7 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
     } else if (QF && warp >= Cfg::WARP_Q0) {
         uint64_t* qbars = reinterpret_cast<uint64_t*>(smem + Cfg::Q_OFF + Cfg::QSTG * Cfg::Q_STAGE);
         if (warp < Cfg::WARP_Q0 + 4)
-            quantise_items(plain_quant_args(p.qthr, p.qimg, p.q_sync, p.qN, p.qC, p.q_nbands, p.Cp, p.H, p.W, p.status), &tmap_q, smem + Cfg::Q_OFF, qbars,
+            quantise_items(plain_quant_args(p.qthr, p.qimg, p.q_sync, p.qN, p.qC, p.q_nbands, p.Cp, p.H, p.W, p.status, p.q_nhwc), &tmap_q, smem + Cfg::Q_OFF, qbars,
                            abort_flag, tid - Cfg::WARP_Q0 * 32);
         else if (lane == 0)
             publish_items(p.q_sync, p.status, qbars, abort_flag);
@@ -1016,7 +1018,7 @@ int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const vo
     a.img = nullptr;
     a.jtab = nullptr;
     a.H = a.W = a.OW = a.Cp = a.SH = a.SW = a.PH = a.PW = 0;
-    a.qx = a.qthr = nullptr; a.qimg = nullptr; a.q_sync = nullptr; a.qN = a.qC = a.q_nbands = a.q_self_clean = 0;
+    a.qx = a.qthr = nullptr; a.qimg = nullptr; a.q_sync = nullptr; a.qN = a.qC = a.q_nbands = a.q_self_clean = a.q_nhwc = 0;
     if (implicit_geom) {
         // d_a is the quantised image of the layer input, not an im2row matrix
         if (!f4 || !w->d_jtab) return tnns_fail(TNNS_ERR_UNSUPPORTED, "implicit im2row needs the 4-bit tensor-core GEMM and layer geometry");
@@ -1104,8 +1106,9 @@ size_t tnns_fused_sync_bytes(int N) { return ((size_t)(Q_FLAG0 + N) * sizeof(uns
 bool tnns_fused_supported(const tnns_cuda_weights* w, const TnnsGeom& g, const float* d_x, int layout) {
     if (!tnns_im2col_supported(w, g)) return false;
     const long long HW = (long long)g.H * g.W;
-    // the quantiser warps receive 128 pixels x 64 channels per tensor copy: rows of H*W floats, 16-byte pitch and base
-    if (!tnns_quantise_tma_supported(d_x, g.H, g.W, layout)) return false;
+    // the quantiser warps receive 128 pixels x 64 channels per item: NCHW as one tensor copy (rows of H*W floats, 16-byte pitch
+    // and base), NHWC as two swizzled boxes of 32 channels (rows of C floats, 16-byte pitch and base)
+    if (layout == TNNS_NHWC ? !tnns_quantise_tma_nhwc_supported(d_x, g.N, g.C, g.H, g.W) : !tnns_quantise_tma_supported(d_x, g.H, g.W, layout)) return false;
     const long long items = (long long)g.N * ((HW + Q_PIX - 1) / Q_PIX) * g.Cp;
     return items < 0x7FFFFFFFLL;
 }
@@ -1149,7 +1152,7 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     if (fused) {
         if (!fused->d_x || !fused->d_thr || !fused->d_sync) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
         if (!tnns_fused_supported(w, g, fused->d_x, layout))
-            return tnns_fail(TNNS_ERR_UNSUPPORTED, "fused quantisation needs NCHW input with H*W a multiple of four and a 16-byte aligned base");
+            return tnns_fail(TNNS_ERR_UNSUPPORTED, "fused quantisation needs a 16-byte aligned input: NCHW with H*W a multiple of four, or NHWC with C a multiple of four");
         if (reinterpret_cast<uintptr_t>(fused->d_sync) & 127) return tnns_fail(TNNS_ERR_INVALID, "synchronisation words must be 128-byte aligned");
         int rc0 = tnns_fused_sync_prepare(ctx, g.N, stream, fused->d_sync, &fused_words, &fused_self_clean);
         if (rc0) return rc0;
@@ -1184,7 +1187,13 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     if (fused) {
         // the fp32 input as a 2-D tensor: one row of H*W floats per (image, channel); box = 128 pixels x 64 channels
         const unsigned long long HW = (unsigned long long)g.H * g.W;
-        if ((rc = tnns_tensor_map_2d(&map_q, 4, fused->d_x, HW, (unsigned long long)g.N * g.C, HW * 4, Q_PIX, 64))) return rc;
+        // (pixel-major input: one row of C floats per pixel of any image; box = 128 pixels x 32 channels, 128-byte swizzle)
+        if (layout == TNNS_NHWC)
+            rc = tnns_tensor_map_2d(&map_q, 4, fused->d_x, (unsigned long long)g.C, (unsigned long long)g.N * HW, (unsigned long long)g.C * 4, 32, Q_PIX, 128);
+        else
+            rc = tnns_tensor_map_2d(&map_q, 4, fused->d_x, HW, (unsigned long long)g.N * g.C, HW * 4, Q_PIX, 64);
+        if (rc) return rc;
+        a.q_nhwc = layout == TNNS_NHWC;
         a.qx = fused->d_x;
         a.qthr = fused->d_thr;
         a.qimg = reinterpret_cast<uint4*>(const_cast<void*>(d_image));

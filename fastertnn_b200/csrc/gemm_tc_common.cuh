@@ -270,12 +270,13 @@ struct QuantArgs {
     // item per image, after its pixel items, that writes the border pixels (the padding value).
     int W, Wp, HpWp, off0, border;
     int binary;  // activations in {-1,+1} (x < t), absent channels and the border +1; else ternary, both 0
+    int nhwc;    // the fp32 input is pixel-major: an item arrives as two 128-byte-swizzled boxes of 128 pixels x 32 channels
 };
 __device__ __forceinline__ QuantArgs plain_quant_args(const float* qthr, uint4* qimg, unsigned int* q_sync, int qN, int qC, int q_nbands, int Cp,
-                                                      int H, int W, unsigned int* status) {
+                                                      int H, int W, unsigned int* status, int nhwc = 0) {
     QuantArgs a;
     a.qthr = qthr; a.qimg = qimg; a.q_sync = q_sync; a.qN = qN; a.qC = qC; a.q_nbands = q_nbands; a.Cp = Cp; a.HW = H * W; a.status = status;
-    a.W = W; a.Wp = W; a.HpWp = H * W; a.off0 = 0; a.border = 0; a.binary = 0;
+    a.W = W; a.Wp = W; a.HpWp = H * W; a.off0 = 0; a.border = 0; a.binary = 0; a.nhwc = nhwc;
     return a;
 }
 // Control words of the quantiser warps and the publisher, behind the quantiser ring's barriers.
@@ -302,8 +303,15 @@ __device__ __noinline__ void quantise_items(const QuantArgs p, const CUtensorMap
         const unsigned int n = i / per_img, r = i - n * per_img;
         if (i < items && r < pix_items) {
             const int ic = (int)(r % (unsigned int)p.Cp), band = (int)(r / (unsigned int)p.Cp);
-            mbar_arrive_expect_tx(bar_full + 8 * s, Q_STAGE);  // the whole box, edges zero-filled
-            tma_tile2d_g2s(smem_u32(stage0 + s * Q_STAGE), tmap_q, band * Q_PIX, (int)n * p.qC + ic * 64, bar_full + 8 * s);
+            mbar_arrive_expect_tx(bar_full + 8 * s, Q_STAGE);  // the whole box(es), edges zero-filled
+            if (p.nhwc) {
+                // rows of the (pixels of all images) x (channels) tensor; a band's last rows may belong to the next image and are not stored
+                const int row0 = (int)n * p.HW + band * Q_PIX;
+                tma_tile2d_g2s(smem_u32(stage0 + s * Q_STAGE), tmap_q, ic * 64, row0, bar_full + 8 * s);
+                tma_tile2d_g2s(smem_u32(stage0 + s * Q_STAGE + Q_STAGE / 2), tmap_q, ic * 64 + 32, row0, bar_full + 8 * s);
+            } else {
+                tma_tile2d_g2s(smem_u32(stage0 + s * Q_STAGE), tmap_q, band * Q_PIX, (int)n * p.qC + ic * 64, bar_full + 8 * s);
+            }
         } else {
             mbar_arrive(bar_full + 8 * s);
         }
@@ -343,7 +351,17 @@ __device__ __noinline__ void quantise_items(const QuantArgs p, const CUtensorMap
         const float* sp = reinterpret_cast<const float*>(stage0 + s * Q_STAGE) + qtid;
         uint32_t sg[2] = {0, 0}, nz[2] = {0, 0};
         // channel b of a half ends at bit b: visit 31 .. 0 and shift left (four independent chains)
-        if (nch == 64 && !p.binary) {
+        if (p.nhwc) {
+            const unsigned char* row = stage0 + s * Q_STAGE + qtid * 128;
+            if (p.binary) {
+                tnns_quantise_row32_swz128<false>(row, nch, t, sg[0], nz[0]);
+                tnns_quantise_row32_swz128<false>(row + Q_STAGE / 2, nch - 32, t, sg[1], nz[1]);
+                nz[0] = nz[1] = 0xFFFFFFFFu;  // no zeros in the binary alphabet
+            } else {
+                tnns_quantise_row32_swz128<true>(row, nch, t, sg[0], nz[0]);
+                tnns_quantise_row32_swz128<true>(row + Q_STAGE / 2, nch - 32, t, sg[1], nz[1]);
+            }
+        } else if (nch == 64 && !p.binary) {
 #pragma unroll
             for (int b = 31; b >= 0; b--) {
 #pragma unroll

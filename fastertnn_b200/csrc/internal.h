@@ -169,6 +169,40 @@ FastDiv tnns_fastdiv(uint32_t d);
 // bits (bits 1, 0); masking x with 0xA gives the nibbles of the elements 4i+3, masking x<<1 those
 // of the elements 4i+2; y does the same for 4i+1 and 4i.  Ten integer operations per 32 elements.
 // Activations and weights go through this same routine, so the permutation cancels in the dot product.
+// 32 channels of one pixel from a pixel-major (NHWC) tile that the copy engine wrote in the 128-byte swizzle
+// pattern: `row` = the pixel's 128 bytes in shared memory; of its eight 16-byte chunks, chunk c sits where
+// address bits 4..6 equal c XOR address bits 7..9 (the pattern is a function of the shared-memory address).
+// Channel b ends at bit b (visit 31 .. 0 and shift left); the predicates are read off sign bits (v < -t <=>
+// signbit(v + t); |v| > t <=> signbit(t - |v|); binary v < t <=> signbit(v - t)); channels at or past nch read
+// as absent (sign 0, non-zero 0).  Lanes of a warp = neighbouring pixels: each load instruction spreads over
+// all banks, where a plain [pixel][channel] tile would put every lane on the same one.
+template <bool TERNARY>
+__device__ __forceinline__ void tnns_quantise_row32_swz128(const unsigned char* row, int nch, float t, uint32_t& sg_out, uint32_t& nz_out) {
+    const uint32_t x = (static_cast<uint32_t>(__cvta_generic_to_shared(row)) >> 7) & 7u;
+    uint32_t sg = 0, nz = 0;
+#pragma unroll
+    for (int c = 7; c >= 0; c--) {
+        const float4 v4 = *reinterpret_cast<const float4*>(row + ((static_cast<uint32_t>(c) ^ x) << 4));
+#pragma unroll
+        for (int e = 3; e >= 0; e--) {
+            const float v = e == 3 ? v4.w : e == 2 ? v4.z : e == 1 ? v4.y : v4.x;
+            if (4 * c + e < nch) {
+                if (TERNARY) {
+                    sg = __funnelshift_l(__float_as_uint(v + t), sg, 1);
+                    nz = __funnelshift_l(__float_as_uint(t - fabsf(v)), nz, 1);
+                } else {
+                    sg = __funnelshift_l(__float_as_uint((v + 0.0f) - t), sg, 1);
+                }
+            } else {
+                sg <<= 1;
+                nz <<= 1;
+            }
+        }
+    }
+    sg_out = sg;
+    nz_out = nz;
+}
+
 __device__ __forceinline__ void tnns_expand32_f4(uint32_t s, uint32_t z, uint32_t (&w)[4]) {
     const uint32_t x = (s & 0xCCCCCCCCu) | (~(z >> 2) & 0x33333333u);
     const uint32_t y = ((s << 2) & 0xCCCCCCCCu) | (~z & 0x33333333u);

@@ -41,35 +41,6 @@ constexpr size_t QSMEM = 1024 + (size_t)QSTG * QSTAGE_BYTES + 128;
 
 __device__ __forceinline__ uint32_t push_sign_bit(uint32_t acc, float d) { return __funnelshift_l(__float_as_uint(d), acc, 1); }
 
-// One pixel's row of a 128-byte-swizzled half-tile: 32 channels = eight 16-byte chunks, chunk c stored at
-// c ^ (p & 7).  Channel b ends at bit b (visit 31 .. 0 and shift left); channels at or past nch read as
-// absent (sign 0, non-zero 0).
-template <bool TERNARY>
-__device__ __forceinline__ void quantise_row32(const unsigned char* row, int p, int nch, float t, uint32_t& sg_out, uint32_t& nz_out) {
-    uint32_t sg = 0, nz = 0;
-#pragma unroll
-    for (int c = 7; c >= 0; c--) {
-        const float4 v4 = *reinterpret_cast<const float4*>(row + ((c ^ (p & 7)) << 4));
-#pragma unroll
-        for (int e = 3; e >= 0; e--) {
-            const float v = e == 3 ? v4.w : e == 2 ? v4.z : e == 1 ? v4.y : v4.x;
-            if (4 * c + e < nch) {
-                if (TERNARY) {
-                    sg = push_sign_bit(sg, v + t);
-                    nz = push_sign_bit(nz, t - fabsf(v));
-                } else {
-                    sg = push_sign_bit(sg, (v + 0.0f) - t);
-                }
-            } else {
-                sg <<= 1;
-                nz <<= 1;
-            }
-        }
-    }
-    sg_out = sg;
-    nz_out = nz;
-}
-
 template <bool TERNARY, int IMG, bool NHWC_IN>
 __global__ void __launch_bounds__(QTHREADS, 1)
 quantise_tma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __restrict__ thr, void* __restrict__ out, int N, int C, int HW,
@@ -177,8 +148,8 @@ quantise_tma_kernel(const __grid_constant__ CUtensorMap tmap, const float* __res
             // off sign bits (v < -t <=> signbit(v + t); |v| > t <=> signbit(t - |v|); v < t <=> signbit(v - t))
             if (NHWC_IN) {
                 const unsigned char* row = smem + s * QSTAGE_BYTES + p * 128;
-                quantise_row32<TERNARY>(row, p, nch, t, sg[0], nz[0]);
-                quantise_row32<TERNARY>(row + QSTAGE_BYTES / 2, p, nch - 32, t, sg[1], nz[1]);
+                tnns_quantise_row32_swz128<TERNARY>(row, nch, t, sg[0], nz[0]);
+                tnns_quantise_row32_swz128<TERNARY>(row + QSTAGE_BYTES / 2, nch - 32, t, sg[1], nz[1]);
             } else if (nch == QC) {
 #pragma unroll
                 for (int half = 0; half < 2; half++) {

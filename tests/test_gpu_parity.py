@@ -613,7 +613,6 @@ def test_fused_quantise_and_tensor_copy_gemm(type_, layer, N, gpu_ctx, checker):
     d_ws = ctx.malloc(nb_ws)
     try:
         assert ctx.conv_fused_supported(w, shape, d_x, ft.NCHW)
-        assert not ctx.conv_fused_supported(w, shape, d_x, ft.NHWC)
         assert not ctx.conv_fused_supported(w, shape, d_x + 4, ft.NCHW)
         ctx.quantise_e2m1(d_x, d_t, d_e, N, layer.C, layer.H, layer.W, ft.NCHW)
         ctx.sync()
@@ -635,6 +634,24 @@ def test_fused_quantise_and_tensor_copy_gemm(type_, layer, N, gpu_ctx, checker):
         ctx.conv(w, d_x, d_t, d_y, shape, case.alpha, ft.NCHW, ft.PACK_AUTO, ft.GEMM_F4_FUSED)
         ctx.sync()
         assert ctx.to_host(d_y, want.shape, np.float32).tobytes() == want.tobytes()
+        # pixel-major input and output: the quantiser warps read 128-byte-swizzled boxes of 128 pixels x 32 channels
+        # (channel counts that are multiples of four, at least 128 pixels in the batch), twice over stale workspace bytes
+        d_xh = ctx.to_device(to_nhwc(case.x))
+        nhwc_ok = layer.C % 4 == 0 and N * layer.H * layer.W >= 128
+        assert ctx.conv_fused_supported(w, shape, d_xh, ft.NHWC) == nhwc_ok
+        if nhwc_ok:
+            for rep in range(2):
+                ctx.fill(d_y, np.full(want.size, np.nan, np.float32))
+                ctx.fill(d_ws, np.full(nb_ws // 4, 0xFFFFFFFF, np.uint32))
+                ctx.conv_ws(w, d_xh, d_t, d_y, d_ws, nb_ws, shape, case.alpha, ft.NHWC, ft.PACK_AUTO, ft.GEMM_F4_FUSED)
+                ctx.sync()
+                got = ctx.to_host(d_y, (N, layer.OH, layer.OW, layer.KN), np.float32)
+                assert to_nchw(got).tobytes() == want.tobytes(), ("NHWC one launch", rep)
+                assert np.array_equal(ctx.to_host(d_ws, (nb_e // 4,), np.uint32), image)
+        else:
+            with pytest.raises(ft.TnnsError):
+                ctx.conv_ws(w, d_xh, d_t, d_y, d_ws, nb_ws, shape, case.alpha, ft.NHWC, ft.PACK_AUTO, ft.GEMM_F4_FUSED)
+        ctx.free(d_xh)
     finally:
         for p in (d_t, d_x, d_y, d_e, d_ws):
             ctx.free(p)
@@ -737,9 +754,8 @@ def test_fused_launches_on_two_streams(gpu_ctx, checker):
 
 @pytest.mark.gpu
 def test_fused_route_declines_what_it_cannot_do(gpu_ctx, checker):
-    """Pixel counts that are not a multiple of four (the rows of the input tensor must be 16-byte
-    multiples for the copy engine) and NHWC input stay on the two-kernel route; asking for the fused
-    one is an error."""
+    """Pixel counts that are not a multiple of four (the rows of an NCHW input tensor must be 16-byte
+    multiples for the copy engine) stay on the two-kernel route; asking for the fused one is an error."""
     ctx = gpu_ctx
     layer = Layer(256, 7, 7, 64, 3, 3, 1, 1)
     case = make_case(TNN, layer, 3, 91, "uniform")
