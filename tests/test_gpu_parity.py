@@ -818,3 +818,54 @@ def test_prelu_slopes_other_than_one_half(alpha, gpu_ctx, checker):
             got = device_conv(ctx, case, wp, ft.NCHW, ft.PACK_AUTO, galgo)
             bad = np.flatnonzero(got.view(np.uint32).ravel() != want.view(np.uint32).ravel())
             assert bad.size == 0, (type_, alpha, galgo, bad.size, got.ravel()[bad[:3]], want.ravel()[bad[:3]])
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("type_", [TNN, BNN])
+@pytest.mark.parametrize("alpha", [0.5, 0.3, 1.0, 0.07, -0.25, 1.5])
+def test_quantising_epilogue_for_any_slope(type_, alpha, gpu_ctx, checker):
+    """The chaining epilogues decide the next layer's activations from the raw accumulator by thresholds when
+    0 < alpha <= 1 and by evaluating the PReLU otherwise.  Either way the bits must be those the quantise
+    kernels make of the layer's fp32 output: thresholds of 0, small, integer-valued, large and negative, all
+    three output formats, on the im2col-fed and the slab-fed GEMM (BNN: accumulator offset; its binary input
+    takes the slab-fed GEMM only)."""
+    ctx = gpu_ctx
+    layer, N = Layer(256, 10, 10, 256, 3, 3, 1, 1), 7
+    tern_in = act_ternary(type_)
+    case = make_case(type_, layer, N, 9800 + type_, "uniform")
+    wp = checker.pack_weights(wgt_ternary(type_), case.w, case.w_thr)
+    want = checker.conv(type_, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, alpha)
+    w = ctx.upload_weights(type_, wp, layer.C, layer.KH, layer.KW)
+    shape = layer.shape(N)
+    thr_next = np.array([0.0, 0.4, 3.0, 17.5, 250.0, -0.2, 1.0], np.float32)
+    nb_b = ft.api.bordered_image_bytes(N, layer.C, layer.H, layer.W, 1, 1)
+    nb_e = ft.api.e2m1_image_bytes(N, layer.C, layer.H, layer.W)
+    nb_o = max(ft.api.e2m1_image_bytes(N, layer.KN, layer.OH, layer.OW), ft.api.packed_image_bytes(True, N, layer.KN, layer.OH, layer.OW))
+    d_x, d_t, d_tn = ctx.to_device(case.x), ctx.to_device(case.thr), ctx.to_device(thr_next)
+    d_f = ctx.to_device(want)
+    d_b, d_e, d_o, d_q = ctx.malloc(nb_b), ctx.malloc(nb_e), ctx.malloc(nb_o), ctx.malloc(nb_o)
+    try:
+        ctx.quantise_e2m1_bordered(tern_in, d_x, d_t, d_b, N, layer.C, layer.H, layer.W, 1, 1)
+        if tern_in:
+            ctx.quantise_e2m1(d_x, d_t, d_e, N, layer.C, layer.H, layer.W)
+        for fmt in (2, 1, 0):
+            # what the quantise kernels make of the checker's fp32 output
+            ctx.fill(d_q, np.zeros(nb_o // 4, np.uint32))
+            if fmt == 2:
+                ctx.quantise_e2m1(d_f, d_tn, d_q, N, layer.KN, layer.OH, layer.OW)
+            else:
+                ctx.quantise(fmt == 1, d_f, d_tn, d_q, N, layer.KN, layer.OH, layer.OW)
+            ctx.sync()
+            expect = ctx.to_host(d_q, (nb_o // 4,), np.uint32)
+            producers = [("slab", lambda: ctx.gemm_slab_packed_out(w, d_b, d_o, d_tn, fmt, (0, 0), shape, alpha))]
+            if tern_in:
+                producers.append(("im2col", lambda: ctx.gemm_im2col_packed_out(w, d_e, d_o, d_tn, fmt, shape, alpha)))
+            for name, run in producers:
+                ctx.fill(d_o, np.zeros(nb_o // 4, np.uint32))
+                run()
+                ctx.sync()
+                assert np.array_equal(ctx.to_host(d_o, (nb_o // 4,), np.uint32), expect), (name, fmt, alpha)
+    finally:
+        for p in (d_x, d_t, d_tn, d_f, d_b, d_e, d_o, d_q):
+            ctx.free(p)
+        w.free()
