@@ -49,6 +49,16 @@ def test_large_layer_full_batch_on_the_default_route(type_, gpu_ctx, checker):
         ctx.conv(w, d_x + 24 * layer.C * layer.H * layer.W * 4, d_t, d_y, layer.shape(8), 0.5)
         ctx.sync()
         assert ctx.to_host(d_y, (8,) + want.shape[1:], np.float32).tobytes() == want[24:32].tobytes()
+        # the same layer pixel-major (NHWC in and out): also the one-launch kernel, its quantiser warps reading
+        # swizzled boxes of pixels x channels and its epilogue writing whole sectors of pixel rows
+        ctx.free(d_x)
+        d_x = ctx.to_device(np.ascontiguousarray(x.transpose(0, 2, 3, 1)))
+        assert ctx.conv_fused_preferred(w, layer.shape(N), d_x, ft.NHWC)
+        ctx.fill(d_y, np.full(1 << 20, np.nan, np.float32))
+        ctx.conv(w, d_x, d_t, d_y, layer.shape(N), 0.5, ft.NHWC)
+        ctx.sync()
+        got = ctx.to_host(d_y, (N, layer.OH, layer.OW, layer.KN), np.float32)
+        assert np.ascontiguousarray(got.transpose(0, 3, 1, 2)).tobytes() == want.tobytes(), "NHWC"
     finally:
         for p in (d_x, d_t, d_y):
             ctx.free(p)
