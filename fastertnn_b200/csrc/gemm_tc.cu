@@ -1181,7 +1181,7 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     a.cp_next = (w->KN + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS;
     a.img = nullptr;
     a.jtab = w->d_jtab;
-    a.qx = a.qthr = nullptr; a.qimg = nullptr; a.q_sync = nullptr; a.qN = a.qC = a.q_nbands = a.q_self_clean = 0;
+    a.qx = a.qthr = nullptr; a.qimg = nullptr; a.q_sync = nullptr; a.qN = a.qC = a.q_nbands = a.q_self_clean = a.q_nhwc = 0;
     a.H = g.H; a.W = g.W; a.OW = g.OW; a.Cp = g.Cp; a.SH = g.SH; a.SW = g.SW; a.PH = g.PH; a.PW = g.PW;
     alignas(64) CUtensorMap map_q;
     if (fused) {
