@@ -388,6 +388,8 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
         const bool by_thr = BN == 256 && p.pimg != nullptr && alpha_in_unit;
         tnns_thr::Pair qt = {0.f, 0.f};
         int qt_img = -1;
+        // pixel-major fp32 output: the accumulator is fetched in the 16x256b shape (four lanes = 32 contiguous bytes of a row)
+        const bool rows16 = p.pimg == nullptr && p.layout == TNNS_NHWC && (p.KN & 1) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 7) == 0;
         for (int t = unit; t < ntiles; t += nunits, lt++) {
             const int buf = lt & 1;
             const int n0 = (t % ntn) * BN;
@@ -406,6 +408,20 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
                 qt = tnns_thr::make(tq, p.alpha, bias_f, next_tern);
                 qt_img = n_img;
             }
+            // rows16: the four rows of the quadrant this thread stores (8*h + lane/4), each mapped to its output pixel
+            float* yrow0[4] = {nullptr, nullptr, nullptr, nullptr};
+            if (rows16) {
+#pragma unroll
+                for (int h = 0; h < 4; h++) {
+                    const int r = (t / ntn) * TILE_M + (int)rank * BM + q * 32 + 8 * h + (lane >> 2);
+                    if (r < p.Mv) {
+                        const int ni = (int)p.div_hpwp.div((uint32_t)r);
+                        const int rm = r - ni * p.HpWp;
+                        const int y2 = (int)p.div_wp.div((uint32_t)rm), x2 = rm - y2 * p.Wp;
+                        if (y2 < p.OH && x2 < p.OW) yrow0[h] = p.y + ((size_t)ni * OHW + (size_t)(y2 * p.OW + x2)) * p.KN;
+                    }
+                }
+            }
             if (!mbar_wait(bar_tfull + 8 * buf, (lt >> 1) & 1, abort_flag, p.status, 5)) goto done;
             tc_fence_after();
             int start = 0;
@@ -415,6 +431,26 @@ gemm_slab_kernel(SlabArgs p, const __grid_constant__ CUtensorMap tmap_a, const _
                 const int cb = ecol * ECOLS + ((i + start) % NSL) * 32;
                 uint32_t v[32];
                 const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * ACC_OFF + cb);
+                if (rows16) {
+                    tmem_ld_16x256b_x4(taddr, v);
+                    tmem_ld_16x256b_x4(taddr + (16u << 16), v + 16);
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    if (OVL ? (i == 0) : (i == NSL - 1)) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) {
+                            if (CG == 2 && rank != 0) mbar_arrive_cluster(bar_release + (OVL ? 0 : 8 * buf));
+                            else mbar_arrive(OVL ? bar_tempty : bar_tempty + 8 * buf);
+                        }
+                    }
+                    float f[32];
+                    prelu32_f4(v, f, alpha_in_unit, p.acc_bias, bias_f, p.alpha, p.zero_passes);
+                    const int c0 = n0 + cb;
+                    float* const yrow[4] = {yrow0[0] ? yrow0[0] + c0 : nullptr, yrow0[1] ? yrow0[1] + c0 : nullptr,
+                                            yrow0[2] ? yrow0[2] + c0 : nullptr, yrow0[3] ? yrow0[3] + c0 : nullptr};
+                    store_rows16_at(f, yrow, p.KN - c0, lane);
+                    continue;
+                }
                 asm volatile(
                     "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
                     "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "

@@ -248,6 +248,22 @@ __device__ __forceinline__ void store_rows16(const float (&f)[32], float* y_quad
     }
 }
 
+// The same for rows that are not neighbours in memory (the slab-fed GEMM's rows are positions of the padded lattice):
+// yrow[h] = where row 8*h + lane/4 of the quadrant starts at the slice's first column, or nullptr if that row is not stored.
+__device__ __forceinline__ void store_rows16_at(const float (&f)[32], float* const (&yrow)[4], int cols_left, int lane) {
+    const int cc = 2 * (lane & 3);
+#pragma unroll
+    for (int h = 0; h < 4; h++) {
+        if (yrow[h]) {
+            float* yr = yrow[h] + cc;
+#pragma unroll
+            for (int k = 0; k < 4; k++)
+                if (8 * k + cc < cols_left)
+                    __stcs(reinterpret_cast<float2*>(yr + 8 * k), make_float2(f[16 * (h >> 1) + 4 * k + 2 * (h & 1)], f[16 * (h >> 1) + 4 * k + 2 * (h & 1) + 1]));
+        }
+    }
+}
+
 // Quantiser role of the fused form, called by the four quantiser warps together (thread = pixel).
 // An item = 128 neighbouring pixels x 64 channels of one image (NCHW, a row of the 2-D tensor
 // (image, channel) x pixels per channel).  The first lane claims items in image order from a
