@@ -9,7 +9,7 @@ raw device pointers (torch tensors supply memory and streams).
 from .api import (  # noqa: F401
     TNN, TBN, BTN, BNN, NCHW, NHWC,
     PACK_AUTO, PACK_GATHER, PACK_STAGED,
-    GEMM_AUTO, GEMM_POPC_SIMPLE, GEMM_POPC_TILED, GEMM_I8_TC, GEMM_F4_TC, GEMM_F4_FUSED, GEMM_F4_SLAB, GEMM_F4_SLAB_FUSED,
+    GEMM_AUTO, GEMM_POPC_SIMPLE, GEMM_POPC_TILED, GEMM_I8_TC, GEMM_F4_TC, GEMM_F4_FUSED, GEMM_F4_SLAB, GEMM_F4_SLAB_FUSED, GEMM_F4_DENSE,
     Shape, Testcase, GemmTestcase, TnnsError, Context, Weights, MultiContext, MultiWeights, shard_range, shard_run,
     tnns_conv, tnns_gemm, mm_tnn, mm_tbn, mm_btn, mm_bnn, t2r_p2_opt, b2r,
     pack_weights_ternary, pack_weights_binary, out_dim, k_words, k_padded, packed_bytes,

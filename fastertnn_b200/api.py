@@ -17,7 +17,7 @@ from ._lib import GemmTestcase, Shape, Testcase, load_library
 TNN, TBN, BTN, BNN = 0, 1, 2, 3
 NCHW, NHWC = 0, 1
 PACK_AUTO, PACK_GATHER, PACK_STAGED = 0, 1, 2
-GEMM_AUTO, GEMM_POPC_SIMPLE, GEMM_POPC_TILED, GEMM_I8_TC, GEMM_F4_TC, GEMM_F4_FUSED, GEMM_F4_SLAB, GEMM_F4_SLAB_FUSED = 0, 1, 2, 3, 4, 5, 6, 7
+GEMM_AUTO, GEMM_POPC_SIMPLE, GEMM_POPC_TILED, GEMM_I8_TC, GEMM_F4_TC, GEMM_F4_FUSED, GEMM_F4_SLAB, GEMM_F4_SLAB_FUSED, GEMM_F4_DENSE = 0, 1, 2, 3, 4, 5, 6, 7, 8
 
 
 class TnnsError(RuntimeError):
@@ -374,6 +374,19 @@ class Context:
         _check(self.lib.tnns_cuda_conv_slab_packed_out(self.handle, w.handle, d_x, d_thr, d_image_out, d_thr_next, next_format, next_pad[0],
                                                        next_pad[1], d_ws, ws_bytes, C.byref(shape), alpha, pairs, stream))
 
+    # -- layers with few input channels as a dense 1x1 layer over the real positions of every window
+    def dense_supported(self, w: Weights, shape: Shape) -> bool:
+        return bool(self.lib.tnns_cuda_dense_supported(self.handle, w.handle, C.byref(shape)))
+
+    def conv_dense(self, w: Weights, d_x: int, d_thr: int, d_y: int, d_ws: int, ws_bytes: int, shape: Shape, alpha: float, layout=NCHW, stream=0):
+        """Whole layer with at most 16 input channels: quantise straight into the virtual layer's 4-bit image, then the GEMM."""
+        _check(self.lib.tnns_cuda_conv_dense(self.handle, w.handle, d_x, d_thr, d_y, d_ws, ws_bytes, C.byref(shape), alpha, layout, stream))
+
+    def conv_dense_packed_out(self, w: Weights, d_x: int, d_thr: int, d_image_out: int, d_thr_next: int, next_format: int, d_ws: int,
+                              ws_bytes: int, shape: Shape, alpha: float, layout=NCHW, stream=0):
+        _check(self.lib.tnns_cuda_conv_dense_packed_out(self.handle, w.handle, d_x, d_thr, d_image_out, d_thr_next, next_format, d_ws, ws_bytes,
+                                                        C.byref(shape), alpha, layout, stream))
+
     def im2col_supported(self, w: Weights, shape: Shape) -> bool:
         return bool(self.lib.tnns_cuda_im2col_supported(w.handle, C.byref(shape)))
 
@@ -532,6 +545,10 @@ def packed_image_bytes(ternary: bool, N: int, C_: int, H: int, W: int) -> int:
 
 def fused_workspace_bytes(N: int, C_: int, H: int, W: int) -> int:
     return int(load_library().tnns_fused_workspace_bytes(N, C_, H, W))
+
+
+def dense_workspace_bytes(shape: Shape) -> int:
+    return load_library().tnns_dense_workspace_bytes(C.byref(shape))
 
 
 def bordered_image_bytes(N: int, C_: int, H: int, W: int, PH: int, PW: int) -> int:

@@ -273,6 +273,23 @@ static int upload_weights_impl(tnns_cuda_ctx* ctx, int type, const int64_t* pack
         tnns_cuda_free_weights(ctx, w);
         return rc;
     }
+    if (C > 0 && tnns_dense_eligible(type, C, KH, KW)) {
+        // few input channels: also keep the kernel as a 1x1 layer over only the real positions of a window.  The
+        // repacked rows are in the reference's packed format, so the same upload builds that layer's operand images.
+        const int Kd = tnns_dense_channels(C, KH, KW), Kw_d = Kd / TNNS_WORD_BITS, Kp_d = 4 * ((Kw_d + 3) / 4);
+        uint64_t* d_tmp = nullptr;
+        e = cudaMalloc(&d_tmp, (size_t)KN * Kp_d * 8 * (type_wgt_ternary(type) ? 2 : 1));
+        if (e == cudaSuccess) {
+            rc = tnns_launch_repack_weights_dense(ctx, w, d_tmp, Kp_d);
+            if (rc == TNNS_OK && (e = cudaDeviceSynchronize()) == cudaSuccess)
+                rc = upload_weights_impl(ctx, type, reinterpret_cast<const int64_t*>(d_tmp), KN, Kd, 1, 1, Kw_d, K_unpack, &w->dense);
+            cudaFree(d_tmp);
+        }
+        if (e != cudaSuccess || rc != TNNS_OK) {
+            tnns_cuda_free_weights(ctx, w);
+            return rc != TNNS_OK ? rc : tnns_fail(e == cudaErrorMemoryAllocation ? TNNS_ERR_NOMEM : TNNS_ERR_CUDA, "dense weight form failed: %s", cudaGetErrorString(e));
+        }
+    }
     *out = w;
     return TNNS_OK;
 }
@@ -295,6 +312,7 @@ void tnns_cuda_free_weights(tnns_cuda_ctx* ctx, tnns_cuda_weights* w) {
     if (w->d_i8) cudaFree(w->d_i8);
     if (w->d_f4) cudaFree(w->d_f4);
     if (w->d_jtab) cudaFree(w->d_jtab);
+    if (w->dense) tnns_cuda_free_weights(nullptr, w->dense);
     delete w;
 }
 
@@ -575,9 +593,69 @@ int tnns_cuda_conv_slab_one_launch_preferred(const tnns_cuda_ctx* ctx, const tnn
     return 0;
 }
 
+// --- layers with few input channels as a dense 1x1 layer (dense.cu) -------------------------------
+// geometry of the virtual layer: N x OH x OW pixels of Kd channels, 1x1 filter, stride 1, no padding
+static bool dense_geom(const tnns_cuda_weights* w, const TnnsGeom& g, TnnsGeom* gv) {
+    if (!w->dense || g.C != w->C || g.KH != w->KH || g.KW != w->KW || g.KN != w->KN) return false;
+    const int Kd = w->dense->C;
+    *gv = g;
+    gv->C = Kd; gv->H = g.OH; gv->W = g.OW; gv->KH = gv->KW = 1; gv->PH = gv->PW = 0; gv->SH = gv->SW = 1;
+    gv->Cp = Kd / TNNS_WORD_BITS; gv->Kw = gv->Cp; gv->Kp = 4 * ((gv->Cp + 3) / 4);
+    return tnns_im2col_supported(w->dense, *gv);
+}
+
+size_t tnns_dense_workspace_bytes(const tnns_shape_t* s) {
+    TnnsGeom g;
+    if (!s || tnns_make_geom(s, &g)) return 0;
+    return (((size_t)g.N * g.OH * g.OW * (size_t)(tnns_dense_channels(g.C, g.KH, g.KW) / 2)) + 127) & ~(size_t)127;
+}
+
+int tnns_cuda_dense_supported(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s) {
+    TnnsGeom g, gv;
+    if (!ctx || !w || !s || tnns_make_geom(s, &g)) return 0;
+    return dense_geom(w, g, &gv) ? 1 : 0;
+}
+
+static int conv_dense_impl(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y, void* d_image_out,
+                           const float* d_thr_next, int next_format, void* d_workspace, size_t workspace_bytes, const tnns_shape_t* s,
+                           float alpha, int layout, void* stream) {
+    if (!ctx || !w || !d_x || !d_thr || !d_workspace) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    if (layout != TNNS_NCHW && layout != TNNS_NHWC) return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
+    TnnsGeom g, gv;
+    int rc = tnns_make_geom(s, &g);
+    if (rc) return rc;
+    if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW)
+        return tnns_fail(TNNS_ERR_INVALID, "shape does not match the uploaded weights");
+    if (!dense_geom(w, g, &gv)) return tnns_fail(TNNS_ERR_UNSUPPORTED, "layer outside the dense few-channel route (ternary activations, at most 16 channels)");
+    if (reinterpret_cast<uintptr_t>(d_workspace) & 127) return tnns_fail(TNNS_ERR_INVALID, "workspace must be 128-byte aligned");
+    const size_t need = tnns_dense_workspace_bytes(s);
+    if (workspace_bytes < need) return tnns_fail(TNNS_ERR_INVALID, "workspace of %zu bytes, need %zu", workspace_bytes, need);
+    TNNS_ENTER(ctx, w);
+    if (g.N == 0) return TNNS_OK;
+    rc = tnns_launch_dense_quantise(ctx, d_x, d_thr, d_workspace, g, gv.C, layout, (cudaStream_t)stream);
+    if (rc) return rc;
+    return tnns_launch_gemm_im2col(ctx, w->dense, d_workspace, d_y, gv, alpha, layout, (cudaStream_t)stream, 0, d_image_out, d_thr_next, next_format);
+}
+
+int tnns_cuda_conv_dense(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y, void* d_workspace,
+                         size_t workspace_bytes, const tnns_shape_t* s, float alpha, int layout, void* stream) {
+    if (!d_y) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    return conv_dense_impl(ctx, w, d_x, d_thr, d_y, nullptr, nullptr, 1, d_workspace, workspace_bytes, s, alpha, layout, stream);
+}
+
+int tnns_cuda_conv_dense_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, void* d_image_out,
+                                    const float* d_thr_next, int next_format, void* d_workspace, size_t workspace_bytes,
+                                    const tnns_shape_t* s, float alpha, int layout, void* stream) {
+    if (!d_image_out || !d_thr_next) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    if (reinterpret_cast<uintptr_t>(d_image_out) & 15) return tnns_fail(TNNS_ERR_INVALID, "output image must be 16-byte aligned");
+    if (next_format < 0 || next_format > 2) return tnns_fail(TNNS_ERR_INVALID, "output format must be 0, 1 or 2");
+    return conv_dense_impl(ctx, w, d_x, d_thr, nullptr, d_image_out, d_thr_next, next_format, d_workspace, workspace_bytes, s, alpha, layout, stream);
+}
+
 // The algorithm tnns_cuda_conv / _conv_ws resolve TNNS_GEMM_AUTO (with TNNS_PACK_AUTO) to, workspace permitting.
 int tnns_cuda_conv_auto_algo(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s, const float* d_x, int layout) {
     if (!ctx || !w || !s) return TNNS_GEMM_AUTO;
+    if (tnns_cuda_dense_supported(ctx, w, s)) return TNNS_GEMM_F4_DENSE;
     if (layout == TNNS_NCHW && tnns_cuda_slab_preferred(ctx, w, s) && tnns_cuda_conv_slab_supported(ctx, w, s, d_x, layout))
         return tnns_cuda_conv_slab_one_launch_preferred(ctx, w, s, d_x, layout) ? TNNS_GEMM_F4_SLAB_FUSED : TNNS_GEMM_F4_SLAB;
     if (layout == TNNS_NHWC && tnns_cuda_slab_preferred(ctx, w, s) && tnns_quantise_tma_nhwc_supported(d_x, s->N, s->C, s->H, s->W))
@@ -715,11 +793,18 @@ int tnns_cuda_conv_ws(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const floa
     if (auto_both) {
         // the library's own choice; a slab-fed form is taken only when the caller's workspace holds its bordered image
         const int pick = tnns_cuda_conv_auto_algo(ctx, w, s, d_x, layout);
+        if (pick == TNNS_GEMM_F4_DENSE && (reinterpret_cast<uintptr_t>(d_workspace) & 127) == 0 && tnns_dense_workspace_bytes(s) <= workspace_bytes)
+            gemm_algo = pick;
         if (pick == TNNS_GEMM_F4_SLAB || pick == TNNS_GEMM_F4_SLAB_FUSED) {
             const size_t ws_need = pick == TNNS_GEMM_F4_SLAB_FUSED ? tnns_slab_workspace_bytes(g.N, g.C, g.H, g.W, g.PH, g.PW)
                                                                    : tnns_bordered_image_bytes(g.N, g.C, g.H, g.W, g.PH, g.PW);
             if ((reinterpret_cast<uintptr_t>(d_workspace) & 127) == 0 && ws_need <= workspace_bytes) gemm_algo = pick;
         }
+    }
+    if (gemm_algo == TNNS_GEMM_F4_DENSE) {
+        // few input channels: only the real positions of every window, as a 1x1 layer
+        if (pack_algo != TNNS_PACK_AUTO) return tnns_fail(TNNS_ERR_UNSUPPORTED, "the dense few-channel route has its own quantise step");
+        return conv_dense_impl(ctx, w, d_x, d_thr, d_y, nullptr, nullptr, 1, d_workspace, workspace_bytes, s, alpha, layout, stream);
     }
     if (gemm_algo == TNNS_GEMM_F4_SLAB || gemm_algo == TNNS_GEMM_F4_SLAB_FUSED) {
         // stride-1 layers from a bordered 4-bit image: one slab of pixels per tile serves every filter tap
@@ -794,6 +879,7 @@ int tnns_cuda_conv(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* 
     size_t need = std::max<size_t>(tnns_packed_bytes(w->type, s), 16);
     if (tnns_im2col_supported(w, g)) need = std::max(need, tnns_fused_workspace_bytes(g.N, g.C, g.H, g.W));
     if (tnns_slab_supported(ctx, w, g, false)) need = std::max(need, tnns_slab_workspace_bytes(g.N, g.C, g.H, g.W, g.PH, g.PW));
+    if (tnns_cuda_dense_supported(ctx, w, s)) need = std::max(need, tnns_dense_workspace_bytes(s));
     if (ctx->workspace_bytes < need) {
         // earlier launches may still read the old workspace
         TNNS_CUDA_TRY(cudaDeviceSynchronize());

@@ -55,6 +55,9 @@ struct tnns_cuda_weights {
     uint8_t* d_f4;        // e2m1 operand image for the 4-bit tensor-core GEMM (may be NULL)
     size_t f4_bytes;
     uint32_t* d_jtab;     // plane word j -> kh<<24 | kw<<16 | ic (implicit im2row), NULL without layer geometry
+    // layers with few input channels: the same kernel as a 1x1 layer over only the real positions of a window
+    // (dense.cu), NULL where that form does not apply
+    tnns_cuda_weights* dense;
 };
 
 // error plumbing (thread local)
@@ -106,6 +109,13 @@ bool tnns_quantise_tma_supported(const float* d_x, int H, int W, int layout);
 bool tnns_quantise_tma_nhwc_supported(const float* d_x, int N, int C, int H, int W);
 int tnns_launch_quantise_tma(tnns_cuda_ctx* ctx, bool ternary, const float* d_x, const float* d_thr, void* d_image, int N, int C, int H,
                              int W, cudaStream_t stream, int format, int PH = 0, int PW = 0, int layout = TNNS_NCHW);
+// dense form of layers with few input channels (dense.cu): channels of the virtual 1x1 layer, whether a kernel
+// qualifies, the repacked kernel of that layer, and the quantise kernel that writes its 4-bit image
+int tnns_dense_channels(int C, int KH, int KW);
+bool tnns_dense_eligible(int type, int C, int KH, int KW);
+int tnns_launch_repack_weights_dense(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, uint64_t* d_out, int Kp_out);
+int tnns_launch_dense_quantise(tnns_cuda_ctx* ctx, const float* d_x, const float* d_thr, void* d_img, const TnnsGeom& g, int Kd, int layout,
+                               cudaStream_t stream);
 // driver-encoded descriptor of a two-dimensional tensor for the copy engine (128 bytes at `map`)
 int tnns_tensor_map_2d(void* map, int elem_bytes, const void* base, unsigned long long dim0, unsigned long long dim1,
                        unsigned long long stride1_bytes, unsigned box0, unsigned box1, int swizzle_bytes = 0);

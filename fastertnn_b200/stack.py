@@ -80,8 +80,11 @@ class ConvStack:
                 ok = want_slab[i] and (self.run_first[i] or (self.mode[i - 1] == "slab" and
                                                             (layers[i - 1].H + 2 * layers[i - 1].P, layers[i - 1].W + 2 * layers[i - 1].P) ==
                                                             (L.H + 2 * L.P, L.W + 2 * L.P)))
-                self.mode.append("slab" if ok else "im2col" if self.fast[i] else "planes")
-            if not self.act_ternary and any(m != "slab" for m in self.mode):
+                # "dense": a run's first layer with few input channels (an image network's first layer) -- fp32 in, only
+                # the real positions of every window multiplied (the library's dense few-channel route)
+                dense = self.run_first[i] and ctx.dense_supported(self.weights[i], shapes[i])
+                self.mode.append("dense" if dense else "slab" if ok else "im2col" if self.fast[i] else "planes")
+            if not self.act_ternary and any(m not in ("slab",) for m in self.mode):
                 raise ValueError("binary activations travel as 4-bit images only between slab-fed (stride-1, same-size) layers; use chain='packed'")
             img = max([max(api.bordered_image_bytes(batch, L.C, L.H, L.W, L.P, L.P), api.e2m1_image_bytes(batch, L.KN, L.OH, L.OW),
                            api.bordered_image_bytes(batch, L.KN, L.OH, L.OW, L.P, L.P)) for L in layers])
@@ -92,7 +95,7 @@ class ConvStack:
             # would choose that form; its workspace holds the input's 4-bit image
             self.fuse = []
             for i, (L, w, sh) in enumerate(zip(layers, self.weights, shapes)):
-                if not self.run_first[i]:
+                if not self.run_first[i] or self.mode[i] == "dense":
                     self.fuse.append(False)
                 elif self.mode[i] == "slab":
                     self.fuse.append(bool(ctx.conv_slab_one_launch_preferred(w, sh, self.buf[0], layout)))
@@ -100,7 +103,8 @@ class ConvStack:
                     self.fuse.append(bool(self.mode[i] == "im2col" and ctx.conv_fused_preferred(w, sh, self.buf[0], layout)))
             self.fuse_first = self.fuse[0]
             self.ws0_bytes = max([max(api.fused_workspace_bytes(batch, L.C, L.H, L.W), api.slab_workspace_bytes(batch, L.C, L.H, L.W, L.P, L.P))
-                                  for L, f in zip(layers, self.fuse) if f] + [0])
+                                  for L, f in zip(layers, self.fuse) if f] +
+                                 [api.dense_workspace_bytes(sh) for sh, m in zip(shapes, self.mode) if m == "dense"] + [0])
             if self.ws0_bytes:
                 self.d_ws0 = ctx.malloc(self.ws0_bytes)
                 self.extra.append(self.d_ws0)
@@ -151,6 +155,14 @@ class ConvStack:
                         nxt, nxt_pad = (3 if tern else 5), (Ln.P, Ln.P)
                     elif self.mode[i + 1] == "im2col":
                         nxt = 2
+                if mode == "dense":
+                    if not last:
+                        self.ctx.conv_dense_packed_out(w, fp, self.d_thr, dst, self.d_thr, nxt, self.d_ws0, self.ws0_bytes, shape, self.alpha, self.layout, stream)
+                    else:
+                        self.ctx.conv_dense(w, fp, self.d_thr, out_fp, self.d_ws0, self.ws0_bytes, shape, self.alpha, self.layout, stream)
+                    if last:
+                        fp, k = out_fp, k + 1
+                    continue
                 if self.run_first[i] and not self.fuse[i]:
                     # the run's input, in the format its first layer reads
                     if mode == "slab":

@@ -172,7 +172,8 @@ enum tnns_gemm_algo {
     TNNS_GEMM_F4_TC = 4,       /* tcgen05 4-bit (e2m1, unit scales) tensor-core GEMM */
     TNNS_GEMM_F4_FUSED = 5,    /* whole layers only: the 4-bit GEMM fed by tensor copies with the quantise step in the same launch */
     TNNS_GEMM_F4_SLAB = 6,     /* whole stride-1 layers only: bordered 4-bit image, then the slab-fed 4-bit GEMM */
-    TNNS_GEMM_F4_SLAB_FUSED = 7 /* the same as one launch */
+    TNNS_GEMM_F4_SLAB_FUSED = 7, /* the same as one launch */
+    TNNS_GEMM_F4_DENSE = 8     /* whole layers with few input channels: only the real positions of a window, as a 1x1 layer */
 };
 
 /* Error codes returned by every tnns_cuda_* function (0 = success). */
@@ -359,6 +360,22 @@ int tnns_cuda_conv_slab(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const fl
 int tnns_cuda_conv_slab_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, void* d_image_out,
                                    const float* d_thr_next, int next_format, int next_PH, int next_PW, void* d_workspace, size_t workspace_bytes,
                                    const tnns_shape_t* s, float alpha, int pairs, void* stream);
+/* Layers with few input channels (C <= 16: the first layer of an image network), no reference counterpart.
+ * The reference pads every filter tap to 64 channels (src/tnns/ternarize2row_avx2.c:285-313); here the
+ * window's KH*KW*C real positions form the row of a virtual 1x1 layer (rounded up to 64, 128 or a multiple
+ * of 256 "channels"), whose packed kernel is derived once at upload: tnns_cuda_conv_dense quantises the
+ * fp32 input (either layout) straight into that layer's 4-bit image -- tnns_dense_workspace_bytes, 128-byte
+ * aligned -- and runs the copy-engine fed GEMM on it.  Same output bits as every other route.  Ternary
+ * activations (TNN, TBN); tnns_cuda_dense_supported tells whether a layer qualifies.  _packed_out writes
+ * the next layer's quantised activations instead (next_format 0 / 1 bit planes, 2 plain 4-bit image).
+ * tnns_cuda_conv / _conv_ws take this route by themselves (TNNS_GEMM_F4_DENSE asks for it). */
+size_t tnns_dense_workspace_bytes(const tnns_shape_t* s);
+int tnns_cuda_dense_supported(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s);
+int tnns_cuda_conv_dense(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y, void* d_workspace,
+                         size_t workspace_bytes, const tnns_shape_t* s, float alpha, int layout, void* stream);
+int tnns_cuda_conv_dense_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, void* d_image_out,
+                                    const float* d_thr_next, int next_format, void* d_workspace, size_t workspace_bytes,
+                                    const tnns_shape_t* s, float alpha, int layout, void* stream);
 /* Chaining on the copy-engine route: the same GEMM with the quantising epilogue of
  * tnns_cuda_gemm_packed_out.  next_format (also accepted as `next_ternary` by
  * tnns_cuda_gemm_packed_out): 0 = binary bit planes, 1 = ternary bit planes, 2 = ternary 4-bit
