@@ -125,7 +125,8 @@ SIGNATURES = {
     "tnns_dense_workspace_bytes": (_sz, [_pshape]),
     "tnns_cuda_dense_supported": (_i, [_vp, _vp, _pshape]),
     "tnns_cuda_conv_dense": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _pshape, C.c_float, _i, _vp]),
-    "tnns_cuda_conv_dense_packed_out": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _vp, _sz, _pshape, C.c_float, _i, _vp]),
+    "tnns_cuda_conv_dense_packed_out": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _pshape, C.c_float, _i, _vp]),
+    "tnns_cuda_gemm_im2col_bordered_out": (_i, [_vp, _vp, _vp, _vp, _vp, _i, _i, _pshape, C.c_float, _i, _vp]),
     "tnns_cuda_conv_slab": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _sz, _pshape, C.c_float, _i, _vp]),
     "tnns_cuda_conv_slab_packed_out": (_i, [_vp, _vp, _vp, _vp, _vp, _vp, _i, _i, _i, _vp, _sz, _pshape, C.c_float, _i, _vp]),
     "tnns_cuda_conv_fused_supported": (_i, [_vp, _vp, _vp, _i]),

@@ -327,6 +327,12 @@ class Context:
         _check(self.lib.tnns_cuda_gemm_im2col_packed_out(self.handle, w.handle, d_image, d_image_out, d_thr_next, next_format,
                                                          C.byref(shape), alpha, pairs, stream))
 
+    def gemm_im2col_bordered_out(self, w: Weights, d_image: int, d_image_out: int, d_thr_next: int, next_pad, shape: Shape, alpha: float,
+                                 stream=0, pairs=0):
+        """The copy-engine GEMM writing the next layer's 4-bit image bordered by next_pad = (PH, PW): what a slab-fed layer reads."""
+        _check(self.lib.tnns_cuda_gemm_im2col_bordered_out(self.handle, w.handle, d_image, d_image_out, d_thr_next, next_pad[0], next_pad[1],
+                                                           C.byref(shape), alpha, pairs, stream))
+
     # -- stride-1 layers from a bordered 4-bit image (slab-fed GEMM)
     def slab_supported(self, w: Weights, shape: Shape) -> bool:
         return bool(self.lib.tnns_cuda_slab_supported(self.handle, w.handle, C.byref(shape)))
@@ -383,9 +389,10 @@ class Context:
         _check(self.lib.tnns_cuda_conv_dense(self.handle, w.handle, d_x, d_thr, d_y, d_ws, ws_bytes, C.byref(shape), alpha, layout, stream))
 
     def conv_dense_packed_out(self, w: Weights, d_x: int, d_thr: int, d_image_out: int, d_thr_next: int, next_format: int, d_ws: int,
-                              ws_bytes: int, shape: Shape, alpha: float, layout=NCHW, stream=0):
-        _check(self.lib.tnns_cuda_conv_dense_packed_out(self.handle, w.handle, d_x, d_thr, d_image_out, d_thr_next, next_format, d_ws, ws_bytes,
-                                                        C.byref(shape), alpha, layout, stream))
+                              ws_bytes: int, shape: Shape, alpha: float, layout=NCHW, stream=0, next_pad=(0, 0)):
+        """next_format 0 / 1 bit planes, 2 plain 4-bit image, 3 the 4-bit image bordered by next_pad = (PH, PW)."""
+        _check(self.lib.tnns_cuda_conv_dense_packed_out(self.handle, w.handle, d_x, d_thr, d_image_out, d_thr_next, next_format, next_pad[0],
+                                                        next_pad[1], d_ws, ws_bytes, C.byref(shape), alpha, layout, stream))
 
     def im2col_supported(self, w: Weights, shape: Shape) -> bool:
         return bool(self.lib.tnns_cuda_im2col_supported(w.handle, C.byref(shape)))

@@ -618,7 +618,7 @@ int tnns_cuda_dense_supported(const tnns_cuda_ctx* ctx, const tnns_cuda_weights*
 
 static int conv_dense_impl(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y, void* d_image_out,
                            const float* d_thr_next, int next_format, void* d_workspace, size_t workspace_bytes, const tnns_shape_t* s,
-                           float alpha, int layout, void* stream) {
+                           float alpha, int layout, void* stream, int next_PH = 0, int next_PW = 0) {
     if (!ctx || !w || !d_x || !d_thr || !d_workspace) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
     if (layout != TNNS_NCHW && layout != TNNS_NHWC) return tnns_fail(TNNS_ERR_INVALID, "unknown layout %d", layout);
     TnnsGeom g, gv;
@@ -634,7 +634,8 @@ static int conv_dense_impl(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const
     if (g.N == 0) return TNNS_OK;
     rc = tnns_launch_dense_quantise(ctx, d_x, d_thr, d_workspace, g, gv.C, layout, (cudaStream_t)stream);
     if (rc) return rc;
-    return tnns_launch_gemm_im2col(ctx, w->dense, d_workspace, d_y, gv, alpha, layout, (cudaStream_t)stream, 0, d_image_out, d_thr_next, next_format);
+    return tnns_launch_gemm_im2col(ctx, w->dense, d_workspace, d_y, gv, alpha, layout, (cudaStream_t)stream, 0, d_image_out, d_thr_next, next_format,
+                                   nullptr, next_PH, next_PW);
 }
 
 int tnns_cuda_conv_dense(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y, void* d_workspace,
@@ -644,12 +645,13 @@ int tnns_cuda_conv_dense(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const f
 }
 
 int tnns_cuda_conv_dense_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, void* d_image_out,
-                                    const float* d_thr_next, int next_format, void* d_workspace, size_t workspace_bytes,
+                                    const float* d_thr_next, int next_format, int next_PH, int next_PW, void* d_workspace, size_t workspace_bytes,
                                     const tnns_shape_t* s, float alpha, int layout, void* stream) {
     if (!d_image_out || !d_thr_next) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
-    if (reinterpret_cast<uintptr_t>(d_image_out) & 15) return tnns_fail(TNNS_ERR_INVALID, "output image must be 16-byte aligned");
-    if (next_format < 0 || next_format > 2) return tnns_fail(TNNS_ERR_INVALID, "output format must be 0, 1 or 2");
-    return conv_dense_impl(ctx, w, d_x, d_thr, nullptr, d_image_out, d_thr_next, next_format, d_workspace, workspace_bytes, s, alpha, layout, stream);
+    if (reinterpret_cast<uintptr_t>(d_image_out) & (next_format == 3 ? 127 : 15)) return tnns_fail(TNNS_ERR_INVALID, "output image must be 16-byte (bordered: 128-byte) aligned");
+    if (next_format < 0 || next_format > 3) return tnns_fail(TNNS_ERR_INVALID, "output format must be 0, 1, 2 or 3");
+    return conv_dense_impl(ctx, w, d_x, d_thr, nullptr, d_image_out, d_thr_next, next_format, d_workspace, workspace_bytes, s, alpha, layout, stream,
+                           next_PH, next_PW);
 }
 
 // The algorithm tnns_cuda_conv / _conv_ws resolve TNNS_GEMM_AUTO (with TNNS_PACK_AUTO) to, workspace permitting.
@@ -762,6 +764,23 @@ int tnns_cuda_gemm_im2col_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights
     if (next_format < 0 || next_format > 2) return tnns_fail(TNNS_ERR_INVALID, "output format must be 0, 1 or 2");
     return tnns_launch_gemm_im2col(ctx, w, d_image, nullptr, g, alpha, TNNS_NCHW, (cudaStream_t)stream, pairs, d_image_out, d_thr_next,
                                    next_format);
+}
+
+int tnns_cuda_gemm_im2col_bordered_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, void* d_image_out,
+                                       const float* d_thr_next, int next_PH, int next_PW, const tnns_shape_t* s, float alpha, int pairs,
+                                       void* stream) {
+    if (!ctx || !w || !d_image || !d_image_out || !d_thr_next) return tnns_fail(TNNS_ERR_INVALID, "NULL argument");
+    TnnsGeom g;
+    int rc = tnns_make_geom(s, &g);
+    if (rc) return rc;
+    if (s->KN != w->KN || s->C != w->C || s->KH != w->KH || s->KW != w->KW)
+        return tnns_fail(TNNS_ERR_INVALID, "shape does not match the uploaded weights");
+    TNNS_ENTER(ctx, w);
+    if ((reinterpret_cast<uintptr_t>(d_image) & 31) || (reinterpret_cast<uintptr_t>(d_image_out) & 127))
+        return tnns_fail(TNNS_ERR_INVALID, "input image must be 32-byte, bordered output image 128-byte aligned");
+    if (pairs < 0 || pairs > 2) return tnns_fail(TNNS_ERR_INVALID, "pairs must be 0, 1 or 2");
+    return tnns_launch_gemm_im2col(ctx, w, d_image, nullptr, g, alpha, TNNS_NCHW, (cudaStream_t)stream, pairs, d_image_out, d_thr_next, 3, nullptr,
+                                   next_PH, next_PW);
 }
 
 int tnns_cuda_im2row_packed(tnns_cuda_ctx* ctx, int ternary, const void* d_image, int64_t* d_packed, const tnns_shape_t* s,

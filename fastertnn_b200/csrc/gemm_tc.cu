@@ -204,6 +204,9 @@ struct GemmArgs {
     const float* thr_next;      // one threshold per image for that quantisation
     int next_ternary, cp_next;  // planes of the next layer's activations, its 64-channel groups
     int pimg_e2m1;              // write that output as a 4-bit operand image [n][pixel][ic][32 B] instead of bit planes
+    // that image bordered for a slab-fed next layer: pixel (oh, ow) of image n at n*o_HpWp + (oh + o_PH)*o_Wp + ow + o_PW,
+    // the frame of o_PH rows / o_PW columns around every image written (zeros) by this launch; o_HpWp = 0: plain image
+    int o_Wp, o_HpWp, o_PH, o_PW;
     // PReLU of a zero sum: mm_tnn scales it (0*alpha, -0 for a negative alpha), mm_tbn / mm_btn / mm_bnn pass
     // +0 through (src/tnns/mm_p2_final_tnn_avx2.c:90-93 against mm_p2_final_tbn_avx2.c:73)
     int zero_passes;
@@ -599,6 +602,20 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
         // quantised output with 0 < alpha <= 1: PReLU and the next layer's rule collapse into thresholds on
         // the accumulator (two instructions per output and plane instead of evaluating the PReLU first)
         const bool by_thr = F4 && p.pimg != nullptr && alpha_in_unit;
+        if (F4 && p.pimg && p.pimg_e2m1 && p.o_HpWp) {
+            // bordered output image: the frame around every image holds the next layer's padding value (ternary 0); written
+            // here, by the epilogue threads of all blocks, after the wait for the launch before (which may still read this buffer)
+            const int H = p.OHW / p.OW, nimg = (int)(p.M / p.OHW), epi_threads = 32 * 4 * MT * EPW;
+            const long long total = (long long)nimg * p.o_HpWp;
+            const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
+            for (long long i = (long long)blockIdx.x * epi_threads + (tid - 32 * WARP_EPI0); i < total; i += (long long)gridDim.x * epi_threads) {
+                const int r = (int)(i % p.o_HpWp), y = r / p.o_Wp, x = r - y * p.o_Wp;
+                if (y < p.o_PH || y >= p.o_PH + H || x < p.o_PW || x >= p.o_PW + p.OW) {
+                    uint4* dst = reinterpret_cast<uint4*>(p.pimg) + (size_t)i * p.cp_next * 2;
+                    for (int u = 0; u < 2 * p.cp_next; u++) dst[u] = z4;
+                }
+            }
+        }
         const bool rows16 = F4 && p.pimg == nullptr && p.layout == TNNS_NHWC && (p.KN & 1) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 7) == 0;
         tnns_thr::Pair qt = {0.f, 0.f};
         long long qt_img = -1;
@@ -613,6 +630,12 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
             const int rem = (int)(row - n_img * p.OHW);
             float* ybase = (p.layout == TNNS_NHWC) ? p.y + (size_t)row * p.KN : p.y + (size_t)n_img * p.KN * p.OHW + rem;
             const float tq = (p.pimg && row_ok) ? __ldg(p.thr_next + n_img) + 0.0f : 0.f;  // + 0.0f: -0 acts as +0
+            // the row's pixel in the next layer's 4-bit image (plain, or inside its border)
+            long long opix = n_img * p.OHW + rem;
+            if (p.pimg && p.o_HpWp) {
+                const int oh = rem / p.OW;
+                opix = n_img * p.o_HpWp + (long long)(oh + p.o_PH) * p.o_Wp + (rem - oh * p.OW) + p.o_PW;
+            }
             if (by_thr && row_ok && n_img != qt_img) {
                 // the next layer's rule as thresholds on the raw accumulator, once per image this thread meets
                 qt = tnns_thr::make(tq, p.alpha, bias_f, p.next_ternary != 0);
@@ -717,7 +740,7 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                                 // of the next layer expects them (same expansion routine as everywhere)
                                 uint32_t w4[4];
                                 tnns_expand32_f4(sg & valid, ~(nz & valid), w4);
-                                uint4* px = reinterpret_cast<uint4*>(p.pimg) + ((size_t)n_img * p.OHW + rem) * ((size_t)p.cp_next * 2) + (c0 >> 5);
+                                uint4* px = reinterpret_cast<uint4*>(p.pimg) + (size_t)opix * ((size_t)p.cp_next * 2) + (c0 >> 5);
                                 *px = make_uint4(w4[0], w4[1], w4[2], w4[3]);
                             } else {
                                 const int planes = p.next_ternary ? 2 : 1;
@@ -1014,6 +1037,7 @@ int tnns_launch_gemm_tc(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const vo
     a.thr_next = d_thr_next;
     a.next_ternary = next_ternary != 0;
     a.pimg_e2m1 = next_ternary == 2;
+    a.o_Wp = a.o_HpWp = a.o_PH = a.o_PW = 0;
     a.cp_next = (w->KN + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS;
     a.img = nullptr;
     a.jtab = nullptr;
@@ -1142,7 +1166,7 @@ int tnns_fused_sync_prepare(tnns_cuda_ctx* ctx, int N, cudaStream_t stream, unsi
 
 int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const TnnsGeom& g, float alpha,
                             int layout, cudaStream_t stream, int pairs, void* d_pimg, const float* d_thr_next, int next_format,
-                            const TnnsFusedInput* fused) {
+                            const TnnsFusedInput* fused, int next_PH, int next_PW) {
     const long long M = (long long)g.N * g.OH * g.OW;
     if (M == 0) return TNNS_OK;
     if (!tnns_im2col_supported(w, g)) return tnns_fail(TNNS_ERR_UNSUPPORTED, "layer shape or type outside the tensor-copy activation path");
@@ -1177,7 +1201,16 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     a.pimg = reinterpret_cast<uint32_t*>(d_pimg);
     a.thr_next = d_thr_next;
     a.next_ternary = next_format != 0;
-    a.pimg_e2m1 = next_format == 2;
+    a.pimg_e2m1 = next_format == 2 || next_format == 3;
+    a.o_Wp = a.o_HpWp = a.o_PH = a.o_PW = 0;
+    if (next_format == 3) {
+        // bordered 4-bit image for a slab-fed next layer with padding (next_PH, next_PW)
+        if (!d_pimg || next_PH < 0 || next_PW < 0) return tnns_fail(TNNS_ERR_INVALID, "bordered output needs an output image and a non-negative border");
+        a.o_PH = next_PH; a.o_PW = next_PW;
+        a.o_Wp = g.OW + 2 * next_PW;
+        a.o_HpWp = (g.OH + 2 * next_PH) * a.o_Wp;
+        if ((long long)g.N * a.o_HpWp >= 0x7FFFFFFFLL) return tnns_fail(TNNS_ERR_UNSUPPORTED, "bordered output image too large");
+    }
     a.cp_next = (w->KN + TNNS_WORD_BITS - 1) / TNNS_WORD_BITS;
     a.img = nullptr;
     a.jtab = w->d_jtab;

@@ -136,7 +136,8 @@ size_t tnns_fused_sync_bytes(int N);
 bool tnns_fused_supported(const tnns_cuda_weights* w, const TnnsGeom& g, const float* d_x, int layout);
 int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, float* d_y, const TnnsGeom& g,
                             float alpha, int layout, cudaStream_t stream, int pairs = 0, void* d_pimg = nullptr,
-                            const float* d_thr_next = nullptr, int next_format = 1, const TnnsFusedInput* fused = nullptr);
+                            const float* d_thr_next = nullptr, int next_format = 1, const TnnsFusedInput* fused = nullptr, int next_PH = 0,
+                            int next_PW = 0);
 
 int tnns_fused_sync_prepare(tnns_cuda_ctx* ctx, int N, cudaStream_t stream, unsigned int* caller_words, unsigned int** words_out, int* self_clean);
 

@@ -70,8 +70,10 @@ class ConvStack:
             self.run_last = [i == n - 1 or not self.link_ok[i] for i in range(n)]
             # mode of every layer = the format its input arrives in:
             #   "slab"    bordered 4-bit image (stride-1 layers; the only 4-bit form of binary activations).  Its
-            #             producer is the quantise step of a run's first layer, or a slab-fed predecessor whose
-            #             padded lattice is this layer's (its epilogue then writes this image with its border)
+            #             producer is the quantise step of a run's first layer, a slab-fed predecessor whose
+            #             padded lattice is this layer's (its epilogue then writes this image with its border), or --
+            #             ternary activations -- an im2col-fed or dense predecessor (any stride: its epilogue places
+            #             every output pixel inside the border and writes the frame)
             #   "im2col"  plain 4-bit image read through im2col tensor copies
             #   "planes"  bit planes + im2row from planes
             want_slab = [use_slab and ctx.slab_preferred(w, sh) for w, sh in zip(self.weights, shapes)]
@@ -79,7 +81,10 @@ class ConvStack:
             for i, L in enumerate(layers):
                 ok = want_slab[i] and (self.run_first[i] or (self.mode[i - 1] == "slab" and
                                                             (layers[i - 1].H + 2 * layers[i - 1].P, layers[i - 1].W + 2 * layers[i - 1].P) ==
-                                                            (L.H + 2 * L.P, L.W + 2 * L.P)))
+                                                            (L.H + 2 * L.P, L.W + 2 * L.P)) or
+                                       (self.act_ternary and self.mode[i - 1] in ("im2col", "dense") and
+                                        not (self.run_first[i - 1] and self.mode[i - 1] == "im2col" and
+                                             ctx.conv_fused_preferred(self.weights[i - 1], shapes[i - 1], self.buf[0], layout))))
                 # "dense": a run's first layer with few input channels (an image network's first layer) -- fp32 in, only
                 # the real positions of every window multiplied (the library's dense few-channel route)
                 dense = self.run_first[i] and ctx.dense_supported(self.weights[i], shapes[i])
@@ -157,7 +162,8 @@ class ConvStack:
                         nxt = 2
                 if mode == "dense":
                     if not last:
-                        self.ctx.conv_dense_packed_out(w, fp, self.d_thr, dst, self.d_thr, nxt, self.d_ws0, self.ws0_bytes, shape, self.alpha, self.layout, stream)
+                        self.ctx.conv_dense_packed_out(w, fp, self.d_thr, dst, self.d_thr, nxt, self.d_ws0, self.ws0_bytes, shape, self.alpha, self.layout, stream,
+                                                       nxt_pad)
                     else:
                         self.ctx.conv_dense(w, fp, self.d_thr, out_fp, self.d_ws0, self.ws0_bytes, shape, self.alpha, self.layout, stream)
                     if last:
@@ -187,6 +193,8 @@ class ConvStack:
                             self.ctx.conv_fused_packed_out(w, fp, self.d_thr, dst, self.d_thr, nxt, self.d_ws0, self.ws0_bytes, shape, self.alpha, 0, stream)
                         else:
                             self.ctx.conv_fused(w, fp, self.d_thr, out_fp, self.d_ws0, self.ws0_bytes, shape, self.alpha, 0, stream)
+                    elif not last and nxt == 3:
+                        self.ctx.gemm_im2col_bordered_out(w, src, dst, self.d_thr, nxt_pad, shape, self.alpha, stream)
                     elif not last:
                         self.ctx.gemm_im2col_packed_out(w, src, dst, self.d_thr, nxt, shape, self.alpha, stream)
                     else:

@@ -367,15 +367,16 @@ int tnns_cuda_conv_slab_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* 
  * fp32 input (either layout) straight into that layer's 4-bit image -- tnns_dense_workspace_bytes, 128-byte
  * aligned -- and runs the copy-engine fed GEMM on it.  Same output bits as every other route.  Ternary
  * activations (TNN, TBN); tnns_cuda_dense_supported tells whether a layer qualifies.  _packed_out writes
- * the next layer's quantised activations instead (next_format 0 / 1 bit planes, 2 plain 4-bit image).
+ * the next layer's quantised activations instead (next_format 0 / 1 bit planes, 2 plain 4-bit image, 3 the 4-bit
+ * image bordered by next_PH rows / next_PW columns for a slab-fed next layer).
  * tnns_cuda_conv / _conv_ws take this route by themselves (TNNS_GEMM_F4_DENSE asks for it). */
 size_t tnns_dense_workspace_bytes(const tnns_shape_t* s);
 int tnns_cuda_dense_supported(const tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const tnns_shape_t* s);
 int tnns_cuda_conv_dense(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, float* d_y, void* d_workspace,
                          size_t workspace_bytes, const tnns_shape_t* s, float alpha, int layout, void* stream);
 int tnns_cuda_conv_dense_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const float* d_x, const float* d_thr, void* d_image_out,
-                                    const float* d_thr_next, int next_format, void* d_workspace, size_t workspace_bytes,
-                                    const tnns_shape_t* s, float alpha, int layout, void* stream);
+                                    const float* d_thr_next, int next_format, int next_PH, int next_PW, void* d_workspace,
+                                    size_t workspace_bytes, const tnns_shape_t* s, float alpha, int layout, void* stream);
 /* Chaining on the copy-engine route: the same GEMM with the quantising epilogue of
  * tnns_cuda_gemm_packed_out.  next_format (also accepted as `next_ternary` by
  * tnns_cuda_gemm_packed_out): 0 = binary bit planes, 1 = ternary bit planes, 2 = ternary 4-bit
@@ -385,6 +386,13 @@ int tnns_cuda_conv_dense_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights*
 int tnns_cuda_gemm_im2col_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, void* d_image_out,
                                      const float* d_thr_next, int next_format, const tnns_shape_t* s, float alpha, int pairs,
                                      void* stream);
+/* The same producer writing the 4-bit image BORDERED (tnns_e2m1_bordered_image_bytes(N, KN, OH, OW, next_PH, next_PW) bytes,
+ * 128-byte aligned): what a slab-fed next layer with padding (next_PH, next_PW) reads.  Any layer the im2col GEMM
+ * takes can produce it -- strided ones too -- each output pixel going to its place inside the border, and the
+ * frame (zeros) written by the same launch. */
+int tnns_cuda_gemm_im2col_bordered_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const void* d_image, void* d_image_out,
+                                       const float* d_thr_next, int next_PH, int next_PW, const tnns_shape_t* s, float alpha, int pairs,
+                                       void* stream);
 int tnns_cuda_gemm_packed_out(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, const int64_t* d_a, void* d_image,
                               const float* d_thr_next, int next_ternary, int N, int OH, int OW, float alpha, void* stream);
 int tnns_cuda_im2row_packed(tnns_cuda_ctx* ctx, int ternary, const void* d_image, int64_t* d_packed, const tnns_shape_t* s,

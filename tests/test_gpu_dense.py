@@ -74,6 +74,18 @@ def test_dense_route_matches_the_checker(type_, layer, N, gpu_ctx, checker):
             ctx.conv_dense_packed_out(w, d_x, d_t, d_o, d_tn, fmt, d_ws, nws, shape, case.alpha)
             ctx.sync()
             assert np.array_equal(ctx.to_host(d_o, (nb_o // 4,), np.uint32), ctx.to_host(d_q, (nb_o // 4,), np.uint32)), fmt
+        # ... and bordered for a slab-fed next layer (padding 1, then 2 rows / 0 columns), over a buffer of stale bytes
+        for pad in ((1, 1), (2, 0)):
+            nb_b = ft.api.bordered_image_bytes(N, layer.KN, layer.OH, layer.OW, pad[0], pad[1])
+            d_ob, d_qb = ctx.malloc(nb_b), ctx.malloc(nb_b)
+            if (layer.OH * layer.OW) % 4 == 0 and layer.OH * layer.OW >= 32:
+                ctx.fill(d_ob, np.full(nb_b // 4, 0x77777777, np.uint32))
+                ctx.quantise_e2m1_bordered(True, d_f, d_tn, d_qb, N, layer.KN, layer.OH, layer.OW, pad[0], pad[1])
+                ctx.conv_dense_packed_out(w, d_x, d_t, d_ob, d_tn, 3, d_ws, nws, shape, case.alpha, ft.NCHW, 0, pad)
+                ctx.sync()
+                assert np.array_equal(ctx.to_host(d_ob, (nb_b // 4,), np.uint32), ctx.to_host(d_qb, (nb_b // 4,), np.uint32)), ("bordered", pad)
+            ctx.free(d_ob)
+            ctx.free(d_qb)
         with pytest.raises(ft.TnnsError):
             ctx.conv_dense(w, d_x, d_t, d_y, d_ws, nws - 128, shape, case.alpha)
     finally:
@@ -123,7 +135,8 @@ def test_image_chain_starts_with_the_dense_layer(gpu_ctx, checker):
         want = checker.conv(TNN, want, thr, pw, (L.KH, L.KW), (L.P, L.P), (L.S, L.S), 0.5)
     st = ConvStack(gpu_ctx, TNN, layers, pws, N, 0.25, chain="image")
     try:
-        assert st.mode[0] == "dense" and st.mode[1] != "slab"
+        # the second layer (64 channels, stride 1) is slab-fed: the dense layer's epilogue writes its bordered image
+        assert st.mode[0] == "dense" and st.mode[1] == "slab"
         for rep in range(2):
             gpu_ctx.fill(st.input_ptr(), x)
             st.run()

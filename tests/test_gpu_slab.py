@@ -259,3 +259,47 @@ def test_quantise_from_nhwc_through_the_copy_engine(tern, C, H, W, N, gpu_ctx, c
     finally:
         for p in (d_x, d_xh, d_t, d_a, d_b):
             ctx.free(p)
+
+
+@pytest.mark.parametrize("layer,N", [(Layer(256, 14, 14, 128, 3, 3, 1, 2), 5), (Layer(64, 16, 16, 64, 3, 3, 1, 1), 3), (Layer(128, 12, 20, 200, 5, 3, 2, 2), 4)],
+                         ids=lambda v: str(v).replace(" ", ""))
+def test_im2col_fed_layer_writes_a_bordered_image(layer, N, gpu_ctx, checker):
+    """A layer on the im2col-fed GEMM (strided ones too) hands a slab-fed successor its bordered 4-bit image: every
+    output pixel inside the border, the frame written by the same launch -- the bytes the bordered quantise kernel
+    makes of the fp32 output, over a buffer of stale bytes, and the successor's output equal to the checker's."""
+    ctx = gpu_ctx
+    case = make_case(TNN, layer, N, 9600 + layer.C, "uniform")
+    wp = checker.pack_weights(True, case.w, case.w_thr)
+    mid = checker.conv(TNN, case.x, case.thr, wp, case.kernel_hw, case.padding, case.stride, case.alpha)
+    w = ctx.upload_weights(TNN, wp, layer.C, layer.KH, layer.KW)
+    nxt = Layer(layer.KN, layer.OH, layer.OW, 64, 3, 3, 1, 1)
+    wv = synth.ternary_values(9601, (nxt.KN, nxt.C, 3, 3))
+    wp2 = checker.pack_weights(True, wv, np.full(nxt.KN, 0.5, np.float32))
+    thr2 = np.linspace(0.3, 2.0, N).astype(np.float32)
+    want = checker.conv(TNN, mid, thr2, wp2, (3, 3), (1, 1), (1, 1), 0.5)
+    w2 = ctx.upload_weights(TNN, wp2, nxt.C, 3, 3)
+    assert ctx.slab_supported(w2, nxt.shape(N))
+    nb_in = ft.api.e2m1_image_bytes(N, layer.C, layer.H, layer.W)
+    nb_b = ft.api.bordered_image_bytes(N, nxt.C, nxt.H, nxt.W, 1, 1)
+    d_x, d_t, d_t2, d_m = ctx.to_device(case.x), ctx.to_device(case.thr), ctx.to_device(thr2), ctx.to_device(mid)
+    d_in, d_b, d_q, d_y = ctx.malloc(nb_in), ctx.malloc(nb_b), ctx.malloc(nb_b), ctx.malloc(want.nbytes)
+    try:
+        ctx.quantise_e2m1(d_x, d_t, d_in, N, layer.C, layer.H, layer.W)
+        for rep in range(2):
+            ctx.fill(d_b, np.full(nb_b // 4, 0x66666666, np.uint32))
+            ctx.gemm_im2col_bordered_out(w, d_in, d_b, d_t2, (1, 1), layer.shape(N), case.alpha)
+            ctx.sync()
+            got = ctx.to_host(d_b, (nb_b // 4,), np.uint32)
+            if (nxt.H * nxt.W) % 4 == 0 and nxt.H * nxt.W >= 32:
+                ctx.quantise_e2m1_bordered(True, d_m, d_t2, d_q, N, nxt.C, nxt.H, nxt.W, 1, 1)
+                ctx.sync()
+                assert np.array_equal(got, ctx.to_host(d_q, (nb_b // 4,), np.uint32)), ("bordered image", rep)
+            ctx.fill(d_y, np.full(want.size, np.nan, np.float32))
+            ctx.gemm_slab(w2, d_b, d_y, nxt.shape(N), 0.5)
+            ctx.sync()
+            assert ctx.to_host(d_y, want.shape, np.float32).tobytes() == want.tobytes(), ("successor", rep)
+    finally:
+        for p in (d_x, d_t, d_t2, d_m, d_in, d_b, d_q, d_y):
+            ctx.free(p)
+        w.free()
+        w2.free()
