@@ -230,6 +230,22 @@ struct GemmArgs {
 
 
 
+// Bordered output image (quantising epilogue, next_format 3): the frame around every image holds the next layer's padding
+// value (ternary 0).  Written by the epilogue threads of all blocks after the wait for the launch before, which may still
+// read this buffer.  Kept out of line: inlined, its registers cost the fp32 path of the large layer a percent.
+__device__ __noinline__ void fill_output_border(uint4* img, int cp_next, int H, int W, int nimg, int o_Wp, int o_HpWp, int o_PH, int o_PW,
+                                                long long first, long long step) {
+    const long long total = (long long)nimg * o_HpWp;
+    const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
+    for (long long i = first; i < total; i += step) {
+        const int r = (int)(i % o_HpWp), y = r / o_Wp, x = r - y * o_Wp;
+        if (y < o_PH || y >= o_PH + H || x < o_PW || x >= o_PW + W) {
+            uint4* dst = img + (size_t)i * cp_next * 2;
+            for (int u = 0; u < 2 * cp_next; u++) dst[u] = z4;
+        }
+    }
+}
+
 // TAPS (tensor-copy form): filter taps per 128-byte stage row -- 1: a tap's 256 channels fill the
 // row (C_pack % 4 == 0); 2: C_pack = 2, two taps of 128 channels in two 64-byte-swizzled sub-tiles;
 // 4: C_pack = 1, four taps of 64 channels in four 32-byte-swizzled sub-tiles.
@@ -602,20 +618,11 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
         // quantised output with 0 < alpha <= 1: PReLU and the next layer's rule collapse into thresholds on
         // the accumulator (two instructions per output and plane instead of evaluating the PReLU first)
         const bool by_thr = F4 && p.pimg != nullptr && alpha_in_unit;
-        if (F4 && p.pimg && p.pimg_e2m1 && p.o_HpWp) {
-            // bordered output image: the frame around every image holds the next layer's padding value (ternary 0); written
-            // here, by the epilogue threads of all blocks, after the wait for the launch before (which may still read this buffer)
-            const int H = p.OHW / p.OW, nimg = (int)(p.M / p.OHW), epi_threads = 32 * 4 * MT * EPW;
-            const long long total = (long long)nimg * p.o_HpWp;
-            const uint4 z4 = make_uint4(0u, 0u, 0u, 0u);
-            for (long long i = (long long)blockIdx.x * epi_threads + (tid - 32 * WARP_EPI0); i < total; i += (long long)gridDim.x * epi_threads) {
-                const int r = (int)(i % p.o_HpWp), y = r / p.o_Wp, x = r - y * p.o_Wp;
-                if (y < p.o_PH || y >= p.o_PH + H || x < p.o_PW || x >= p.o_PW + p.OW) {
-                    uint4* dst = reinterpret_cast<uint4*>(p.pimg) + (size_t)i * p.cp_next * 2;
-                    for (int u = 0; u < 2 * p.cp_next; u++) dst[u] = z4;
-                }
-            }
-        }
+        // (not in the one-launch form, whose producers write plain images only: the code is compiled out there, where
+        // its mere presence measured one percent of the large layer)
+        if (F4 && !QF && p.pimg && p.pimg_e2m1 && p.o_HpWp)
+            fill_output_border(reinterpret_cast<uint4*>(p.pimg), p.cp_next, p.OHW / p.OW, p.OW, (int)(p.M / p.OHW), p.o_Wp, p.o_HpWp, p.o_PH, p.o_PW,
+                               (long long)blockIdx.x * (32 * 4 * MT * EPW) + (tid - 32 * WARP_EPI0), (long long)gridDim.x * (32 * 4 * MT * EPW));
         const bool rows16 = F4 && p.pimg == nullptr && p.layout == TNNS_NHWC && (p.KN & 1) == 0 && (reinterpret_cast<uintptr_t>(p.y) & 7) == 0;
         tnns_thr::Pair qt = {0.f, 0.f};
         long long qt_img = -1;
@@ -630,12 +637,6 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
             const int rem = (int)(row - n_img * p.OHW);
             float* ybase = (p.layout == TNNS_NHWC) ? p.y + (size_t)row * p.KN : p.y + (size_t)n_img * p.KN * p.OHW + rem;
             const float tq = (p.pimg && row_ok) ? __ldg(p.thr_next + n_img) + 0.0f : 0.f;  // + 0.0f: -0 acts as +0
-            // the row's pixel in the next layer's 4-bit image (plain, or inside its border)
-            long long opix = n_img * p.OHW + rem;
-            if (p.pimg && p.o_HpWp) {
-                const int oh = rem / p.OW;
-                opix = n_img * p.o_HpWp + (long long)(oh + p.o_PH) * p.o_Wp + (rem - oh * p.OW) + p.o_PW;
-            }
             if (by_thr && row_ok && n_img != qt_img) {
                 // the next layer's rule as thresholds on the raw accumulator, once per image this thread meets
                 qt = tnns_thr::make(tq, p.alpha, bias_f, p.next_ternary != 0);
@@ -740,6 +741,13 @@ gemm_tc_kernel(GemmArgs p, const __grid_constant__ CUtensorMap tmap_a, const __g
                                 // of the next layer expects them (same expansion routine as everywhere)
                                 uint32_t w4[4];
                                 tnns_expand32_f4(sg & valid, ~(nz & valid), w4);
+                                // the row's pixel in the next layer's image: plain, or inside its border (worked out here, in the
+                                // branch that stores it: as a value kept across the slices it cost the fp32 path 3 % on the large layer)
+                                long long opix = n_img * p.OHW + rem;
+                                if (!QF && p.o_HpWp) {
+                                    const int oh = rem / p.OW;
+                                    opix = n_img * p.o_HpWp + (long long)(oh + p.o_PH) * p.o_Wp + (rem - oh * p.OW) + p.o_PW;
+                                }
                                 uint4* px = reinterpret_cast<uint4*>(p.pimg) + (size_t)opix * ((size_t)p.cp_next * 2) + (c0 >> 5);
                                 *px = make_uint4(w4[0], w4[1], w4[2], w4[3]);
                             } else {
@@ -1205,6 +1213,7 @@ int tnns_launch_gemm_im2col(tnns_cuda_ctx* ctx, const tnns_cuda_weights* w, cons
     a.o_Wp = a.o_HpWp = a.o_PH = a.o_PW = 0;
     if (next_format == 3) {
         // bordered 4-bit image for a slab-fed next layer with padding (next_PH, next_PW)
+        if (fused) return tnns_fail(TNNS_ERR_UNSUPPORTED, "the one-launch form writes plain output images only");
         if (!d_pimg || next_PH < 0 || next_PW < 0) return tnns_fail(TNNS_ERR_INVALID, "bordered output needs an output image and a non-negative border");
         a.o_PH = next_PH; a.o_PW = next_PW;
         a.o_Wp = g.OW + 2 * next_PW;
