@@ -646,6 +646,25 @@ def run_layer(args, name, type_, N_cfg, layer: Layer):
         del run2
         torch.cuda.empty_cache()
 
+    # ---- the same job in the other memory layout alongside (default route only): the layer configurations are worded
+    # for pixel-major (NHWC) tensors, the reference's C API takes NCHW; both go through the same kernels
+    other_layout = None
+    if args.route == "auto" and args.gemm == "auto" and layer.C % 4 == 0:
+        args2 = argparse.Namespace(**vars(args))
+        args2.layout = "nhwc" if args.layout == "nchw" else "nchw"
+        run3 = LayerRun(D, ft, ctx, w, type_, layer, x_h, thr_h, nloc, args2)
+        ok3 = True if args.no_check else check_rank_slice(D, run3, type_, layer, x_h, thr_h, wp)
+        if not D.all_true(ok3):
+            raise SystemExit("bench: GPU output in the other layout differs from the CPU checker on some rank")
+        for i in range(args.warmup):
+            run3.step(i)
+        l_ms = timed_region(D, run3.stream, run3.step, args.steps, args.warmup) / args.steps
+        other_layout = {"layout": args2.layout.upper(), "ms_per_step": l_ms, "value": layer.ops(N_total) / (l_ms * 1e-3) / 1e9, "unit": "GOPS",
+                        "route": run3.route_name()}
+        run3.free()
+        del run3
+        torch.cuda.empty_cache()
+
     # ---- end to end: ONE host batch in, host buffers out, copies inside the timed region --------
     # through the library call that takes a host batch: tnns_cuda_conv_host on one GPU,
     # tnns_cuda_multi_conv_host (one host thread per device behind one call) on several; rank 0 makes
@@ -783,6 +802,8 @@ def run_layer(args, name, type_, N_cfg, layer: Layer):
             line["sustained"]["frac_of_sustained_peak"] = (ops_loc / (sustained["ms_per_step_median"] * 1e-3) / 1e12) / (4.0 * pk["bf16_tflops_sustained"]) if args.gemm in ("auto", "f4tc") else None
         if other:
             line["weak_scaling" if strong else "fixed_total_batch"] = other
+        if other_layout:
+            line["other_layout"] = other_layout
         if world == 1 and not args.no_cpu:
             line["cpu_baseline"] = cpu_baseline("layer", type_, N_total, [layer], passes=args.cpu_passes)
         print(json.dumps(line), flush=True)
